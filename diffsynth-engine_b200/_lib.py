@@ -1,0 +1,72 @@
+"""ctypes binding of ``libdsb.so``.  There is no fallback: if the library is missing or does not
+load, every op raises - the CUDA path is the only path."""
+import ctypes
+import os
+import re
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(HERE, "libdsb.so")
+HEADER = os.path.join(os.path.dirname(HERE), "include", "dsb.h")
+
+OK, ERR_ARG, ERR_CUDA, ERR_TIMEOUT, ERR_UNSUPPORTED = 0, -1, -2, -3, -4
+FMT_BF16, FMT_E4M3, FMT_INT8 = 0, 1, 2
+ACT_NONE, ACT_GELU_TANH, ACT_SILU = 0, 1, 2
+
+_ERR_NAMES = {
+    ERR_ARG: "DSB_ERR_ARG (bad pointer, size, alignment or flag combination)",
+    ERR_CUDA: "DSB_ERR_CUDA (a CUDA call failed)",
+    ERR_TIMEOUT: "DSB_ERR_TIMEOUT (a bounded device wait ran out)",
+    ERR_UNSUPPORTED: "DSB_ERR_UNSUPPORTED (shape outside what the kernel supports)",
+}
+
+c_i, c_i64, c_f, c_p = ctypes.c_int, ctypes.c_int64, ctypes.c_float, ctypes.c_void_p
+
+# argument lists, in the order of include/dsb.h
+_SIGS = {
+    "dsb_version": [],
+    "dsb_ln_modulate": [c_p, c_i64, c_p, c_p, c_p, c_i64, c_p, c_i, c_i, c_f, c_i, c_p],
+    "dsb_gate_residual": [c_p, c_i64, c_p, c_i64, c_p, c_p, c_i64, c_i, c_i, c_p],
+    "dsb_rmsnorm_rope_heads": [c_p, c_i64, c_i, c_i, c_i, c_i, c_p, c_p, c_p, c_i, c_f, c_p],
+    "dsb_rmsnorm_full": [c_p, c_i64, c_i, c_i, c_p, c_p, c_i, c_f, c_p],
+    "dsb_quant_rows": [c_p, c_i64, c_p, c_i64, c_p, c_i, c_i, c_i, c_p],
+    "dsb_gemv": [c_p, c_i64, c_i, c_p, c_p, c_i, c_p, c_p, c_i, c_i, c_i, c_i, c_p],
+    "dsb_euler_step": [c_p, c_p, c_p, c_p, c_f, c_p, c_i64, c_i, c_p],
+    "dsb_gemm": [c_p, c_i64, c_p, c_i64, c_i, c_i, c_i, c_i, c_p, c_p, c_i, c_p, c_i, c_i, c_p, c_p, c_i64, c_p,
+                 c_i64, c_p, c_i64, c_i, c_p, c_p],
+    "dsb_flash_attn": [c_p, c_p, c_p, c_p, c_i, c_i, c_i, c_i, c_i] + [c_i64] * 12 + [c_f, c_p, c_p],
+    "dsb_pack_quant_weight": [c_p, c_i64, c_i, c_p, c_i64, c_p, c_i, c_i, c_i, c_i, c_p, c_p],
+}
+
+_lib = None
+
+
+class DsbError(RuntimeError):
+    pass
+
+
+def declared_symbols():
+    """Names of every function declared in include/dsb.h."""
+    with open(HEADER) as f:
+        text = f.read()
+    return sorted(set(re.findall(r"^int\s+(dsb_\w+)\s*\(", text, flags=re.M)))
+
+
+def lib():
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise DsbError(
+                f"{LIB_PATH} is missing: build it with `python diffsynth-engine_b200/build.py` "
+                "(there is no CPU or PyTorch fallback)")
+        handle = ctypes.CDLL(LIB_PATH)
+        for name, args in _SIGS.items():
+            fn = getattr(handle, name)
+            fn.argtypes = args
+            fn.restype = c_i
+        _lib = handle
+    return _lib
+
+
+def check(rc: int, what: str):
+    if rc != OK:
+        raise DsbError(f"{what} failed: {_ERR_NAMES.get(rc, rc)}")

@@ -1,0 +1,620 @@
+// Bandwidth-bound kernels of the DiT step: AdaLN (LayerNorm + shift/scale,
+// optionally emitting the FP8/INT8 operand of the next GEMM with its per-row
+// scale), gate-residual, per-head and full-width QK-RMSNorm with RoPE, row
+// quantisation, the M=1 modulation/embedding GEMV, and the flow-match Euler
+// update.  All global accesses are 128-bit; one CTA (or one warp) owns a row
+// so every reduction stays on chip.
+#include "common.cuh"
+#include "dsb.h"
+
+namespace dsb {
+
+constexpr int kRowThreads = 128;
+
+struct alignas(16) bf16x8 {
+  uint32_t u[4];
+};
+
+__device__ __forceinline__ float block_sum_128(float v, float* red) {
+  v = warp_sum(v);
+  const int w = threadIdx.x >> 5, l = threadIdx.x & 31;
+  __syncthreads();
+  if (l == 0) red[w] = v;
+  __syncthreads();
+  return red[0] + red[1] + red[2] + red[3];
+}
+__device__ __forceinline__ float block_max_128(float v, float* red) {
+  v = warp_max(v);
+  const int w = threadIdx.x >> 5, l = threadIdx.x & 31;
+  __syncthreads();
+  if (l == 0) red[w] = v;
+  __syncthreads();
+  return fmaxf(fmaxf(red[0], red[1]), fmaxf(red[2], red[3]));
+}
+
+__device__ __forceinline__ uint32_t pack_e4m3x4(float a, float b, float c, float d) {
+  // satfinite conversion; inputs are already scaled into [-448, 448].
+  __nv_fp8x2_storage_t lo = __nv_cvt_float2_to_fp8x2(make_float2(a, b), __NV_SATFINITE, __NV_E4M3);
+  __nv_fp8x2_storage_t hi = __nv_cvt_float2_to_fp8x2(make_float2(c, d), __NV_SATFINITE, __NV_E4M3);
+  return static_cast<uint32_t>(lo) | (static_cast<uint32_t>(hi) << 16);
+}
+__device__ __forceinline__ uint32_t pack_s8x4(float a, float b, float c, float d) {
+  // round-half-even, clamp to [-127, 127]
+  int ia = max(-127, min(127, __float2int_rn(a)));
+  int ib = max(-127, min(127, __float2int_rn(b)));
+  int ic = max(-127, min(127, __float2int_rn(c)));
+  int id = max(-127, min(127, __float2int_rn(d)));
+  return (ia & 0xff) | ((ib & 0xff) << 8) | ((ic & 0xff) << 16) | ((id & 0xff) << 24);
+}
+
+// Per-row scale shared by the quantising kernels: amax / qmax, with a floor so
+// an all-zero row gives scale 1 (and a zero payload) instead of a division by 0.
+__device__ __forceinline__ float row_scale_from_amax(float amax, float qmax) {
+  return amax > 0.f ? amax / qmax : 1.0f;
+}
+
+// ------------------------------------------------------------ ln_modulate
+// y = LayerNorm(x; eps, no affine) * (1 + scale[d]) + shift[d]
+// NV = 128-bit vectors per thread (row width D <= 128 * 8 * NV).
+// OUT: 0 bf16, 1 e4m3 + row scale, 2 int8 + row scale.
+template <int NV, int OUT>
+__global__ void __launch_bounds__(kRowThreads) ln_modulate_kernel(const __nv_bfloat16* __restrict__ x, int64_t ld_x,
+                                                                  const float* __restrict__ shift,
+                                                                  const float* __restrict__ scale, void* __restrict__ y,
+                                                                  int64_t ld_y, float* __restrict__ row_scale, int M,
+                                                                  int D, float eps) {
+  __shared__ float red[4];
+  const int row = blockIdx.x;
+  if (row >= M) return;
+  const int nvec = D >> 3;
+  const __nv_bfloat16* xr = x + static_cast<int64_t>(row) * ld_x;
+  float v[NV][8];
+  float s = 0.f;
+#pragma unroll
+  for (int i = 0; i < NV; ++i) {
+    const int vi = threadIdx.x + i * kRowThreads;
+    if (vi < nvec) {
+      bf16x8 p = *reinterpret_cast<const bf16x8*>(xr + vi * 8);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        float2 f = unpack_bf16x2(p.u[j]);
+        v[i][2 * j] = f.x;
+        v[i][2 * j + 1] = f.y;
+        s += f.x + f.y;
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) v[i][j] = 0.f;
+    }
+  }
+  const float mean = block_sum_128(s, red) / static_cast<float>(D);
+  float q = 0.f;
+#pragma unroll
+  for (int i = 0; i < NV; ++i) {
+    const int vi = threadIdx.x + i * kRowThreads;
+    if (vi < nvec) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        float d = v[i][j] - mean;
+        q += d * d;
+      }
+    }
+  }
+  const float var = block_sum_128(q, red) / static_cast<float>(D);
+  const float rstd = rsqrtf(var + eps);
+  float amax = 0.f;
+#pragma unroll
+  for (int i = 0; i < NV; ++i) {
+    const int vi = threadIdx.x + i * kRowThreads;
+    if (vi < nvec) {
+      const float4 sc0 = *reinterpret_cast<const float4*>(scale + vi * 8);
+      const float4 sc1 = *reinterpret_cast<const float4*>(scale + vi * 8 + 4);
+      const float4 sh0 = *reinterpret_cast<const float4*>(shift + vi * 8);
+      const float4 sh1 = *reinterpret_cast<const float4*>(shift + vi * 8 + 4);
+      const float sc[8] = {sc0.x, sc0.y, sc0.z, sc0.w, sc1.x, sc1.y, sc1.z, sc1.w};
+      const float sh[8] = {sh0.x, sh0.y, sh0.z, sh0.w, sh1.x, sh1.y, sh1.z, sh1.w};
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        float o = (v[i][j] - mean) * rstd * (1.0f + sc[j]) + sh[j];
+        v[i][j] = o;
+        amax = fmaxf(amax, fabsf(o));
+      }
+    }
+  }
+  if constexpr (OUT == 0) {
+    __nv_bfloat16* yr = reinterpret_cast<__nv_bfloat16*>(y) + static_cast<int64_t>(row) * ld_y;
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+      const int vi = threadIdx.x + i * kRowThreads;
+      if (vi < nvec) {
+        bf16x8 p;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) p.u[j] = pack_bf16x2(v[i][2 * j], v[i][2 * j + 1]);
+        *reinterpret_cast<bf16x8*>(yr + vi * 8) = p;
+      }
+    }
+  } else {
+    amax = block_max_128(amax, red);
+    const float qmax = (OUT == 1) ? 448.0f : 127.0f;
+    const float sc = row_scale_from_amax(amax, qmax);
+    const float inv = 1.0f / sc;
+    if (threadIdx.x == 0) row_scale[row] = sc;
+    uint8_t* yr = reinterpret_cast<uint8_t*>(y) + static_cast<int64_t>(row) * ld_y;
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+      const int vi = threadIdx.x + i * kRowThreads;
+      if (vi < nvec) {
+        uint2 p;
+        if constexpr (OUT == 1) {
+          p.x = pack_e4m3x4(v[i][0] * inv, v[i][1] * inv, v[i][2] * inv, v[i][3] * inv);
+          p.y = pack_e4m3x4(v[i][4] * inv, v[i][5] * inv, v[i][6] * inv, v[i][7] * inv);
+        } else {
+          p.x = pack_s8x4(v[i][0] * inv, v[i][1] * inv, v[i][2] * inv, v[i][3] * inv);
+          p.y = pack_s8x4(v[i][4] * inv, v[i][5] * inv, v[i][6] * inv, v[i][7] * inv);
+        }
+        *reinterpret_cast<uint2*>(yr + vi * 8) = p;
+      }
+    }
+  }
+}
+
+template <int OUT>
+static int launch_ln_modulate(const void* x, int64_t ld_x, const float* shift, const float* scale, void* y,
+                              int64_t ld_y, float* row_scale, int M, int D, float eps, cudaStream_t st) {
+  const int nv = (D / 8 + kRowThreads - 1) / kRowThreads;
+  const __nv_bfloat16* xp = reinterpret_cast<const __nv_bfloat16*>(x);
+#define DSB_LN_CASE(NV)                                                                                         \
+  case NV:                                                                                                      \
+    ln_modulate_kernel<NV, OUT><<<M, kRowThreads, 0, st>>>(xp, ld_x, shift, scale, y, ld_y, row_scale, M, D, eps); \
+    break;
+  switch (nv) {
+    DSB_LN_CASE(1) DSB_LN_CASE(2) DSB_LN_CASE(3) DSB_LN_CASE(4) DSB_LN_CASE(5) DSB_LN_CASE(6) DSB_LN_CASE(7)
+    DSB_LN_CASE(8)
+    default:
+      return DSB_ERR_UNSUPPORTED;
+  }
+#undef DSB_LN_CASE
+  return cudaGetLastError() == cudaSuccess ? DSB_OK : DSB_ERR_CUDA;
+}
+
+// ---------------------------------------------------------- gate_residual
+// out = x + gate[d] * y   (gate == nullptr: out = x + y)
+__global__ void __launch_bounds__(256) gate_residual_kernel(const __nv_bfloat16* __restrict__ x, int64_t ld_x,
+                                                            const __nv_bfloat16* __restrict__ y, int64_t ld_y,
+                                                            const float* __restrict__ gate,
+                                                            __nv_bfloat16* __restrict__ out, int64_t ld_o, int M,
+                                                            int D) {
+  const int nvec = D >> 3;
+  const int64_t total = static_cast<int64_t>(M) * nvec;
+  for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < total;
+       i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const int64_t r = i / nvec;
+    const int c = static_cast<int>(i - r * nvec) * 8;
+    bf16x8 a = *reinterpret_cast<const bf16x8*>(x + r * ld_x + c);
+    bf16x8 b = *reinterpret_cast<const bf16x8*>(y + r * ld_y + c);
+    float g[8];
+    if (gate) {
+      const float4 g0 = *reinterpret_cast<const float4*>(gate + c);
+      const float4 g1 = *reinterpret_cast<const float4*>(gate + c + 4);
+      g[0] = g0.x, g[1] = g0.y, g[2] = g0.z, g[3] = g0.w, g[4] = g1.x, g[5] = g1.y, g[6] = g1.z, g[7] = g1.w;
+    } else {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) g[j] = 1.f;
+    }
+    bf16x8 o;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      float2 fa = unpack_bf16x2(a.u[j]), fb = unpack_bf16x2(b.u[j]);
+      o.u[j] = pack_bf16x2(fa.x + g[2 * j] * fb.x, fa.y + g[2 * j + 1] * fb.y);
+    }
+    *reinterpret_cast<bf16x8*>(out + r * ld_o + c) = o;
+  }
+}
+
+// ---------------------------------------------------- rmsnorm_rope_heads
+// Per-head RMSNorm (head_dim 128, weight[128]) followed by RoPE on adjacent
+// pairs, in place, for `nsel` head groups (q and k) of a [S, ld] buffer.
+// One warp per (token, head).  rope == nullptr skips the rotation.
+// rope row for token s is rope[(rope_row0 + s) * 64 + j] = (cos, sin).
+__global__ void __launch_bounds__(256) rmsnorm_rope_heads_kernel(__nv_bfloat16* __restrict__ buf, int64_t ld, int S,
+                                                                 int H, int nsel, const float* __restrict__ w_q,
+                                                                 const float* __restrict__ w_k,
+                                                                 const float2* __restrict__ rope, int rope_row0,
+                                                                 float eps) {
+  const int warps_per_block = blockDim.x >> 5;
+  const int64_t wid = static_cast<int64_t>(blockIdx.x) * warps_per_block + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  const int64_t total = static_cast<int64_t>(S) * nsel * H;
+  if (wid >= total) return;
+  const int s = static_cast<int>(wid / (nsel * H));
+  const int hh = static_cast<int>(wid - static_cast<int64_t>(s) * (nsel * H));  // [0, nsel*H): q heads then k heads
+  const float* w = (hh < H) ? w_q : w_k;
+  __nv_bfloat16* p = buf + static_cast<int64_t>(s) * ld + hh * 128 + lane * 4;
+  uint2 raw = *reinterpret_cast<const uint2*>(p);
+  float2 a = unpack_bf16x2(raw.x), b = unpack_bf16x2(raw.y);
+  float ss = a.x * a.x + a.y * a.y + b.x * b.x + b.y * b.y;
+  ss = warp_sum(ss);
+  const float r = rsqrtf(ss * (1.0f / 128.0f) + eps);
+  const float4 wv = *reinterpret_cast<const float4*>(w + lane * 4);
+  float x0 = a.x * r * wv.x, x1 = a.y * r * wv.y, x2 = b.x * r * wv.z, x3 = b.y * r * wv.w;
+  if (rope) {
+    const float2* rr = rope + (static_cast<int64_t>(rope_row0) + s) * 64 + lane * 2;
+    const float2 c0 = rr[0], c1 = rr[1];
+    const float y0 = c0.x * x0 - c0.y * x1, y1 = c0.y * x0 + c0.x * x1;
+    const float y2 = c1.x * x2 - c1.y * x3, y3 = c1.y * x2 + c1.x * x3;
+    x0 = y0, x1 = y1, x2 = y2, x3 = y3;
+  }
+  uint2 o;
+  o.x = pack_bf16x2(x0, x1);
+  o.y = pack_bf16x2(x2, x3);
+  *reinterpret_cast<uint2*>(p) = o;
+}
+
+// ------------------------------------------------------ rmsnorm_full_rope
+// RMSNorm over the whole row (all heads, width D = H*128) with weight[D],
+// then per-head RoPE (same 64 (cos,sin) pairs for every head of a token).
+// One CTA per row; in place.  rope == nullptr skips the rotation.
+template <int NV>
+__global__ void __launch_bounds__(kRowThreads) rmsnorm_full_rope_kernel(__nv_bfloat16* __restrict__ buf, int64_t ld,
+                                                                        int M, int D, const float* __restrict__ w,
+                                                                        const float2* __restrict__ rope,
+                                                                        int rope_row0, float eps) {
+  __shared__ float red[4];
+  const int row = blockIdx.x;
+  if (row >= M) return;
+  const int nvec = D >> 3;
+  __nv_bfloat16* xr = buf + static_cast<int64_t>(row) * ld;
+  float v[NV][8];
+  float ss = 0.f;
+#pragma unroll
+  for (int i = 0; i < NV; ++i) {
+    const int vi = threadIdx.x + i * kRowThreads;
+    if (vi < nvec) {
+      bf16x8 p = *reinterpret_cast<const bf16x8*>(xr + vi * 8);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        float2 f = unpack_bf16x2(p.u[j]);
+        v[i][2 * j] = f.x;
+        v[i][2 * j + 1] = f.y;
+        ss += f.x * f.x + f.y * f.y;
+      }
+    }
+  }
+  const float r = rsqrtf(block_sum_128(ss, red) / static_cast<float>(D) + eps);
+#pragma unroll
+  for (int i = 0; i < NV; ++i) {
+    const int vi = threadIdx.x + i * kRowThreads;
+    if (vi < nvec) {
+      const float4 w0 = *reinterpret_cast<const float4*>(w + vi * 8);
+      const float4 w1 = *reinterpret_cast<const float4*>(w + vi * 8 + 4);
+      const float ww[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
+      float o[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) o[j] = v[i][j] * r * ww[j];
+      if (rope) {
+        const int pair0 = ((vi * 8) & 127) >> 1;  // pair index inside the head
+        const float2* rr = rope + (static_cast<int64_t>(rope_row0) + row) * 64 + pair0;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float2 c = rr[j];
+          const float a = o[2 * j], b = o[2 * j + 1];
+          o[2 * j] = c.x * a - c.y * b;
+          o[2 * j + 1] = c.y * a + c.x * b;
+        }
+      }
+      bf16x8 p;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) p.u[j] = pack_bf16x2(o[2 * j], o[2 * j + 1]);
+      *reinterpret_cast<bf16x8*>(xr + vi * 8) = p;
+    }
+  }
+}
+
+// ------------------------------------------------------------- quant_rows
+// bf16 [M, K] -> e4m3 or int8 [M, K] plus row_scale[M] (dynamic, amax based).
+// The row is read twice; the second read is served by L1/L2.
+template <int OUT>
+__global__ void __launch_bounds__(256) quant_rows_kernel(const __nv_bfloat16* __restrict__ x, int64_t ld_x,
+                                                         uint8_t* __restrict__ y, int64_t ld_y,
+                                                         float* __restrict__ row_scale, int M, int K) {
+  __shared__ float red[8];
+  const int row = blockIdx.x;
+  if (row >= M) return;
+  const int nvec = K >> 3;
+  const __nv_bfloat16* xr = x + static_cast<int64_t>(row) * ld_x;
+  float amax = 0.f;
+  for (int vi = threadIdx.x; vi < nvec; vi += blockDim.x) {
+    bf16x8 p = *reinterpret_cast<const bf16x8*>(xr + vi * 8);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      float2 f = unpack_bf16x2(p.u[j]);
+      amax = fmaxf(amax, fmaxf(fabsf(f.x), fabsf(f.y)));
+    }
+  }
+  amax = warp_max(amax);
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = amax;
+  __syncthreads();
+  amax = red[0];
+#pragma unroll
+  for (int i = 1; i < 8; ++i) amax = fmaxf(amax, red[i]);
+  const float qmax = (OUT == 1) ? 448.0f : 127.0f;
+  const float sc = row_scale_from_amax(amax, qmax);
+  const float inv = 1.0f / sc;
+  if (threadIdx.x == 0) row_scale[row] = sc;
+  uint8_t* yr = y + static_cast<int64_t>(row) * ld_y;
+  for (int vi = threadIdx.x; vi < nvec; vi += blockDim.x) {
+    bf16x8 p = *reinterpret_cast<const bf16x8*>(xr + vi * 8);
+    float f[8];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      float2 t = unpack_bf16x2(p.u[j]);
+      f[2 * j] = t.x * inv;
+      f[2 * j + 1] = t.y * inv;
+    }
+    uint2 o;
+    if constexpr (OUT == 1) {
+      o.x = pack_e4m3x4(f[0], f[1], f[2], f[3]);
+      o.y = pack_e4m3x4(f[4], f[5], f[6], f[7]);
+    } else {
+      o.x = pack_s8x4(f[0], f[1], f[2], f[3]);
+      o.y = pack_s8x4(f[4], f[5], f[6], f[7]);
+    }
+    *reinterpret_cast<uint2*>(yr + vi * 8) = o;
+  }
+}
+
+// ------------------------------------------------------------------- gemv
+// y[n] = (sum_k W[n,k] * f(x[k])) * w_scale[n or 0] + bias[n],  one warp per
+// output row, the activation vector staged once per CTA in shared memory.
+// WFMT: 0 bf16, 1 e4m3, 2 int8.  ACT_IN: 0 identity, 1 SiLU on x.
+// ACT_OUT: 0 none, 1 SiLU, 2 GELU-tanh on y.
+template <int WFMT>
+__global__ void __launch_bounds__(256) gemv_kernel(const void* __restrict__ W, int64_t ld_w_bytes,
+                                                   const float* __restrict__ x, const float* __restrict__ w_scale,
+                                                   int w_scale_stride, const float* __restrict__ bias,
+                                                   float* __restrict__ y, int N, int K, int act_in, int act_out) {
+  extern __shared__ float xs[];
+  for (int k = threadIdx.x; k < K; k += blockDim.x) {
+    float t = x[k];
+    xs[k] = act_in == 1 ? silu(t) : t;
+  }
+  __syncthreads();
+  const int lane = threadIdx.x & 31;
+  const int warps = blockDim.x >> 5;
+  for (int n = blockIdx.x * warps + (threadIdx.x >> 5); n < N; n += gridDim.x * warps) {
+    const uint8_t* wr = reinterpret_cast<const uint8_t*>(W) + static_cast<int64_t>(n) * ld_w_bytes;
+    float acc = 0.f;
+    if constexpr (WFMT == 0) {
+      for (int k = lane * 8; k < K; k += 256) {
+        bf16x8 p = *reinterpret_cast<const bf16x8*>(wr + k * 2);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          float2 f = unpack_bf16x2(p.u[j]);
+          acc += f.x * xs[k + 2 * j] + f.y * xs[k + 2 * j + 1];
+        }
+      }
+    } else {
+      for (int k = lane * 16; k < K; k += 512) {
+        const uint4 p = *reinterpret_cast<const uint4*>(wr + k);
+        const uint32_t u[4] = {p.x, p.y, p.z, p.w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          if constexpr (WFMT == 1) {
+            const __half2_raw h0 =
+                __nv_cvt_fp8x2_to_halfraw2(static_cast<__nv_fp8x2_storage_t>(u[j] & 0xffffu), __NV_E4M3);
+            const __half2_raw h1 =
+                __nv_cvt_fp8x2_to_halfraw2(static_cast<__nv_fp8x2_storage_t>(u[j] >> 16), __NV_E4M3);
+            const float2 f0 = __half22float2(*reinterpret_cast<const __half2*>(&h0));
+            const float2 f1 = __half22float2(*reinterpret_cast<const __half2*>(&h1));
+            acc += f0.x * xs[k + 4 * j] + f0.y * xs[k + 4 * j + 1] + f1.x * xs[k + 4 * j + 2] +
+                   f1.y * xs[k + 4 * j + 3];
+          } else {
+            const int v = static_cast<int>(u[j]);
+            acc += static_cast<float>(static_cast<int8_t>(v & 0xff)) * xs[k + 4 * j] +
+                   static_cast<float>(static_cast<int8_t>((v >> 8) & 0xff)) * xs[k + 4 * j + 1] +
+                   static_cast<float>(static_cast<int8_t>((v >> 16) & 0xff)) * xs[k + 4 * j + 2] +
+                   static_cast<float>(static_cast<int8_t>((v >> 24) & 0xff)) * xs[k + 4 * j + 3];
+          }
+        }
+      }
+    }
+    acc = warp_sum(acc);
+    if (lane == 0) {
+      float sc = w_scale ? w_scale[static_cast<int64_t>(n) * w_scale_stride] : 1.0f;
+      float o = acc * sc + (bias ? bias[n] : 0.f);
+      if (act_out == 1) o = silu(o);
+      if (act_out == 2) o = gelu_tanh(o);
+      y[n] = o;
+    }
+  }
+}
+
+// ------------------------------------------------------------ euler step
+// out = cast(latents_fp32 + model_out * dt); optional inpaint blend
+// model_out' = model_out * mask + init * (1 - mask) applied first.
+__global__ void __launch_bounds__(256) euler_step_kernel(const __nv_bfloat16* __restrict__ latents,
+                                                         const __nv_bfloat16* __restrict__ model_out,
+                                                         const __nv_bfloat16* __restrict__ init,
+                                                         const __nv_bfloat16* __restrict__ mask, float dt,
+                                                         __nv_bfloat16* __restrict__ out, int64_t n) {
+  for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < n;
+       i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    float m = __bfloat162float(model_out[i]);
+    if (mask) {
+      // the reference evaluates the blend in the model-output dtype
+      const float k = __bfloat162float(mask[i]);
+      const float a = __bfloat162float(__float2bfloat16(m * k));
+      const float om = __bfloat162float(__float2bfloat16(1.0f - k));
+      const float b = __bfloat162float(__float2bfloat16(__bfloat162float(init[i]) * om));
+      m = __bfloat162float(__float2bfloat16(a + b));
+    }
+    // bf16 tensor times a 0-dim fp32 sigma difference stays bf16 in the reference
+    const float step = __bfloat162float(__float2bfloat16(m * dt));
+    out[i] = __float2bfloat16(__bfloat162float(latents[i]) + step);
+  }
+}
+__global__ void __launch_bounds__(256) euler_step_f32_kernel(const float* __restrict__ latents,
+                                                             const float* __restrict__ model_out,
+                                                             const float* __restrict__ init,
+                                                             const float* __restrict__ mask, float dt,
+                                                             float* __restrict__ out, int64_t n) {
+  for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < n;
+       i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    float m = model_out[i];
+    if (mask) m = m * mask[i] + init[i] * (1.0f - mask[i]);
+    out[i] = latents[i] + m * dt;
+  }
+}
+
+static bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+}  // namespace dsb
+
+using namespace dsb;
+
+extern "C" {
+
+int dsb_ln_modulate(const void* x, int64_t ld_x, const float* shift, const float* scale, void* y, int64_t ld_y,
+                    float* row_scale, int M, int D, float eps, int out_fmt, void* stream) {
+  if (!x || !shift || !scale || !y || M < 0 || D <= 0 || (D & 7) || (ld_x & 7) || !aligned16(x) || !aligned16(y) ||
+      !aligned16(shift) || !aligned16(scale))
+    return DSB_ERR_ARG;
+  if (out_fmt != DSB_FMT_BF16 && !row_scale) return DSB_ERR_ARG;
+  if ((out_fmt == DSB_FMT_BF16 && (ld_y & 7)) || (out_fmt != DSB_FMT_BF16 && (ld_y & 15))) return DSB_ERR_ARG;
+  if (M == 0) return DSB_OK;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  switch (out_fmt) {
+    case DSB_FMT_BF16:
+      return launch_ln_modulate<0>(x, ld_x, shift, scale, y, ld_y, row_scale, M, D, eps, st);
+    case DSB_FMT_E4M3:
+      return launch_ln_modulate<1>(x, ld_x, shift, scale, y, ld_y, row_scale, M, D, eps, st);
+    case DSB_FMT_INT8:
+      return launch_ln_modulate<2>(x, ld_x, shift, scale, y, ld_y, row_scale, M, D, eps, st);
+    default:
+      return DSB_ERR_ARG;
+  }
+}
+
+int dsb_gate_residual(const void* x, int64_t ld_x, const void* y, int64_t ld_y, const float* gate, void* out,
+                      int64_t ld_o, int M, int D, void* stream) {
+  if (!x || !y || !out || M < 0 || D <= 0 || (D & 7) || (ld_x & 7) || (ld_y & 7) || (ld_o & 7) || !aligned16(x) ||
+      !aligned16(y) || !aligned16(out) || (gate && !aligned16(gate)))
+    return DSB_ERR_ARG;
+  if (M == 0) return DSB_OK;
+  const int64_t total = static_cast<int64_t>(M) * (D / 8);
+  int blocks = static_cast<int>((total + 255) / 256);
+  const int cap = sm_count() * 8;
+  if (blocks > cap) blocks = cap;
+  gate_residual_kernel<<<blocks, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      reinterpret_cast<const __nv_bfloat16*>(x), ld_x, reinterpret_cast<const __nv_bfloat16*>(y), ld_y, gate,
+      reinterpret_cast<__nv_bfloat16*>(out), ld_o, M, D);
+  return cudaGetLastError() == cudaSuccess ? DSB_OK : DSB_ERR_CUDA;
+}
+
+int dsb_rmsnorm_rope_heads(void* buf, int64_t ld, int S, int H, int head_dim, int nsel, const float* w_q,
+                           const float* w_k, const float* rope, int rope_row0, float eps, void* stream) {
+  if (!buf || !w_q || S < 0 || H <= 0 || head_dim != 128 || (nsel != 1 && nsel != 2) || (nsel == 2 && !w_k) ||
+      (ld & 7) || !aligned16(buf) || !aligned16(w_q) || (w_k && !aligned16(w_k)) || (rope && !aligned16(rope)))
+    return DSB_ERR_ARG;
+  if (S == 0) return DSB_OK;
+  const int64_t total = static_cast<int64_t>(S) * nsel * H;
+  const int blocks = static_cast<int>((total + 7) / 8);
+  rmsnorm_rope_heads_kernel<<<blocks, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      reinterpret_cast<__nv_bfloat16*>(buf), ld, S, H, nsel, w_q, w_k ? w_k : w_q,
+      reinterpret_cast<const float2*>(rope), rope_row0, eps);
+  return cudaGetLastError() == cudaSuccess ? DSB_OK : DSB_ERR_CUDA;
+}
+
+int dsb_rmsnorm_full(void* buf, int64_t ld, int M, int D, const float* w, const float* rope, int rope_row0, float eps,
+                     void* stream) {
+  if (!buf || !w || M < 0 || D <= 0 || (D & 127) || (ld & 7) || !aligned16(buf) || !aligned16(w) ||
+      (rope && !aligned16(rope)))
+    return DSB_ERR_ARG;
+  if (M == 0) return DSB_OK;
+  const int nv = (D / 8 + kRowThreads - 1) / kRowThreads;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  __nv_bfloat16* b = reinterpret_cast<__nv_bfloat16*>(buf);
+  const float2* rp = reinterpret_cast<const float2*>(rope);
+#define DSB_RMS_CASE(NV)                                                                              \
+  case NV:                                                                                            \
+    rmsnorm_full_rope_kernel<NV><<<M, kRowThreads, 0, st>>>(b, ld, M, D, w, rp, rope_row0, eps);      \
+    break;
+  switch (nv) {
+    DSB_RMS_CASE(1) DSB_RMS_CASE(2) DSB_RMS_CASE(3) DSB_RMS_CASE(4) DSB_RMS_CASE(5) DSB_RMS_CASE(6) DSB_RMS_CASE(7)
+    DSB_RMS_CASE(8)
+    default:
+      return DSB_ERR_UNSUPPORTED;
+  }
+#undef DSB_RMS_CASE
+  return cudaGetLastError() == cudaSuccess ? DSB_OK : DSB_ERR_CUDA;
+}
+
+int dsb_quant_rows(const void* x, int64_t ld_x, void* y, int64_t ld_y, float* row_scale, int M, int K, int out_fmt,
+                   void* stream) {
+  if (!x || !y || !row_scale || M < 0 || K <= 0 || (K & 7) || (ld_x & 7) || (ld_y & 15) || !aligned16(x) ||
+      !aligned16(y))
+    return DSB_ERR_ARG;
+  if (M == 0) return DSB_OK;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  const __nv_bfloat16* xp = reinterpret_cast<const __nv_bfloat16*>(x);
+  uint8_t* yp = reinterpret_cast<uint8_t*>(y);
+  if (out_fmt == DSB_FMT_E4M3)
+    quant_rows_kernel<1><<<M, 256, 0, st>>>(xp, ld_x, yp, ld_y, row_scale, M, K);
+  else if (out_fmt == DSB_FMT_INT8)
+    quant_rows_kernel<2><<<M, 256, 0, st>>>(xp, ld_x, yp, ld_y, row_scale, M, K);
+  else
+    return DSB_ERR_ARG;
+  return cudaGetLastError() == cudaSuccess ? DSB_OK : DSB_ERR_CUDA;
+}
+
+int dsb_gemv(const void* W, int64_t ld_w, int w_fmt, const float* x, const float* w_scale, int w_scale_stride,
+             const float* bias, float* y, int N, int K, int act_in, int act_out, void* stream) {
+  if (!W || !x || !y || N < 0 || K <= 0 || !aligned16(W)) return DSB_ERR_ARG;
+  const int esz = (w_fmt == DSB_FMT_BF16) ? 2 : 1;
+  const int kq = (w_fmt == DSB_FMT_BF16) ? 8 : 16;
+  if ((K % kq) || ((ld_w * esz) & 15)) return DSB_ERR_ARG;
+  if (static_cast<size_t>(K) * 4 > 96 * 1024) return DSB_ERR_UNSUPPORTED;
+  if (N == 0) return DSB_OK;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  int blocks = (N + 7) / 8;
+  const int cap = sm_count() * 8;
+  if (blocks > cap) blocks = cap;
+  const size_t smem = static_cast<size_t>(K) * 4;
+  const int64_t ldb = ld_w * esz;
+#define DSB_GEMV(F)                                                                                             \
+  {                                                                                                             \
+    auto kern = gemv_kernel<F>;                                                                                 \
+    DSB_ENSURE_SMEM(kern, 96 * 1024);                                                                           \
+    gemv_kernel<F><<<blocks, 256, smem, st>>>(W, ldb, x, w_scale, w_scale_stride, bias, y, N, K, act_in, act_out); \
+  }
+  if (w_fmt == DSB_FMT_BF16) DSB_GEMV(0)
+  else if (w_fmt == DSB_FMT_E4M3) DSB_GEMV(1)
+  else if (w_fmt == DSB_FMT_INT8) DSB_GEMV(2)
+  else return DSB_ERR_ARG;
+#undef DSB_GEMV
+  return cudaGetLastError() == cudaSuccess ? DSB_OK : DSB_ERR_CUDA;
+}
+
+int dsb_euler_step(const void* latents, const void* model_out, const void* init, const void* mask, float dt, void* out,
+                   int64_t n, int is_f32, void* stream) {
+  if (!latents || !model_out || !out || n < 0 || (mask && !init)) return DSB_ERR_ARG;
+  if (n == 0) return DSB_OK;
+  int blocks = static_cast<int>((n + 255) / 256);
+  const int cap = sm_count() * 8;
+  if (blocks > cap) blocks = cap;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  if (is_f32)
+    euler_step_f32_kernel<<<blocks, 256, 0, st>>>(reinterpret_cast<const float*>(latents),
+                                                  reinterpret_cast<const float*>(model_out),
+                                                  reinterpret_cast<const float*>(init),
+                                                  reinterpret_cast<const float*>(mask), dt,
+                                                  reinterpret_cast<float*>(out), n);
+  else
+    euler_step_kernel<<<blocks, 256, 0, st>>>(
+        reinterpret_cast<const __nv_bfloat16*>(latents), reinterpret_cast<const __nv_bfloat16*>(model_out),
+        reinterpret_cast<const __nv_bfloat16*>(init), reinterpret_cast<const __nv_bfloat16*>(mask), dt,
+        reinterpret_cast<__nv_bfloat16*>(out), n);
+  return cudaGetLastError() == cudaSuccess ? DSB_OK : DSB_ERR_CUDA;
+}
+
+}  // extern "C"

@@ -1,0 +1,370 @@
+// Quantised / bf16 Linear as a persistent, warp-specialised tcgen05 GEMM.
+//
+//   out[m,n] = epilogue( sum_k A[m,k] * W[n,k] )      A: [M,K], W: [N,K], K contiguous in both
+//
+// One CTA per SM walks output tiles of 128 x BLOCK_N.  Warp 0 feeds a ring of
+// shared-memory stages with plain TMA loads (128-byte swizzle, one 128-byte
+// K-slab per stage), warp 1 issues tcgen05.mma (M=128, N=BLOCK_N, 32 bytes of K
+// per instruction) into one of two TMEM accumulators, and warps 2..5 drain the
+// other accumulator with tcgen05.ld, apply the fused epilogue (dequant scales,
+// bias, GELU-tanh, gate-residual, output routing) and store bf16 rows.
+//
+// HBM layout: A and W are row-major with K contiguous, so both operands are
+// "K-major" for the tensor core and no transpose or repack is ever needed; the
+// FP8/INT8 payload is the plain [N,K] byte matrix produced by the prepack.
+#include <mutex>
+
+#include "common.cuh"
+#include "dsb.h"
+
+namespace dsb {
+
+constexpr int kBlockM = 128;
+constexpr int kSlabBytes = 128;  // bytes of K per stage row (one swizzle row)
+constexpr int kGemmThreads = 192;
+
+struct GemmEpilogue {
+  const float* row_scale;
+  const float* col_scale;
+  int col_scale_stride;
+  const float* bias;
+  int act;
+  int act_col0;
+  const float* gate;
+  const __nv_bfloat16* resid;
+  int64_t ld_resid;
+  __nv_bfloat16* out0;
+  int64_t ld_out0;
+  __nv_bfloat16* out1;
+  int64_t ld_out1;
+  int split_col;
+  int* status;
+};
+
+template <int BLOCK_N>
+struct GemmSmem {
+  static constexpr int kStageA = kBlockM * kSlabBytes;
+  static constexpr int kStageB = BLOCK_N * kSlabBytes;
+  static constexpr int kStage = kStageA + kStageB;
+  static constexpr int kStages = (BLOCK_N == 256) ? 4 : 6;
+  static constexpr int kBarBytes = 256;
+  static constexpr int kTotal = kStages * kStage + kBarBytes + 1024;  // + alignment slack
+};
+
+template <int KIND, int BLOCK_N>
+__global__ void __launch_bounds__(kGemmThreads, 1)
+    gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b, int M, int N,
+                int K, GemmEpilogue ep) {
+  using SM = GemmSmem<BLOCK_N>;
+  constexpr int kStages = SM::kStages;
+  constexpr int kElemBytes = (KIND == KIND_F16) ? 2 : 1;
+  constexpr int kSlabElems = kSlabBytes / kElemBytes;
+  constexpr uint32_t kTmemCols = 2 * BLOCK_N;
+  constexpr uint32_t kIdesc =
+      (KIND == KIND_F16)  ? make_idesc(DFMT_F32, FMT_BF16, FMT_BF16, 0, 0, kBlockM, BLOCK_N)
+      : (KIND == KIND_F8) ? make_idesc(DFMT_F32, FMT_E4M3, FMT_E4M3, 0, 0, kBlockM, BLOCK_N)
+                          : make_idesc(DFMT_S32, FMT_S8, FMT_S8, 0, 0, kBlockM, BLOCK_N);
+
+  extern __shared__ uint8_t smem_raw[];
+  // 1024-byte alignment: the 128-byte swizzle pattern repeats every 8 rows = 1024 bytes.
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* bar_base = smem + kStages * SM::kStage;
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(bar_base);
+  uint64_t* empty_bar = full_bar + kStages;
+  uint64_t* tmem_full = empty_bar + kStages;
+  uint64_t* tmem_empty = tmem_full + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tmem_empty + 2);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(&tmem_full[a], 1);
+      mbar_init(&tmem_empty[a], 128);
+    }
+    *abort_flag = 0;
+    fence_mbar_init();
+  }
+  if (warp == 0 && lane == 0) {
+    tma_prefetch_desc(&tmap_a);
+    tma_prefetch_desc(&tmap_b);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  const int tiles_m = (M + kBlockM - 1) / kBlockM;
+  const int tiles_n = (N + BLOCK_N - 1) / BLOCK_N;
+  const int num_tiles = tiles_m * tiles_n;
+  const int num_kb = (K + kSlabElems - 1) / kSlabElems;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      for (int t = blockIdx.x; t < num_tiles; t += gridDim.x) {
+        const int m0 = (t % tiles_m) * kBlockM;
+        const int n0 = (t / tiles_m) * BLOCK_N;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag)) goto producer_done;
+          uint8_t* sa = smem + stage * SM::kStage;
+          uint8_t* sb = sa + SM::kStageA;
+          mbar_expect_tx(&full_bar[stage], SM::kStage);
+          tma_load_2d(sa, &tmap_a, &full_bar[stage], kb * kSlabElems, m0);
+          tma_load_2d(sb, &tmap_b, &full_bar[stage], kb * kSlabElems, n0);
+          if (++stage == kStages) {
+            stage = 0;
+            phase ^= 1;
+          }
+        }
+      }
+    }
+  producer_done:;
+  } else if (warp == 1) {
+    // -------------------------------------------------------------- MMA issuer
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      int it = 0;
+      for (int t = blockIdx.x; t < num_tiles; t += gridDim.x, ++it) {
+        const int acc = it & 1;
+        const uint32_t acc_phase = (it >> 1) & 1;
+        if (!mbar_wait(&tmem_empty[acc], acc_phase ^ 1, abort_flag)) goto mma_done;
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * BLOCK_N;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(&full_bar[stage], phase, abort_flag)) goto mma_done;
+          tc_fence_after();
+          const uint32_t sa = smem_u32(smem + stage * SM::kStage);
+          const uint64_t adesc = make_desc_k_sw128(sa);
+          const uint64_t bdesc = make_desc_k_sw128(sa + SM::kStageA);
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {
+            // advancing 32 bytes along K inside the swizzle row = +2 in the (addr >> 4) field
+            mma_ss<KIND>(d_tmem, adesc + 2 * k, bdesc + 2 * k, kIdesc, (kb | k) != 0 ? 1u : 0u);
+          }
+          tc_commit(&empty_bar[stage]);
+          if (++stage == kStages) {
+            stage = 0;
+            phase ^= 1;
+          }
+        }
+        tc_commit(&tmem_full[acc]);
+      }
+    }
+  mma_done:;
+  } else {
+    // ---------------------------------------------------------------- epilogue
+    const int quad = warp & 3;  // TMEM lane quadrant this warp may read
+    int it = 0;
+    for (int t = blockIdx.x; t < num_tiles; t += gridDim.x, ++it) {
+      const int acc = it & 1;
+      const uint32_t acc_phase = (it >> 1) & 1;
+      const int m0 = (t % tiles_m) * kBlockM;
+      const int n0 = (t / tiles_m) * BLOCK_N;
+      if (!mbar_wait(&tmem_full[acc], acc_phase, abort_flag)) break;
+      tc_fence_after();
+      const int m = m0 + quad * 32 + lane;
+      const bool row_ok = m < M;
+      const float rs = (ep.row_scale && row_ok) ? ep.row_scale[m] : 1.0f;
+      __nv_bfloat16* out;
+      int64_t ld_out;
+      int col_shift;
+      if (n0 >= ep.split_col) {
+        out = ep.out1, ld_out = ep.ld_out1, col_shift = ep.split_col;
+      } else {
+        out = ep.out0, ld_out = ep.ld_out0, col_shift = 0;
+      }
+      const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + acc * BLOCK_N;
+#pragma unroll 1
+      for (int c = 0; c < BLOCK_N / 32; ++c) {
+        const int nc = n0 + c * 32;
+        if (nc >= N) break;  // uniform across the CTA
+        uint32_t r[32];
+        tmem_ld32(t_row + c * 32, r);
+        tc_wait_ld();
+        if (row_ok) {
+#pragma unroll
+          for (int g = 0; g < 4; ++g) {
+            const int n = nc + g * 8;
+            if (n < N) {
+              float v[8];
+#pragma unroll
+              for (int j = 0; j < 8; ++j) {
+                if constexpr (KIND == KIND_I8)
+                  v[j] = static_cast<float>(static_cast<int>(r[g * 8 + j]));
+                else
+                  v[j] = __uint_as_float(r[g * 8 + j]);
+              }
+              if (ep.col_scale) {
+                if (ep.col_scale_stride) {
+                  const float4 c0 = __ldg(reinterpret_cast<const float4*>(ep.col_scale + n));
+                  const float4 c1 = __ldg(reinterpret_cast<const float4*>(ep.col_scale + n + 4));
+                  v[0] *= c0.x * rs, v[1] *= c0.y * rs, v[2] *= c0.z * rs, v[3] *= c0.w * rs;
+                  v[4] *= c1.x * rs, v[5] *= c1.y * rs, v[6] *= c1.z * rs, v[7] *= c1.w * rs;
+                } else {
+                  const float cs = __ldg(ep.col_scale) * rs;
+#pragma unroll
+                  for (int j = 0; j < 8; ++j) v[j] *= cs;
+                }
+              } else if (ep.row_scale) {
+#pragma unroll
+                for (int j = 0; j < 8; ++j) v[j] *= rs;
+              }
+              if (ep.bias) {
+                const float4 b0 = __ldg(reinterpret_cast<const float4*>(ep.bias + n));
+                const float4 b1 = __ldg(reinterpret_cast<const float4*>(ep.bias + n + 4));
+                v[0] += b0.x, v[1] += b0.y, v[2] += b0.z, v[3] += b0.w;
+                v[4] += b1.x, v[5] += b1.y, v[6] += b1.z, v[7] += b1.w;
+              }
+              if (ep.act != DSB_ACT_NONE && n >= ep.act_col0) {
+                if (ep.act == DSB_ACT_GELU_TANH) {
+#pragma unroll
+                  for (int j = 0; j < 8; ++j) v[j] = gelu_tanh(v[j]);
+                } else {
+#pragma unroll
+                  for (int j = 0; j < 8; ++j) v[j] = silu(v[j]);
+                }
+              }
+              if (ep.resid) {
+                const uint4 rr = *reinterpret_cast<const uint4*>(ep.resid + static_cast<int64_t>(m) * ep.ld_resid + n);
+                const uint32_t ru[4] = {rr.x, rr.y, rr.z, rr.w};
+                float gte[8];
+                if (ep.gate) {
+                  const float4 g0 = __ldg(reinterpret_cast<const float4*>(ep.gate + n));
+                  const float4 g1 = __ldg(reinterpret_cast<const float4*>(ep.gate + n + 4));
+                  gte[0] = g0.x, gte[1] = g0.y, gte[2] = g0.z, gte[3] = g0.w;
+                  gte[4] = g1.x, gte[5] = g1.y, gte[6] = g1.z, gte[7] = g1.w;
+                } else {
+#pragma unroll
+                  for (int j = 0; j < 8; ++j) gte[j] = 1.0f;
+                }
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                  const float2 f = unpack_bf16x2(ru[j]);
+                  v[2 * j] = f.x + gte[2 * j] * v[2 * j];
+                  v[2 * j + 1] = f.y + gte[2 * j + 1] * v[2 * j + 1];
+                }
+              }
+              uint4 o;
+              o.x = pack_bf16x2(v[0], v[1]);
+              o.y = pack_bf16x2(v[2], v[3]);
+              o.z = pack_bf16x2(v[4], v[5]);
+              o.w = pack_bf16x2(v[6], v[7]);
+              *reinterpret_cast<uint4*>(out + static_cast<int64_t>(m) * ld_out + (n - col_shift)) = o;
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      mbar_arrive(&tmem_empty[acc]);
+    }
+  }
+
+  // Common exit: on the abort path give copies still in flight time to land
+  // before shared memory and TMEM go back to the SM.
+  if (*abort_flag) __nanosleep(200000);
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, kTmemCols);
+  }
+  if (threadIdx.x == 0 && *abort_flag && ep.status) atomicCAS(ep.status, 0, DSB_ERR_TIMEOUT);
+}
+
+template <int KIND, int BLOCK_N>
+static int launch_gemm(const void* A, int64_t lda, const void* W, int64_t ldw, int M, int N, int K,
+                       const GemmEpilogue& ep, cudaStream_t st) {
+  using SM = GemmSmem<BLOCK_N>;
+  constexpr int esz = (KIND == KIND_F16) ? 2 : 1;
+  constexpr int slab_elems = kSlabBytes / esz;
+  const CUtensorMapDataType dt = (KIND == KIND_F16) ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_UINT8;
+  CUtensorMap ta, tb;
+  if (make_tmap_2d(&ta, dt, esz, A, M, K, lda * esz, kBlockM, slab_elems) != DSB_OK) return DSB_ERR_CUDA;
+  if (make_tmap_2d(&tb, dt, esz, W, N, K, ldw * esz, BLOCK_N, slab_elems) != DSB_OK) return DSB_ERR_CUDA;
+  auto kern = gemm_kernel<KIND, BLOCK_N>;
+  DSB_ENSURE_SMEM(kern, SM::kTotal);
+  const int tiles = ((M + kBlockM - 1) / kBlockM) * ((N + BLOCK_N - 1) / BLOCK_N);
+  const int grid = tiles < sm_count() ? tiles : sm_count();
+  gemm_kernel<KIND, BLOCK_N><<<grid, kGemmThreads, SM::kTotal, st>>>(ta, tb, M, N, K, ep);
+  return cudaGetLastError() == cudaSuccess ? DSB_OK : DSB_ERR_CUDA;
+}
+
+// Tile width: 256 columns unless that leaves SMs idle that 128-wide tiles would fill.
+static int pick_block_n(int M, int N) {
+  const int tm = (M + kBlockM - 1) / kBlockM;
+  const int t256 = tm * ((N + 255) / 256);
+  const int t128 = tm * ((N + 127) / 128);
+  const int sms = sm_count();
+  if (N <= 128) return 128;
+  if (t256 >= sms) {
+    // compare the waves each choice needs, counting a 128-wide tile as half the work
+    const double w256 = static_cast<double>((t256 + sms - 1) / sms);
+    const double w128 = 0.5 * static_cast<double>((t128 + sms - 1) / sms);
+    return (w128 < w256 * 0.92) ? 128 : 256;
+  }
+  return 128;
+}
+
+}  // namespace dsb
+
+using namespace dsb;
+
+extern "C" int dsb_gemm(const void* A, int64_t lda, const void* W, int64_t ldw, int fmt, int M, int N, int K,
+                        const float* row_scale, const float* col_scale, int col_scale_stride, const float* bias,
+                        int act, int act_col0, const float* gate, const void* resid, int64_t ld_resid, void* out0,
+                        int64_t ld_out0, void* out1, int64_t ld_out1, int split_col, int* status, void* stream) {
+  if (!A || !W || !out0 || M < 0 || N < 0 || K <= 0) return DSB_ERR_ARG;
+  if (fmt != DSB_FMT_BF16 && fmt != DSB_FMT_E4M3 && fmt != DSB_FMT_INT8) return DSB_ERR_ARG;
+  const int esz = (fmt == DSB_FMT_BF16) ? 2 : 1;
+  auto al16 = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; };
+  if (!al16(A) || !al16(W) || !al16(out0) || (out1 && !al16(out1)) || (resid && !al16(resid)) ||
+      (bias && !al16(bias)) || (gate && !al16(gate)) || (col_scale && col_scale_stride && !al16(col_scale)))
+    return DSB_ERR_ARG;
+  if (((lda * esz) & 15) || ((ldw * esz) & 15) || (N & 7) || (ld_out0 & 7) || (ld_resid & 7) || (ld_out1 & 7))
+    return DSB_ERR_ARG;
+  if (col_scale_stride != 0 && col_scale_stride != 1) return DSB_ERR_ARG;
+  if (act != DSB_ACT_NONE && act != DSB_ACT_GELU_TANH && act != DSB_ACT_SILU) return DSB_ERR_ARG;
+  if (!out1) split_col = INT32_MAX;
+  else if (split_col < 0 || (split_col % 256) != 0) return DSB_ERR_ARG;
+  if (gate && !resid) return DSB_ERR_ARG;
+  if (M == 0 || N == 0) return DSB_OK;
+  GemmEpilogue ep;
+  ep.row_scale = row_scale;
+  ep.col_scale = col_scale;
+  ep.col_scale_stride = col_scale_stride;
+  ep.bias = bias;
+  ep.act = act;
+  ep.act_col0 = act_col0;
+  ep.gate = gate;
+  ep.resid = reinterpret_cast<const __nv_bfloat16*>(resid);
+  ep.ld_resid = ld_resid;
+  ep.out0 = reinterpret_cast<__nv_bfloat16*>(out0);
+  ep.ld_out0 = ld_out0;
+  ep.out1 = reinterpret_cast<__nv_bfloat16*>(out1);
+  ep.ld_out1 = ld_out1;
+  ep.split_col = split_col;
+  ep.status = status;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  const int bn = pick_block_n(M, N);
+#define DSB_GEMM_DISPATCH(KIND)                                                        \
+  (bn == 256 ? launch_gemm<KIND, 256>(A, lda, W, ldw, M, N, K, ep, st)                 \
+             : launch_gemm<KIND, 128>(A, lda, W, ldw, M, N, K, ep, st))
+  if (fmt == DSB_FMT_BF16) return DSB_GEMM_DISPATCH(KIND_F16);
+  if (fmt == DSB_FMT_E4M3) return DSB_GEMM_DISPATCH(KIND_F8);
+  return DSB_GEMM_DISPATCH(KIND_I8);
+#undef DSB_GEMM_DISPATCH
+}

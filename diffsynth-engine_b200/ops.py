@@ -1,0 +1,201 @@
+"""Thin torch-tensor front end of the C ABI (``include/dsb.h``).  Tensors only carry device memory
+and the current stream; all arithmetic happens in ``libdsb.so``."""
+import ctypes
+import math
+from typing import Optional, Tuple
+
+import torch
+
+from . import _lib
+from ._lib import ACT_GELU_TANH, ACT_NONE, ACT_SILU, FMT_BF16, FMT_E4M3, FMT_INT8, check  # noqa: F401
+
+_status = {}
+
+
+def _ptr(t: Optional[torch.Tensor]):
+    return None if t is None else ctypes.c_void_p(t.data_ptr())
+
+
+def _stream():
+    return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _require_cuda(*ts):
+    for t in ts:
+        if t is not None and not t.is_cuda:
+            raise _lib.DsbError("dsb ops take CUDA tensors only (no CPU fallback exists)")
+
+
+def status_word(device) -> torch.Tensor:
+    """Per-device int32 the kernels set to DSB_ERR_TIMEOUT when a bounded wait runs out."""
+    key = torch.device(device).index if torch.device(device).index is not None else torch.cuda.current_device()
+    if key not in _status:
+        _status[key] = torch.zeros(1, dtype=torch.int32, device=f"cuda:{key}")
+    return _status[key]
+
+
+def check_status(device=None):
+    """Synchronising read of the status word; raises if a kernel reported a timeout."""
+    dev = torch.cuda.current_device() if device is None else device
+    code = int(status_word(dev).item())
+    if code != 0:
+        status_word(dev).zero_()
+        _lib.check(code, "device kernel")
+
+
+def _fmt_of(t: torch.Tensor) -> int:
+    if t.dtype == torch.bfloat16:
+        return FMT_BF16
+    if t.dtype == torch.float8_e4m3fn:
+        return FMT_E4M3
+    if t.dtype == torch.int8:
+        return FMT_INT8
+    raise _lib.DsbError(f"unsupported operand dtype {t.dtype}")
+
+
+_OUT_DTYPE = {FMT_BF16: torch.bfloat16, FMT_E4M3: torch.float8_e4m3fn, FMT_INT8: torch.int8}
+
+
+def _rows(t: torch.Tensor) -> Tuple[int, int, int]:
+    """(M, D, ld) of a 2-D row view with unit inner stride."""
+    if t.dim() != 2 or t.stride(1) != 1:
+        raise _lib.DsbError("expected a 2-D tensor with contiguous rows")
+    return t.shape[0], t.shape[1], t.stride(0)
+
+
+def ln_modulate(x, shift, scale, eps=1e-6, out_fmt=FMT_BF16, out=None, row_scale=None):
+    """LayerNorm (no affine) then ``* (1 + scale) + shift``; optionally quantised per row.
+    Returns ``(y, row_scale)`` (row_scale is None for bf16 output)."""
+    _require_cuda(x, shift, scale)
+    M, D, ld_x = _rows(x)
+    if out is None:
+        out = torch.empty((M, D), dtype=_OUT_DTYPE[out_fmt], device=x.device)
+    if out_fmt != FMT_BF16 and row_scale is None:
+        row_scale = torch.empty(M, dtype=torch.float32, device=x.device)
+    rc = _lib.lib().dsb_ln_modulate(_ptr(x), ld_x, _ptr(shift), _ptr(scale), _ptr(out), out.stride(0),
+                                    _ptr(row_scale), M, D, eps, out_fmt, _stream())
+    check(rc, "dsb_ln_modulate")
+    return out, row_scale
+
+
+def gate_residual(x, y, gate=None, out=None):
+    _require_cuda(x, y, gate)
+    M, D, ld_x = _rows(x)
+    if out is None:
+        out = torch.empty((M, D), dtype=torch.bfloat16, device=x.device)
+    rc = _lib.lib().dsb_gate_residual(_ptr(x), ld_x, _ptr(y), y.stride(0), _ptr(gate), _ptr(out), out.stride(0), M, D,
+                                      _stream())
+    check(rc, "dsb_gate_residual")
+    return out
+
+
+def rmsnorm_rope_heads(buf, H, w_q, w_k=None, rope=None, rope_row0=0, eps=1e-6):
+    """In place on ``buf[S, ld]``: the first H (w_k None) or 2H heads of each row."""
+    _require_cuda(buf, w_q, w_k, rope)
+    S, _, ld = _rows(buf)
+    rc = _lib.lib().dsb_rmsnorm_rope_heads(_ptr(buf), ld, S, H, 128, 1 if w_k is None else 2, _ptr(w_q), _ptr(w_k),
+                                           _ptr(rope), rope_row0, eps, _stream())
+    check(rc, "dsb_rmsnorm_rope_heads")
+    return buf
+
+
+def rmsnorm_full(buf, w, rope=None, rope_row0=0, eps=1e-6):
+    _require_cuda(buf, w, rope)
+    M, D, ld = _rows(buf)
+    rc = _lib.lib().dsb_rmsnorm_full(_ptr(buf), ld, M, D, _ptr(w), _ptr(rope), rope_row0, eps, _stream())
+    check(rc, "dsb_rmsnorm_full")
+    return buf
+
+
+def quant_rows(x, out_fmt=FMT_E4M3, out=None, row_scale=None):
+    _require_cuda(x)
+    M, K, ld_x = _rows(x)
+    if out is None:
+        out = torch.empty((M, K), dtype=_OUT_DTYPE[out_fmt], device=x.device)
+    if row_scale is None:
+        row_scale = torch.empty(M, dtype=torch.float32, device=x.device)
+    rc = _lib.lib().dsb_quant_rows(_ptr(x), ld_x, _ptr(out), out.stride(0), _ptr(row_scale), M, K, out_fmt, _stream())
+    check(rc, "dsb_quant_rows")
+    return out, row_scale
+
+
+def gemv(W, x, w_scale=None, bias=None, act_in=ACT_NONE, act_out=ACT_NONE, out=None):
+    """y = act_out((W @ act_in(x)) * w_scale + bias) for one fp32 activation row."""
+    _require_cuda(W, x, w_scale, bias)
+    N, K, ld_w = _rows(W)
+    if out is None:
+        out = torch.empty(N, dtype=torch.float32, device=x.device)
+    stride = 0 if (w_scale is None or w_scale.numel() == 1) else 1
+    rc = _lib.lib().dsb_gemv(_ptr(W), ld_w, _fmt_of(W), _ptr(x), _ptr(w_scale), stride, _ptr(bias), _ptr(out), N, K,
+                             act_in, act_out, _stream())
+    check(rc, "dsb_gemv")
+    return out
+
+
+def euler_step(latents, model_out, dt: float, init=None, mask=None, out=None):
+    _require_cuda(latents, model_out, init, mask)
+    if out is None:
+        out = torch.empty_like(model_out)
+    is_f32 = 1 if model_out.dtype == torch.float32 else 0
+    rc = _lib.lib().dsb_euler_step(_ptr(latents), _ptr(model_out), _ptr(init), _ptr(mask), float(dt), _ptr(out),
+                                   latents.numel(), is_f32, _stream())
+    check(rc, "dsb_euler_step")
+    return out
+
+
+def gemm(a, w, row_scale=None, col_scale=None, bias=None, act=ACT_NONE, act_col0=0, gate=None, resid=None, out=None,
+         out1=None, split_col=None):
+    """out = epilogue(a @ w.T): see ``dsb_gemm`` in include/dsb.h.  a: [M,K], w: [N,K] of one format."""
+    _require_cuda(a, w, row_scale, col_scale, bias, gate, resid, out, out1)
+    M, K, lda = _rows(a)
+    N, Kw, ldw = _rows(w)
+    if K != Kw or _fmt_of(a) != _fmt_of(w):
+        raise _lib.DsbError("gemm operands disagree in K or format")
+    if out is None:
+        n0 = N if out1 is None else split_col
+        out = torch.empty((M, n0), dtype=torch.bfloat16, device=a.device)
+    cs_stride = 0 if (col_scale is None or col_scale.numel() == 1) else 1
+    rc = _lib.lib().dsb_gemm(
+        _ptr(a), lda, _ptr(w), ldw, _fmt_of(a), M, N, K, _ptr(row_scale), _ptr(col_scale), cs_stride, _ptr(bias), act,
+        act_col0, _ptr(gate), _ptr(resid), 0 if resid is None else resid.stride(0), _ptr(out), out.stride(0),
+        _ptr(out1), 0 if out1 is None else out1.stride(0), N if split_col is None else split_col,
+        _ptr(status_word(a.device)), _stream())
+    check(rc, "dsb_gemm")
+    return out
+
+
+def flash_attn(q, k, v, out=None, sm_scale=None):
+    """q: [B, Sq, H, 128], k/v: [B, Sk, H, 128] views (any strides that are multiples of 8, unit inner
+    stride); returns o as [B, Sq, H, 128] contiguous unless ``out`` is given."""
+    _require_cuda(q, k, v, out)
+    B, Sq, H, D = q.shape
+    Sk = k.shape[1]
+    for t in (q, k, v):
+        if t.stride(3) != 1 or t.dtype != torch.bfloat16:
+            raise _lib.DsbError("flash_attn needs bf16 tensors with a contiguous head dimension")
+    if out is None:
+        out = torch.empty((B, Sq, H, D), dtype=torch.bfloat16, device=q.device)
+    if sm_scale is None:
+        sm_scale = 1.0 / math.sqrt(D)
+    rc = _lib.lib().dsb_flash_attn(
+        _ptr(q), _ptr(k), _ptr(v), _ptr(out), B, H, Sq, Sk, D,
+        q.stride(0), q.stride(1), q.stride(2), k.stride(0), k.stride(1), k.stride(2),
+        v.stride(0), v.stride(1), v.stride(2), out.stride(0), out.stride(1), out.stride(2),
+        float(sm_scale), _ptr(status_word(q.device)), _stream())
+    check(rc, "dsb_flash_attn")
+    return out
+
+
+def pack_quant_weight(W, fmt=FMT_E4M3, per_channel=False):
+    """Quantise a [N,K] fp32/bf16 weight on the device; returns (payload, scales)."""
+    _require_cuda(W)
+    N, K, ld = _rows(W)
+    if W.dtype not in (torch.float32, torch.bfloat16):
+        raise _lib.DsbError("pack_quant_weight takes fp32 or bf16 weights")
+    payload = torch.empty((N, K), dtype=_OUT_DTYPE[fmt], device=W.device)
+    scales = torch.empty(N if per_channel else 1, dtype=torch.float32, device=W.device)
+    work = torch.zeros(1, dtype=torch.float32, device=W.device)
+    rc = _lib.lib().dsb_pack_quant_weight(_ptr(W), ld, 1 if W.dtype == torch.bfloat16 else 0, _ptr(payload), K,
+                                          _ptr(scales), N, K, fmt, 1 if per_channel else 0, _ptr(work), _stream())
+    check(rc, "dsb_pack_quant_weight")
+    return payload, scales

@@ -1,0 +1,158 @@
+/*
+ * dsb.h - C ABI of libdsb.so: the B200 (sm_100a) kernels behind the DiT
+ * denoising step of DiffSynth-Engine (Flux / Wan2.1 / MMDiT double-stream
+ * blocks).
+ *
+ * Conventions
+ *   - Every pointer is a DEVICE pointer owned by the caller unless said
+ *     otherwise; the library allocates nothing and never synchronises.
+ *   - `stream` is a cudaStream_t passed as void*; kernels are enqueued on it.
+ *   - Return value: 0 on success, a negative DSB_ERR_* code otherwise.  The
+ *     functions never throw and never terminate the process.
+ *   - `status` (where present) is an optional device int the kernel sets to
+ *     DSB_ERR_TIMEOUT if one of its bounded on-chip waits ran out; it is never
+ *     cleared by the library.
+ *   - Leading dimensions (`ld_*`) are in ELEMENTS of the tensor they describe.
+ *   - bf16 tensors need 16-byte aligned bases and leading dimensions that are
+ *     multiples of 8 elements; 8-bit tensors need multiples of 16.
+ *
+ * Each entry point names the code of the reference (paths inside
+ * modelscope/DiffSynth-Engine v0.1.1) whose arithmetic it replaces.
+ */
+#ifndef DSB_H_
+#define DSB_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define DSB_OK 0
+#define DSB_ERR_ARG (-1)
+#define DSB_ERR_CUDA (-2)
+#define DSB_ERR_TIMEOUT (-3)
+#define DSB_ERR_UNSUPPORTED (-4)
+
+/* element formats */
+#define DSB_FMT_BF16 0
+#define DSB_FMT_E4M3 1
+#define DSB_FMT_INT8 2
+
+/* epilogue activation */
+#define DSB_ACT_NONE 0
+#define DSB_ACT_GELU_TANH 1
+#define DSB_ACT_SILU 2
+
+/* Library/ABI version (major*100 + minor). */
+int dsb_version(void);
+
+/*
+ * AdaLN: y = LayerNorm(x; eps, no affine) * (1 + scale[d]) + shift[d] over rows of width D.
+ * out_fmt BF16 writes bf16; E4M3 / INT8 write the quantised operand of the next GEMM and
+ * row_scale[m] = amax(row)/448 (or /127), y_q = round(y / row_scale).
+ * Replaces: models/basic/transformer_helper.py:13-22,32-36 (AdaLayerNorm, AdaLayerNormSingle),
+ * models/flux/flux_dit.py:228,233,331-335, models/wan/wan_dit.py:25-26,188,191 (modulate(norm(x))),
+ * and, with scale = weight-1 / shift = bias, the affine LayerNorm models/wan/wan_dit.py:178,190.
+ */
+int dsb_ln_modulate(const void* x, int64_t ld_x, const float* shift, const float* scale, void* y, int64_t ld_y,
+                    float* row_scale, int M, int D, float eps, int out_fmt, void* stream);
+
+/*
+ * out = x + gate[d] * y (gate NULL: out = x + y); bf16 in/out, fp32 gate.
+ * Replaces: models/flux/flux_dit.py:227,229,232,234,318-319; models/wan/wan_dit.py:189,190,192.
+ */
+int dsb_gate_residual(const void* x, int64_t ld_x, const void* y, int64_t ld_y, const float* gate, void* out,
+                      int64_t ld_o, int M, int D, void* stream);
+
+/*
+ * In-place per-head RMSNorm (head_dim 128, fp32 weights w_q/w_k[128]) + RoPE on adjacent pairs for
+ * the first nsel*H heads of each row of buf[S, ld] (nsel=2: q heads then k heads; nsel=1: q only).
+ * rope: fp32 [rows, 64, 2] = (cos, sin) per pair, row (rope_row0 + s) for token s; NULL = no rotation.
+ * Replaces: models/basic/transformer_helper.py:73-78 (RMSNorm) and models/flux/flux_dit.py:154-159 (apply_rope).
+ */
+int dsb_rmsnorm_rope_heads(void* buf, int64_t ld, int S, int H, int head_dim, int nsel, const float* w_q,
+                           const float* w_k, const float* rope, int rope_row0, float eps, void* stream);
+
+/*
+ * In-place RMSNorm over the whole row (width D = heads*128, fp32 weight w[D]) followed by per-head RoPE
+ * with the token's 64 (cos, sin) pairs (rope NULL = none).
+ * Replaces: models/wan/wan_dit.py:61-78 (RMSNorm over all heads) and :54-58 (rope_apply).
+ */
+int dsb_rmsnorm_full(void* buf, int64_t ld, int M, int D, const float* w, const float* rope, int rope_row0,
+                     float eps, void* stream);
+
+/*
+ * Dynamic per-row quantisation of a bf16 activation: y_q[m,:] = round(x[m,:] / s_m), s_m = amax/448 (E4M3,
+ * round-to-nearest-even, saturating) or amax/127 (INT8, round-half-even); an all-zero row gets s_m = 1.
+ * Replaces: the activation cast of utils/fp8_linear.py:35 (which uses unit scale).
+ */
+int dsb_quant_rows(const void* x, int64_t ld_x, void* y, int64_t ld_y, float* row_scale, int M, int K, int out_fmt,
+                   void* stream);
+
+/*
+ * y[n] = act_out((sum_k W[n,k] * act_in(x[k])) * w_scale[n*w_scale_stride] + bias[n]) for one activation row
+ * (fp32 x, fp32 y).  W is [N, ld_w] in w_fmt.  act_in: 0 none, DSB_ACT_SILU; act_out: DSB_ACT_*.
+ * Replaces the M=1 Linears: models/basic/transformer_helper.py:14,33 and models/flux/flux_dit.py:332
+ * (SiLU -> Linear of the AdaLN layers), models/basic/timestep.py:73-81, models/flux/flux_dit.py:348-352,
+ * models/wan/wan_dit.py:279-287,327-328.
+ */
+int dsb_gemv(const void* W, int64_t ld_w, int w_fmt, const float* x, const float* w_scale, int w_scale_stride,
+             const float* bias, float* y, int N, int K, int act_in, int act_out, void* stream);
+
+/*
+ * out = cast(latents + model_out * dt), optionally after the inpaint blend
+ * model_out = model_out*mask + init*(1-mask).  is_f32 selects fp32 or bf16 tensors.
+ * Replaces: algorithm/sampler/flow_match/flow_match_euler.py:11-19.
+ */
+int dsb_euler_step(const void* latents, const void* model_out, const void* init, const void* mask, float dt,
+                   void* out, int64_t n, int is_f32, void* stream);
+
+/*
+ * Quantised / bf16 Linear on the tensor cores:
+ *   acc[m,n]  = sum_k A[m,k] * W[n,k]                      (fp32 accumulate; int32 for INT8)
+ *   v         = acc * row_scale[m] * col_scale[n*col_scale_stride] + bias[n]
+ *   v         = act(v)            for columns n >= act_col0 (act = DSB_ACT_*)
+ *   v         = resid[m,n] + gate[n] * v                    when resid != NULL (gate NULL = 1)
+ *   out0[m,n] = bf16(v) for n < split_col, out1[m, n-split_col] = bf16(v) otherwise
+ * A is [M, lda] and W is [N, ldw], both with K contiguous, in `fmt` (BF16, E4M3 or INT8).  row_scale,
+ * col_scale, bias, gate, resid and out1 may be NULL (pass split_col >= N when out1 is unused; split_col
+ * must be a multiple of 256).  K-tails and M/N-tails are handled; N and split_col must be multiples of 8.
+ * Replaces: utils/fp8_linear.py:27-60 (cast + torch._scaled_mm + bias), the dequantise-then-F.linear of
+ * utils/gguf.py:77-84, and the elementwise code the reference runs after each Linear:
+ * GELU-tanh (models/flux/flux_dit.py:209,215,315; models/wan/wan_dit.py:180) and the gate-residual lines above.
+ */
+int dsb_gemm(const void* A, int64_t lda, const void* W, int64_t ldw, int fmt, int M, int N, int K,
+             const float* row_scale, const float* col_scale, int col_scale_stride, const float* bias, int act,
+             int act_col0, const float* gate, const void* resid, int64_t ld_resid, void* out0, int64_t ld_out0,
+             void* out1, int64_t ld_out1, int split_col, int* status, void* stream);
+
+/*
+ * Attention without mask: o[b,s,h,:] = softmax(q[b,s,h,:] . k[b,:,h,:]^T * sm_scale) v[b,:,h,:], head_dim 128,
+ * bf16 in/out, fp32 softmax statistics.  Tensors are addressed as base + b*stride_b + s*stride_s + h*stride_h
+ * (+ d, contiguous); strides are in elements and need to be multiples of 8.  Covers the joint text+image
+ * self-attention (Sq == Sk) and cross-attention (Sk = context length).
+ * Replaces: the default of models/flux/flux_dit.py:21 (_attn_func, called at :182,:267,:303) and
+ * models/wan/wan_dit.py:18-22 (attention).
+ */
+int dsb_flash_attn(const void* q, const void* k, const void* v, void* o, int B, int H, int Sq, int Sk, int head_dim,
+                   int64_t q_stride_b, int64_t q_stride_s, int64_t q_stride_h, int64_t k_stride_b,
+                   int64_t k_stride_s, int64_t k_stride_h, int64_t v_stride_b, int64_t v_stride_s,
+                   int64_t v_stride_h, int64_t o_stride_b, int64_t o_stride_s, int64_t o_stride_h, float sm_scale,
+                   int* status, void* stream);
+
+/*
+ * Weight prepack: W[N,K] (fp32 or bf16 by src_is_bf16) -> quantised payload [N,K] row-major plus scales.
+ *   fmt E4M3, per_channel 0: s = amax(|W|)/448 (one scale);   per_channel 1: s_n = amax(|W[n,:]|)/448
+ *   fmt INT8 (per_channel 1 only): s_n = amax/127, q = round-half-even(W/s) clamped to +-127
+ * scales receives 1 or N floats.  `work` is a device float (scratch for the per-tensor amax).
+ * No reference counterpart beyond the plain cast of utils/fp8_linear.py:12-17; the quantisation rule is
+ * defined by this library and restated by the oracle.
+ */
+int dsb_pack_quant_weight(const void* W, int64_t ld_w, int src_is_bf16, void* Wq, int64_t ld_q, float* scales, int N,
+                          int K, int fmt, int per_channel, float* work, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* DSB_H_ */

@@ -1,0 +1,182 @@
+"""Elementary operations of the DiT step, restated in fp32 on the CPU.  Paths cite
+modelscope/DiffSynth-Engine v0.1.1 (``diffsynth_engine/...``)."""
+import math
+
+import torch
+import torch.nn.functional as F
+
+E4M3_MAX = 448.0
+INT8_MAX = 127.0
+
+
+# ------------------------------------------------------------------ normalisation / modulation
+def layer_norm(x, eps=1e-6):
+    """nn.LayerNorm(dim, elementwise_affine=False, eps=1e-6): models/basic/transformer_helper.py:11,30;
+    models/flux/flux_dit.py:207,212,329; models/wan/wan_dit.py:176-177,231."""
+    return F.layer_norm(x.float(), (x.shape[-1],), eps=eps)
+
+
+def ln_modulate(x, shift, scale, eps=1e-6):
+    """norm(x) * (1 + scale) + shift: models/basic/transformer_helper.py:17,21,35;
+    models/flux/flux_dit.py:228,233,334; models/wan/wan_dit.py:25-26."""
+    return layer_norm(x, eps) * (1.0 + scale.float()) + shift.float()
+
+
+def gate_residual(x, y, gate=None):
+    """x + gate * y: models/flux/flux_dit.py:227,229,318-319; models/wan/wan_dit.py:189-192."""
+    return x.float() + (y.float() if gate is None else gate.float() * y.float())
+
+
+def rmsnorm(x, weight, eps=1e-6):
+    """x * rsqrt(mean(x^2) + eps) * weight over the last dimension:
+    models/basic/transformer_helper.py:73-78 (per head) and models/wan/wan_dit.py:74-78 (full width).
+    The reference rounds to the input dtype before the weight multiply; in fp32 that is a no-op."""
+    x = x.float()
+    var = x.square().mean(-1, keepdim=True)
+    return x * torch.rsqrt(var + eps) * weight.float()
+
+
+def gelu_tanh(x):
+    """nn.GELU(approximate="tanh"): models/flux/flux_dit.py:209,215,315; models/wan/wan_dit.py:180."""
+    return F.gelu(x.float(), approximate="tanh")
+
+
+# ------------------------------------------------------------------------------------ RoPE
+def flux_rope_table(ids, axes_dim=(16, 56, 56), theta=10000):
+    """(cos, sin) per pair, [S, 64, 2] fp32, from position ids [S, 3].
+    models/basic/transformer_helper.py:46-64: omega in fp64, angle = pos * omega, table rounded to fp32.
+    The reference stores [[cos, -sin], [sin, cos]]; (cos, sin) carries the same information."""
+    cols = []
+    for i, d in enumerate(axes_dim):
+        scale = torch.arange(0, d, 2, dtype=torch.float64) / d
+        omega = 1.0 / (theta ** scale)
+        ang = ids[..., i].to(torch.float64)[:, None] * omega[None, :]
+        cols.append(torch.stack([torch.cos(ang), torch.sin(ang)], dim=-1))
+    return torch.cat(cols, dim=1).float()
+
+
+def apply_rope_pairs(x, table):
+    """Rotate adjacent pairs (2j, 2j+1) of the last dimension: out0 = cos*x0 - sin*x1, out1 = sin*x0 + cos*x1.
+    models/flux/flux_dit.py:154-159.  x: [..., S, 128]; table: [S, 64, 2]."""
+    x = x.float()
+    xp = x.reshape(*x.shape[:-1], -1, 2)
+    cos, sin = table[..., 0], table[..., 1]
+    o0 = cos * xp[..., 0] - sin * xp[..., 1]
+    o1 = sin * xp[..., 0] + cos * xp[..., 1]
+    return torch.stack([o0, o1], dim=-1).reshape(x.shape)
+
+
+def wan_rope_table(f, h, w, head_dim=128, theta=10000.0):
+    """(cos, sin) per pair for the (f, h, w) grid in raster order, [f*h*w, 64, 2] fp32.
+    models/wan/wan_dit.py:38-51 (frequencies in fp64, split 44/42/42 of the 128 dims) and :335-346."""
+    def freqs(dim, end):
+        fr = 1.0 / (theta ** (torch.arange(0, dim, 2)[: dim // 2].double() / dim))
+        return torch.outer(torch.arange(end, dtype=torch.float64), fr)
+
+    d_h = head_dim // 3
+    d_f = head_dim - 2 * d_h
+    af, ah, aw = freqs(d_f, f), freqs(d_h, h), freqs(d_h, w)
+    ang = torch.cat([
+        af.view(f, 1, 1, -1).expand(f, h, w, -1),
+        ah.view(1, h, 1, -1).expand(f, h, w, -1),
+        aw.view(1, 1, w, -1).expand(f, h, w, -1),
+    ], dim=-1).reshape(f * h * w, -1)
+    return torch.stack([torch.cos(ang), torch.sin(ang)], dim=-1).float()
+
+
+# ------------------------------------------------------------------------------- attention
+def attention(q, k, v, sm_scale=None):
+    """softmax(q k^T / sqrt(d)) v without mask; q,k,v: [B, H, S, D].
+    models/flux/flux_dit.py:21 (default _attn_func = SDPA); models/wan/wan_dit.py:18-22."""
+    return F.scaled_dot_product_attention(q.float(), k.float(), v.float(), scale=sm_scale)
+
+
+# ---------------------------------------------------------------------------- quantisation
+def quant_rows_e4m3(x):
+    """Dynamic per-row FP8 quantisation: s = amax/448 (1 for an all-zero row), q = e4m3(clamp(x * (1/s))).
+    The reference casts with unit scale (utils/fp8_linear.py:35); the scale is this library's extension."""
+    x = x.float()
+    amax = x.abs().amax(dim=1)
+    s = torch.where(amax > 0, amax / E4M3_MAX, torch.ones_like(amax))
+    q = (x * (1.0 / s)[:, None]).clamp(-E4M3_MAX, E4M3_MAX).to(torch.float8_e4m3fn)
+    return q, s
+
+
+def quant_rows_int8(x):
+    x = x.float()
+    amax = x.abs().amax(dim=1)
+    s = torch.where(amax > 0, amax / INT8_MAX, torch.ones_like(amax))
+    q = torch.round(x * (1.0 / s)[:, None]).clamp(-INT8_MAX, INT8_MAX).to(torch.int8)
+    return q, s
+
+
+def quant_weight(W, fmt="fp8_tensor"):
+    """Weight prepack rule: fp8_tensor: s = amax|W|/448; fp8_channel: s_n = amax|W[n,:]|/448;
+    int8_channel: s_n = amax/127 with round-half-even.  q = clamp(W / s).  (An all-zero row gets s = 1.)
+    The reference only casts (utils/fp8_linear.py:12-17)."""
+    W = W.float()
+    if fmt == "fp8_tensor":
+        amax = W.abs().amax().reshape(1)
+    else:
+        amax = W.abs().amax(dim=1)
+    qmax = INT8_MAX if fmt == "int8_channel" else E4M3_MAX
+    s = torch.where(amax > 0, amax / qmax, torch.ones_like(amax))
+    sd = s if fmt == "fp8_tensor" else s[:, None]
+    q = (W / sd).clamp(-qmax, qmax)
+    q = torch.round(q).to(torch.int8) if fmt == "int8_channel" else q.to(torch.float8_e4m3fn)
+    return q, s
+
+
+def linear_quant(x_q, x_s, W_q, W_s, bias=None):
+    """Quantised Linear with fp32 accumulation: ((x_q W_q^T) * x_s[m] * W_s[n]) + bias.
+    Dataflow of utils/fp8_linear.py:33-50 with scales added; products of e4m3 (or int8) values are exact in fp32
+    only up to accumulation order, so comparisons use a tolerance, not bit equality."""
+    acc = x_q.float() @ W_q.float().t()
+    ws = W_s if W_s.numel() > 1 else W_s.reshape(1)
+    y = acc * x_s[:, None] * ws[None, :]
+    return y if bias is None else y + bias.float()
+
+
+# ------------------------------------------------------------------------------- embeddings
+def timestep_embedding_flux(t, dim=256, max_period=10000):
+    """[cos | sin] sinusoid in fp32 (flip_sin_to_cos=True, downscale_freq_shift=0):
+    models/basic/timestep.py:6-44 as configured at :68-70."""
+    half = dim // 2
+    exponent = -math.log(max_period) * torch.arange(0, half, dtype=torch.float32) / half
+    emb = t[:, None].float() * torch.exp(exponent)[None, :]
+    return torch.cat([torch.cos(emb), torch.sin(emb)], dim=-1)
+
+
+def sinusoidal_embedding_wan(dim, position):
+    """[cos | sin] from an fp64 outer product: models/wan/wan_dit.py:29-35."""
+    sinusoid = torch.outer(position.double(),
+                           torch.pow(10000, -torch.arange(dim // 2, dtype=torch.float64).div(dim // 2)))
+    return torch.cat([torch.cos(sinusoid), torch.sin(sinusoid)], dim=1)
+
+
+# ------------------------------------------------------------------------ sampler / scheduler
+def euler_step(latents, model_out, sigmas, i, init=None, mask=None):
+    """algorithm/sampler/flow_match/flow_match_euler.py:11-19."""
+    if mask is not None:
+        model_out = model_out * mask + init * (1 - mask)
+    dt = sigmas[i + 1] - sigmas[i]
+    out = latents.to(torch.float32) + model_out * dt
+    return out.to(model_out.dtype)
+
+
+def rectified_flow_schedule(num_steps, shift=1.0, sigma_min=0.001, sigma_max=1.0, num_train_timesteps=1000,
+                            mu=None):
+    """algorithm/noise_scheduler/flow_match/recifited_flow.py:34-50 (mu given = dynamic shifting, as Flux uses)."""
+    sigmas = torch.linspace(sigma_max, sigma_min, num_steps)
+    if mu is not None:
+        sigmas = math.exp(mu) / (math.exp(mu) + (1 / sigmas - 1) ** 1.0)
+    else:
+        sigmas = shift * sigmas / (1 + (shift - 1) * sigmas)
+    timesteps = sigmas * num_train_timesteps
+    sigmas = torch.cat([sigmas, sigmas.new_zeros([1])])
+    return sigmas, timesteps
+
+
+def rel_l2(a, b):
+    a, b = a.double(), b.double()
+    return float((a - b).norm() / b.norm().clamp_min(1e-30))

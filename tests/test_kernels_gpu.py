@@ -1,0 +1,334 @@
+"""Kernel-level parity: every C-ABI entry point against the CPU oracle on the same seeded inputs."""
+import math
+
+import pytest
+import torch
+
+from oracle import ops as O
+
+pytestmark = pytest.mark.gpu
+
+
+def _gen(seed):
+    return torch.Generator().manual_seed(seed)
+
+
+def _bf(t):
+    return t.to(torch.bfloat16)
+
+
+# ------------------------------------------------------------------------------ ln_modulate
+@pytest.mark.parametrize("M,D", [(1, 256), (37, 3072), (130, 5120), (5, 1024), (3, 64), (9, 8192)])
+def test_ln_modulate_bf16(dsb, cuda_dev, M, D):
+    g = _gen(1)
+    x = _bf(torch.randn(M, D, generator=g) * 2 + 0.3)
+    shift, scale = torch.randn(D, generator=g) * 0.1, torch.randn(D, generator=g) * 0.1
+    ref = O.ln_modulate(x, shift, scale)
+    y, _ = dsb.ops.ln_modulate(x.to(cuda_dev), shift.to(cuda_dev), scale.to(cuda_dev))
+    assert O.rel_l2(y.float().cpu(), ref) < 3e-3  # bf16 output rounding only
+
+
+@pytest.mark.parametrize("fmt", ["e4m3", "int8"])
+@pytest.mark.parametrize("M,D", [(33, 3072), (7, 5120), (4, 256)])
+def test_ln_modulate_quantised(dsb, cuda_dev, fmt, M, D):
+    g = _gen(2)
+    x = _bf(torch.randn(M, D, generator=g))
+    shift, scale = torch.randn(D, generator=g) * 0.1, torch.randn(D, generator=g) * 0.1
+    ref = O.ln_modulate(x, shift, scale)
+    code = dsb.ops.FMT_E4M3 if fmt == "e4m3" else dsb.ops.FMT_INT8
+    q, s = dsb.ops.ln_modulate(x.to(cuda_dev), shift.to(cuda_dev), scale.to(cuda_dev), out_fmt=code)
+    qmax = 448.0 if fmt == "e4m3" else 127.0
+    s_ref = ref.abs().amax(dim=1) / qmax
+    assert torch.allclose(s.cpu(), s_ref, rtol=1e-5, atol=0)
+    deq = q.float().cpu() * s.cpu()[:, None]
+    # e4m3 has 3 mantissa bits (relative step 2^-4 half-ulp), int8 an absolute step of s/2
+    tol = 0.04 if fmt == "e4m3" else 0.02
+    assert O.rel_l2(deq, ref) < tol
+    # the payload must be what the oracle quantiser produces from the kernel's own fp32 values, up to
+    # values that sit within float rounding of a quantisation boundary
+    fn = O.quant_rows_e4m3 if fmt == "e4m3" else O.quant_rows_int8
+    q_ref, _ = fn(ref)
+    mismatch = (q_ref.float() != q.float().cpu()).float().mean().item()
+    assert mismatch < 2e-3
+
+
+def test_ln_modulate_ragged_and_errors(dsb, cuda_dev):
+    x = torch.zeros(0, 3072, dtype=torch.bfloat16, device=cuda_dev)
+    sh = torch.zeros(3072, device=cuda_dev)
+    y, _ = dsb.ops.ln_modulate(x, sh, sh)
+    assert y.shape == (0, 3072)
+    with pytest.raises(dsb.DsbError):  # D not a multiple of 8
+        dsb.ops.ln_modulate(torch.zeros(2, 100, dtype=torch.bfloat16, device=cuda_dev), sh[:100], sh[:100])
+    with pytest.raises(dsb.DsbError):  # CPU tensor: there is no fallback
+        dsb.ops.ln_modulate(torch.zeros(2, 64, dtype=torch.bfloat16), torch.zeros(64), torch.zeros(64))
+    # strided rows (a column slice of a wider buffer)
+    g = _gen(3)
+    wide = _bf(torch.randn(16, 4096, generator=g))
+    shift, scale = torch.randn(1024, generator=g), torch.randn(1024, generator=g)
+    y, _ = dsb.ops.ln_modulate(wide.to(cuda_dev)[:, 1024:2048], shift.to(cuda_dev), scale.to(cuda_dev))
+    assert O.rel_l2(y.float().cpu(), O.ln_modulate(wide[:, 1024:2048], shift, scale)) < 3e-3
+
+
+# ---------------------------------------------------------------------------- gate_residual
+@pytest.mark.parametrize("M,D,gated", [(4608, 3072, True), (17, 5120, True), (3, 64, False)])
+def test_gate_residual(dsb, cuda_dev, M, D, gated):
+    g = _gen(4)
+    x, y = _bf(torch.randn(M, D, generator=g)), _bf(torch.randn(M, D, generator=g))
+    gate = torch.randn(D, generator=g) if gated else None
+    ref = O.gate_residual(x, y, gate).to(torch.bfloat16)
+    out = dsb.ops.gate_residual(x.to(cuda_dev), y.to(cuda_dev), None if gate is None else gate.to(cuda_dev))
+    # one fp32 fma then one rounding on both sides: at most 1 bf16 ulp apart
+    assert O.rel_l2(out.float().cpu(), ref.float()) < 1e-3
+
+
+# ----------------------------------------------------------------------- rmsnorm + rope
+def _flux_ids(S_txt, side):
+    ids = torch.zeros(S_txt + side * side, 3)
+    r = torch.arange(side)
+    ids[S_txt:, 1] = r[:, None].expand(side, side).reshape(-1)
+    ids[S_txt:, 2] = r[None, :].expand(side, side).reshape(-1)
+    return ids
+
+
+@pytest.mark.parametrize("S,H", [(96, 24), (1536, 24), (5, 2)])
+def test_rmsnorm_rope_heads(dsb, cuda_dev, S, H):
+    g = _gen(5)
+    D = 128
+    qkv = _bf(torch.randn(S, 3 * H * D, generator=g))
+    wq, wk = 1 + 0.1 * torch.randn(D, generator=g), 1 + 0.1 * torch.randn(D, generator=g)
+    side = int(math.isqrt(S)) if int(math.isqrt(S)) ** 2 == S else None
+    ids = _flux_ids(0, side) if side else torch.cat([torch.zeros(S, 1), torch.arange(S)[:, None] % 32,
+                                                     torch.arange(S)[:, None] // 32], dim=1).float()
+    table = O.flux_rope_table(ids)
+    q = qkv[:, : H * D].float().reshape(S, H, D)
+    k = qkv[:, H * D: 2 * H * D].float().reshape(S, H, D)
+    q_ref = O.apply_rope_pairs(O.rmsnorm(q, wq).transpose(0, 1), table).transpose(0, 1).reshape(S, H * D)
+    k_ref = O.apply_rope_pairs(O.rmsnorm(k, wk).transpose(0, 1), table).transpose(0, 1).reshape(S, H * D)
+    buf = qkv.to(cuda_dev).clone()
+    dsb.ops.rmsnorm_rope_heads(buf, H, wq.to(cuda_dev), wk.to(cuda_dev), table.to(cuda_dev).contiguous())
+    out = buf.float().cpu()
+    assert O.rel_l2(out[:, : H * D], q_ref) < 3e-3
+    assert O.rel_l2(out[:, H * D: 2 * H * D], k_ref) < 3e-3
+    assert torch.equal(out[:, 2 * H * D:], qkv[:, 2 * H * D:].float())  # v untouched
+
+
+@pytest.mark.parametrize("M,H,rope", [(60, 40, True), (33, 40, False), (7, 12, True)])
+def test_rmsnorm_full(dsb, cuda_dev, M, H, rope):
+    g = _gen(6)
+    D = H * 128
+    x = _bf(torch.randn(M, D, generator=g))
+    w = 1 + 0.1 * torch.randn(D, generator=g)
+    table = O.wan_rope_table(3, 4, 5)[:M] if rope else None
+    ref = O.rmsnorm(x, w)
+    if rope:
+        ref = O.apply_rope_pairs(ref.reshape(M, H, 128).transpose(0, 1), table).transpose(0, 1).reshape(M, D)
+    buf = x.to(cuda_dev).clone()
+    dsb.ops.rmsnorm_full(buf, w.to(cuda_dev), None if table is None else table.to(cuda_dev).contiguous())
+    assert O.rel_l2(buf.float().cpu(), ref) < 3e-3
+
+
+# -------------------------------------------------------------------------- quantisation
+@pytest.mark.parametrize("fmt", ["e4m3", "int8"])
+@pytest.mark.parametrize("M,K", [(64, 3072), (5, 15360), (3, 128)])
+def test_quant_rows_bit_exact(dsb, cuda_dev, fmt, M, K):
+    g = _gen(7)
+    x = _bf(torch.randn(M, K, generator=g) * 3)
+    x[0] = 0  # an all-zero row
+    fn = O.quant_rows_e4m3 if fmt == "e4m3" else O.quant_rows_int8
+    q_ref, s_ref = fn(x)
+    code = dsb.ops.FMT_E4M3 if fmt == "e4m3" else dsb.ops.FMT_INT8
+    q, s = dsb.ops.quant_rows(x.to(cuda_dev), out_fmt=code)
+    assert torch.equal(s.cpu(), s_ref)
+    assert torch.equal(q.cpu().view(torch.uint8), q_ref.view(torch.uint8))
+
+
+@pytest.mark.parametrize("fmt", ["fp8_tensor", "fp8_channel", "int8_channel"])
+@pytest.mark.parametrize("src", [torch.float32, torch.bfloat16])
+def test_pack_quant_weight_bit_exact(dsb, cuda_dev, fmt, src):
+    g = _gen(8)
+    W = (torch.randn(200, 384, generator=g) * 0.02).to(src)
+    W[3] = 0
+    q_ref, s_ref = O.quant_weight(W, fmt)
+    code = dsb.ops.FMT_INT8 if fmt == "int8_channel" else dsb.ops.FMT_E4M3
+    q, s = dsb.ops.pack_quant_weight(W.to(cuda_dev), code, per_channel=fmt != "fp8_tensor")
+    assert torch.equal(s.cpu(), s_ref)
+    assert torch.equal(q.cpu().view(torch.uint8), q_ref.view(torch.uint8))
+
+
+# ---------------------------------------------------------------------------------- gemv
+@pytest.mark.parametrize("wfmt", ["bf16", "e4m3", "int8"])
+def test_gemv(dsb, cuda_dev, wfmt):
+    g = _gen(9)
+    N, K = 1000, 3072
+    W = torch.randn(N, K, generator=g) * 0.02
+    x = torch.randn(K, generator=g)
+    bias = torch.randn(N, generator=g) * 0.02
+    if wfmt == "bf16":
+        Wd, scale, Wref = _bf(W), None, _bf(W).float()
+    else:
+        q, s = O.quant_weight(W, "fp8_channel" if wfmt == "e4m3" else "int8_channel")
+        Wd, scale, Wref = q, s, q.float() * s[:, None]
+    ref = Wref @ torch.nn.functional.silu(x) + bias
+    y = dsb.ops.gemv(Wd.to(cuda_dev), x.to(cuda_dev), None if scale is None else scale.to(cuda_dev),
+                     bias.to(cuda_dev), act_in=dsb.ops.ACT_SILU)
+    assert O.rel_l2(y.cpu(), ref) < 1e-5
+    ref2 = torch.nn.functional.silu(Wref @ x + bias)
+    y2 = dsb.ops.gemv(Wd.to(cuda_dev), x.to(cuda_dev), None if scale is None else scale.to(cuda_dev),
+                      bias.to(cuda_dev), act_out=dsb.ops.ACT_SILU)
+    assert O.rel_l2(y2.cpu(), ref2) < 1e-5
+
+
+# ---------------------------------------------------------------------------- euler step
+def test_euler_step(dsb, cuda_dev):
+    g = _gen(10)
+    lat, mo = torch.randn(1, 4096, 64, generator=g), torch.randn(1, 4096, 64, generator=g)
+    sig = torch.linspace(1, 0, 11)
+    ref = O.euler_step(lat, mo, sig, 3)
+    out = dsb.ops.euler_step(lat.to(cuda_dev), mo.to(cuda_dev), float(sig[4] - sig[3]))
+    assert torch.allclose(out.cpu(), ref, rtol=1e-6, atol=1e-6)
+    lb, mb = _bf(lat), _bf(mo)
+    refb = O.euler_step(lb, mb, sig, 3)
+    outb = dsb.ops.euler_step(lb.to(cuda_dev), mb.to(cuda_dev), float(sig[4] - sig[3]))
+    assert torch.equal(outb.cpu(), refb)
+
+
+# ---------------------------------------------------------------------------------- gemm
+def _gemm_case(dsb, dev, fmt, M, N, K, per_channel, bias, act, gated, seed=11):
+    g = _gen(seed)
+    x = _bf(torch.randn(M, K, generator=g))
+    W = torch.randn(N, K, generator=g) * 0.02
+    b = torch.randn(N, generator=g) * 0.1 if bias else None
+    resid = _bf(torch.randn(M, N, generator=g)) if gated else None
+    gate = torch.randn(N, generator=g) if gated else None
+    if fmt == "bf16":
+        a_d, w_d, rs, cs = x, _bf(W), None, None
+        acc = x.float() @ _bf(W).float().t()
+    elif fmt == "e4m3":
+        xq, xs = O.quant_rows_e4m3(x)
+        wq, ws = O.quant_weight(W, "fp8_channel" if per_channel else "fp8_tensor")
+        a_d, w_d, rs, cs = xq, wq, xs, ws
+        acc = O.linear_quant(xq, xs, wq, ws)
+    else:
+        xq, xs = O.quant_rows_int8(x)
+        wq, ws = O.quant_weight(W, "int8_channel")
+        a_d, w_d, rs, cs = xq, wq, xs, ws
+        acc = O.linear_quant(xq, xs, wq, ws)
+    ref = acc if b is None else acc + b
+    if act:
+        ref = O.gelu_tanh(ref)
+    if gated:
+        ref = resid.float() + gate * ref
+    to = lambda t: None if t is None else t.to(dev)
+    out = dsb.ops.gemm(to(a_d), to(w_d), row_scale=to(rs), col_scale=to(cs), bias=to(b),
+                       act=dsb.ops.ACT_GELU_TANH if act else dsb.ops.ACT_NONE, gate=to(gate), resid=to(resid))
+    return out.float().cpu(), ref
+
+
+@pytest.mark.parametrize("fmt", ["e4m3", "bf16", "int8"])
+@pytest.mark.parametrize("M,N,K", [(128, 256, 128), (256, 512, 3072), (300, 3072, 256), (4095, 1024, 512),
+                                   (1, 64, 64), (130, 136, 200 * 8)])
+def test_gemm_plain(dsb, cuda_dev, fmt, M, N, K):
+    if fmt != "bf16" and K % 16:
+        pytest.skip("8-bit operands need K % 16 == 0")
+    out, ref = _gemm_case(dsb, cuda_dev, fmt, M, N, K, per_channel=False, bias=False, act=False, gated=False)
+    assert O.rel_l2(out, ref) < 3e-3, (fmt, M, N, K)
+
+
+@pytest.mark.parametrize("fmt,per_channel", [("e4m3", False), ("e4m3", True), ("int8", True), ("bf16", False)])
+def test_gemm_epilogues(dsb, cuda_dev, fmt, per_channel):
+    for bias, act, gated in [(True, False, False), (True, True, False), (True, False, True), (False, True, True)]:
+        out, ref = _gemm_case(dsb, cuda_dev, fmt, 517, 768, 1024, per_channel, bias, act, gated)
+        assert O.rel_l2(out, ref) < 4e-3, (fmt, per_channel, bias, act, gated)
+
+
+def test_gemm_split_output_and_act_range(dsb, cuda_dev):
+    """Columns below split_col go to out0, the rest to out1; GELU only from act_col0 on
+    (the single-stream block's fused qkv|mlp projection, models/flux/flux_dit.py:311-317)."""
+    g = _gen(12)
+    M, K, N, split = 200, 512, 1024, 512
+    x, W = _bf(torch.randn(M, K, generator=g)), _bf(torch.randn(N, K, generator=g) * 0.05)
+    b = torch.randn(N, generator=g) * 0.1
+    ref = x.float() @ W.float().t() + b
+    ref0, ref1 = ref[:, :split], O.gelu_tanh(ref[:, split:])
+    out0 = torch.empty(M, split, dtype=torch.bfloat16, device=cuda_dev)
+    wide = torch.zeros(M, 256 + N - split, dtype=torch.bfloat16, device=cuda_dev)
+    dsb.ops.gemm(x.to(cuda_dev), W.to(cuda_dev), bias=b.to(cuda_dev), act=dsb.ops.ACT_GELU_TANH, act_col0=split,
+                 out=out0, out1=wide[:, 256:], split_col=split)
+    assert O.rel_l2(out0.float().cpu(), ref0) < 3e-3
+    assert O.rel_l2(wide[:, 256:].float().cpu(), ref1) < 3e-3
+    assert float(wide[:, :256].abs().max()) == 0.0  # nothing written left of the routed block
+
+
+def test_gemm_canary_rows(dsb, cuda_dev):
+    """M and N tails must not write outside [M, N]."""
+    g = _gen(13)
+    M, N, K = 130, 136, 384
+    x, W = _bf(torch.randn(M, K, generator=g)), _bf(torch.randn(N, K, generator=g) * 0.05)
+    big = torch.full((M + 8, N + 64), 7.0, dtype=torch.bfloat16, device=cuda_dev)
+    dsb.ops.gemm(x.to(cuda_dev), W.to(cuda_dev), out=big[:M, :N])
+    assert O.rel_l2(big[:M, :N].float().cpu(), x.float() @ W.float().t()) < 3e-3
+    assert bool((big[M:, :] == 7.0).all()) and bool((big[:, N:] == 7.0).all())
+
+
+def test_gemm_run_twice_identical(dsb, cuda_dev):
+    g = _gen(14)
+    x, W = _bf(torch.randn(1000, 1024, generator=g)).to(cuda_dev), _bf(torch.randn(768, 1024, generator=g)).to(cuda_dev)
+    a = dsb.ops.gemm(x, W)
+    b = dsb.ops.gemm(x, W)
+    assert torch.equal(a, b)
+
+
+def test_gemm_empty_and_bad_args(dsb, cuda_dev):
+    x = torch.zeros(0, 128, dtype=torch.bfloat16, device=cuda_dev)
+    W = torch.zeros(64, 128, dtype=torch.bfloat16, device=cuda_dev)
+    assert dsb.ops.gemm(x, W).shape == (0, 64)
+    with pytest.raises(dsb.DsbError):  # N not a multiple of 8
+        dsb.ops.gemm(torch.zeros(4, 128, dtype=torch.bfloat16, device=cuda_dev),
+                     torch.zeros(60, 128, dtype=torch.bfloat16, device=cuda_dev))
+
+
+# ----------------------------------------------------------------------------- attention
+@pytest.mark.parametrize("B,H,Sq,Sk", [(1, 2, 256, 256), (1, 24, 1536, 1536), (1, 3, 300, 300), (2, 2, 257, 512),
+                                       (1, 2, 1000, 77), (1, 1, 1, 1), (1, 40, 384, 512)])
+def test_flash_attn(dsb, cuda_dev, B, H, Sq, Sk):
+    g = _gen(15)
+    q = _bf(torch.randn(B, Sq, H, 128, generator=g))
+    k = _bf(torch.randn(B, Sk, H, 128, generator=g))
+    v = _bf(torch.randn(B, Sk, H, 128, generator=g))
+    ref = O.attention(q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2)).transpose(1, 2)
+    out = dsb.ops.flash_attn(q.to(cuda_dev), k.to(cuda_dev), v.to(cuda_dev))
+    assert O.rel_l2(out.float().cpu(), ref) < 4e-3, (B, H, Sq, Sk)
+
+
+def test_flash_attn_peaked_rows(dsb, cuda_dev):
+    """Large logits late in the sequence force the lazy running-max refresh and O rescale."""
+    g = _gen(16)
+    H, S = 2, 1024
+    q = _bf(torch.randn(1, S, H, 128, generator=g))
+    k = _bf(torch.randn(1, S, H, 128, generator=g))
+    v = _bf(torch.randn(1, S, H, 128, generator=g))
+    k[:, 700:720] *= 6.0
+    k[:, 1000:1003] *= 12.0
+    ref = O.attention(q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2)).transpose(1, 2)
+    out = dsb.ops.flash_attn(q.to(cuda_dev), k.to(cuda_dev), v.to(cuda_dev))
+    assert O.rel_l2(out.float().cpu(), ref) < 4e-3
+
+
+def test_flash_attn_strided_views(dsb, cuda_dev):
+    """q/k/v as column blocks of one fused projection buffer [S, 3*H*128] (text rows first), and
+    [B,H,S,D]-strided tensors as the reference's _attn_func receives them (models/flux/flux_dit.py:166-182)."""
+    g = _gen(17)
+    H, S = 4, 640
+    qkv = _bf(torch.randn(S, 3 * H * 128, generator=g))
+    q, k, v = (qkv[:, i * H * 128:(i + 1) * H * 128].reshape(1, S, H, 128) for i in range(3))
+    ref = O.attention(q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2)).transpose(1, 2)
+    d = qkv.to(cuda_dev)
+    qd, kd, vd = (d[:, i * H * 128:(i + 1) * H * 128].unflatten(1, (H, 128)).unsqueeze(0) for i in range(3))
+    out = dsb.ops.flash_attn(qd, kd, vd)
+    assert O.rel_l2(out.float().cpu(), ref) < 4e-3
+    # [B,H,S,D] contiguous inputs viewed as [B,S,H,D]
+    qh = q.transpose(1, 2).contiguous().to(cuda_dev).transpose(1, 2)
+    kh = k.transpose(1, 2).contiguous().to(cuda_dev).transpose(1, 2)
+    vh = v.transpose(1, 2).contiguous().to(cuda_dev).transpose(1, 2)
+    out2 = dsb.ops.flash_attn(qh, kh, vh)
+    assert O.rel_l2(out2.float().cpu(), ref) < 4e-3
