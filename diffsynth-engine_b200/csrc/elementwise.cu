@@ -366,8 +366,7 @@ __global__ void __launch_bounds__(256) quant_rows_kernel(const __nv_bfloat16* __
 // ------------------------------------------------------------------- gemv
 // y[n] = (sum_k W[n,k] * f(x[k])) * w_scale[n or 0] + bias[n],  one warp per
 // output row, the activation vector staged once per CTA in shared memory.
-// WFMT: 0 bf16, 1 e4m3, 2 int8.  ACT_IN: 0 identity, 1 SiLU on x.
-// ACT_OUT: 0 none, 1 SiLU, 2 GELU-tanh on y.
+// WFMT: 0 bf16, 1 e4m3, 2 int8.  act_in: DSB_ACT_NONE or DSB_ACT_SILU on x; act_out: any DSB_ACT_* on y.
 template <int WFMT>
 __global__ void __launch_bounds__(256) gemv_kernel(const void* __restrict__ W, int64_t ld_w_bytes,
                                                    const float* __restrict__ x, const float* __restrict__ w_scale,
@@ -376,7 +375,7 @@ __global__ void __launch_bounds__(256) gemv_kernel(const void* __restrict__ W, i
   extern __shared__ float xs[];
   for (int k = threadIdx.x; k < K; k += blockDim.x) {
     float t = x[k];
-    xs[k] = act_in == 1 ? silu(t) : t;
+    xs[k] = act_in == DSB_ACT_SILU ? silu(t) : t;
   }
   __syncthreads();
   const int lane = threadIdx.x & 31;
@@ -422,8 +421,8 @@ __global__ void __launch_bounds__(256) gemv_kernel(const void* __restrict__ W, i
     if (lane == 0) {
       float sc = w_scale ? w_scale[static_cast<int64_t>(n) * w_scale_stride] : 1.0f;
       float o = acc * sc + (bias ? bias[n] : 0.f);
-      if (act_out == 1) o = silu(o);
-      if (act_out == 2) o = gelu_tanh(o);
+      if (act_out == DSB_ACT_SILU) o = silu(o);
+      if (act_out == DSB_ACT_GELU_TANH) o = gelu_tanh(o);
       y[n] = o;
     }
   }
@@ -476,6 +475,7 @@ extern "C" {
 
 int dsb_ln_modulate(const void* x, int64_t ld_x, const float* shift, const float* scale, void* y, int64_t ld_y,
                     float* row_scale, int M, int D, float eps, int out_fmt, void* stream) {
+  if (M == 0 && D > 0 && !(D & 7)) return DSB_OK;
   if (!x || !shift || !scale || !y || M < 0 || D <= 0 || (D & 7) || (ld_x & 7) || !aligned16(x) || !aligned16(y) ||
       !aligned16(shift) || !aligned16(scale))
     return DSB_ERR_ARG;
@@ -497,6 +497,7 @@ int dsb_ln_modulate(const void* x, int64_t ld_x, const float* shift, const float
 
 int dsb_gate_residual(const void* x, int64_t ld_x, const void* y, int64_t ld_y, const float* gate, void* out,
                       int64_t ld_o, int M, int D, void* stream) {
+  if (M == 0 && D > 0 && !(D & 7)) return DSB_OK;
   if (!x || !y || !out || M < 0 || D <= 0 || (D & 7) || (ld_x & 7) || (ld_y & 7) || (ld_o & 7) || !aligned16(x) ||
       !aligned16(y) || !aligned16(out) || (gate && !aligned16(gate)))
     return DSB_ERR_ARG;
@@ -551,6 +552,7 @@ int dsb_rmsnorm_full(void* buf, int64_t ld, int M, int D, const float* w, const 
 
 int dsb_quant_rows(const void* x, int64_t ld_x, void* y, int64_t ld_y, float* row_scale, int M, int K, int out_fmt,
                    void* stream) {
+  if (M == 0 && K > 0 && !(K & 7)) return DSB_OK;
   if (!x || !y || !row_scale || M < 0 || K <= 0 || (K & 7) || (ld_x & 7) || (ld_y & 15) || !aligned16(x) ||
       !aligned16(y))
     return DSB_ERR_ARG;

@@ -327,7 +327,9 @@ extern "C" int dsb_gemm(const void* A, int64_t lda, const void* W, int64_t ldw, 
                         const float* row_scale, const float* col_scale, int col_scale_stride, const float* bias,
                         int act, int act_col0, const float* gate, const void* resid, int64_t ld_resid, void* out0,
                         int64_t ld_out0, void* out1, int64_t ld_out1, int split_col, int* status, void* stream) {
-  if (!A || !W || !out0 || M < 0 || N < 0 || K <= 0) return DSB_ERR_ARG;
+  if (M < 0 || N < 0 || K <= 0 || (N & 7)) return DSB_ERR_ARG;
+  if (M == 0 || N == 0) return DSB_OK;  // an empty product: nothing to read or write
+  if (!A || !W || !out0) return DSB_ERR_ARG;
   if (fmt != DSB_FMT_BF16 && fmt != DSB_FMT_E4M3 && fmt != DSB_FMT_INT8) return DSB_ERR_ARG;
   const int esz = (fmt == DSB_FMT_BF16) ? 2 : 1;
   auto al16 = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; };

@@ -1,0 +1,88 @@
+"""Wan2.1 DiT forward restated functionally over a reference-named state dict (fp32 on the CPU).
+Citations: ``diffsynth_engine/models/wan/wan_dit.py`` of modelscope/DiffSynth-Engine v0.1.1."""
+import torch
+import torch.nn.functional as F
+
+from . import ops as O
+from .linear import LinearEval
+
+
+def _ident(x):
+    return x
+
+
+def _mh(x, H):
+    return x.reshape(x.shape[0], H, -1).transpose(0, 1)  # [H, S, D]
+
+
+def _attend(q, k, v, H):
+    """wan_dit.py:18-22."""
+    o = O.attention(_mh(q, H)[None], _mh(k, H)[None], _mh(v, H)[None])[0]
+    return o.transpose(0, 1).reshape(q.shape[0], -1)
+
+
+def _rope(x, table, H):
+    """wan_dit.py:54-58 (complex multiply of adjacent pairs == the 2x2 rotation)."""
+    return O.apply_rope_pairs(_mh(x, H), table).transpose(0, 1).reshape(x.shape[0], -1)
+
+
+def wan_block(x, context, t_mod, table, w, pre, H, lin: LinearEval, rt=_ident, eps=1e-6):
+    """DiTBlock.forward, wan_dit.py:185-193.  x [S,d], context [L,d], t_mod [6,d]."""
+    mod = w[pre + "modulation"].float().reshape(6, -1) + t_mod.float()
+    sh_msa, sc_msa, g_msa, sh_mlp, sc_mlp, g_mlp = mod
+    def L(inp, name, **kw):
+        return lin(inp, w[pre + name + ".weight"], w[pre + name + ".bias"], **kw)
+    # self-attention, wan_dit.py:101-107
+    n = O.ln_modulate(x, sh_msa, sc_msa, eps)
+    q = rt(O.rmsnorm(rt(L(n, "self_attn.q")), w[pre + "self_attn.norm_q.weight"], eps))
+    k = rt(O.rmsnorm(rt(L(n, "self_attn.k")), w[pre + "self_attn.norm_k.weight"], eps))
+    v = rt(L(n, "self_attn.v"))
+    q, k = rt(_rope(q, table, H)), rt(_rope(k, table, H))
+    x = rt(x.float() + g_msa * L(rt(_attend(q, k, v, H)), "self_attn.o"))
+    # cross-attention (t2v: no image branch), wan_dit.py:136-152; norm3 is an affine LayerNorm (:178,190)
+    n3 = O.layer_norm(x, eps) * w[pre + "norm3.weight"].float() + w[pre + "norm3.bias"].float()
+    q = rt(O.rmsnorm(rt(L(n3, "cross_attn.q")), w[pre + "cross_attn.norm_q.weight"], eps))
+    k = rt(O.rmsnorm(rt(L(context, "cross_attn.k")), w[pre + "cross_attn.norm_k.weight"], eps))
+    v = rt(L(context, "cross_attn.v"))
+    x = rt(x + L(rt(_attend(q, k, v, H)), "cross_attn.o"))
+    # FFN, wan_dit.py:179-182,191-192
+    n2 = O.ln_modulate(x, sh_mlp, sc_mlp, eps)
+    hid = rt(O.gelu_tanh(L(n2, "ffn.0")))
+    return rt(x + g_mlp * L(hid, "ffn.2"))
+
+
+def patchify(x, w, lin):
+    """Conv3d with kernel = stride = (1,2,2) == a Linear over (c, 1, y, z) patches, then
+    b c f h w -> b (f h w) c (wan_dit.py:271-273,301-305).  x: [1, C, F, Hh, Ww]."""
+    _, C, Fr, Hh, Ww = x.shape
+    p = x[0].reshape(C, Fr, Hh // 2, 2, Ww // 2, 2).permute(1, 2, 4, 0, 3, 5).reshape(Fr * (Hh // 2) * (Ww // 2), C * 4)
+    Wc = w["patch_embedding.weight"]
+    return lin(p, Wc.reshape(Wc.shape[0], -1), w["patch_embedding.bias"]), (Fr, Hh // 2, Ww // 2)
+
+
+def unpatchify(x, grid, out_dim):
+    """b (f h w) (x y z c) -> b c (f x) (h y) (w z) with (x,y,z) = (1,2,2) (wan_dit.py:307-317)."""
+    f, h, ww = grid
+    return x.reshape(f, h, ww, 1, 2, 2, out_dim).permute(6, 0, 3, 1, 4, 2, 5).reshape(1, out_dim, f, h * 2, ww * 2)
+
+
+def wan_dit_forward(w, x, context, timestep, num_layers, H, freq_dim=256, eps=1e-6, lin: LinearEval = None,
+                    rt=_ident):
+    """WanDiT.forward (t2v), wan_dit.py:319-351, batch 1."""
+    lin = lin or LinearEval("fp32")
+    d = w["time_embedding.0.weight"].shape[0]
+    def L(inp, name, **kw):
+        return lin(inp, w[name + ".weight"], w[name + ".bias"], **kw)
+    sin = rt(O.sinusoidal_embedding_wan(freq_dim, timestep).float())
+    t = L(F.silu(L(sin, "time_embedding.0", act_quant=False)), "time_embedding.2", act_quant=False)   # [1,d]
+    t_mod = L(F.silu(t), "time_projection.1", act_quant=False).reshape(6, d)
+    ctx = rt(L(rt(O.gelu_tanh(L(context[0], "text_embedding.0"))), "text_embedding.2"))
+    h, grid = patchify(x, w, lin)
+    h = rt(h)
+    table = O.wan_rope_table(*grid, head_dim=d // H)
+    for i in range(num_layers):
+        h = wan_block(h, ctx, t_mod, table, w, f"blocks.{i}.", H, lin, rt, eps)
+    mod = w["head.modulation"].float().reshape(2, d) + t[0]
+    shift, scale = mod
+    out = rt(L(O.ln_modulate(h, shift, scale, eps), "head.head"))
+    return unpatchify(out, grid, out.shape[1] // 4)
