@@ -1,0 +1,331 @@
+#!/usr/bin/env python
+"""Benchmark of the DiT denoising step (Flux.1-dev architecture, 1024x1024, FP8 e4m3 per-tensor weights, bf16
+activations, batch 1, random-init weights, synthetic inputs) on B200.
+
+    python bench.py --gpus N --steps K --warmup W            # this library
+    python bench.py --impl reference --steps K --warmup W     # the reference arithmetic on the host CPU cores
+
+Prints ONE JSON line.  `value` = whole-job denoise steps/s with inputs resident in HBM (CUDA-graph replay of the
+step, CUDA events, max over ranks); `e2e` = the same through `FluxDiTEngine.forward`-style host buffers (pinned
+host -> device copies of every input and a device -> host read of the model output inside the timed region).
+With N > 1 every rank denoises its own latent (independent replicas, weak scaling, no data-path collective).
+"""
+import argparse
+import importlib
+import importlib.util
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+PKG_DIR = os.path.join(ROOT, "diffsynth-engine_b200")
+sys.path.insert(0, ROOT)
+
+FLUX = dict(d=3072, H=24, n_double=19, n_single=38, S_txt=512, height=128, width=128, txt_dim=4096, pooled_dim=768)
+
+
+def load_package():
+    name = "diffsynth_engine_b200"
+    if name not in sys.modules:
+        spec = importlib.util.spec_from_file_location(name, os.path.join(PKG_DIR, "__init__.py"),
+                                                      submodule_search_locations=[PKG_DIR])
+        mod = importlib.util.module_from_spec(spec)
+        sys.modules[name] = mod
+        spec.loader.exec_module(mod)
+    return sys.modules[name]
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            p = json.load(f)
+        return dict(hbm_gbs=p["hbm_gbs"], bf16=p["bf16_tflops"], bf16_sustained=p.get("bf16_tflops_sustained"),
+                    source="measured")
+    return dict(hbm_gbs=6650.0, bf16=1590.0, bf16_sustained=1400.0, source="fallback")
+
+
+def flux_step_flops(c=FLUX):
+    """Algorithmic work of one step: 2MKN per Linear on token rows, 4*S^2*H*D per attention."""
+    d, St, Si = c["d"], c["S_txt"], (c["height"] // 2) * (c["width"] // 2)
+    S = St + Si
+    lin_double = 2 * S * d * (3 * d + d + 4 * d + 4 * d)
+    lin_single = 2 * S * d * (7 * d + 5 * d)
+    lin = c["n_double"] * lin_double + c["n_single"] * lin_single
+    lin += 2 * St * c["txt_dim"] * d + 2 * Si * 64 * d * 2
+    attn = (c["n_double"] + c["n_single"]) * 4 * S * S * d
+    return lin, attn
+
+
+# ------------------------------------------------------------------------------------ clocks
+class ClockSampler:
+    FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index=0):
+        self.gpu_index, self.rows, self.proc, self.thread = gpu_index, [], None, None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
+                                          "-lms", "100", "-i", str(self.gpu_index)],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            return self
+        self.thread = threading.Thread(target=self._read, daemon=True)
+        self.thread.start()
+        return self
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def stop(self):
+        if self.proc is not None:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=5)
+            except subprocess.TimeoutExpired:
+                self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for r in self.rows:
+            if len(r) < 9:
+                continue
+            try:
+                sm.append(float(r[1]))
+                mx.append(float(r[2]))
+            except ValueError:
+                continue
+            for name, val in zip(names, r[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        if not sm:
+            return dict(sm_mhz=None, sm_max_mhz=None, reasons=[], samples=0)
+        return dict(sm_mhz=statistics.median(sm), sm_max_mhz=max(mx), reasons=sorted(reasons), samples=len(sm))
+
+
+# ------------------------------------------------------------------------- CPU arm (oracle port)
+def cpu_reference_arm(steps=1, warmup=0, budget_s=150.0):
+    """The reference's arithmetic on the host cores: the fp32 PyTorch restatement of one double-stream and one
+    single-stream block (oracle/flux.py) at the full sequence length, extrapolated by the block counts."""
+    import torch
+    from oracle import flux as OF
+    from oracle import ops as O
+    from oracle.linear import LinearEval
+    load_package()
+    synth = importlib.import_module("diffsynth_engine_b200.synth")
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    c = FLUX
+    d, H = c["d"], c["H"]
+    St, side = c["S_txt"], c["height"] // 2
+    wd = synth.make_state_dict(synth.flux_block_shapes("", d, H, "double"), seed=0)
+    ws = synth.make_state_dict(synth.flux_block_shapes("", d, H, "single"), seed=1)
+    xa, xb, temb = synth.randn((side * side, d), 2), synth.randn((St, d), 3), synth.randn((d,), 4)
+    table = O.flux_rope_table(torch.cat([torch.zeros(St, 3), OF.image_ids(c["height"], c["width"])]))
+    lin = LinearEval("fp32")
+    times, t_start = [], time.time()
+    with torch.no_grad():
+        for i in range(warmup + steps):
+            if times and time.time() - t_start > budget_s:
+                break
+            t0 = time.time()
+            OF.double_block(xa, xb, temb, table, wd, "", H, lin)
+            t1 = time.time()
+            OF.single_block(torch.cat([xb, xa]), temb, table, ws, "", H, lin)
+            t2 = time.time()
+            if i >= warmup or (warmup + steps) == 1:
+                times.append((t1 - t0, t2 - t1))
+    td = statistics.mean(t[0] for t in times)
+    tsg = statistics.mean(t[1] for t in times)
+    step_s = c["n_double"] * td + c["n_single"] * tsg
+    return dict(value=1.0 / step_s, unit="steps/s", cores=cores, kind="port",
+                sample=(f"1 double-stream + 1 single-stream block at S=512+4096, fp32, {cores} threads "
+                        f"({td:.2f}s + {tsg:.2f}s, mean of {len(times)}), extrapolated x19 / x38; embedders and "
+                        f"final layer (<0.1% of the work) left out"),
+                ms_per_step=step_s * 1e3, samples=len(times))
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--fmt", default="fp8_tensor")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--blocks", default=None, help="n_double,n_single override (reduced-depth debugging; not a bench)")
+    args = ap.parse_args()
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    cfg = dict(FLUX)
+    if args.blocks:
+        cfg["n_double"], cfg["n_single"] = (int(v) for v in args.blocks.split(","))
+    config = {"workload": "flux1-dev-arch DiT step, 1024x1024 (4096 image + 512 text tokens), batch 1, "
+                          f"{cfg['n_double']} double + {cfg['n_single']} single blocks, weights {args.fmt}, bf16 activations",
+              "parallelism": f"replicas x{world}" if world > 1 else "single GPU",
+              "l2": "per-step working set (11.9 GB of weights) exceeds the 126 MB L2; no flush between steps"}
+
+    if args.impl == "reference":
+        if rank != 0:
+            return
+        r = cpu_reference_arm(steps=max(1, args.steps), warmup=args.warmup)
+        line = {"impl": "reference", "metric": "DiT denoise steps/s", "value": r["value"], "unit": "steps/s",
+                "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": r["ms_per_step"],
+                "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "fp32", "data": "synthetic",
+                "config": config, "cpu_baseline": {k: r[k] for k in ("value", "unit", "cores", "kind", "sample")},
+                "e2e": {"value": r["value"], "unit": "steps/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+        print(json.dumps(line), flush=True)
+        return
+
+    import torch
+    pkg = load_package()
+    ops = pkg.ops
+    synth = importlib.import_module("diffsynth_engine_b200.synth")
+    flux = importlib.import_module("diffsynth_engine_b200.flux")
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the library has no CPU path")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device(f"cuda:{local_rank}")
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=dev)
+
+    # random-init weights of the architecture, drawn on the device, packed to FP8 layer by layer
+    shapes = synth.flux_dit_shapes(d=cfg["d"], H=cfg["H"], n_double=cfg["n_double"], n_single=cfg["n_single"],
+                                   txt_dim=cfg["txt_dim"], pooled_dim=cfg["pooled_dim"])
+    sd = synth.make_state_dict(shapes, seed=rank, device=dev, dtype=torch.bfloat16)
+    eng = flux.FluxDiTEngine(sd, fmt=args.fmt, device=dev, n_double=cfg["n_double"], n_single=cfg["n_single"],
+                             num_heads=cfg["H"], release_source=True)
+    del sd
+    torch.cuda.empty_cache()
+    eng.prepare(cfg["S_txt"], cfg["height"], cfg["width"], cfg["txt_dim"], cfg["pooled_dim"])
+    # inputs on the host (pinned), as a pipeline would hold them between steps
+    h_lat = synth.randn((1, 16, cfg["height"], cfg["width"]), 100 + rank).bfloat16().pin_memory()
+    h_pe = synth.randn((1, cfg["S_txt"], cfg["txt_dim"]), 200 + rank).bfloat16().pin_memory()
+    h_pool = synth.randn((1, cfg["pooled_dim"]), 300 + rank).pin_memory()
+    h_t, h_g = torch.tensor([500.0]).pin_memory(), torch.tensor([3.5]).pin_memory()
+    h_out = torch.empty((1, 16, cfg["height"], cfg["width"]), dtype=torch.bfloat16).pin_memory()
+    h2d = sum(t.numel() * t.element_size() for t in (h_lat, h_pe, h_pool, h_t, h_g))
+    d2h = h_out.numel() * h_out.element_size()
+    eng.set_inputs(h_lat, h_t, h_pe, h_pool, h_g)
+    n0 = pkg._lib.launches
+    eng.step()
+    launches_per_step = pkg._lib.launches - n0
+    torch.cuda.synchronize()
+    ops.check_status(local_rank)
+    eng.capture()
+
+    def barrier():
+        torch.cuda.synchronize()
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def max_over_ranks(ms):
+        if dist is None:
+            return ms
+        t = torch.tensor([ms], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    # ---- device-resident throughput
+    for _ in range(max(3, args.warmup)):
+        eng.step()
+    sampler = ClockSampler(local_rank).start() if rank == 0 else None
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        eng.step()
+    e1.record()
+    barrier()
+    ms_total = max_over_ranks(e0.elapsed_time(e1))
+    clocks = sampler.stop() if sampler else None
+    ms_per_step = ms_total / args.steps
+    value = world * 1e3 / ms_per_step
+
+    # ---- end to end: host buffers in, host buffer out, every step
+    def e2e_step():
+        eng.set_inputs(h_lat, h_t, h_pe, h_pool, h_g)
+        out = eng.step()
+        h_out.copy_(out, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+
+    for _ in range(3):
+        e2e_step()
+    barrier()
+    t0 = time.perf_counter()
+    e0.record()
+    for _ in range(args.steps):
+        e2e_step()
+    e1.record()
+    barrier()
+    e2e_ms = max_over_ranks(max(e0.elapsed_time(e1), 0.0)) / args.steps
+    e2e_wall_ms = (time.perf_counter() - t0) * 1e3 / args.steps
+    ops.check_status(local_rank)
+
+    # ---- roofline of the dominant kernel (the FP8 GEMM): CUDA events around every launch of one eager step
+    peaks = measured_peaks()
+    recs = []
+    real_gemm = ops.gemm
+
+    def timed_gemm(a, w, **kw):
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s.record()
+        r = real_gemm(a, w, **kw)
+        e.record()
+        recs.append((2.0 * a.shape[0] * a.shape[1] * w.shape[0], s, e))
+        return r
+
+    eng._graph_saved, eng._graph = eng._graph, None
+    ops.gemm = timed_gemm
+    try:
+        eng.step()
+        torch.cuda.synchronize()
+    finally:
+        ops.gemm = real_gemm
+        eng._graph = eng._graph_saved
+    gemm_flops = sum(r[0] for r in recs)
+    gemm_ms = sum(r[1].elapsed_time(r[2]) for r in recs)
+    fp8 = args.fmt != "bf16"
+    peak_tf = peaks["bf16"] * (2.0 if fp8 else 1.0)
+    ach_tf = gemm_flops / (gemm_ms * 1e-3) / 1e12
+    lin_f, attn_f = flux_step_flops(cfg)
+    roofline = {"kernel": "gemm_kernel<fp8,128x256>" if fp8 else "gemm_kernel<bf16,128x256>", "bound": "tensor",
+                "achieved": ach_tf, "peak": peak_tf, "unit": "TFLOP/s", "frac": ach_tf / peak_tf, "traffic": None,
+                "peak_source": (f"2 x bf16_tflops of MEASURED_PEAKS.json ({peaks['source']}); no FP8 peak was measured"
+                                if fp8 else f"bf16_tflops of MEASURED_PEAKS.json ({peaks['source']})"),
+                "launches_per_step": len(recs), "gemm_ms_per_step": gemm_ms,
+                "method": "CUDA events around each GEMM launch of one eager (un-graphed) step; 2MNK per launch",
+                "step_tflop": (lin_f + attn_f) / 1e12,
+                "step_frac_of_roofline": ((lin_f / (peak_tf * 1e12) + attn_f / (peaks["bf16"] * 1e12)) * 1e3) / ms_per_step}
+
+    line = {"metric": "DiT denoise steps/s", "value": value, "unit": "steps/s", "n_gpus": world, "steps": args.steps,
+            "warmup": max(3, args.warmup), "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "fp8_e4m3 x fp8_e4m3 -> fp32 (linear), bf16 (attention)" if fp8 else "bf16",
+            "data": "synthetic", "config": config, "clocks": clocks,
+            "e2e": {"value": world * 1e3 / e2e_ms, "unit": "steps/s", "h2d_bytes_per_step": h2d,
+                    "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms, "wall_ms_per_step": e2e_wall_ms},
+            "gpu_launches": launches_per_step * args.steps, "gpu_launches_per_step": launches_per_step,
+            "roofline": roofline}
+    if rank == 0:
+        if not args.no_cpu_baseline and world == 1:
+            r = cpu_reference_arm(steps=1, warmup=0)
+            line["cpu_baseline"] = {k: r[k] for k in ("value", "unit", "cores", "kind", "sample")}
+        print(json.dumps(line), flush=True)
+    if dist is not None:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -29,7 +29,8 @@ _SIGS = {
     "dsb_rmsnorm_rope_heads": [c_p, c_i64, c_i, c_i, c_i, c_i, c_p, c_p, c_p, c_i, c_f, c_p],
     "dsb_rmsnorm_full": [c_p, c_i64, c_i, c_i, c_p, c_p, c_i, c_f, c_p],
     "dsb_quant_rows": [c_p, c_i64, c_p, c_i64, c_p, c_i, c_i, c_i, c_p],
-    "dsb_gemv": [c_p, c_i64, c_i, c_p, c_p, c_i, c_p, c_p, c_i, c_i, c_i, c_i, c_p],
+    "dsb_gemv": [c_p, c_i64, c_i, c_p, c_p, c_i, c_p, c_p, c_i, c_i, c_i, c_i, c_i, c_p],
+    "dsb_timestep_embedding": [c_p, c_i, c_i, c_f, c_i, c_i, c_p, c_p],
     "dsb_euler_step": [c_p, c_p, c_p, c_p, c_f, c_p, c_i64, c_i, c_p],
     "dsb_gemm": [c_p, c_i64, c_p, c_i64, c_i, c_i, c_i, c_i, c_p, c_p, c_i, c_p, c_i, c_i, c_p, c_p, c_i64, c_p,
                  c_i64, c_p, c_i64, c_i, c_p, c_p],
@@ -67,6 +68,11 @@ def lib():
     return _lib
 
 
+launches = 0  # successful op calls so far (one kernel launch each on the step's path)
+
+
 def check(rc: int, what: str):
+    global launches
+    launches += 1
     if rc != OK:
         raise DsbError(f"{what} failed: {_ERR_NAMES.get(rc, rc)}")

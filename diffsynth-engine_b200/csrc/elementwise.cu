@@ -371,7 +371,8 @@ template <int WFMT>
 __global__ void __launch_bounds__(256) gemv_kernel(const void* __restrict__ W, int64_t ld_w_bytes,
                                                    const float* __restrict__ x, const float* __restrict__ w_scale,
                                                    int w_scale_stride, const float* __restrict__ bias,
-                                                   float* __restrict__ y, int N, int K, int act_in, int act_out) {
+                                                   float* __restrict__ y, int N, int K, int act_in, int act_out,
+                                                   int accumulate) {
   extern __shared__ float xs[];
   for (int k = threadIdx.x; k < K; k += blockDim.x) {
     float t = x[k];
@@ -423,7 +424,7 @@ __global__ void __launch_bounds__(256) gemv_kernel(const void* __restrict__ W, i
       float o = acc * sc + (bias ? bias[n] : 0.f);
       if (act_out == DSB_ACT_SILU) o = silu(o);
       if (act_out == DSB_ACT_GELU_TANH) o = gelu_tanh(o);
-      y[n] = o;
+      y[n] = accumulate ? y[n] + o : o;
     }
   }
 }
@@ -463,6 +464,32 @@ __global__ void __launch_bounds__(256) euler_step_f32_kernel(const float* __rest
     if (mask) m = m * mask[i] + init[i] * (1.0f - mask[i]);
     out[i] = latents[i] + m * dt;
   }
+}
+
+// ------------------------------------------------------- timestep embedding
+// mode 0: fp32 sinusoid [cos | sin], freq_i = exp(-ln(10000) * i / half)      (Flux)
+// mode 1: fp64 sinusoid [cos | sin], freq_i = 10000^(-i / half)               (Wan)
+__global__ void timestep_embedding_kernel(const float* __restrict__ t, int n, int dim, float t_scale, int mode,
+                                          int round_bf16, float* __restrict__ out) {
+  const int half = dim / 2;
+  const int idx = blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= n * half) return;
+  const int r = idx / half, i = idx - r * half;
+  float c, s;
+  if (mode == 0) {
+    const float exponent = -9.210340371976184f * static_cast<float>(i) / static_cast<float>(half);
+    const float ang = (t[r] * t_scale) * expf(exponent);
+    c = cosf(ang), s = sinf(ang);
+  } else {
+    const double ang = static_cast<double>(t[r] * t_scale) * pow(10000.0, -static_cast<double>(i) / half);
+    c = static_cast<float>(cos(ang)), s = static_cast<float>(sin(ang));
+  }
+  if (round_bf16) {
+    c = __bfloat162float(__float2bfloat16(c));
+    s = __bfloat162float(__float2bfloat16(s));
+  }
+  out[r * dim + i] = c;
+  out[r * dim + half + i] = s;
 }
 
 static bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
@@ -570,7 +597,7 @@ int dsb_quant_rows(const void* x, int64_t ld_x, void* y, int64_t ld_y, float* ro
 }
 
 int dsb_gemv(const void* W, int64_t ld_w, int w_fmt, const float* x, const float* w_scale, int w_scale_stride,
-             const float* bias, float* y, int N, int K, int act_in, int act_out, void* stream) {
+             const float* bias, float* y, int N, int K, int act_in, int act_out, int accumulate, void* stream) {
   if (!W || !x || !y || N < 0 || K <= 0 || !aligned16(W)) return DSB_ERR_ARG;
   const int esz = (w_fmt == DSB_FMT_BF16) ? 2 : 1;
   const int kq = (w_fmt == DSB_FMT_BF16) ? 8 : 16;
@@ -587,13 +614,23 @@ int dsb_gemv(const void* W, int64_t ld_w, int w_fmt, const float* x, const float
   {                                                                                                             \
     auto kern = gemv_kernel<F>;                                                                                 \
     DSB_ENSURE_SMEM(kern, 96 * 1024);                                                                           \
-    gemv_kernel<F><<<blocks, 256, smem, st>>>(W, ldb, x, w_scale, w_scale_stride, bias, y, N, K, act_in, act_out); \
+    gemv_kernel<F><<<blocks, 256, smem, st>>>(W, ldb, x, w_scale, w_scale_stride, bias, y, N, K, act_in, act_out, \
+                                               accumulate);                                                       \
   }
   if (w_fmt == DSB_FMT_BF16) DSB_GEMV(0)
   else if (w_fmt == DSB_FMT_E4M3) DSB_GEMV(1)
   else if (w_fmt == DSB_FMT_INT8) DSB_GEMV(2)
   else return DSB_ERR_ARG;
 #undef DSB_GEMV
+  return cudaGetLastError() == cudaSuccess ? DSB_OK : DSB_ERR_CUDA;
+}
+
+int dsb_timestep_embedding(const float* t, int n, int dim, float t_scale, int mode, int round_bf16, float* out,
+                           void* stream) {
+  if (!t || !out || n <= 0 || dim <= 0 || (dim & 1) || (mode != 0 && mode != 1)) return DSB_ERR_ARG;
+  const int total = n * (dim / 2);
+  timestep_embedding_kernel<<<(total + 127) / 128, 128, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      t, n, dim, t_scale, mode, round_bf16, out);
   return cudaGetLastError() == cudaSuccess ? DSB_OK : DSB_ERR_CUDA;
 }
 

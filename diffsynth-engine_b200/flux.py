@@ -1,0 +1,287 @@
+"""One Flux-architecture DiT denoising step on the library's kernels (the job of ``FluxDiT.forward``,
+models/flux/flux_dit.py:392-461 of DiffSynth-Engine, batch 1).
+
+Dataflow per block (each arrow one kernel of ``libdsb.so``; nothing runs in PyTorch except the two
+patchify/unpatchify reshapes at the model boundary):
+
+  step start : sinusoid -> 6 GEMVs (time, guidance, pooled MLPs, summed in fp32) -> ONE GEMV over the stacked
+               AdaLN weights of all blocks = every shift/scale/gate of the step
+  double     : per stream  ln_modulate(+quantise) -> qkv GEMM (+bias) into the joint [S, 3d] buffer (text rows
+               first) -> per-head RMSNorm+RoPE in place;   joint flash attention;
+               per stream  quantise -> out-proj GEMM with x += gate*(.) fused -> ln_modulate(+quantise)
+               -> FF1 GEMM (+GELU) -> quantise -> FF2 GEMM with x += gate*(.) fused
+  single     : ln_modulate(+quantise) -> ONE GEMM N=7d whose epilogue routes [q|k|v] to the attention buffer and
+               GELU(mlp) next to where attention will write its output (no torch.cat) -> RMSNorm+RoPE ->
+               flash attention -> quantise -> proj GEMM K=5d with x = x + gate*(.) fused
+
+The text and image streams live in one [S_txt + S_img, d] buffer (text first), so the hand-over from double
+to single blocks (flux_dit.py:442) is free.  All buffers are allocated once; the step can be captured in a
+CUDA graph."""
+from typing import Dict, Optional
+
+import torch
+
+from . import ops
+from .packed import PackedLinear, act_format, pack_linear, stack_for_gemv
+
+
+def flux_rope_table(ids: torch.Tensor, axes_dim=(16, 56, 56), theta=10000) -> torch.Tensor:
+    """(cos, sin) per rotated pair, fp32 [S, 64, 2], from position ids [S, 3]; angles in fp64 as
+    models/basic/transformer_helper.py:46-64 computes them."""
+    cols = []
+    for i, d in enumerate(axes_dim):
+        omega = 1.0 / (theta ** (torch.arange(0, d, 2, dtype=torch.float64, device=ids.device) / d))
+        ang = ids[:, i].to(torch.float64)[:, None] * omega[None, :]
+        cols.append(torch.stack([torch.cos(ang), torch.sin(ang)], dim=-1))
+    return torch.cat(cols, dim=1).float().contiguous()
+
+
+class FluxDiTEngine:
+    def __init__(self, state_dict: Dict[str, torch.Tensor], fmt: str = "fp8_tensor", device="cuda:0",
+                 n_double: int = 19, n_single: int = 38, num_heads: int = 24, use_guidance: bool = True,
+                 release_source: bool = False):
+        self.dev = torch.device(device)
+        self.fmt = fmt
+        self.afmt = act_format(fmt)
+        self.n_double, self.n_single, self.H = n_double, n_single, num_heads
+        self.use_guidance = use_guidance
+        sd = state_dict
+        self.d = sd["x_embedder.weight"].shape[0]
+        self.in_ch = sd["x_embedder.weight"].shape[1]
+        if self.d // num_heads != 128:
+            raise ValueError("head_dim must be 128")
+
+        def P(name):
+            p = pack_linear(sd[name + ".weight"], sd.get(name + ".bias"), fmt, self.dev)
+            if release_source:
+                sd.pop(name + ".weight", None)
+                sd.pop(name + ".bias", None)
+            return p
+
+        def V(name):
+            v = sd[name].to(device=self.dev, dtype=torch.float32).contiguous()
+            if release_source:
+                sd.pop(name, None)
+            return v
+
+        self.time0, self.time2 = P("time_embedder.timestep_embedder.0"), P("time_embedder.timestep_embedder.2")
+        if use_guidance:
+            self.guid0 = P("guidance_embedder.timestep_embedder.0")
+            self.guid2 = P("guidance_embedder.timestep_embedder.2")
+        self.pool0, self.pool2 = P("pooled_text_embedder.0"), P("pooled_text_embedder.2")
+        self.ctx_emb, self.x_emb = P("context_embedder"), P("x_embedder")
+        mods = []
+        self.double = []
+        for i in range(n_double):
+            pre = f"blocks.{i}."
+            mods += [P(pre + "norm1_a.linear"), P(pre + "norm1_b.linear")]
+            self.double.append(dict(
+                qkv_a=P(pre + "attn.a_to_qkv"), qkv_b=P(pre + "attn.b_to_qkv"),
+                nq_a=V(pre + "attn.norm_q_a.weight"), nk_a=V(pre + "attn.norm_k_a.weight"),
+                nq_b=V(pre + "attn.norm_q_b.weight"), nk_b=V(pre + "attn.norm_k_b.weight"),
+                out_a=P(pre + "attn.a_to_out"), out_b=P(pre + "attn.b_to_out"),
+                ff0_a=P(pre + "ff_a.0"), ff2_a=P(pre + "ff_a.2"), ff0_b=P(pre + "ff_b.0"), ff2_b=P(pre + "ff_b.2")))
+        self.single = []
+        for i in range(n_single):
+            pre = f"single_blocks.{i}."
+            mods.append(P(pre + "norm.linear"))
+            self.single.append(dict(qkv_mlp=P(pre + "to_qkv_mlp"), nq=V(pre + "norm_q_a.weight"),
+                                    nk=V(pre + "norm_k_a.weight"), proj=P(pre + "proj_out")))
+        mods.append(P("final_norm_out.linear"))
+        self.final_proj = P("final_proj_out")
+        self.mod = stack_for_gemv(mods)
+        del mods
+        self._bufs = None
+        self._graph = None
+
+    # ------------------------------------------------------------------ buffers
+    def _alloc(self, S_txt: int, height: int, width: int, txt_dim: int, pooled_dim: int):
+        d, dev = self.d, self.dev
+        S_img = (height // 2) * (width // 2)
+        S = S_txt + S_img
+        qdt = {ops.FMT_BF16: torch.bfloat16, ops.FMT_E4M3: torch.float8_e4m3fn, ops.FMT_INT8: torch.int8}[self.afmt]
+        bf = torch.bfloat16
+        b = dict(S_txt=S_txt, S_img=S_img, S=S, height=height, width=width)
+        # static inputs
+        b["latents"] = torch.zeros(1, self.in_ch // 4, height, width, dtype=bf, device=dev)
+        b["prompt"] = torch.zeros(S_txt, txt_dim, dtype=bf, device=dev)
+        b["pooled"] = torch.zeros(pooled_dim, dtype=torch.float32, device=dev)
+        b["tg"] = torch.zeros(2, dtype=torch.float32, device=dev)      # timestep, guidance
+        b["sin"] = torch.zeros(2, 256, dtype=torch.float32, device=dev)
+        b["hid"] = torch.zeros(d, dtype=torch.float32, device=dev)
+        b["cond"] = torch.zeros(d, dtype=torch.float32, device=dev)
+        b["modv"] = torch.zeros(self.mod.out_features, dtype=torch.float32, device=dev)
+        b["x"] = torch.zeros(S, d, dtype=bf, device=dev)
+        b["xq"] = torch.zeros(S, max(d, txt_dim), dtype=qdt, device=dev)       # quantised LN output / embedder input
+        b["rs"] = torch.zeros(S, dtype=torch.float32, device=dev)
+        b["qkv"] = torch.zeros(S, 3 * d, dtype=bf, device=dev)
+        b["cat"] = torch.zeros(S, 5 * d, dtype=bf, device=dev)                 # [attention out | gelu(mlp)]
+        b["catq"] = torch.zeros(S if self.afmt != ops.FMT_BF16 else 1, 5 * d, dtype=qdt, device=dev)
+        b["patches"] = torch.zeros(S_img, self.in_ch, dtype=bf, device=dev)
+        b["out_tok"] = torch.zeros(S_img, self.in_ch, dtype=bf, device=dev)
+        b["ids_key"] = None
+        b["rope"] = None
+        self._bufs = b
+        self._graph = None
+        return b
+
+    # -------------------------------------------------------------------- pieces
+    def _gemv(self, p: PackedLinear, x, out, act_in=ops.ACT_NONE, act_out=ops.ACT_NONE, accumulate=False):
+        ops.gemv(p.w, x, p.scale, p.bias, act_in=act_in, act_out=act_out, out=out, accumulate=accumulate)
+
+    def _quant(self, x, out, rs):
+        """bf16 rows -> the GEMM's activation operand (+ per-row scale); a no-op view for bf16 weights."""
+        if self.afmt == ops.FMT_BF16:
+            return x, None
+        ops.quant_rows(x, self.afmt, out=out, row_scale=rs)
+        return out, rs
+
+    def _ln(self, x, shift, scale, out, rs):
+        y, s = ops.ln_modulate(x, shift, scale, 1e-6, self.afmt, out=out, row_scale=rs)
+        return y, (s if self.afmt != ops.FMT_BF16 else None)
+
+    def _gemm(self, a, rs, p: PackedLinear, **kw):
+        return ops.gemm(a, p.w, row_scale=rs, col_scale=p.scale, bias=p.bias, **kw)
+
+    # ---------------------------------------------------------------------- step
+    def _run(self):
+        b, d, H = self._bufs, self.d, self.H
+        S_txt, S = b["S_txt"], b["S"]
+        x, qkv, cat, catq, xq, rs = b["x"], b["qkv"], b["cat"], b["catq"], b["xq"], b["rs"]
+        xq_d = xq[:, :d]
+        # conditioning (flux_dit.py:409-415): time + guidance + pooled, fp32
+        ops.timestep_embedding(b["tg"], 256, 1.0, 0, round_bf16=True, out=b["sin"])
+        self._gemv(self.time0, b["sin"][0], b["hid"], act_out=ops.ACT_SILU)
+        self._gemv(self.time2, b["hid"], b["cond"])
+        if self.use_guidance:
+            self._gemv(self.guid0, b["sin"][1], b["hid"], act_out=ops.ACT_SILU)
+            self._gemv(self.guid2, b["hid"], b["cond"], accumulate=True)
+        self._gemv(self.pool0, b["pooled"], b["hid"], act_out=ops.ACT_SILU)
+        self._gemv(self.pool2, b["hid"], b["cond"], accumulate=True)
+        # every AdaLN shift/scale/gate of the step in one launch (they all read SiLU(cond))
+        self._gemv(self.mod, b["cond"], b["modv"], act_in=ops.ACT_SILU)
+        mv = b["modv"]
+        # token embedders (flux_dit.py:416,419-421)
+        txt_dim = b["prompt"].shape[1]
+        a, s = self._quant(b["prompt"], xq[:S_txt, :txt_dim], rs[:S_txt])
+        self._gemm(a, s, self.ctx_emb, out=x[:S_txt])
+        b["patches"].copy_(b["latents"].reshape(self.in_ch // 4, b["height"] // 2, 2, b["width"] // 2, 2)
+                           .permute(1, 3, 0, 2, 4).reshape(b["S_img"], self.in_ch))
+        a, s = self._quant(b["patches"], xq[S_txt:, :self.in_ch], rs[S_txt:])
+        self._gemm(a, s, self.x_emb, out=x[S_txt:])
+
+        rope = b["rope"]
+        attn_o = cat[:, :d]                      # attention output lands in the first d columns of `cat`
+        q4 = qkv[:, :d].unflatten(1, (H, 128)).unsqueeze(0)
+        k4 = qkv[:, d:2 * d].unflatten(1, (H, 128)).unsqueeze(0)
+        v4 = qkv[:, 2 * d:].unflatten(1, (H, 128)).unsqueeze(0)
+        o4 = attn_o.unflatten(1, (H, 128)).unsqueeze(0)
+        off = 0
+        streams = ((slice(S_txt, S), "a", 0), (slice(0, S_txt), "b", 6 * d))
+        for blk in self.double:
+            m = mv[off:off + 12 * d]
+            off += 12 * d
+            for rows, s_, mo in streams:
+                sh_msa, sc_msa = m[mo:mo + d], m[mo + d:mo + 2 * d]
+                a, sc = self._ln(x[rows], sh_msa, sc_msa, xq_d[rows], rs[rows])
+                self._gemm(a, sc, blk["qkv_" + s_], out=qkv[rows])
+                ops.rmsnorm_rope_heads(qkv[rows], H, blk["nq_" + s_], blk["nk_" + s_], rope, rows.start)
+            ops.flash_attn(q4, k4, v4, out=o4)
+            for rows, s_, mo in streams:
+                g_msa = m[mo + 2 * d:mo + 3 * d]
+                sh_mlp, sc_mlp, g_mlp = m[mo + 3 * d:mo + 4 * d], m[mo + 4 * d:mo + 5 * d], m[mo + 5 * d:mo + 6 * d]
+                a, sc = self._quant(attn_o[rows], catq[rows, :d], rs[rows])
+                self._gemm(a, sc, blk["out_" + s_], gate=g_msa, resid=x[rows], out=x[rows])
+                a, sc = self._ln(x[rows], sh_mlp, sc_mlp, xq_d[rows], rs[rows])
+                hid = cat[rows, d:5 * d]
+                self._gemm(a, sc, blk["ff0_" + s_], act=ops.ACT_GELU_TANH, out=hid)
+                a, sc = self._quant(hid, catq[rows, d:5 * d], rs[rows])
+                self._gemm(a, sc, blk["ff2_" + s_], gate=g_mlp, resid=x[rows], out=x[rows])
+        for blk in self.single:
+            m = mv[off:off + 3 * d]
+            off += 3 * d
+            a, sc = self._ln(x, m[:d], m[d:2 * d], xq_d, rs)
+            self._gemm(a, sc, blk["qkv_mlp"], act=ops.ACT_GELU_TANH, act_col0=3 * d, out=qkv, out1=cat[:, d:],
+                       split_col=3 * d)
+            ops.rmsnorm_rope_heads(qkv, H, blk["nq"], blk["nk"], rope, 0)
+            ops.flash_attn(q4, k4, v4, out=o4)
+            a, sc = self._quant(cat, catq, rs)
+            self._gemm(a, sc, blk["proj"], gate=m[2 * d:3 * d], resid=x, out=x)
+        # final AdaLN (scale first, flux_dit.py:333) + projection on the image tokens
+        m = mv[off:off + 2 * d]
+        rows = slice(S_txt, S)
+        a, sc = self._ln(x[rows], m[d:2 * d], m[:d], xq_d[rows], rs[rows])
+        self._gemm(a, sc, self.final_proj, out=b["out_tok"])
+        return b["out_tok"]
+
+    def prepare(self, S_txt: int, height: int, width: int, txt_dim: int = 4096, pooled_dim: int = 768,
+                text_ids: Optional[torch.Tensor] = None, image_ids: Optional[torch.Tensor] = None):
+        """Allocate the step's buffers for one input geometry and build the RoPE table from the position ids
+        (zeros for text and (0,row,col) for image tokens unless given; flux_dit.py:376-390,417)."""
+        b = self._alloc(S_txt, height, width, txt_dim, pooled_dim)
+        if image_ids is None:
+            hh, ww = height // 2, width // 2
+            image_ids = torch.zeros(hh, ww, 3, device=self.dev)
+            image_ids[..., 1] += torch.arange(hh, device=self.dev)[:, None]
+            image_ids[..., 2] += torch.arange(ww, device=self.dev)[None, :]
+            image_ids = image_ids.reshape(-1, 3)
+        if text_ids is None:
+            text_ids = torch.zeros(S_txt, 3, device=self.dev)
+        ids = torch.cat([text_ids.reshape(-1, 3).float().to(self.dev), image_ids.reshape(-1, 3).float().to(self.dev)])
+        b["rope"] = flux_rope_table(ids)
+        return self
+
+    def set_inputs(self, latents, timestep, prompt_emb, pooled, guidance):
+        """Copy one step's inputs (host or device tensors) into the static input buffers."""
+        b = self._bufs
+        b["latents"].copy_(latents.reshape(b["latents"].shape), non_blocking=True)
+        b["prompt"].copy_(prompt_emb.reshape(b["prompt"].shape), non_blocking=True)
+        b["pooled"].copy_(pooled.reshape(-1), non_blocking=True)
+        b["tg"][0:1].copy_(timestep.reshape(1), non_blocking=True)
+        b["tg"][1:2].copy_(guidance.reshape(1).float() * 1000.0, non_blocking=True)  # flux_dit.py:413
+
+    def capture(self):
+        """Record the step into a CUDA graph (inputs must be set once before)."""
+        torch.cuda.synchronize(self.dev)
+        side = torch.cuda.Stream(self.dev)
+        with torch.cuda.stream(side):
+            self._run()
+        torch.cuda.synchronize(self.dev)
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, stream=side):
+            self._run()
+        self._graph = g
+        return self
+
+    def step(self):
+        """Run the DiT forward on the current inputs; returns the [1, C, h, w] model output (a view of a
+        static buffer)."""
+        if self._graph is not None:
+            self._graph.replay()
+        else:
+            self._run()
+        b = self._bufs
+        C = self.in_ch // 4
+        return (b["out_tok"].reshape(b["height"] // 2, b["width"] // 2, C, 2, 2).permute(2, 0, 3, 1, 4)
+                .reshape(1, C, b["height"], b["width"]))
+
+    def forward(self, hidden_states, timestep, prompt_emb, pooled_prompt_emb, guidance, text_ids=None,
+                image_ids=None, **kwargs):
+        """Signature of ``FluxDiT.forward`` (flux_dit.py:392-403), batch 1."""
+        S_txt = prompt_emb.shape[1]
+        height, width = hidden_states.shape[-2:]
+        b = self._bufs
+        if b is None or (b["S_txt"], b["height"], b["width"]) != (S_txt, height, width):
+            self.prepare(S_txt, height, width, prompt_emb.shape[-1], pooled_prompt_emb.shape[-1], text_ids, image_ids)
+        self.set_inputs(hidden_states, timestep, prompt_emb, pooled_prompt_emb, guidance)
+        return self.step().clone()
+
+    __call__ = forward
+
+    def kernel_launches_per_step(self) -> int:
+        """Launches of this library's kernels in one step (the count of the dataflow above)."""
+        per_stream = 3 + (2 if self.afmt != ops.FMT_BF16 else 0) + 4
+        dbl = 2 * per_stream + 1
+        sgl = 4 + (1 if self.afmt != ops.FMT_BF16 else 0) + 1
+        pre = 1 + (6 if self.use_guidance else 4) + 1 + 2 + (2 if self.afmt != ops.FMT_BF16 else 0)
+        return pre + self.n_double * dbl + self.n_single * sgl + 2

@@ -119,7 +119,7 @@ def quant_rows(x, out_fmt=FMT_E4M3, out=None, row_scale=None):
     return out, row_scale
 
 
-def gemv(W, x, w_scale=None, bias=None, act_in=ACT_NONE, act_out=ACT_NONE, out=None):
+def gemv(W, x, w_scale=None, bias=None, act_in=ACT_NONE, act_out=ACT_NONE, out=None, accumulate=False):
     """y = act_out((W @ act_in(x)) * w_scale + bias) for one fp32 activation row."""
     _require_cuda(W, x, w_scale, bias)
     N, K, ld_w = _rows(W)
@@ -127,8 +127,20 @@ def gemv(W, x, w_scale=None, bias=None, act_in=ACT_NONE, act_out=ACT_NONE, out=N
         out = torch.empty(N, dtype=torch.float32, device=x.device)
     stride = 0 if (w_scale is None or w_scale.numel() == 1) else 1
     rc = _lib.lib().dsb_gemv(_ptr(W), ld_w, _fmt_of(W), _ptr(x), _ptr(w_scale), stride, _ptr(bias), _ptr(out), N, K,
-                             act_in, act_out, _stream())
+                             act_in, act_out, 1 if accumulate else 0, _stream())
     check(rc, "dsb_gemv")
+    return out
+
+
+def timestep_embedding(t, dim=256, t_scale=1.0, mode=0, round_bf16=False, out=None):
+    """[n, dim] fp32 sinusoid of a device fp32 vector t (mode 0 Flux fp32 angles, 1 Wan fp64 angles)."""
+    _require_cuda(t)
+    n = t.numel()
+    if out is None:
+        out = torch.empty((n, dim), dtype=torch.float32, device=t.device)
+    rc = _lib.lib().dsb_timestep_embedding(_ptr(t), n, dim, float(t_scale), mode, 1 if round_bf16 else 0, _ptr(out),
+                                           _stream())
+    check(rc, "dsb_timestep_embedding")
     return out
 
 

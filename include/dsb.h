@@ -92,13 +92,24 @@ int dsb_quant_rows(const void* x, int64_t ld_x, void* y, int64_t ld_y, float* ro
 
 /*
  * y[n] = act_out((sum_k W[n,k] * act_in(x[k])) * w_scale[n*w_scale_stride] + bias[n]) for one activation row
- * (fp32 x, fp32 y).  W is [N, ld_w] in w_fmt.  act_in: 0 none, DSB_ACT_SILU; act_out: DSB_ACT_*.
+ * (fp32 x, fp32 y).  W is [N, ld_w] in w_fmt.  act_in: 0 none, DSB_ACT_SILU; act_out: DSB_ACT_*;
+ * accumulate != 0 adds the result to y instead of overwriting it.
  * Replaces the M=1 Linears: models/basic/transformer_helper.py:14,33 and models/flux/flux_dit.py:332
  * (SiLU -> Linear of the AdaLN layers), models/basic/timestep.py:73-81, models/flux/flux_dit.py:348-352,
  * models/wan/wan_dit.py:279-287,327-328.
  */
 int dsb_gemv(const void* W, int64_t ld_w, int w_fmt, const float* x, const float* w_scale, int w_scale_stride,
-             const float* bias, float* y, int N, int K, int act_in, int act_out, void* stream);
+             const float* bias, float* y, int N, int K, int act_in, int act_out, int accumulate, void* stream);
+
+/*
+ * Sinusoidal timestep embedding of n scalars t[r] * t_scale into out[n, dim] = [cos | sin] (fp32, optionally
+ * rounded to bf16 values as the reference casts to the model dtype).
+ *   mode 0: fp32 angles, freq_i = exp(-ln(10000) i / (dim/2))   models/basic/timestep.py:6-44 (flip_sin_to_cos,
+ *           downscale_freq_shift 0, as configured at :68-70)
+ *   mode 1: fp64 angles, freq_i = 10000^(-i / (dim/2))          models/wan/wan_dit.py:29-35
+ */
+int dsb_timestep_embedding(const float* t, int n, int dim, float t_scale, int mode, int round_bf16, float* out,
+                           void* stream);
 
 /*
  * out = cast(latents + model_out * dt), optionally after the inpaint blend

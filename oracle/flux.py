@@ -109,7 +109,7 @@ def image_ids(height, width):
 
 
 def flux_dit_forward(w, latents, timestep, prompt_emb, pooled, guidance, text_ids=None, n_double=19, n_single=38,
-                     H=24, lin: LinearEval = None, rt=_ident, use_guidance=True):
+                     H=24, lin: LinearEval = None, rt=_ident, use_guidance=True, return_hidden=False):
     """FluxDiT.forward, flux_dit.py:392-461, batch 1.  latents [1,C,h,w], timestep [1] (0..1000 units),
     prompt_emb [1,S_txt,4096], pooled [1,768], guidance [1]."""
     lin = lin or LinearEval("fp32")
@@ -132,10 +132,12 @@ def flux_dit_forward(w, latents, timestep, prompt_emb, pooled, guidance, text_id
     x = torch.cat([xb, xa], dim=0)
     for i in range(n_single):
         x = single_block(x, cond, table, w, f"single_blocks.{i}.", H, lin, rt)
+    hidden = x
     x = x[S_txt:]
     emb = lin(F.silu(cond)[None], w["final_norm_out.linear.weight"], w["final_norm_out.linear.bias"],
               act_quant=False)[0]
     scale, shift = emb.chunk(2)  # flux_dit.py:333: scale first
     x = O.ln_modulate(x, shift, scale)
     x = rt(lin(x, w["final_proj_out.weight"], w["final_proj_out.bias"]))
-    return unpatchify(x[None], height, width)
+    out = unpatchify(x[None], height, width)
+    return (out, hidden) if return_hidden else out

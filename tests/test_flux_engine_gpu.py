@@ -1,0 +1,92 @@
+"""The Flux step engine against the CPU oracle on seeded weights and inputs (reduced width and depth so the
+oracle finishes in seconds; same code path as the full model)."""
+import pytest
+import torch
+
+from oracle import flux as OF
+from oracle import ops as O
+from oracle.linear import LinearEval
+
+pytestmark = pytest.mark.gpu
+synth = __import__("importlib").import_module("diffsynth_engine_b200.synth")
+
+
+def _case(d, H, n_double, n_single, S_txt, hw, seed=0, txt_dim=512, pooled_dim=96):
+    shapes = synth.flux_dit_shapes(d=d, H=H, n_double=n_double, n_single=n_single, txt_dim=txt_dim,
+                                   pooled_dim=pooled_dim)
+    w = synth.make_state_dict(shapes, seed=seed)
+    # weights as a bf16 checkpoint holds them
+    w = {k: v.bfloat16().float() for k, v in w.items()}
+    lat = synth.randn((1, 16, hw, hw), seed + 1).bfloat16().float()
+    pe = synth.randn((1, S_txt, txt_dim), seed + 2).bfloat16().float()
+    pooled = synth.randn((1, pooled_dim), seed + 3)
+    return w, lat, pe, pooled, torch.tensor([500.0]), torch.tensor([3.5])
+
+
+def _engine_out(dsb, dev, w, fmt, args, n_double, n_single, H, graph=False):
+    from diffsynth_engine_b200.flux import FluxDiTEngine
+    lat, pe, pooled, t, g = args
+    eng = FluxDiTEngine(dict(w), fmt=fmt, device=dev, n_double=n_double, n_single=n_single, num_heads=H)
+    eng.prepare(pe.shape[1], lat.shape[2], lat.shape[3], pe.shape[2], pooled.shape[1])
+    eng.set_inputs(lat.to(dev), t.to(dev), pe.to(dev), pooled.to(dev), g.to(dev))
+    if graph:
+        eng.capture()
+    out = eng.step().float().cpu()
+    hidden = eng._bufs["x"].float().cpu()
+    dsb.ops.check_status(0)
+    return out, hidden, eng
+
+
+@pytest.mark.parametrize("fmt,mode", [("fp8_tensor", "fp8_tensor"), ("fp8_channel", "fp8_channel"),
+                                      ("int8_channel", "int8_channel"), ("bf16", "bf16")])
+def test_one_double_block_output(dsb, cuda_dev, fmt, mode):
+    """Block output (hidden state after one double-stream block) against the same-quantisation oracle:
+    rel-L2 <= 1e-2 for FP8/INT8 and <= 2e-3 for BF16 (the stated tolerances)."""
+    d, H = 256, 2
+    w, lat, pe, pooled, t, g = _case(d, H, 1, 0, 32, 16)
+    _, hid_ref = OF.flux_dit_forward(w, lat, t, pe, pooled, g, n_double=1, n_single=0, H=H, lin=LinearEval(mode),
+                                     rt=OF.round_bf16, return_hidden=True)
+    _, hid, _ = _engine_out(dsb, cuda_dev, w, fmt, (lat, pe, pooled, t, g), 1, 0, H)
+    err = O.rel_l2(hid, hid_ref)
+    print(f"double block {fmt}: rel-L2 vs same-quantisation oracle {err:.3e}")
+    assert err < (2e-3 if fmt == "bf16" else 1e-2)
+
+
+@pytest.mark.parametrize("fmt", ["fp8_tensor", "bf16"])
+def test_one_single_block_output(dsb, cuda_dev, fmt):
+    d, H = 256, 2
+    w, lat, pe, pooled, t, g = _case(d, H, 0, 1, 32, 16, seed=10)
+    _, hid_ref = OF.flux_dit_forward(w, lat, t, pe, pooled, g, n_double=0, n_single=1, H=H, lin=LinearEval(fmt),
+                                     rt=OF.round_bf16, return_hidden=True)
+    _, hid, _ = _engine_out(dsb, cuda_dev, w, fmt, (lat, pe, pooled, t, g), 0, 1, H)
+    err = O.rel_l2(hid, hid_ref)
+    print(f"single block {fmt}: rel-L2 {err:.3e}")
+    assert err < (2e-3 if fmt == "bf16" else 1e-2)
+
+
+@pytest.mark.parametrize("fmt", ["fp8_tensor", "bf16"])
+def test_small_model_end_to_end(dsb, cuda_dev, fmt):
+    """2 double + 3 single blocks, text 40 tokens (not a tile multiple), 24x16 latents: full forward, eager and
+    graph-replayed, against the oracle; also reports the distance to exact fp32 math."""
+    d, H, nd, ns = 512, 4, 2, 3
+    shapes = synth.flux_dit_shapes(d=d, H=H, n_double=nd, n_single=ns, txt_dim=256, pooled_dim=64)
+    w = {k: v.bfloat16().float() for k, v in synth.make_state_dict(shapes, seed=3).items()}
+    lat = synth.randn((1, 16, 24, 16), 4).bfloat16().float()
+    pe, pooled = synth.randn((1, 40, 256), 5).bfloat16().float(), synth.randn((1, 64), 6)
+    t, g = torch.tensor([731.0]), torch.tensor([3.5])
+    ref_q = OF.flux_dit_forward(w, lat, t, pe, pooled, g, n_double=nd, n_single=ns, H=H, lin=LinearEval(fmt),
+                                rt=OF.round_bf16)
+    ref_exact = OF.flux_dit_forward(w, lat, t, pe, pooled, g, n_double=nd, n_single=ns, H=H)
+    from diffsynth_engine_b200.flux import FluxDiTEngine
+    eng = FluxDiTEngine(dict(w), fmt=fmt, device=cuda_dev, n_double=nd, n_single=ns, num_heads=H)
+    out = eng(lat.to(cuda_dev), t.to(cuda_dev), pe.to(cuda_dev), pooled.to(cuda_dev), g.to(cuda_dev)).float().cpu()
+    err_q, err_x = O.rel_l2(out, ref_q), O.rel_l2(out, ref_exact)
+    print(f"small model {fmt}: vs same-quantisation oracle {err_q:.3e}, vs exact fp32 {err_x:.3e}")
+    assert err_q < (6e-3 if fmt == "bf16" else 2e-2)
+    eng.capture()
+    out_g = eng.step().float().cpu()
+    assert torch.equal(out_g, out)          # graph replay is bit-identical to the eager launch sequence
+    n0 = dsb._lib.launches
+    eng._graph = None
+    eng.step()
+    assert dsb._lib.launches - n0 == eng.kernel_launches_per_step()
