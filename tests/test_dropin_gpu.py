@@ -1,0 +1,111 @@
+"""The drop-in seams on the GPU: patched ``F.linear`` with ``QuantLinearWeight`` parameters, and the attention
+functions installed where the reference dispatches (same call shapes as models/flux/flux_dit.py:166-183,297-304 and
+models/wan/wan_dit.py:18-22)."""
+import pytest
+import torch
+import torch.nn as nn
+import torch.nn.functional as F
+
+from oracle import ops as O
+from oracle.linear import LinearEval
+
+pytestmark = pytest.mark.gpu
+synth = __import__("importlib").import_module("diffsynth_engine_b200.synth")
+
+
+class FF(nn.Module):  # the shape of FluxJointTransformerBlock.ff_a (flux_dit.py:208-210)
+    def __init__(self, d):
+        super().__init__()
+        self.net = nn.Sequential(nn.Linear(d, 4 * d), nn.GELU(approximate="tanh"), nn.Linear(4 * d, d))
+
+    def forward(self, x):
+        return self.net(x)
+
+
+@pytest.mark.parametrize("fmt", ["fp8_tensor", "fp8_channel", "int8_channel", "bf16"])
+def test_patched_linear_module(dsb, cuda_dev, fmt):
+    from diffsynth_engine_b200.quant import QuantLinearWeight, b200_inference, enable_b200_linear
+    d = 256
+    ff = FF(d)
+    with torch.no_grad():
+        for i, p in enumerate(ff.parameters()):
+            p.copy_(synth.randn(tuple(p.shape), 40 + i) * (0.05 if p.dim() == 2 else 0.1))
+    x = synth.randn((2, 75, d), 50).bfloat16()
+    w = {k: v.detach().clone().bfloat16().float() for k, v in ff.state_dict().items()}
+    lin = LinearEval(fmt)
+    h = O.gelu_tanh(lin(x.reshape(-1, d).float(), w["net.0.weight"], w["net.0.bias"])).bfloat16().float()
+    ref = lin(h, w["net.2.weight"], w["net.2.bias"]).reshape(2, 75, d)
+    ff = ff.to(cuda_dev, torch.bfloat16)
+    enable_b200_linear(ff, fmt)
+    assert ff.b200_linear_enabled and isinstance(ff.net[0].weight, QuantLinearWeight)
+    origin = F.linear
+    with torch.no_grad(), b200_inference():
+        assert F.linear is not origin
+        y = ff(x.to(cuda_dev))
+    assert F.linear is origin
+    assert y.dtype == torch.bfloat16 and y.shape == (2, 75, d)
+    assert O.rel_l2(y.float().cpu(), ref) < (4e-3 if fmt == "bf16" else 1e-2)
+    # M=1 conditioning vector goes through the GEMV path
+    v = synth.randn((1, d), 51).bfloat16()
+    with torch.no_grad(), b200_inference():
+        y1 = ff.net[0](v.to(cuda_dev))
+    ref1 = lin(v.float(), w["net.0.weight"], w["net.0.bias"], act_quant=False)
+    assert O.rel_l2(y1.float().cpu(), ref1) < 5e-3
+
+
+def test_patched_linear_restores_on_error_and_falls_through(dsb, cuda_dev):
+    from diffsynth_engine_b200.quant import b200_inference
+    origin = F.linear
+    plain = nn.Linear(64, 32).to(cuda_dev, torch.bfloat16)
+    x = torch.randn(5, 64, device=cuda_dev, dtype=torch.bfloat16)
+    with pytest.raises(RuntimeError, match="boom"):
+        with b200_inference():
+            y = plain(x)          # not a QuantLinearWeight: original F.linear
+            assert torch.equal(y, origin(x, plain.weight, plain.bias))
+            raise RuntimeError("boom")
+    assert F.linear is origin
+    with b200_inference(False):
+        assert F.linear is origin
+
+
+def test_b200_attn_flux_call_shapes(dsb, cuda_dev):
+    """q, k contiguous [B,H,S,D]; v a strided view of the fused [B,S,7d] projection (flux_dit.py:297-312)."""
+    from diffsynth_engine_b200.attention import b200_attn
+    B, H, S, D = 1, 4, 333, 128
+    d = H * D
+    fused = synth.randn((B, S, 7 * d), 60).bfloat16()
+    qkv = fused[:, :, :3 * d].view(B, S, 3 * H, D).transpose(1, 2)
+    q, k, v = qkv.chunk(3, dim=1)
+    ref = O.attention(q, k, v)
+    fd = fused.to(cuda_dev)
+    qd, kd, vd = fd[:, :, :3 * d].view(B, S, 3 * H, D).transpose(1, 2).chunk(3, dim=1)
+    out = b200_attn(qd.contiguous(), kd.contiguous(), vd)
+    assert out.shape == (B, H, S, D)
+    flat = out.transpose(1, 2).reshape(B, S, d)      # what the caller does next (flux_dit.py:304)
+    assert flat.data_ptr() == out.data_ptr()         # ... and it is a view, not a copy
+    assert O.rel_l2(flat.float().cpu(), ref.transpose(1, 2).reshape(B, S, d)) < 4e-3
+    with pytest.raises(dsb.DsbError):
+        b200_attn(q, k, v)  # CPU tensors: no fallback
+
+
+def test_b200_wan_attention_call_shapes(dsb, cuda_dev):
+    from diffsynth_engine_b200.attention import b200_wan_attention
+    B, S, L, H = 1, 420, 77, 5
+    q, k, v = (synth.randn((B, n, H * 128), 70 + i).bfloat16() for i, n in enumerate((S, L, L)))
+    mh = lambda t: t.unflatten(2, (H, 128)).transpose(1, 2)
+    ref = O.attention(mh(q), mh(k), mh(v)).transpose(1, 2).flatten(2)
+    out = b200_wan_attention(q.to(cuda_dev), k.to(cuda_dev), v.to(cuda_dev), num_heads=H)
+    assert out.shape == (B, S, H * 128)
+    assert O.rel_l2(out.float().cpu(), ref) < 4e-3
+
+
+def test_set_attn_implementation_names(dsb):
+    import types
+    from diffsynth_engine_b200 import attention as A
+    fake_flux, fake_wan = types.SimpleNamespace(_attn_func=None), types.SimpleNamespace(attention=lambda *a: None)
+    with pytest.raises(ValueError):
+        A.set_attn_implementation("flash9", fake_flux)
+    A.set_attn_implementation("b200", fake_flux, fake_wan)
+    assert fake_flux._attn_func is A.b200_attn and fake_wan.attention is A.b200_wan_attention
+    A.set_attn_implementation("sdpa", fake_flux, fake_wan)
+    assert fake_flux._attn_func is F.scaled_dot_product_attention and fake_wan.attention is not A.b200_wan_attention
