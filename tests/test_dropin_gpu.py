@@ -33,7 +33,9 @@ def test_patched_linear_module(dsb, cuda_dev, fmt):
     x = synth.randn((2, 75, d), 50).bfloat16()
     w = {k: v.detach().clone().bfloat16().float() for k, v in ff.state_dict().items()}
     lin = LinearEval(fmt)
-    h = O.gelu_tanh(lin(x.reshape(-1, d).float(), w["net.0.weight"], w["net.0.bias"])).bfloat16().float()
+    # the module rounds the first Linear's output to bf16, then nn.GELU rounds again
+    h = lin(x.reshape(-1, d).float(), w["net.0.weight"], w["net.0.bias"]).bfloat16().float()
+    h = O.gelu_tanh(h).bfloat16().float()
     ref = lin(h, w["net.2.weight"], w["net.2.bias"]).reshape(2, 75, d)
     ff = ff.to(cuda_dev, torch.bfloat16)
     enable_b200_linear(ff, fmt)
