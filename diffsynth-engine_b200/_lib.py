@@ -8,7 +8,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(HERE, "libdsb.so")
 HEADER = os.path.join(os.path.dirname(HERE), "include", "dsb.h")
 
-OK, ERR_ARG, ERR_CUDA, ERR_TIMEOUT, ERR_UNSUPPORTED = 0, -1, -2, -3, -4
+OK, ERR_ARG, ERR_CUDA, ERR_TIMEOUT, ERR_UNSUPPORTED, ERR_TOO_LARGE = 0, -1, -2, -3, -4, -5
 FMT_BF16, FMT_E4M3, FMT_INT8 = 0, 1, 2
 ACT_NONE, ACT_GELU_TANH, ACT_SILU = 0, 1, 2
 
@@ -17,6 +17,8 @@ _ERR_NAMES = {
     ERR_CUDA: "DSB_ERR_CUDA (a CUDA call failed)",
     ERR_TIMEOUT: "DSB_ERR_TIMEOUT (a bounded device wait ran out)",
     ERR_UNSUPPORTED: "DSB_ERR_UNSUPPORTED (shape outside what the kernel supports)",
+    ERR_TOO_LARGE: "DSB_ERR_TOO_LARGE (the problem does not fit the fixed scratch of a *_static entry point: "
+                   "M*K <= 64 Mi elements and M <= 65536)",
 }
 
 c_i, c_i64, c_f, c_p = ctypes.c_int, ctypes.c_int64, ctypes.c_float, ctypes.c_void_p
@@ -36,6 +38,7 @@ _SIGS = {
                  c_i64, c_p, c_i64, c_i, c_p, c_p],
     "dsb_flash_attn": [c_p, c_p, c_p, c_p, c_i, c_i, c_i, c_i, c_i] + [c_i64] * 12 + [c_f, c_p, c_p],
     "dsb_pack_quant_weight": [c_p, c_i64, c_i, c_p, c_i64, c_p, c_i, c_i, c_i, c_i, c_p, c_p],
+    "dsb_linear_static": [c_p, c_i64, c_p, c_i64, c_i, c_i, c_i, c_i, c_p, c_i, c_p, c_i, c_p, c_i64, c_p, c_p],
 }
 
 _lib = None

@@ -12,7 +12,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 INCLUDE = os.path.join(os.path.dirname(HERE), "include")
 LIB = os.path.join(HERE, "libdsb.so")
-SOURCES = ["host.cu", "elementwise.cu", "gemm.cu", "attention.cu"]
+SOURCES = ["host.cu", "elementwise.cu", "gemm.cu", "attention.cu", "linear_static.cu"]
 
 
 def _nvcc() -> str:

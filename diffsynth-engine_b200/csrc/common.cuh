@@ -22,7 +22,8 @@ enum : int {
   DSB_ERR_ARG = -1,        // bad pointer, size, alignment or flag combination
   DSB_ERR_CUDA = -2,       // a CUDA runtime/driver call failed
   DSB_ERR_TIMEOUT = -3,    // a bounded device wait ran out
-  DSB_ERR_UNSUPPORTED = -4 // shape outside what the kernel was built for
+  DSB_ERR_UNSUPPORTED = -4, // shape outside what the kernel was built for
+  DSB_ERR_TOO_LARGE_ = -5   // mirrors DSB_ERR_TOO_LARGE of dsb.h
 };
 
 constexpr long long kWaitLimitCycles = 2000000000LL;  // about one second of SM clocks

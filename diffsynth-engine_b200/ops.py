@@ -211,3 +211,23 @@ def pack_quant_weight(W, fmt=FMT_E4M3, per_channel=False):
                                           _ptr(scales), N, K, fmt, 1 if per_channel else 0, _ptr(work), _stream())
     check(rc, "dsb_pack_quant_weight")
     return payload, scales
+
+
+def linear_static(x, w_payload, w_scale, bias=None, act=ACT_NONE, out=None):
+    """``dsb_linear_static``: quantise the bf16 rows of ``x`` and multiply by the prepacked ``w_payload`` without
+    any caller-provided scratch - the intermediates live in a fixed array inside the library (see
+    include/dsb.h for who needs that, the size limit and the sharing rules).  Only the output is allocated here,
+    and not at all when ``out`` is given."""
+    _require_cuda(x, w_payload, w_scale, bias, out)
+    M, K, ld_x = _rows(x)
+    N, Kw, ld_w = _rows(w_payload)
+    if K != Kw:
+        raise _lib.DsbError("linear_static operands disagree in K")
+    if out is None:
+        out = torch.empty((M, N), dtype=torch.bfloat16, device=x.device)
+    stride = 0 if w_scale.numel() == 1 else 1
+    rc = _lib.lib().dsb_linear_static(_ptr(x), ld_x, _ptr(w_payload), ld_w, _fmt_of(w_payload), M, N, K,
+                                      _ptr(w_scale), stride, _ptr(bias), act, _ptr(out), out.stride(0),
+                                      _ptr(status_word(x.device)), _stream())
+    check(rc, "dsb_linear_static")
+    return out

@@ -33,6 +33,7 @@ extern "C" {
 #define DSB_ERR_CUDA (-2)
 #define DSB_ERR_TIMEOUT (-3)
 #define DSB_ERR_UNSUPPORTED (-4)
+#define DSB_ERR_TOO_LARGE (-5) /* problem exceeds the fixed scratch of a *_static entry point */
 
 /* element formats */
 #define DSB_FMT_BF16 0
@@ -162,6 +163,22 @@ int dsb_flash_attn(const void* q, const void* k, const void* v, void* o, int B, 
  */
 int dsb_pack_quant_weight(const void* W, int64_t ld_w, int src_is_bf16, void* Wq, int64_t ld_q, float* scales, int N,
                           int K, int fmt, int per_channel, float* work, void* stream);
+
+/*
+ * Quantised Linear that allocates nothing: out = act((quantise_rows(x) . Wq^T) * row_scale * w_scale + bias),
+ * i.e. dsb_quant_rows followed by dsb_gemm, with the 8-bit activation copy and the row scales kept in a
+ * fixed __device__ array inside the library instead of caller-provided scratch.  For callers that cannot
+ * allocate device memory (a plugin inside another runtime's fixed memory plan, an FFI binding that only passes
+ * the tensors it was given).  This entry point has no counterpart in the reference.
+ *   x: bf16 [M, ld_x]; Wq: [N, ld_w] in w_fmt (E4M3 or INT8); w_scale: 1 or N floats (w_scale_stride 0 or 1);
+ *   bias fp32 [N] or NULL; act = DSB_ACT_*; out: bf16 [M, ld_out].  K must be a multiple of 16.
+ * Limits: M*K <= 64 Mi elements and M <= 65536, else DSB_ERR_TOO_LARGE.  The array (64.25 MiB) is resident on
+ * every GPU that loads the library.  All calls share it: calls that overlap on the GPU race, so serialise them.
+ * The first call on each device looks up the array's device address; make that call outside stream capture.
+ */
+int dsb_linear_static(const void* x, int64_t ld_x, const void* Wq, int64_t ld_w, int w_fmt, int M, int N, int K,
+                      const float* w_scale, int w_scale_stride, const float* bias, int act, void* out,
+                      int64_t ld_out, int* status, void* stream);
 
 #ifdef __cplusplus
 }
