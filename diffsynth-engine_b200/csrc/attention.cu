@@ -31,6 +31,8 @@ constexpr int kNQ = 2;
 constexpr int kKVStages = 2;
 constexpr int kTileBytes = 128 * 128 * 2;  // 32 KiB: one 128 x 128 bf16 tile as two 64-column halves
 constexpr int kHalfBytes = kTileBytes / 2;
+constexpr int kCtrlRegs = 72;      // registers per thread kept by the control warps
+constexpr int kSoftmaxRegs = 208;  // registers per thread of the softmax warps
 constexpr int kAttnSmem = (kNQ + 2 * kKVStages) * kTileBytes + 256 + 1024;
 
 struct AttnParams {
@@ -42,6 +44,15 @@ struct AttnParams {
   int q_pos[3], k_pos[3], v_pos[3];
   int* status;
 };
+
+template <int N>
+__device__ __forceinline__ void reg_alloc() {
+  asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(N));
+}
+template <int N>
+__device__ __forceinline__ void reg_dealloc() {
+  asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(N));
+}
 
 __device__ __forceinline__ void load_tile(uint8_t* dst, const CUtensorMap* m, uint64_t* bar, const int (&pos)[3], int s0,
                                           int h, int b) {
@@ -110,6 +121,12 @@ __global__ void __launch_bounds__(kAttnThreads, 1)
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
+  // Registers move from the four control warps (TMA, MMA, two idle) to the softmax warps, which hold a whole
+  // 128-wide score row per thread.  The kernel launches with 168 registers per thread (384 threads); the 128
+  // control threads give back 168-72 = 96 each (12288), the 256 softmax threads take 208-168 = 40 each (10240).
+  // The increase must never ask for more than was released: setmaxnreg.inc blocks until it is satisfied.
+  static_assert((168 - kCtrlRegs) * 128 >= (kSoftmaxRegs - 168) * 256, "setmaxnreg.inc could never be satisfied");
+  if (warp < 4) reg_dealloc<kCtrlRegs>();
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer
     if (lane == 0) {
@@ -193,6 +210,7 @@ __global__ void __launch_bounds__(kAttnThreads, 1)
   mma_done:;
   } else if (warp >= 4) {
     // ----------------------------------------------------------------- softmax
+    reg_alloc<kSoftmaxRegs>();
     const int q = (warp - 4) >> 2;
     const int quad = warp & 3;
     const int row = quad * 32 + lane;
@@ -209,23 +227,24 @@ __global__ void __launch_bounds__(kAttnThreads, 1)
       }
       tc_fence_after();
       const int valid = min(kTileKV, p.Sk - j * kTileKV);
-      uint32_t r[32];
-      // pass 1: row maximum
-      float mx = -INFINITY;
-#pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
-        tmem_ld32(t_s + c * 32, r);
-        tc_wait_ld();
-        if (valid == kTileKV) {
+      // the whole score row (128 fp32) in registers: four loads in flight, one wait
+      uint32_t s[128];
 #pragma unroll
-          for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(r[i]));
-        } else {
+      for (int c = 0; c < 4; ++c) tmem_ld32(t_s + c * 32, reinterpret_cast<uint32_t(&)[32]>(s[c * 32]));
+      tc_wait_ld();
+      if (valid != kTileKV) {
 #pragma unroll
-          for (int i = 0; i < 32; ++i)
-            if (c * 32 + i < valid) mx = fmaxf(mx, __uint_as_float(r[i]));
-        }
+        for (int i = 0; i < 128; ++i)
+          if (i >= valid) s[i] = 0xff800000u;  // -inf: masked keys of the last tile
       }
-      const float m_new = mx * cs;
+      float mx[8];
+#pragma unroll
+      for (int a = 0; a < 8; ++a) mx[a] = __uint_as_float(s[a]);
+#pragma unroll
+      for (int i = 8; i < 128; ++i) mx[i & 7] = fmaxf(mx[i & 7], __uint_as_float(s[i]));
+      const float mrow = fmaxf(fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])),
+                               fmaxf(fmaxf(mx[4], mx[5]), fmaxf(mx[6], mx[7])));
+      const float m_new = mrow * cs;
       if (j == 0) {
         m = m_new;
       } else if (__any_sync(0xffffffffu, m_new > m + 8.0f)) {
@@ -235,34 +254,29 @@ __global__ void __launch_bounds__(kAttnThreads, 1)
         l *= alpha;
 #pragma unroll 1
         for (int c = 0; c < 4; ++c) {
+          uint32_t r[32];
           tmem_ld32(t_o + c * 32, r);
           tc_wait_ld();
 #pragma unroll
           for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
           tmem_st32(t_o + c * 32, r);
         }
-        tc_wait_st();
       }
-      // pass 2: probabilities, written over S as packed bf16 (P chunk c covers columns [16c, 16c+16),
-      // which lie inside S chunks already read)
-#pragma unroll 1
+      // probabilities, written over S as packed bf16 (64 columns)
+      float ls[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
       for (int c = 0; c < 4; ++c) {
-        tmem_ld32(t_s + c * 32, r);
-        tc_wait_ld();
         uint32_t pk[16];
 #pragma unroll
         for (int i = 0; i < 16; ++i) {
-          float p0 = fast_exp2(fmaf(__uint_as_float(r[2 * i]), cs, -m));
-          float p1 = fast_exp2(fmaf(__uint_as_float(r[2 * i + 1]), cs, -m));
-          if (valid != kTileKV) {
-            if (c * 32 + 2 * i >= valid) p0 = 0.f;
-            if (c * 32 + 2 * i + 1 >= valid) p1 = 0.f;
-          }
-          l += p0 + p1;
+          const float p0 = fast_exp2(fmaf(__uint_as_float(s[c * 32 + 2 * i]), cs, -m));
+          const float p1 = fast_exp2(fmaf(__uint_as_float(s[c * 32 + 2 * i + 1]), cs, -m));
+          ls[i & 3] += p0 + p1;
           pk[i] = pack_bf16x2(p0, p1);
         }
         tmem_st16(t_s + c * 16, pk);
       }
+      l += (ls[0] + ls[1]) + (ls[2] + ls[3]);
       tc_wait_st();
       tc_fence_before();
       mbar_arrive(&p_full[q]);

@@ -7,7 +7,10 @@
 // K-slab per stage), warp 1 issues tcgen05.mma (M=128, N=BLOCK_N, 32 bytes of K
 // per instruction) into one of two TMEM accumulators, and warps 2..5 drain the
 // other accumulator with tcgen05.ld, apply the fused epilogue (dequant scales,
-// bias, GELU-tanh, gate-residual, output routing) and store bf16 rows.
+// bias, GELU-tanh, gate-residual, output routing) and hand bf16 tiles of
+// 32 rows x 64 columns to TMA stores through a swizzled staging buffer, so every
+// global write (and every residual read, a TMA load into the same buffer) moves
+// whole 128-byte lines instead of 16 bytes per row.
 //
 // HBM layout: A and W are row-major with K contiguous, so both operands are
 // "K-major" for the tensor core and no transpose or repack is ever needed; the
@@ -31,15 +34,14 @@ struct GemmEpilogue {
   int act;
   int act_col0;
   const float* gate;
-  const __nv_bfloat16* resid;
-  int64_t ld_resid;
-  __nv_bfloat16* out0;
-  int64_t ld_out0;
-  __nv_bfloat16* out1;
-  int64_t ld_out1;
+  int has_resid;
   int split_col;
   int* status;
 };
+
+constexpr int kEpiWarps = 4;
+constexpr int kStageSlotBytes = 32 * 128;  // 32 rows x 64 bf16
+constexpr int kStageBytes = kEpiWarps * 2 * kStageSlotBytes;
 
 template <int BLOCK_N>
 struct GemmSmem {
@@ -48,13 +50,14 @@ struct GemmSmem {
   static constexpr int kStage = kStageA + kStageB;
   static constexpr int kStages = (BLOCK_N == 256) ? 4 : 6;
   static constexpr int kBarBytes = 256;
-  static constexpr int kTotal = kStages * kStage + kBarBytes + 1024;  // + alignment slack
+  static constexpr int kTotal = kStages * kStage + kStageBytes + kBarBytes + 1024;  // + alignment slack
 };
 
 template <int KIND, int BLOCK_N>
 __global__ void __launch_bounds__(kGemmThreads, 1)
-    gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b, int M, int N,
-                int K, GemmEpilogue ep) {
+    gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                const __grid_constant__ CUtensorMap tmap_o0, const __grid_constant__ CUtensorMap tmap_o1,
+                const __grid_constant__ CUtensorMap tmap_r, int M, int N, int K, GemmEpilogue ep) {
   using SM = GemmSmem<BLOCK_N>;
   constexpr int kStages = SM::kStages;
   constexpr int kElemBytes = (KIND == KIND_F16) ? 2 : 1;
@@ -68,12 +71,14 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
   extern __shared__ uint8_t smem_raw[];
   // 1024-byte alignment: the 128-byte swizzle pattern repeats every 8 rows = 1024 bytes.
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint8_t* bar_base = smem + kStages * SM::kStage;
+  uint8_t* stage_base = smem + kStages * SM::kStage;  // 1024-aligned: stages are multiples of 16 KiB
+  uint8_t* bar_base = stage_base + kStageBytes;
   uint64_t* full_bar = reinterpret_cast<uint64_t*>(bar_base);
   uint64_t* empty_bar = full_bar + kStages;
   uint64_t* tmem_full = empty_bar + kStages;
   uint64_t* tmem_empty = tmem_full + 2;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tmem_empty + 2);
+  uint64_t* resid_bar = tmem_empty + 2;  // kEpiWarps x 2
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(resid_bar + kEpiWarps * 2);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5;
@@ -88,12 +93,14 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
       mbar_init(&tmem_full[a], 1);
       mbar_init(&tmem_empty[a], 128);
     }
+    for (int i = 0; i < kEpiWarps * 2; ++i) mbar_init(&resid_bar[i], 1);
     *abort_flag = 0;
     fence_mbar_init();
   }
   if (warp == 0 && lane == 0) {
     tma_prefetch_desc(&tmap_a);
     tma_prefetch_desc(&tmap_b);
+    tma_prefetch_desc(&tmap_o0);
   }
   if (warp == 1) {
     tmem_alloc(tmem_slot, kTmemCols);
@@ -168,6 +175,12 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
   } else {
     // ---------------------------------------------------------------- epilogue
     const int quad = warp & 3;  // TMEM lane quadrant this warp may read
+    const int ew = warp - 2;
+    uint8_t* stg = stage_base + ew * (2 * kStageSlotBytes);
+    uint64_t* rbar = resid_bar + ew * 2;
+    uint32_t rphase = 0, slot_ctr = 0;
+    const uint32_t row_off = static_cast<uint32_t>(lane) * 128u;
+    const uint32_t sw = static_cast<uint32_t>(lane & 7);
     int it = 0;
     for (int t = blockIdx.x; t < num_tiles; t += gridDim.x, ++it) {
       const int acc = it & 1;
@@ -176,38 +189,54 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
       const int n0 = (t / tiles_m) * BLOCK_N;
       if (!mbar_wait(&tmem_full[acc], acc_phase, abort_flag)) break;
       tc_fence_after();
-      const int m = m0 + quad * 32 + lane;
-      const bool row_ok = m < M;
-      const float rs = (ep.row_scale && row_ok) ? ep.row_scale[m] : 1.0f;
-      __nv_bfloat16* out;
-      int64_t ld_out;
-      int col_shift;
-      if (n0 >= ep.split_col) {
-        out = ep.out1, ld_out = ep.ld_out1, col_shift = ep.split_col;
-      } else {
-        out = ep.out0, ld_out = ep.ld_out0, col_shift = 0;
-      }
+      const int r0 = m0 + quad * 32;
+      const int m = r0 + lane;
+      const float rs = (ep.row_scale && m < M) ? ep.row_scale[m] : 1.0f;
+      const bool second = n0 >= ep.split_col;
+      const CUtensorMap* tmap_out = second ? &tmap_o1 : &tmap_o0;
+      const int col_shift = second ? ep.split_col : 0;
       const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + acc * BLOCK_N;
+      bool alive = true;
 #pragma unroll 1
-      for (int c = 0; c < BLOCK_N / 32; ++c) {
-        const int nc = n0 + c * 32;
-        if (nc >= N) break;  // uniform across the CTA
-        uint32_t r[32];
-        tmem_ld32(t_row + c * 32, r);
-        tc_wait_ld();
-        if (row_ok) {
+      for (int cb = 0; cb < BLOCK_N / 64 && alive; ++cb) {
+        const int nb = n0 + cb * 64;
+        if (nb >= N) break;  // uniform across the CTA
+        const uint32_t slot = slot_ctr & 1;
+        ++slot_ctr;
+        uint8_t* sbuf = stg + slot * kStageSlotBytes;
+        // the store that last used this slot (two blocks ago) must have read it out
+        if (lane == 0) bulk_wait_read<1>();
+        __syncwarp();
+        if (ep.has_resid) {
+          if (lane == 0) {
+            mbar_expect_tx(&rbar[slot], kStageSlotBytes);
+            tma_load_2d(sbuf, &tmap_r, &rbar[slot], nb, r0);
+          }
+          if (!mbar_wait(&rbar[slot], (rphase >> slot) & 1, abort_flag)) {
+            alive = false;
+            break;
+          }
+          rphase ^= 1u << slot;
+        }
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          const int nc = nb + h * 32;
+          uint32_t r[32];
+          tmem_ld32(t_row + cb * 64 + h * 32, r);
+          tc_wait_ld();
 #pragma unroll
           for (int g = 0; g < 4; ++g) {
             const int n = nc + g * 8;
-            if (n < N) {
-              float v[8];
+            uint8_t* cell = sbuf + row_off + (((static_cast<uint32_t>(h * 4 + g)) ^ sw) << 4);
+            float v[8];
 #pragma unroll
-              for (int j = 0; j < 8; ++j) {
-                if constexpr (KIND == KIND_I8)
-                  v[j] = static_cast<float>(static_cast<int>(r[g * 8 + j]));
-                else
-                  v[j] = __uint_as_float(r[g * 8 + j]);
-              }
+            for (int j = 0; j < 8; ++j) {
+              if constexpr (KIND == KIND_I8)
+                v[j] = static_cast<float>(static_cast<int>(r[g * 8 + j]));
+              else
+                v[j] = __uint_as_float(r[g * 8 + j]);
+            }
+            if (n < N) {
               if (ep.col_scale) {
                 if (ep.col_scale_stride) {
                   const float4 c0 = __ldg(reinterpret_cast<const float4*>(ep.col_scale + n));
@@ -238,8 +267,8 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
                   for (int j = 0; j < 8; ++j) v[j] = silu(v[j]);
                 }
               }
-              if (ep.resid) {
-                const uint4 rr = *reinterpret_cast<const uint4*>(ep.resid + static_cast<int64_t>(m) * ep.ld_resid + n);
+              if (ep.has_resid) {
+                const uint4 rr = *reinterpret_cast<const uint4*>(cell);
                 const uint32_t ru[4] = {rr.x, rr.y, rr.z, rr.w};
                 float gte[8];
                 if (ep.gate) {
@@ -258,19 +287,27 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
                   v[2 * j + 1] = f.y + gte[2 * j + 1] * v[2 * j + 1];
                 }
               }
-              uint4 o;
-              o.x = pack_bf16x2(v[0], v[1]);
-              o.y = pack_bf16x2(v[2], v[3]);
-              o.z = pack_bf16x2(v[4], v[5]);
-              o.w = pack_bf16x2(v[6], v[7]);
-              *reinterpret_cast<uint4*>(out + static_cast<int64_t>(m) * ld_out + (n - col_shift)) = o;
             }
+            uint4 o;
+            o.x = pack_bf16x2(v[0], v[1]);
+            o.y = pack_bf16x2(v[2], v[3]);
+            o.z = pack_bf16x2(v[4], v[5]);
+            o.w = pack_bf16x2(v[6], v[7]);
+            *reinterpret_cast<uint4*>(cell) = o;
           }
+        }
+        fence_proxy_async();
+        __syncwarp();
+        if (lane == 0) {
+          tma_store_2d(tmap_out, sbuf, nb - col_shift, r0);
+          bulk_commit();
         }
       }
       tc_fence_before();
       mbar_arrive(&tmem_empty[acc]);
+      if (!alive) break;
     }
+    if (lane == 0) bulk_wait<0>();  // every store of this warp has left shared memory and been written
   }
 
   // Common exit: on the abort path give copies still in flight time to land
@@ -287,7 +324,8 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
 
 template <int KIND, int BLOCK_N>
 static int launch_gemm(const void* A, int64_t lda, const void* W, int64_t ldw, int M, int N, int K,
-                       const GemmEpilogue& ep, cudaStream_t st) {
+                       const GemmEpilogue& ep, const CUtensorMap& to0, const CUtensorMap& to1, const CUtensorMap& tr,
+                       cudaStream_t st) {
   using SM = GemmSmem<BLOCK_N>;
   constexpr int esz = (KIND == KIND_F16) ? 2 : 1;
   constexpr int slab_elems = kSlabBytes / esz;
@@ -299,7 +337,7 @@ static int launch_gemm(const void* A, int64_t lda, const void* W, int64_t ldw, i
   DSB_ENSURE_SMEM(kern, SM::kTotal);
   const int tiles = ((M + kBlockM - 1) / kBlockM) * ((N + BLOCK_N - 1) / BLOCK_N);
   const int grid = tiles < sm_count() ? tiles : sm_count();
-  gemm_kernel<KIND, BLOCK_N><<<grid, kGemmThreads, SM::kTotal, st>>>(ta, tb, M, N, K, ep);
+  gemm_kernel<KIND, BLOCK_N><<<grid, kGemmThreads, SM::kTotal, st>>>(ta, tb, to0, to1, tr, M, N, K, ep);
   return cudaGetLastError() == cudaSuccess ? DSB_OK : DSB_ERR_CUDA;
 }
 
@@ -343,6 +381,7 @@ extern "C" int dsb_gemm(const void* A, int64_t lda, const void* W, int64_t ldw, 
   if (!out1) split_col = INT32_MAX;
   else if (split_col < 0 || (split_col % 256) != 0) return DSB_ERR_ARG;
   if (gate && !resid) return DSB_ERR_ARG;
+  if (resid && out1) return DSB_ERR_ARG;  // the residual form writes one output
   if (M == 0 || N == 0) return DSB_OK;
   GemmEpilogue ep;
   ep.row_scale = row_scale;
@@ -352,19 +391,26 @@ extern "C" int dsb_gemm(const void* A, int64_t lda, const void* W, int64_t ldw, 
   ep.act = act;
   ep.act_col0 = act_col0;
   ep.gate = gate;
-  ep.resid = reinterpret_cast<const __nv_bfloat16*>(resid);
-  ep.ld_resid = ld_resid;
-  ep.out0 = reinterpret_cast<__nv_bfloat16*>(out0);
-  ep.ld_out0 = ld_out0;
-  ep.out1 = reinterpret_cast<__nv_bfloat16*>(out1);
-  ep.ld_out1 = ld_out1;
+  ep.has_resid = resid ? 1 : 0;
   ep.split_col = split_col;
   ep.status = status;
+  // bf16 output / residual tiles of 32 rows x 64 columns (128 bytes per row, 128-byte swizzle)
+  CUtensorMap to0, to1, tr;
+  const int n0cols = out1 ? (split_col < N ? split_col : N) : N;
+  if (make_tmap_2d(&to0, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, out0, M, n0cols, ld_out0 * 2, 32, 64) != DSB_OK)
+    return DSB_ERR_CUDA;
+  to1 = to0;
+  if (out1 && split_col < N &&
+      make_tmap_2d(&to1, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, out1, M, N - split_col, ld_out1 * 2, 32, 64) != DSB_OK)
+    return DSB_ERR_CUDA;
+  tr = to0;
+  if (resid && make_tmap_2d(&tr, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, resid, M, N, ld_resid * 2, 32, 64) != DSB_OK)
+    return DSB_ERR_CUDA;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   const int bn = pick_block_n(M, N);
 #define DSB_GEMM_DISPATCH(KIND)                                                        \
-  (bn == 256 ? launch_gemm<KIND, 256>(A, lda, W, ldw, M, N, K, ep, st)                 \
-             : launch_gemm<KIND, 128>(A, lda, W, ldw, M, N, K, ep, st))
+  (bn == 256 ? launch_gemm<KIND, 256>(A, lda, W, ldw, M, N, K, ep, to0, to1, tr, st)   \
+             : launch_gemm<KIND, 128>(A, lda, W, ldw, M, N, K, ep, to0, to1, tr, st))
   if (fmt == DSB_FMT_BF16) return DSB_GEMM_DISPATCH(KIND_F16);
   if (fmt == DSB_FMT_E4M3) return DSB_GEMM_DISPATCH(KIND_F8);
   return DSB_GEMM_DISPATCH(KIND_I8);
