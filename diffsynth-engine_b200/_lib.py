@@ -36,6 +36,8 @@ _SIGS = {
     "dsb_euler_step": [c_p, c_p, c_p, c_p, c_f, c_p, c_i64, c_i, c_p],
     "dsb_gemm": [c_p, c_i64, c_p, c_i64, c_i, c_i, c_i, c_i, c_p, c_p, c_i, c_p, c_i, c_i, c_p, c_p, c_i64, c_p,
                  c_i64, c_p, c_i64, c_i, c_p, c_p],
+    "dsb_gemm_qkv": [c_p, c_i64, c_p, c_i64, c_i, c_i, c_i, c_i, c_p, c_p, c_i, c_p, c_i, c_i, c_p, c_i64, c_p, c_i64, c_i,
+                     c_p, c_p, c_i, c_p, c_i, c_f, c_p, c_p],
     "dsb_flash_attn": [c_p, c_p, c_p, c_p, c_i, c_i, c_i, c_i, c_i] + [c_i64] * 12 + [c_f, c_p, c_p],
     "dsb_pack_quant_weight": [c_p, c_i64, c_i, c_p, c_i64, c_p, c_i, c_i, c_i, c_i, c_p, c_p],
     "dsb_linear_static": [c_p, c_i64, c_p, c_i64, c_i, c_i, c_i, c_i, c_p, c_i, c_p, c_i, c_p, c_i64, c_p, c_p],

@@ -364,9 +364,31 @@ __global__ void __launch_bounds__(256) quant_rows_kernel(const __nv_bfloat16* __
 }
 
 // ------------------------------------------------------------------- gemv
-// y[n] = (sum_k W[n,k] * f(x[k])) * w_scale[n or 0] + bias[n],  one warp per
-// output row, the activation vector staged once per CTA in shared memory.
+// y[n] = (sum_k W[n,k] * f(x[k])) * w_scale[n or 0] + bias[n].  The activation vector is staged once per CTA
+// in shared memory; each warp walks groups of four consecutive rows so that every 64-byte read of the
+// activations serves four weight rows and four 16-byte weight loads per lane are in flight.
 // WFMT: 0 bf16, 1 e4m3, 2 int8.  act_in: DSB_ACT_NONE or DSB_ACT_SILU on x; act_out: any DSB_ACT_* on y.
+template <int WFMT>
+__device__ __forceinline__ void dequant16(const uint4& p, float (&w)[16]) {
+  const uint32_t u[4] = {p.x, p.y, p.z, p.w};
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    if constexpr (WFMT == 1) {
+      const __half2_raw h0 = __nv_cvt_fp8x2_to_halfraw2(static_cast<__nv_fp8x2_storage_t>(u[j] & 0xffffu), __NV_E4M3);
+      const __half2_raw h1 = __nv_cvt_fp8x2_to_halfraw2(static_cast<__nv_fp8x2_storage_t>(u[j] >> 16), __NV_E4M3);
+      const float2 f0 = __half22float2(*reinterpret_cast<const __half2*>(&h0));
+      const float2 f1 = __half22float2(*reinterpret_cast<const __half2*>(&h1));
+      w[4 * j] = f0.x, w[4 * j + 1] = f0.y, w[4 * j + 2] = f1.x, w[4 * j + 3] = f1.y;
+    } else {
+      const int v = static_cast<int>(u[j]);
+      w[4 * j] = static_cast<float>(static_cast<int8_t>(v & 0xff));
+      w[4 * j + 1] = static_cast<float>(static_cast<int8_t>((v >> 8) & 0xff));
+      w[4 * j + 2] = static_cast<float>(static_cast<int8_t>((v >> 16) & 0xff));
+      w[4 * j + 3] = static_cast<float>(static_cast<int8_t>((v >> 24) & 0xff));
+    }
+  }
+}
+
 template <int WFMT>
 __global__ void __launch_bounds__(256) gemv_kernel(const void* __restrict__ W, int64_t ld_w_bytes,
                                                    const float* __restrict__ x, const float* __restrict__ w_scale,
@@ -381,47 +403,53 @@ __global__ void __launch_bounds__(256) gemv_kernel(const void* __restrict__ W, i
   __syncthreads();
   const int lane = threadIdx.x & 31;
   const int warps = blockDim.x >> 5;
-  for (int n = blockIdx.x * warps + (threadIdx.x >> 5); n < N; n += gridDim.x * warps) {
-    const uint8_t* wr = reinterpret_cast<const uint8_t*>(W) + static_cast<int64_t>(n) * ld_w_bytes;
-    float acc = 0.f;
-    if constexpr (WFMT == 0) {
-      for (int k = lane * 8; k < K; k += 256) {
-        bf16x8 p = *reinterpret_cast<const bf16x8*>(wr + k * 2);
+  constexpr int R = 4;
+  constexpr int EPL = (WFMT == 0) ? 8 : 16;  // elements per 16-byte load
+  const int groups = (N + R - 1) / R;
+  for (int g = blockIdx.x * warps + (threadIdx.x >> 5); g < groups; g += gridDim.x * warps) {
+    const int n0 = g * R;
+    const uint8_t* wr[R];
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          float2 f = unpack_bf16x2(p.u[j]);
-          acc += f.x * xs[k + 2 * j] + f.y * xs[k + 2 * j + 1];
-        }
+    for (int r = 0; r < R; ++r)
+      wr[r] = reinterpret_cast<const uint8_t*>(W) + static_cast<int64_t>(min(n0 + r, N - 1)) * ld_w_bytes;
+    float acc[R] = {0.f, 0.f, 0.f, 0.f};
+    for (int k = lane * EPL; k < K; k += 32 * EPL) {
+      uint4 p[R];
+#pragma unroll
+      for (int r = 0; r < R; ++r) p[r] = *reinterpret_cast<const uint4*>(wr[r] + k * (WFMT == 0 ? 2 : 1));
+      float xv[EPL];
+#pragma unroll
+      for (int e = 0; e < EPL; e += 4) {
+        const float4 t = *reinterpret_cast<const float4*>(xs + k + e);
+        xv[e] = t.x, xv[e + 1] = t.y, xv[e + 2] = t.z, xv[e + 3] = t.w;
       }
-    } else {
-      for (int k = lane * 16; k < K; k += 512) {
-        const uint4 p = *reinterpret_cast<const uint4*>(wr + k);
-        const uint32_t u[4] = {p.x, p.y, p.z, p.w};
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          if constexpr (WFMT == 1) {
-            const __half2_raw h0 =
-                __nv_cvt_fp8x2_to_halfraw2(static_cast<__nv_fp8x2_storage_t>(u[j] & 0xffffu), __NV_E4M3);
-            const __half2_raw h1 =
-                __nv_cvt_fp8x2_to_halfraw2(static_cast<__nv_fp8x2_storage_t>(u[j] >> 16), __NV_E4M3);
-            const float2 f0 = __half22float2(*reinterpret_cast<const __half2*>(&h0));
-            const float2 f1 = __half22float2(*reinterpret_cast<const __half2*>(&h1));
-            acc += f0.x * xs[k + 4 * j] + f0.y * xs[k + 4 * j + 1] + f1.x * xs[k + 4 * j + 2] +
-                   f1.y * xs[k + 4 * j + 3];
-          } else {
-            const int v = static_cast<int>(u[j]);
-            acc += static_cast<float>(static_cast<int8_t>(v & 0xff)) * xs[k + 4 * j] +
-                   static_cast<float>(static_cast<int8_t>((v >> 8) & 0xff)) * xs[k + 4 * j + 1] +
-                   static_cast<float>(static_cast<int8_t>((v >> 16) & 0xff)) * xs[k + 4 * j + 2] +
-                   static_cast<float>(static_cast<int8_t>((v >> 24) & 0xff)) * xs[k + 4 * j + 3];
+      for (int r = 0; r < R; ++r) {
+        if constexpr (WFMT == 0) {
+          const uint32_t u[4] = {p[r].x, p[r].y, p[r].z, p[r].w};
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const float2 f = unpack_bf16x2(u[j]);
+            acc[r] += f.x * xv[2 * j] + f.y * xv[2 * j + 1];
           }
+        } else {
+          float w[16];
+          dequant16<WFMT>(p[r], w);
+#pragma unroll
+          for (int e = 0; e < 16; ++e) acc[r] += w[e] * xv[e];
         }
       }
     }
-    acc = warp_sum(acc);
-    if (lane == 0) {
-      float sc = w_scale ? w_scale[static_cast<int64_t>(n) * w_scale_stride] : 1.0f;
-      float o = acc * sc + (bias ? bias[n] : 0.f);
+#pragma unroll
+    for (int r = 0; r < R; ++r) acc[r] = warp_sum(acc[r]);
+    if (lane < R && n0 + lane < N) {
+      const int n = n0 + lane;
+      float a = acc[0];
+      if (lane == 1) a = acc[1];
+      if (lane == 2) a = acc[2];
+      if (lane == 3) a = acc[3];
+      const float sc = w_scale ? w_scale[static_cast<int64_t>(n) * w_scale_stride] : 1.0f;
+      float o = a * sc + (bias ? bias[n] : 0.f);
       if (act_out == DSB_ACT_SILU) o = silu(o);
       if (act_out == DSB_ACT_GELU_TANH) o = gelu_tanh(o);
       y[n] = accumulate ? y[n] + o : o;
@@ -605,15 +633,16 @@ int dsb_gemv(const void* W, int64_t ld_w, int w_fmt, const float* x, const float
   if (static_cast<size_t>(K) * 4 > 96 * 1024) return DSB_ERR_UNSUPPORTED;
   if (N == 0) return DSB_OK;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
-  int blocks = (N + 7) / 8;
-  const int cap = sm_count() * 8;
-  if (blocks > cap) blocks = cap;
   const size_t smem = static_cast<size_t>(K) * 4;
   const int64_t ldb = ld_w * esz;
+  int blocks = (N + 31) / 32;  // one warp per group of four rows
 #define DSB_GEMV(F)                                                                                             \
   {                                                                                                             \
     auto kern = gemv_kernel<F>;                                                                                 \
     DSB_ENSURE_SMEM(kern, 96 * 1024);                                                                           \
+    int occ = 1;                                                                                                \
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, kern, 256, smem) != cudaSuccess || occ < 1) occ = 1; \
+    if (blocks > occ * sm_count()) blocks = occ * sm_count(); /* exactly the resident set: no second wave */     \
     gemv_kernel<F><<<blocks, 256, smem, st>>>(W, ldb, x, w_scale, w_scale_stride, bias, y, N, K, act_in, act_out, \
                                                accumulate);                                                       \
   }

@@ -24,7 +24,7 @@ namespace dsb {
 
 constexpr int kBlockM = 128;
 constexpr int kSlabBytes = 128;  // bytes of K per stage row (one swizzle row)
-constexpr int kGemmThreads = 192;
+constexpr int kGemmThreads = 320;  // TMA warp, MMA warp, 8 epilogue warps
 
 struct GemmEpilogue {
   const float* row_scale;
@@ -37,11 +37,18 @@ struct GemmEpilogue {
   int has_resid;
   int split_col;
   int* status;
+  // fused per-head QK-RMSNorm + RoPE on the projection's q and k column ranges (nq_w == nullptr: off)
+  const float* nq_w;   // [128] weights of the q heads (columns [0, d_model))
+  const float* nk_w;   // [128] weights of the k heads (columns [d_model, 2 d_model))
+  const float2* rope;  // [(rope_row0 + m) * 64 + pair] = (cos, sin); nullptr: no rotation
+  int rope_row0;
+  int d_model;
+  float norm_eps;
 };
 
-constexpr int kEpiWarps = 4;
+constexpr int kEpiWarps = 8;               // two per TMEM lane quadrant, each draining half of the tile's columns
 constexpr int kStageSlotBytes = 32 * 128;  // 32 rows x 64 bf16
-constexpr int kStageBytes = kEpiWarps * 2 * kStageSlotBytes;
+constexpr int kStageBytes = kEpiWarps * kStageSlotBytes;
 
 template <int BLOCK_N>
 struct GemmSmem {
@@ -77,8 +84,8 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
   uint64_t* empty_bar = full_bar + kStages;
   uint64_t* tmem_full = empty_bar + kStages;
   uint64_t* tmem_empty = tmem_full + 2;
-  uint64_t* resid_bar = tmem_empty + 2;  // kEpiWarps x 2
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(resid_bar + kEpiWarps * 2);
+  uint64_t* resid_bar = tmem_empty + 2;  // kEpiWarps
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(resid_bar + kEpiWarps);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5;
@@ -91,9 +98,9 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(&tmem_full[a], 1);
-      mbar_init(&tmem_empty[a], 128);
+      mbar_init(&tmem_empty[a], kEpiWarps * 32);
     }
-    for (int i = 0; i < kEpiWarps * 2; ++i) mbar_init(&resid_bar[i], 1);
+    for (int i = 0; i < kEpiWarps; ++i) mbar_init(&resid_bar[i], 1);
     *abort_flag = 0;
     fence_mbar_init();
   }
@@ -176,9 +183,11 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
     // ---------------------------------------------------------------- epilogue
     const int quad = warp & 3;  // TMEM lane quadrant this warp may read
     const int ew = warp - 2;
-    uint8_t* stg = stage_base + ew * (2 * kStageSlotBytes);
-    uint64_t* rbar = resid_bar + ew * 2;
-    uint32_t rphase = 0, slot_ctr = 0;
+    const int half = ew >> 2;  // which half of the tile's 64-column blocks this warp drains
+    uint8_t* sbuf = stage_base + ew * kStageSlotBytes;
+    uint64_t* rbar = resid_bar + ew;
+    uint32_t rphase = 0;
+    constexpr int kBlocksPerWarp = BLOCK_N / 64 / 2;
     const uint32_t row_off = static_cast<uint32_t>(lane) * 128u;
     const uint32_t sw = static_cast<uint32_t>(lane & 7);
     int it = 0;
@@ -192,31 +201,77 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
       const int r0 = m0 + quad * 32;
       const int m = r0 + lane;
       const float rs = (ep.row_scale && m < M) ? ep.row_scale[m] : 1.0f;
+      const float rs_t = (ep.col_scale && !ep.col_scale_stride) ? rs * __ldg(ep.col_scale) : rs;  // per-tensor scale folded in
       const bool second = n0 >= ep.split_col;
       const CUtensorMap* tmap_out = second ? &tmap_o1 : &tmap_o0;
       const int col_shift = second ? ep.split_col : 0;
       const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + acc * BLOCK_N;
+      // Fused QK-RMSNorm (+RoPE): with 256-wide tiles this warp's 128 columns are exactly one head, one row per
+      // thread, so the row's sum of squares needs no cross-thread traffic - just a first pass over TMEM.
+      const int head_col0 = n0 + half * 128;
+      const bool fuse_norm = (BLOCK_N == 256) && ep.nq_w != nullptr && head_col0 < 2 * ep.d_model && head_col0 < N;
+      const float* head_w = head_col0 < ep.d_model ? ep.nq_w : ep.nk_w;
+      float rnorm = 1.0f;
+      if (fuse_norm) {
+        float ss = 0.f;
+#pragma unroll 1
+        for (int c = 0; c < 4; ++c) {
+          uint32_t r[32];
+          tmem_ld32(t_row + half * 128 + c * 32, r);
+          tc_wait_ld();
+#pragma unroll
+          for (int g = 0; g < 4; ++g) {
+            const int n = head_col0 + c * 32 + g * 8;
+            float cs8[8], b8[8];
+            if (ep.col_scale && ep.col_scale_stride) {
+              const float4 c0 = __ldg(reinterpret_cast<const float4*>(ep.col_scale + n));
+              const float4 c1 = __ldg(reinterpret_cast<const float4*>(ep.col_scale + n + 4));
+              cs8[0] = c0.x * rs, cs8[1] = c0.y * rs, cs8[2] = c0.z * rs, cs8[3] = c0.w * rs;
+              cs8[4] = c1.x * rs, cs8[5] = c1.y * rs, cs8[6] = c1.z * rs, cs8[7] = c1.w * rs;
+            } else {
+#pragma unroll
+              for (int j = 0; j < 8; ++j) cs8[j] = rs_t;
+            }
+            if (ep.bias) {
+              const float4 b0 = __ldg(reinterpret_cast<const float4*>(ep.bias + n));
+              const float4 b1 = __ldg(reinterpret_cast<const float4*>(ep.bias + n + 4));
+              b8[0] = b0.x, b8[1] = b0.y, b8[2] = b0.z, b8[3] = b0.w, b8[4] = b1.x, b8[5] = b1.y, b8[6] = b1.z, b8[7] = b1.w;
+            } else {
+#pragma unroll
+              for (int j = 0; j < 8; ++j) b8[j] = 0.f;
+            }
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              float a;
+              if constexpr (KIND == KIND_I8)
+                a = static_cast<float>(static_cast<int>(r[g * 8 + j]));
+              else
+                a = __uint_as_float(r[g * 8 + j]);
+              const float v = fmaf(a, cs8[j], b8[j]);
+              ss = fmaf(v, v, ss);
+            }
+          }
+        }
+        rnorm = rsqrtf(ss * (1.0f / 128.0f) + ep.norm_eps);
+      }
       bool alive = true;
 #pragma unroll 1
-      for (int cb = 0; cb < BLOCK_N / 64 && alive; ++cb) {
+      for (int cb = half * kBlocksPerWarp; cb < (half + 1) * kBlocksPerWarp && alive; ++cb) {
         const int nb = n0 + cb * 64;
-        if (nb >= N) break;  // uniform across the CTA
-        const uint32_t slot = slot_ctr & 1;
-        ++slot_ctr;
-        uint8_t* sbuf = stg + slot * kStageSlotBytes;
-        // the store that last used this slot (two blocks ago) must have read it out
-        if (lane == 0) bulk_wait_read<1>();
+        if (nb >= N) break;  // uniform across the warp
+        // this warp's previous store must have read the staging slot out
+        if (lane == 0) bulk_wait_read<0>();
         __syncwarp();
         if (ep.has_resid) {
           if (lane == 0) {
-            mbar_expect_tx(&rbar[slot], kStageSlotBytes);
-            tma_load_2d(sbuf, &tmap_r, &rbar[slot], nb, r0);
+            mbar_expect_tx(rbar, kStageSlotBytes);
+            tma_load_2d(sbuf, &tmap_r, rbar, nb, r0);
           }
-          if (!mbar_wait(&rbar[slot], (rphase >> slot) & 1, abort_flag)) {
+          if (!mbar_wait(rbar, rphase, abort_flag)) {
             alive = false;
             break;
           }
-          rphase ^= 1u << slot;
+          rphase ^= 1u;
         }
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
@@ -244,9 +299,8 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
                   v[0] *= c0.x * rs, v[1] *= c0.y * rs, v[2] *= c0.z * rs, v[3] *= c0.w * rs;
                   v[4] *= c1.x * rs, v[5] *= c1.y * rs, v[6] *= c1.z * rs, v[7] *= c1.w * rs;
                 } else {
-                  const float cs = __ldg(ep.col_scale) * rs;
 #pragma unroll
-                  for (int j = 0; j < 8; ++j) v[j] *= cs;
+                  for (int j = 0; j < 8; ++j) v[j] *= rs_t;
                 }
               } else if (ep.row_scale) {
 #pragma unroll
@@ -257,6 +311,26 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
                 const float4 b1 = __ldg(reinterpret_cast<const float4*>(ep.bias + n + 4));
                 v[0] += b0.x, v[1] += b0.y, v[2] += b0.z, v[3] += b0.w;
                 v[4] += b1.x, v[5] += b1.y, v[6] += b1.z, v[7] += b1.w;
+              }
+              if (fuse_norm) {
+                const int ch = n - head_col0;  // column inside the head
+                const float4 w0 = __ldg(reinterpret_cast<const float4*>(head_w + ch));
+                const float4 w1 = __ldg(reinterpret_cast<const float4*>(head_w + ch + 4));
+                v[0] *= rnorm * w0.x, v[1] *= rnorm * w0.y, v[2] *= rnorm * w0.z, v[3] *= rnorm * w0.w;
+                v[4] *= rnorm * w1.x, v[5] *= rnorm * w1.y, v[6] *= rnorm * w1.z, v[7] *= rnorm * w1.w;
+                if (ep.rope && m < M) {
+                  const float4* rp = reinterpret_cast<const float4*>(
+                      ep.rope + (static_cast<int64_t>(ep.rope_row0) + m) * 64 + (ch >> 1));
+                  const float4 c01 = __ldg(rp), c23 = __ldg(rp + 1);  // (cos, sin) of four pairs
+                  float t0 = c01.x * v[0] - c01.y * v[1], t1 = c01.y * v[0] + c01.x * v[1];
+                  v[0] = t0, v[1] = t1;
+                  t0 = c01.z * v[2] - c01.w * v[3], t1 = c01.w * v[2] + c01.z * v[3];
+                  v[2] = t0, v[3] = t1;
+                  t0 = c23.x * v[4] - c23.y * v[5], t1 = c23.y * v[4] + c23.x * v[5];
+                  v[4] = t0, v[5] = t1;
+                  t0 = c23.z * v[6] - c23.w * v[7], t1 = c23.w * v[6] + c23.z * v[7];
+                  v[6] = t0, v[7] = t1;
+                }
               }
               if (ep.act != DSB_ACT_NONE && n >= ep.act_col0) {
                 if (ep.act == DSB_ACT_GELU_TANH) {
@@ -361,10 +435,12 @@ static int pick_block_n(int M, int N) {
 
 using namespace dsb;
 
-extern "C" int dsb_gemm(const void* A, int64_t lda, const void* W, int64_t ldw, int fmt, int M, int N, int K,
-                        const float* row_scale, const float* col_scale, int col_scale_stride, const float* bias,
-                        int act, int act_col0, const float* gate, const void* resid, int64_t ld_resid, void* out0,
-                        int64_t ld_out0, void* out1, int64_t ld_out1, int split_col, int* status, void* stream) {
+static int gemm_common(const void* A, int64_t lda, const void* W, int64_t ldw, int fmt, int M, int N, int K,
+                       const float* row_scale, const float* col_scale, int col_scale_stride, const float* bias,
+                       int act, int act_col0, const float* gate, const void* resid, int64_t ld_resid, void* out0,
+                       int64_t ld_out0, void* out1, int64_t ld_out1, int split_col, const float* nq_w,
+                       const float* nk_w, int d_model, const float* rope, int rope_row0, float norm_eps, int* status,
+                       void* stream) {
   if (M < 0 || N < 0 || K <= 0 || (N & 7)) return DSB_ERR_ARG;
   if (M == 0 || N == 0) return DSB_OK;  // an empty product: nothing to read or write
   if (!A || !W || !out0) return DSB_ERR_ARG;
@@ -374,7 +450,7 @@ extern "C" int dsb_gemm(const void* A, int64_t lda, const void* W, int64_t ldw, 
   if (!al16(A) || !al16(W) || !al16(out0) || (out1 && !al16(out1)) || (resid && !al16(resid)) ||
       (bias && !al16(bias)) || (gate && !al16(gate)) || (col_scale && col_scale_stride && !al16(col_scale)))
     return DSB_ERR_ARG;
-  if (((lda * esz) & 15) || ((ldw * esz) & 15) || (N & 7) || (ld_out0 & 7) || (ld_resid & 7) || (ld_out1 & 7))
+  if (((lda * esz) & 15) || ((ldw * esz) & 15) || (ld_out0 & 7) || (ld_resid & 7) || (ld_out1 & 7))
     return DSB_ERR_ARG;
   if (col_scale_stride != 0 && col_scale_stride != 1) return DSB_ERR_ARG;
   if (act != DSB_ACT_NONE && act != DSB_ACT_GELU_TANH && act != DSB_ACT_SILU) return DSB_ERR_ARG;
@@ -382,7 +458,11 @@ extern "C" int dsb_gemm(const void* A, int64_t lda, const void* W, int64_t ldw, 
   else if (split_col < 0 || (split_col % 256) != 0) return DSB_ERR_ARG;
   if (gate && !resid) return DSB_ERR_ARG;
   if (resid && out1) return DSB_ERR_ARG;  // the residual form writes one output
-  if (M == 0 || N == 0) return DSB_OK;
+  if (nq_w) {
+    if (!nk_w || d_model <= 0 || (d_model % 128) || 2 * d_model > N || resid || !al16(nq_w) || !al16(nk_w) ||
+        (rope && !al16(rope)))
+      return DSB_ERR_ARG;
+  }
   GemmEpilogue ep;
   ep.row_scale = row_scale;
   ep.col_scale = col_scale;
@@ -394,6 +474,12 @@ extern "C" int dsb_gemm(const void* A, int64_t lda, const void* W, int64_t ldw, 
   ep.has_resid = resid ? 1 : 0;
   ep.split_col = split_col;
   ep.status = status;
+  ep.nq_w = nq_w;
+  ep.nk_w = nk_w;
+  ep.rope = reinterpret_cast<const float2*>(rope);
+  ep.rope_row0 = rope_row0;
+  ep.d_model = d_model;
+  ep.norm_eps = norm_eps;
   // bf16 output / residual tiles of 32 rows x 64 columns (128 bytes per row, 128-byte swizzle)
   CUtensorMap to0, to1, tr;
   const int n0cols = out1 ? (split_col < N ? split_col : N) : N;
@@ -407,7 +493,7 @@ extern "C" int dsb_gemm(const void* A, int64_t lda, const void* W, int64_t ldw, 
   if (resid && make_tmap_2d(&tr, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, resid, M, N, ld_resid * 2, 32, 64) != DSB_OK)
     return DSB_ERR_CUDA;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
-  const int bn = pick_block_n(M, N);
+  const int bn = nq_w ? 256 : pick_block_n(M, N);  // the fused norm needs a whole head per epilogue warp
 #define DSB_GEMM_DISPATCH(KIND)                                                        \
   (bn == 256 ? launch_gemm<KIND, 256>(A, lda, W, ldw, M, N, K, ep, to0, to1, tr, st)   \
              : launch_gemm<KIND, 128>(A, lda, W, ldw, M, N, K, ep, to0, to1, tr, st))
@@ -415,4 +501,24 @@ extern "C" int dsb_gemm(const void* A, int64_t lda, const void* W, int64_t ldw, 
   if (fmt == DSB_FMT_E4M3) return DSB_GEMM_DISPATCH(KIND_F8);
   return DSB_GEMM_DISPATCH(KIND_I8);
 #undef DSB_GEMM_DISPATCH
+}
+
+extern "C" int dsb_gemm(const void* A, int64_t lda, const void* W, int64_t ldw, int fmt, int M, int N, int K,
+                        const float* row_scale, const float* col_scale, int col_scale_stride, const float* bias,
+                        int act, int act_col0, const float* gate, const void* resid, int64_t ld_resid, void* out0,
+                        int64_t ld_out0, void* out1, int64_t ld_out1, int split_col, int* status, void* stream) {
+  return gemm_common(A, lda, W, ldw, fmt, M, N, K, row_scale, col_scale, col_scale_stride, bias, act, act_col0, gate,
+                     resid, ld_resid, out0, ld_out0, out1, ld_out1, split_col, nullptr, nullptr, 0, nullptr, 0, 0.f,
+                     status, stream);
+}
+
+extern "C" int dsb_gemm_qkv(const void* A, int64_t lda, const void* W, int64_t ldw, int fmt, int M, int N, int K,
+                            const float* row_scale, const float* col_scale, int col_scale_stride, const float* bias,
+                            int act, int act_col0, void* out0, int64_t ld_out0, void* out1, int64_t ld_out1,
+                            int split_col, const float* nq_w, const float* nk_w, int d_model, const float* rope,
+                            int rope_row0, float norm_eps, int* status, void* stream) {
+  if (!nq_w || !nk_w) return DSB_ERR_ARG;
+  return gemm_common(A, lda, W, ldw, fmt, M, N, K, row_scale, col_scale, col_scale_stride, bias, act, act_col0,
+                     nullptr, nullptr, 0, out0, ld_out0, out1, ld_out1, split_col, nq_w, nk_w, d_model, rope,
+                     rope_row0, norm_eps, status, stream);
 }

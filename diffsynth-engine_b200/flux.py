@@ -6,13 +6,13 @@ patchify/unpatchify reshapes at the model boundary):
 
   step start : sinusoid -> 6 GEMVs (time, guidance, pooled MLPs, summed in fp32) -> ONE GEMV over the stacked
                AdaLN weights of all blocks = every shift/scale/gate of the step
-  double     : per stream  ln_modulate(+quantise) -> qkv GEMM (+bias) into the joint [S, 3d] buffer (text rows
-               first) -> per-head RMSNorm+RoPE in place;   joint flash attention;
+  double     : per stream  ln_modulate(+quantise) -> qkv GEMM (+bias, per-head RMSNorm+RoPE of q and k in the
+               epilogue) into the joint [S, 3d] buffer (text rows first);   joint flash attention;
                per stream  quantise -> out-proj GEMM with x += gate*(.) fused -> ln_modulate(+quantise)
                -> FF1 GEMM (+GELU) -> quantise -> FF2 GEMM with x += gate*(.) fused
   single     : ln_modulate(+quantise) -> ONE GEMM N=7d whose epilogue routes [q|k|v] to the attention buffer and
-               GELU(mlp) next to where attention will write its output (no torch.cat) -> RMSNorm+RoPE ->
-               flash attention -> quantise -> proj GEMM K=5d with x = x + gate*(.) fused
+               GELU(mlp) next to where attention will write its output (no torch.cat), RMSNorm+RoPE applied to the
+               q and k columns on the way -> flash attention -> quantise -> proj GEMM K=5d with x = x + gate*(.) fused
 
 The text and image streams live in one [S_txt + S_img, d] buffer (text first), so the hand-over from double
 to single blocks (flux_dit.py:442) is free.  All buffers are allocated once; the step can be captured in a
@@ -184,8 +184,9 @@ class FluxDiTEngine:
             for rows, s_, mo in streams:
                 sh_msa, sc_msa = m[mo:mo + d], m[mo + d:mo + 2 * d]
                 a, sc = self._ln(x[rows], sh_msa, sc_msa, xq_d[rows], rs[rows])
-                self._gemm(a, sc, blk["qkv_" + s_], out=qkv[rows])
-                ops.rmsnorm_rope_heads(qkv[rows], H, blk["nq_" + s_], blk["nk_" + s_], rope, rows.start)
+                p = blk["qkv_" + s_]
+                ops.gemm_qkv(a, p.w, blk["nq_" + s_], blk["nk_" + s_], d, rope, rows.start, 1e-6, row_scale=sc,
+                             col_scale=p.scale, bias=p.bias, out=qkv[rows])
             ops.flash_attn(q4, k4, v4, out=o4)
             for rows, s_, mo in streams:
                 g_msa = m[mo + 2 * d:mo + 3 * d]
@@ -201,9 +202,9 @@ class FluxDiTEngine:
             m = mv[off:off + 3 * d]
             off += 3 * d
             a, sc = self._ln(x, m[:d], m[d:2 * d], xq_d, rs)
-            self._gemm(a, sc, blk["qkv_mlp"], act=ops.ACT_GELU_TANH, act_col0=3 * d, out=qkv, out1=cat[:, d:],
-                       split_col=3 * d)
-            ops.rmsnorm_rope_heads(qkv, H, blk["nq"], blk["nk"], rope, 0)
+            p = blk["qkv_mlp"]
+            ops.gemm_qkv(a, p.w, blk["nq"], blk["nk"], d, rope, 0, 1e-6, row_scale=sc, col_scale=p.scale, bias=p.bias,
+                         act=ops.ACT_GELU_TANH, act_col0=3 * d, out=qkv, out1=cat[:, d:], split_col=3 * d)
             ops.flash_attn(q4, k4, v4, out=o4)
             a, sc = self._quant(cat, catq, rs)
             self._gemm(a, sc, blk["proj"], gate=m[2 * d:3 * d], resid=x, out=x)
@@ -280,8 +281,8 @@ class FluxDiTEngine:
 
     def kernel_launches_per_step(self) -> int:
         """Launches of this library's kernels in one step (the count of the dataflow above)."""
-        per_stream = 3 + (2 if self.afmt != ops.FMT_BF16 else 0) + 4
+        per_stream = 2 + (2 if self.afmt != ops.FMT_BF16 else 0) + 4
         dbl = 2 * per_stream + 1
-        sgl = 4 + (1 if self.afmt != ops.FMT_BF16 else 0) + 1
+        sgl = 3 + (1 if self.afmt != ops.FMT_BF16 else 0) + 1
         pre = 1 + (6 if self.use_guidance else 4) + 1 + 2 + (2 if self.afmt != ops.FMT_BF16 else 0)
         return pre + self.n_double * dbl + self.n_single * sgl + 2

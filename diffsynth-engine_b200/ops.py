@@ -176,6 +176,26 @@ def gemm(a, w, row_scale=None, col_scale=None, bias=None, act=ACT_NONE, act_col0
     return out
 
 
+def gemm_qkv(a, w, nq_w, nk_w, d_model, rope=None, rope_row0=0, eps=1e-6, row_scale=None, col_scale=None, bias=None,
+             act=ACT_NONE, act_col0=0, out=None, out1=None, split_col=None):
+    """``dsb_gemm_qkv``: the fused q|k|v(|mlp) projection with per-head RMSNorm + RoPE on the q and k columns."""
+    _require_cuda(a, w, nq_w, nk_w, rope, row_scale, col_scale, bias, out, out1)
+    M, K, lda = _rows(a)
+    N, Kw, ldw = _rows(w)
+    if K != Kw or _fmt_of(a) != _fmt_of(w):
+        raise _lib.DsbError("gemm operands disagree in K or format")
+    if out is None:
+        out = torch.empty((M, N if out1 is None else split_col), dtype=torch.bfloat16, device=a.device)
+    cs_stride = 0 if (col_scale is None or col_scale.numel() == 1) else 1
+    rc = _lib.lib().dsb_gemm_qkv(
+        _ptr(a), lda, _ptr(w), ldw, _fmt_of(a), M, N, K, _ptr(row_scale), _ptr(col_scale), cs_stride, _ptr(bias), act,
+        act_col0, _ptr(out), out.stride(0), _ptr(out1), 0 if out1 is None else out1.stride(0),
+        N if split_col is None else split_col, _ptr(nq_w), _ptr(nk_w), d_model, _ptr(rope), rope_row0, float(eps),
+        _ptr(status_word(a.device)), _stream())
+    check(rc, "dsb_gemm_qkv")
+    return out
+
+
 def flash_attn(q, k, v, out=None, sm_scale=None):
     """q: [B, Sq, H, 128], k/v: [B, Sk, H, 128] views (any strides that are multiples of 8, unit inner
     stride); returns o as [B, Sq, H, 128] contiguous unless ``out`` is given."""

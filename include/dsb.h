@@ -140,6 +140,20 @@ int dsb_gemm(const void* A, int64_t lda, const void* W, int64_t ldw, int fmt, in
              void* out1, int64_t ld_out1, int split_col, int* status, void* stream);
 
 /*
+ * dsb_gemm for a fused q|k|v (|mlp) projection, with the per-head QK-RMSNorm and RoPE applied in the epilogue:
+ * columns [0, d_model) are q heads (weights nq_w[128]), [d_model, 2 d_model) k heads (nk_w[128]); each head's 128
+ * columns are scaled by rsqrt(mean(v^2) + norm_eps) * w and then rotated pairwise with rope[(rope_row0 + m)*64 + j]
+ * = (cos, sin) (rope NULL: no rotation).  Columns from 2 d_model on follow dsb_gemm (bias, activation from act_col0,
+ * split output).  Replaces, on top of dsb_gemm: models/basic/transformer_helper.py:73-78 (RMSNorm) and
+ * models/flux/flux_dit.py:154-159 (apply_rope) as used at flux_dit.py:165-180 and :297-301.
+ */
+int dsb_gemm_qkv(const void* A, int64_t lda, const void* W, int64_t ldw, int fmt, int M, int N, int K,
+                 const float* row_scale, const float* col_scale, int col_scale_stride, const float* bias, int act,
+                 int act_col0, void* out0, int64_t ld_out0, void* out1, int64_t ld_out1, int split_col,
+                 const float* nq_w, const float* nk_w, int d_model, const float* rope, int rope_row0, float norm_eps,
+                 int* status, void* stream);
+
+/*
  * Attention without mask: o[b,s,h,:] = softmax(q[b,s,h,:] . k[b,:,h,:]^T * sm_scale) v[b,:,h,:], head_dim 128,
  * bf16 in/out, fp32 softmax statistics.  Tensors are addressed as base + b*stride_b + s*stride_s + h*stride_h
  * (+ d, contiguous); strides are in elements and need to be multiples of 8.  Covers the joint text+image

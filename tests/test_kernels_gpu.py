@@ -332,3 +332,40 @@ def test_flash_attn_strided_views(dsb, cuda_dev):
     vh = v.transpose(1, 2).contiguous().to(cuda_dev).transpose(1, 2)
     out2 = dsb.ops.flash_attn(qh, kh, vh)
     assert O.rel_l2(out2.float().cpu(), ref) < 4e-3
+
+
+@pytest.mark.parametrize("fmt", ["e4m3", "bf16"])
+@pytest.mark.parametrize("M,H", [(300, 2), (1000, 4)])
+def test_gemm_qkv_fused_norm_rope(dsb, cuda_dev, fmt, M, H):
+    """q|k|v|mlp projection whose epilogue applies the per-head RMSNorm + RoPE to q and k, GELU to the mlp
+    columns and routes the two column ranges to two buffers (models/flux/flux_dit.py:297-317)."""
+    g = _gen(21)
+    d, K = H * 128, 512
+    N = 7 * d
+    x = _bf(torch.randn(M, K, generator=g))
+    W = torch.randn(N, K, generator=g) * 0.05
+    b = torch.randn(N, generator=g) * 0.1
+    wq, wk = 1 + 0.1 * torch.randn(128, generator=g), 1 + 0.1 * torch.randn(128, generator=g)
+    ids = torch.stack([torch.zeros(M + 7), torch.arange(M + 7) % 37, torch.arange(M + 7) // 37], dim=1).float()
+    table = O.flux_rope_table(ids)
+    if fmt == "bf16":
+        a_d, w_d, rs, cs = x, _bf(W), None, None
+        acc = x.float() @ _bf(W).float().t() + b
+    else:
+        xq, xs = O.quant_rows_e4m3(x)
+        wq8, ws = O.quant_weight(W, "fp8_tensor")
+        a_d, w_d, rs, cs = xq, wq8, xs, ws
+        acc = O.linear_quant(xq, xs, wq8, ws, b)
+    q = O.apply_rope_pairs(O.rmsnorm(acc[:, :d].reshape(M, H, 128), wq).transpose(0, 1), table[7:7 + M]).transpose(0, 1)
+    k = O.apply_rope_pairs(O.rmsnorm(acc[:, d:2 * d].reshape(M, H, 128), wk).transpose(0, 1), table[7:7 + M]).transpose(0, 1)
+    ref_qkv = torch.cat([q.reshape(M, d), k.reshape(M, d), acc[:, 2 * d:3 * d]], dim=1)
+    ref_mlp = O.gelu_tanh(acc[:, 3 * d:])
+    to = lambda t: None if t is None else t.to(cuda_dev)
+    qkv = torch.empty(M, 3 * d, dtype=torch.bfloat16, device=cuda_dev)
+    cat = torch.zeros(M, 5 * d, dtype=torch.bfloat16, device=cuda_dev)
+    dsb.ops.gemm_qkv(to(a_d), to(w_d), to(wq), to(wk), d, to(table).contiguous(), 7, 1e-6, row_scale=to(rs),
+                     col_scale=to(cs), bias=to(b), act=dsb.ops.ACT_GELU_TANH, act_col0=3 * d, out=qkv, out1=cat[:, d:],
+                     split_col=3 * d)
+    assert O.rel_l2(qkv.float().cpu(), ref_qkv) < 4e-3
+    assert O.rel_l2(cat[:, d:].float().cpu(), ref_mlp) < 4e-3
+    assert float(cat[:, :d].abs().max()) == 0.0
