@@ -29,7 +29,8 @@ _SIGS = {
     "dsb_ln_modulate": [c_p, c_i64, c_p, c_p, c_p, c_i64, c_p, c_i, c_i, c_f, c_i, c_p],
     "dsb_gate_residual": [c_p, c_i64, c_p, c_i64, c_p, c_p, c_i64, c_i, c_i, c_p],
     "dsb_rmsnorm_rope_heads": [c_p, c_i64, c_i, c_i, c_i, c_i, c_p, c_p, c_p, c_i, c_f, c_p],
-    "dsb_rmsnorm_full": [c_p, c_i64, c_i, c_i, c_p, c_p, c_i, c_f, c_p],
+    "dsb_rmsnorm_full": [c_p, c_i64, c_p, c_i64, c_i, c_i64, c_i, c_i, c_p, c_p, c_i, c_f, c_p],
+    "dsb_quant_rows_chunked": [c_p, c_i64, c_i, c_i64, c_p, c_i64, c_p, c_i, c_i, c_i, c_p],
     "dsb_quant_rows": [c_p, c_i64, c_p, c_i64, c_p, c_i, c_i, c_i, c_p],
     "dsb_gemv": [c_p, c_i64, c_i, c_p, c_p, c_i, c_p, c_p, c_i, c_i, c_i, c_i, c_i, c_p],
     "dsb_timestep_embedding": [c_p, c_i, c_i, c_f, c_i, c_i, c_p, c_p],

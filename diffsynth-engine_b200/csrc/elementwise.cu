@@ -254,16 +254,20 @@ __global__ void __launch_bounds__(256) rmsnorm_rope_heads_kernel(__nv_bfloat16* 
 // RMSNorm over the whole row (all heads, width D = H*128) with weight[D],
 // then per-head RoPE (same 64 (cos,sin) pairs for every head of a token).
 // One CTA per row; in place.  rope == nullptr skips the rotation.
+// The output may be "chunked": column c of row m goes to out[(c / chunk_cols) * chunk_stride + m * ld_out +
+// c % chunk_cols] - the per-peer-contiguous send layout of a head/sequence all-to-all ([P][rows][D/P]).
 template <int NV>
-__global__ void __launch_bounds__(kRowThreads) rmsnorm_full_rope_kernel(__nv_bfloat16* __restrict__ buf, int64_t ld,
-                                                                        int M, int D, const float* __restrict__ w,
+__global__ void __launch_bounds__(kRowThreads) rmsnorm_full_rope_kernel(const __nv_bfloat16* buf, int64_t ld,
+                                                                        __nv_bfloat16* out, int64_t ld_out,
+                                                                        int chunk_cols, int64_t chunk_stride, int M,
+                                                                        int D, const float* __restrict__ w,
                                                                         const float2* __restrict__ rope,
                                                                         int rope_row0, float eps) {
   __shared__ float red[4];
   const int row = blockIdx.x;
   if (row >= M) return;
   const int nvec = D >> 3;
-  __nv_bfloat16* xr = buf + static_cast<int64_t>(row) * ld;
+  const __nv_bfloat16* xr = buf + static_cast<int64_t>(row) * ld;
   float v[NV][8];
   float ss = 0.f;
 #pragma unroll
@@ -305,7 +309,10 @@ __global__ void __launch_bounds__(kRowThreads) rmsnorm_full_rope_kernel(__nv_bfl
       bf16x8 p;
 #pragma unroll
       for (int j = 0; j < 4; ++j) p.u[j] = pack_bf16x2(o[2 * j], o[2 * j + 1]);
-      *reinterpret_cast<bf16x8*>(xr + vi * 8) = p;
+      const int col = vi * 8;
+      const int ck = col / chunk_cols;
+      *reinterpret_cast<bf16x8*>(out + ck * chunk_stride + static_cast<int64_t>(row) * ld_out + (col - ck * chunk_cols)) =
+          p;
     }
   }
 }
@@ -315,16 +322,24 @@ __global__ void __launch_bounds__(kRowThreads) rmsnorm_full_rope_kernel(__nv_bfl
 // The row is read twice; the second read is served by L1/L2.
 template <int OUT>
 __global__ void __launch_bounds__(256) quant_rows_kernel(const __nv_bfloat16* __restrict__ x, int64_t ld_x,
+                                                         int chunk_cols, int64_t chunk_stride,
                                                          uint8_t* __restrict__ y, int64_t ld_y,
                                                          float* __restrict__ row_scale, int M, int K) {
   __shared__ float red[8];
   const int row = blockIdx.x;
   if (row >= M) return;
   const int nvec = K >> 3;
-  const __nv_bfloat16* xr = x + static_cast<int64_t>(row) * ld_x;
+  // chunked input: column c of row m lives at x[(c / chunk_cols) * chunk_stride + m * ld_x + c % chunk_cols]
+  // (what a sequence/head all-to-all delivers: [P][rows][K/P]); chunk_cols == K is the plain row-major case
+  const __nv_bfloat16* xrow = x + static_cast<int64_t>(row) * ld_x;
+  auto src = [&](int vi) {
+    const int col = vi * 8;
+    const int ck = col / chunk_cols;
+    return xrow + ck * chunk_stride + (col - ck * chunk_cols);
+  };
   float amax = 0.f;
   for (int vi = threadIdx.x; vi < nvec; vi += blockDim.x) {
-    bf16x8 p = *reinterpret_cast<const bf16x8*>(xr + vi * 8);
+    bf16x8 p = *reinterpret_cast<const bf16x8*>(src(vi));
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
       float2 f = unpack_bf16x2(p.u[j]);
@@ -343,7 +358,7 @@ __global__ void __launch_bounds__(256) quant_rows_kernel(const __nv_bfloat16* __
   if (threadIdx.x == 0) row_scale[row] = sc;
   uint8_t* yr = y + static_cast<int64_t>(row) * ld_y;
   for (int vi = threadIdx.x; vi < nvec; vi += blockDim.x) {
-    bf16x8 p = *reinterpret_cast<const bf16x8*>(xr + vi * 8);
+    bf16x8 p = *reinterpret_cast<const bf16x8*>(src(vi));
     float f[8];
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
@@ -581,19 +596,24 @@ int dsb_rmsnorm_rope_heads(void* buf, int64_t ld, int S, int H, int head_dim, in
   return cudaGetLastError() == cudaSuccess ? DSB_OK : DSB_ERR_CUDA;
 }
 
-int dsb_rmsnorm_full(void* buf, int64_t ld, int M, int D, const float* w, const float* rope, int rope_row0, float eps,
-                     void* stream) {
-  if (!buf || !w || M < 0 || D <= 0 || (D & 127) || (ld & 7) || !aligned16(buf) || !aligned16(w) ||
-      (rope && !aligned16(rope)))
+int dsb_rmsnorm_full(const void* x, int64_t ld_x, void* out, int64_t ld_out, int out_chunk_cols,
+                     int64_t out_chunk_stride, int M, int D, const float* w, const float* rope, int rope_row0,
+                     float eps, void* stream) {
+  if (M == 0 && D > 0 && !(D & 127)) return DSB_OK;
+  if (!x || !out || !w || M < 0 || D <= 0 || (D & 127) || (ld_x & 7) || (ld_out & 7) || !aligned16(x) ||
+      !aligned16(out) || !aligned16(w) || (rope && !aligned16(rope)))
     return DSB_ERR_ARG;
-  if (M == 0) return DSB_OK;
+  if (out_chunk_cols == 0) out_chunk_cols = D, out_chunk_stride = 0;
+  if (out_chunk_cols < 0 || (out_chunk_cols & 7) || (D % out_chunk_cols) || (out_chunk_stride & 7)) return DSB_ERR_ARG;
   const int nv = (D / 8 + kRowThreads - 1) / kRowThreads;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
-  __nv_bfloat16* b = reinterpret_cast<__nv_bfloat16*>(buf);
+  const __nv_bfloat16* b = reinterpret_cast<const __nv_bfloat16*>(x);
+  __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(out);
   const float2* rp = reinterpret_cast<const float2*>(rope);
-#define DSB_RMS_CASE(NV)                                                                              \
-  case NV:                                                                                            \
-    rmsnorm_full_rope_kernel<NV><<<M, kRowThreads, 0, st>>>(b, ld, M, D, w, rp, rope_row0, eps);      \
+#define DSB_RMS_CASE(NV)                                                                                          \
+  case NV:                                                                                                        \
+    rmsnorm_full_rope_kernel<NV><<<M, kRowThreads, 0, st>>>(b, ld_x, o, ld_out, out_chunk_cols, out_chunk_stride, \
+                                                           M, D, w, rp, rope_row0, eps);                        \
     break;
   switch (nv) {
     DSB_RMS_CASE(1) DSB_RMS_CASE(2) DSB_RMS_CASE(3) DSB_RMS_CASE(4) DSB_RMS_CASE(5) DSB_RMS_CASE(6) DSB_RMS_CASE(7)
@@ -605,8 +625,24 @@ int dsb_rmsnorm_full(void* buf, int64_t ld, int M, int D, const float* w, const 
   return cudaGetLastError() == cudaSuccess ? DSB_OK : DSB_ERR_CUDA;
 }
 
+static int quant_rows_impl(const void* x, int64_t ld_x, int chunk_cols, int64_t chunk_stride, void* y, int64_t ld_y,
+                           float* row_scale, int M, int K, int out_fmt, void* stream);
+
 int dsb_quant_rows(const void* x, int64_t ld_x, void* y, int64_t ld_y, float* row_scale, int M, int K, int out_fmt,
                    void* stream) {
+  return quant_rows_impl(x, ld_x, K, 0, y, ld_y, row_scale, M, K, out_fmt, stream);
+}
+
+int dsb_quant_rows_chunked(const void* x, int64_t ld_x, int chunk_cols, int64_t chunk_stride, void* y, int64_t ld_y,
+                           float* row_scale, int M, int K, int out_fmt, void* stream) {
+  if (chunk_cols <= 0 || (chunk_cols & 7) || K <= 0 || (K % chunk_cols) || (chunk_stride & 7)) return DSB_ERR_ARG;
+  return quant_rows_impl(x, ld_x, chunk_cols, chunk_stride, y, ld_y, row_scale, M, K, out_fmt, stream);
+}
+
+}  // extern "C"
+
+static int quant_rows_impl(const void* x, int64_t ld_x, int chunk_cols, int64_t chunk_stride, void* y, int64_t ld_y,
+                           float* row_scale, int M, int K, int out_fmt, void* stream) {
   if (M == 0 && K > 0 && !(K & 7)) return DSB_OK;
   if (!x || !y || !row_scale || M < 0 || K <= 0 || (K & 7) || (ld_x & 7) || (ld_y & 15) || !aligned16(x) ||
       !aligned16(y))
@@ -616,13 +652,15 @@ int dsb_quant_rows(const void* x, int64_t ld_x, void* y, int64_t ld_y, float* ro
   const __nv_bfloat16* xp = reinterpret_cast<const __nv_bfloat16*>(x);
   uint8_t* yp = reinterpret_cast<uint8_t*>(y);
   if (out_fmt == DSB_FMT_E4M3)
-    quant_rows_kernel<1><<<M, 256, 0, st>>>(xp, ld_x, yp, ld_y, row_scale, M, K);
+    quant_rows_kernel<1><<<M, 256, 0, st>>>(xp, ld_x, chunk_cols, chunk_stride, yp, ld_y, row_scale, M, K);
   else if (out_fmt == DSB_FMT_INT8)
-    quant_rows_kernel<2><<<M, 256, 0, st>>>(xp, ld_x, yp, ld_y, row_scale, M, K);
+    quant_rows_kernel<2><<<M, 256, 0, st>>>(xp, ld_x, chunk_cols, chunk_stride, yp, ld_y, row_scale, M, K);
   else
     return DSB_ERR_ARG;
   return cudaGetLastError() == cudaSuccess ? DSB_OK : DSB_ERR_CUDA;
 }
+
+extern "C" {
 
 int dsb_gemv(const void* W, int64_t ld_w, int w_fmt, const float* x, const float* w_scale, int w_scale_stride,
              const float* bias, float* y, int N, int K, int act_in, int act_out, int accumulate, void* stream) {

@@ -99,12 +99,23 @@ def rmsnorm_rope_heads(buf, H, w_q, w_k=None, rope=None, rope_row0=0, eps=1e-6):
     return buf
 
 
-def rmsnorm_full(buf, w, rope=None, rope_row0=0, eps=1e-6):
-    _require_cuda(buf, w, rope)
+def rmsnorm_full(buf, w, rope=None, rope_row0=0, eps=1e-6, out=None, chunks=1):
+    """RMSNorm over whole rows (+RoPE); in place unless ``out`` is given.  ``chunks`` = P > 1 writes ``out`` as
+    ``[P, M, D/P]`` (contiguous), the send layout of the head exchange."""
+    _require_cuda(buf, w, rope, out)
     M, D, ld = _rows(buf)
-    rc = _lib.lib().dsb_rmsnorm_full(_ptr(buf), ld, M, D, _ptr(w), _ptr(rope), rope_row0, eps, _stream())
+    if out is None:
+        out, ld_out, cc, cs = buf, ld, 0, 0
+    elif chunks > 1:
+        if tuple(out.shape) != (chunks, M, D // chunks) or not out.is_contiguous():
+            raise _lib.DsbError("chunked rmsnorm_full output must be a contiguous [P, M, D/P] tensor")
+        ld_out, cc, cs = D // chunks, D // chunks, M * (D // chunks)
+    else:
+        ld_out, cc, cs = out.stride(0), 0, 0
+    rc = _lib.lib().dsb_rmsnorm_full(_ptr(buf), ld, _ptr(out), ld_out, cc, cs, M, D, _ptr(w), _ptr(rope), rope_row0,
+                                     eps, _stream())
     check(rc, "dsb_rmsnorm_full")
-    return buf
+    return out
 
 
 def quant_rows(x, out_fmt=FMT_E4M3, out=None, row_scale=None):
@@ -116,6 +127,23 @@ def quant_rows(x, out_fmt=FMT_E4M3, out=None, row_scale=None):
         row_scale = torch.empty(M, dtype=torch.float32, device=x.device)
     rc = _lib.lib().dsb_quant_rows(_ptr(x), ld_x, _ptr(out), out.stride(0), _ptr(row_scale), M, K, out_fmt, _stream())
     check(rc, "dsb_quant_rows")
+    return out, row_scale
+
+
+def quant_rows_chunked(x3, out_fmt=FMT_E4M3, out=None, row_scale=None):
+    """Quantise rows delivered as ``[P, M, K/P]`` (contiguous) into plain ``[M, K]`` rows."""
+    _require_cuda(x3)
+    if x3.dim() != 3 or not x3.is_contiguous():
+        raise _lib.DsbError("quant_rows_chunked takes a contiguous [P, M, K/P] tensor")
+    P, M, C = x3.shape
+    K = P * C
+    if out is None:
+        out = torch.empty((M, K), dtype=_OUT_DTYPE[out_fmt], device=x3.device)
+    if row_scale is None:
+        row_scale = torch.empty(M, dtype=torch.float32, device=x3.device)
+    rc = _lib.lib().dsb_quant_rows_chunked(_ptr(x3), C, C, M * C, _ptr(out), out.stride(0), _ptr(row_scale), M, K,
+                                           out_fmt, _stream())
+    check(rc, "dsb_quant_rows_chunked")
     return out, row_scale
 
 

@@ -1,0 +1,321 @@
+"""One Wan2.1-architecture DiT denoising step on the library's kernels (the job of ``WanDiT.forward``,
+models/wan/wan_dit.py:319-351 of DiffSynth-Engine, text-to-video, batch 1), optionally sequence-parallel over
+the ranks of a ``torch.distributed`` group (Ulysses):
+
+  * every rank owns a contiguous slice of S/P tokens in (f, h, w) raster order and runs all token-wise work on
+    it: AdaLN, every Linear, the full-width QK-RMSNorm, RoPE with the slice's own positions, cross-attention
+    (queries of the slice against the replicated 512-token context), FFN;
+  * self-attention needs one exchange on each side: q, k, v go from ``[S/P, H, 128]`` to ``[S, H/P, 128]`` (all
+    tokens, this rank's heads) and the attention output goes back.  The RMSNorm/RoPE kernel writes q and k straight
+    into the per-peer-contiguous send layout ``[P][S/P][H/P*128]``, and the quantiser that feeds the output
+    projection reads the returned ``[P][S/P][H/P*128]`` directly, so neither direction needs a pack kernel;
+  * the exchange of q runs on a second stream while the k projection computes, the exchange of k under the v
+    projection; weights (14 GB in FP8) are replicated.
+
+Per block, in launch order (P = 1 drops the exchanges):
+  ln_modulate+quantise -> q GEMM -> rmsnorm_full+rope -> [a2a q] | k GEMM -> rmsnorm_full+rope -> [a2a k] | v GEMM
+  -> [a2a v] -> flash attention (H/P heads, all tokens) -> [a2a o] -> quantise -> o GEMM with x += gate*(.)
+  -> affine LN3+quantise -> q GEMM -> rmsnorm_full ; context k GEMM -> rmsnorm_full ; context v GEMM
+  -> flash attention (Sk = context) -> quantise -> o GEMM with x += (.) -> ln_modulate+quantise
+  -> FFN GEMM (+GELU) -> quantise -> FFN GEMM with x += gate*(.)
+"""
+from typing import Dict, Optional
+
+import torch
+
+from . import ops
+from .packed import PackedLinear, act_format, pack_linear
+
+
+def wan_rope_table(f: int, h: int, w: int, head_dim: int = 128, theta: float = 10000.0, device="cpu") -> torch.Tensor:
+    """(cos, sin) per rotated pair for the (f, h, w) grid in raster order, fp32 [f*h*w, 64, 2]; angles in fp64 and the
+    44/42/42 split of the 128 head dims as models/wan/wan_dit.py:38-51,335-346 build them."""
+    def freqs(dim, end):
+        fr = 1.0 / (theta ** (torch.arange(0, dim, 2, device=device)[: dim // 2].double() / dim))
+        return torch.outer(torch.arange(end, dtype=torch.float64, device=device), fr)
+
+    d_h = head_dim // 3
+    d_f = head_dim - 2 * d_h
+    ang = torch.cat([
+        freqs(d_f, f).view(f, 1, 1, -1).expand(f, h, w, -1),
+        freqs(d_h, h).view(1, h, 1, -1).expand(f, h, w, -1),
+        freqs(d_h, w).view(1, 1, w, -1).expand(f, h, w, -1),
+    ], dim=-1).reshape(f * h * w, -1)
+    return torch.stack([torch.cos(ang), torch.sin(ang)], dim=-1).float().contiguous()
+
+
+class HeadExchange:
+    """The Ulysses all-to-all.  ``send`` is ``[P, rows, C]``: chunk p goes to rank p; the result's chunk r came from
+    rank r.  Forward (tokens -> heads): rows = S/P own tokens, chunk p = head group p; result = all S tokens of the
+    own head group.  Backward (heads -> tokens) is the same call on the attention output viewed ``[P, S/P, C]``."""
+
+    def __init__(self, group=None):
+        import torch.distributed as dist
+        self.dist = dist
+        self.group = group
+        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+
+    def __call__(self, send: torch.Tensor, recv: Optional[torch.Tensor] = None) -> torch.Tensor:
+        if self.world == 1:
+            return send
+        if recv is None:
+            recv = torch.empty_like(send)
+        self.dist.all_to_all_single(recv, send, group=self.group)
+        return recv
+
+
+class WanDiTEngine:
+    def __init__(self, state_dict: Dict[str, torch.Tensor], fmt: str = "fp8_channel", device="cuda:0",
+                 num_layers: int = 40, num_heads: int = 40, eps: float = 1e-6, freq_dim: int = 256, group=None,
+                 release_source: bool = False, overlap: bool = True):
+        self.dev = torch.device(device)
+        self.fmt, self.afmt = fmt, act_format(fmt)
+        self.L, self.H, self.eps, self.freq_dim = num_layers, num_heads, eps, freq_dim
+        self.xchg = HeadExchange(group)
+        self.P, self.rank = self.xchg.world, self.xchg.rank
+        if num_heads % self.P:
+            raise ValueError(f"{num_heads} heads do not split over {self.P} ranks")
+        sd = state_dict
+        self.d = sd["time_embedding.0.weight"].shape[0]
+        if self.d // num_heads != 128:
+            raise ValueError("head_dim must be 128")
+        self.overlap = overlap and self.P > 1
+
+        def P_(name):
+            p = pack_linear(sd[name + ".weight"], sd.get(name + ".bias"), fmt, self.dev)
+            if release_source:
+                sd.pop(name + ".weight", None), sd.pop(name + ".bias", None)
+            return p
+
+        def V(name):
+            v = sd[name].to(device=self.dev, dtype=torch.float32).contiguous()
+            if release_source:
+                sd.pop(name, None)
+            return v
+
+        self.patch = P_("patch_embedding")
+        self.text0, self.text2 = P_("text_embedding.0"), P_("text_embedding.2")
+        self.time0, self.time2, self.tproj = P_("time_embedding.0"), P_("time_embedding.2"), P_("time_projection.1")
+        self.blocks = []
+        mods = []
+        for i in range(num_layers):
+            pre = f"blocks.{i}."
+            mods.append(V(pre + "modulation").reshape(6, self.d))
+            self.blocks.append(dict(
+                sq=P_(pre + "self_attn.q"), sk=P_(pre + "self_attn.k"), sv=P_(pre + "self_attn.v"),
+                so=P_(pre + "self_attn.o"), snq=V(pre + "self_attn.norm_q.weight"),
+                snk=V(pre + "self_attn.norm_k.weight"),
+                cq=P_(pre + "cross_attn.q"), ck=P_(pre + "cross_attn.k"), cv=P_(pre + "cross_attn.v"),
+                co=P_(pre + "cross_attn.o"), cnq=V(pre + "cross_attn.norm_q.weight"),
+                cnk=V(pre + "cross_attn.norm_k.weight"),
+                n3_scale=V(pre + "norm3.weight") - 1.0, n3_shift=V(pre + "norm3.bias"),
+                f0=P_(pre + "ffn.0"), f2=P_(pre + "ffn.2")))
+        self.mod = torch.stack(mods).contiguous()          # [L, 6, d]
+        self.head = P_("head.head")
+        self.head_mod = V("head.modulation").reshape(2, self.d)
+        self.out_dim = self.head.out_features // 4
+        self._bufs = None
+        self._comm = torch.cuda.Stream(self.dev) if self.overlap else None
+
+    # ------------------------------------------------------------------ buffers
+    def prepare(self, frames: int, height: int, width: int, ctx_len: int = 512, text_dim: int = 4096):
+        """Buffers for latents [1, C, frames, height, width]; this rank's token slice and RoPE rows."""
+        d, dev, P = self.d, self.dev, self.P
+        gh, gw = height // 2, width // 2
+        S = frames * gh * gw
+        if S % P:
+            raise ValueError(f"{S} tokens do not split over {P} ranks (pad the grid)")
+        Sl = S // P
+        ffn = self.blocks[0]["f0"].out_features if self.blocks else 4 * d
+        qdt = {ops.FMT_BF16: torch.bfloat16, ops.FMT_E4M3: torch.float8_e4m3fn, ops.FMT_INT8: torch.int8}[self.afmt]
+        bf, f32 = torch.bfloat16, torch.float32
+        C = d // P
+        b = dict(S=S, Sl=Sl, grid=(frames, gh, gw), ctx_len=ctx_len, in_ch=self.patch.in_features // 4)
+        b["rope"] = wan_rope_table(frames, gh, gw, device=dev)
+        b["latents"] = torch.zeros(1, b["in_ch"], frames, height, width, dtype=bf, device=dev)
+        b["context_in"] = torch.zeros(ctx_len, text_dim, dtype=bf, device=dev)
+        b["t"] = torch.zeros(1, dtype=f32, device=dev)
+        b["sin"] = torch.zeros(1, self.freq_dim, dtype=f32, device=dev)
+        b["th"], b["tvec"] = torch.zeros(d, dtype=f32, device=dev), torch.zeros(d, dtype=f32, device=dev)
+        b["tmod"] = torch.zeros(6 * d, dtype=f32, device=dev)
+        b["modall"] = torch.zeros(self.L, 6, d, dtype=f32, device=dev)
+        b["headmod"] = torch.zeros(2, d, dtype=f32, device=dev)
+        b["patches"] = torch.zeros(Sl, self.patch.in_features, dtype=bf, device=dev)
+        b["x"] = torch.zeros(Sl, d, dtype=bf, device=dev)
+        b["xq"] = torch.zeros(Sl, max(d, ffn), dtype=qdt, device=dev)
+        b["rs"] = torch.zeros(max(Sl, ctx_len), dtype=f32, device=dev)
+        b["proj"] = torch.zeros(3, Sl, d, dtype=bf, device=dev)              # q, k, v projections of the slice
+        b["send"] = torch.zeros(3, P, Sl, C, dtype=bf, device=dev) if P > 1 else None
+        b["recv"] = torch.zeros(3, P, Sl, C, dtype=bf, device=dev) if P > 1 else None
+        b["ao"] = torch.zeros(P, Sl, C, dtype=bf, device=dev)                # attention out: [S, H/P*128]
+        b["ao_back"] = torch.zeros(P, Sl, C, dtype=bf, device=dev) if P > 1 else None
+        b["hid"] = torch.zeros(Sl, ffn, dtype=bf, device=dev)
+        b["ctx"] = torch.zeros(ctx_len, d, dtype=bf, device=dev)
+        b["ctx_h"] = torch.zeros(ctx_len, d, dtype=bf, device=dev)
+        b["ctxq"] = torch.zeros(ctx_len, max(d, text_dim), dtype=qdt, device=dev)
+        b["ctx_rs"] = torch.zeros(ctx_len, dtype=f32, device=dev)
+        b["ck"], b["cv"] = torch.zeros(ctx_len, d, dtype=bf, device=dev), torch.zeros(ctx_len, d, dtype=bf, device=dev)
+        b["out_tok"] = torch.zeros(Sl, self.head.out_features, dtype=bf, device=dev)
+        b["out_all"] = torch.zeros(S, self.head.out_features, dtype=bf, device=dev) if P > 1 else None
+        self._bufs = b
+        return self
+
+    # -------------------------------------------------------------------- pieces
+    def _gemv(self, p: PackedLinear, x, out, **kw):
+        ops.gemv(p.w, x, p.scale, p.bias, out=out, **kw)
+
+    def _quant(self, x, out, rs):
+        if self.afmt == ops.FMT_BF16:
+            return x, None
+        ops.quant_rows(x, self.afmt, out=out, row_scale=rs)
+        return out, rs
+
+    def _ln(self, x, shift, scale, out, rs):
+        y, s = ops.ln_modulate(x, shift, scale, self.eps, self.afmt, out=out, row_scale=rs)
+        return y, (s if self.afmt != ops.FMT_BF16 else None)
+
+    def _gemm(self, a, rs, p: PackedLinear, **kw):
+        return ops.gemm(a, p.w, row_scale=rs, col_scale=p.scale, bias=p.bias, **kw)
+
+    def set_inputs(self, x, context, timestep):
+        b = self._bufs
+        b["latents"].copy_(x.reshape(b["latents"].shape), non_blocking=True)
+        b["context_in"].copy_(context.reshape(b["context_in"].shape), non_blocking=True)
+        b["t"].copy_(timestep.reshape(1), non_blocking=True)
+
+    def _exchange(self, send, recv, after_event=None):
+        """all-to-all on the communication stream (when overlapping) once the producing kernel has finished;
+        returns an event the consumer waits on."""
+        if not self.overlap:
+            self.xchg(send, recv)
+            return None
+        cur = torch.cuda.current_stream(self.dev)
+        ready = torch.cuda.Event()
+        ready.record(cur)
+        with torch.cuda.stream(self._comm):
+            self._comm.wait_event(ready)
+            self.xchg(send, recv)
+            done = torch.cuda.Event()
+            done.record(self._comm)
+        return done
+
+    def step(self):
+        b, d, H, P = self._bufs, self.d, self.H, self.P
+        Sl, S, Hl, C = b["Sl"], b["S"], self.H // self.P, self.d // self.P
+        x, xq, rs = b["x"], b["xq"], b["rs"]
+        xq_d = xq[:, :d]
+        row0 = self.rank * Sl
+        cur = torch.cuda.current_stream(self.dev)
+        # time embedding / projection (wan_dit.py:327-328); the reference casts the fp64 sinusoid to the model dtype
+        ops.timestep_embedding(b["t"], self.freq_dim, 1.0, 1, round_bf16=True, out=b["sin"])
+        self._gemv(self.time0, b["sin"][0], b["th"], act_out=ops.ACT_SILU)
+        self._gemv(self.time2, b["th"], b["tvec"])
+        self._gemv(self.tproj, b["tvec"], b["tmod"], act_in=ops.ACT_SILU)
+        torch.add(self.mod, b["tmod"].view(1, 6, d), out=b["modall"])          # (modulation + t_mod), every block
+        torch.add(self.head_mod, b["tvec"].view(1, d), out=b["headmod"])       # wan_dit.py:235
+        # text embedding (wan_dit.py:329), replicated on every rank
+        tdim = b["context_in"].shape[1]
+        a, s = self._quant(b["context_in"], b["ctxq"][:, :tdim], b["ctx_rs"])
+        self._gemm(a, s, self.text0, act=ops.ACT_GELU_TANH, out=b["ctx_h"])
+        a, s = self._quant(b["ctx_h"], b["ctxq"][:, :d], b["ctx_rs"])
+        self._gemm(a, s, self.text2, out=b["ctx"])
+        cq_, cs_ = self._quant(b["ctx"], b["ctxq"][:, :d], b["ctx_rs"])        # quantised context, reused by all blocks
+        # patch embedding: Conv3d with kernel = stride = (1,2,2) is a Linear over (c, y, z) patches (wan_dit.py:271-273)
+        fr, gh, gw = b["grid"]
+        Cin = b["in_ch"]
+        pat = (b["latents"][0].reshape(Cin, fr, gh, 2, gw, 2).permute(1, 2, 4, 0, 3, 5).reshape(S, Cin * 4))
+        b["patches"].copy_(pat[row0:row0 + Sl])
+        a, s = self._quant(b["patches"], xq[:, :Cin * 4], rs[:Sl])
+        self._gemm(a, s, self.patch, out=x)
+
+        rope = b["rope"]
+        proj = b["proj"]
+        ao = b["ao"]
+        for li, blk in enumerate(self.blocks):
+            m = b["modall"][li]
+            # ---- self-attention (wan_dit.py:101-107) with the head exchange around it
+            a, sc = self._ln(x, m[0], m[1], xq_d, rs[:Sl])
+            if P == 1:
+                self._gemm(a, sc, blk["sq"], out=proj[0])
+                ops.rmsnorm_full(proj[0], blk["snq"], rope, row0, self.eps)
+                self._gemm(a, sc, blk["sk"], out=proj[1])
+                ops.rmsnorm_full(proj[1], blk["snk"], rope, row0, self.eps)
+                self._gemm(a, sc, blk["sv"], out=proj[2])
+                q4, k4, v4 = (proj[i].view(1, S, H, 128) for i in range(3))
+                ops.flash_attn(q4, k4, v4, out=ao.view(1, S, H, 128))
+                att3 = None
+            else:
+                send, recv = b["send"], b["recv"]
+                self._gemm(a, sc, blk["sq"], out=proj[0])
+                ops.rmsnorm_full(proj[0], blk["snq"], rope, row0, self.eps, out=send[0], chunks=P)
+                e0 = self._exchange(send[0], recv[0])
+                self._gemm(a, sc, blk["sk"], out=proj[1])
+                ops.rmsnorm_full(proj[1], blk["snk"], rope, row0, self.eps, out=send[1], chunks=P)
+                e1 = self._exchange(send[1], recv[1])
+                self._gemm(a, sc, blk["sv"], out=proj[2])
+                send[2].copy_(proj[2].view(Sl, P, C).permute(1, 0, 2))
+                e2 = self._exchange(send[2], recv[2])
+                for e in (e0, e1, e2):
+                    if e is not None:
+                        cur.wait_event(e)
+                q4, k4, v4 = (recv[i].view(1, S, Hl, 128) for i in range(3))
+                ops.flash_attn(q4, k4, v4, out=ao.view(1, S, Hl, 128))
+                e3 = self._exchange(ao, b["ao_back"])
+                if e3 is not None:
+                    cur.wait_event(e3)
+                att3 = b["ao_back"]
+            if self.afmt == ops.FMT_BF16:
+                att = ao.view(S, d) if P == 1 else att3.permute(1, 0, 2).reshape(Sl, d)
+                a, sc = att, None
+            elif P == 1:
+                a, sc = self._quant(ao.view(S, d), xq_d, rs[:Sl])
+            else:
+                a, sc = ops.quant_rows_chunked(att3, self.afmt, out=xq_d, row_scale=rs[:Sl])
+            self._gemm(a, sc, blk["so"], gate=m[2], resid=x, out=x)
+            # ---- cross-attention (wan_dit.py:136-152): no exchange, the context is replicated
+            a, sc = self._ln(x, blk["n3_shift"], blk["n3_scale"], xq_d, rs[:Sl])
+            self._gemm(a, sc, blk["cq"], out=proj[0])
+            ops.rmsnorm_full(proj[0], blk["cnq"], None, 0, self.eps)
+            self._gemm(cq_, cs_, blk["ck"], out=b["ck"])
+            ops.rmsnorm_full(b["ck"], blk["cnk"], None, 0, self.eps)
+            self._gemm(cq_, cs_, blk["cv"], out=b["cv"])
+            L = b["ctx_len"]
+            ops.flash_attn(proj[0].view(1, Sl, H, 128), b["ck"].view(1, L, H, 128), b["cv"].view(1, L, H, 128),
+                           out=proj[1].view(1, Sl, H, 128))
+            a, sc = self._quant(proj[1], xq_d, rs[:Sl])
+            self._gemm(a, sc, blk["co"], resid=x, out=x)
+            # ---- FFN (wan_dit.py:179-182,191-192)
+            a, sc = self._ln(x, m[3], m[4], xq_d, rs[:Sl])
+            self._gemm(a, sc, blk["f0"], act=ops.ACT_GELU_TANH, out=b["hid"])
+            a, sc = self._quant(b["hid"], xq[:, :b["hid"].shape[1]], rs[:Sl])
+            self._gemm(a, sc, blk["f2"], gate=m[5], resid=x, out=x)
+        # ---- head (wan_dit.py:234-237) and unpatchify (:307-317)
+        hm = b["headmod"]
+        a, sc = self._ln(x, hm[0], hm[1], xq_d, rs[:Sl])
+        self._gemm(a, sc, self.head, out=b["out_tok"])
+        if P > 1:
+            self.xchg.dist.all_gather_into_tensor(b["out_all"], b["out_tok"], group=self.xchg.group)
+            tok = b["out_all"]
+        else:
+            tok = b["out_tok"]
+        od = self.out_dim
+        return tok.reshape(fr, gh, gw, 1, 2, 2, od).permute(6, 0, 3, 1, 4, 2, 5).reshape(1, od, fr, gh * 2, gw * 2)
+
+    def forward(self, x, context, timestep, clip_feature=None, y=None):
+        """Signature of ``WanDiT.forward`` (wan_dit.py:319-326); text-to-video only (no image branch)."""
+        if clip_feature is not None or y is not None:
+            raise NotImplementedError("the image-to-video branch (clip_feature / y) is not part of this engine")
+        b = self._bufs
+        shape = (x.shape[2], x.shape[3], x.shape[4], context.shape[1], context.shape[2])
+        if b is None or (b["latents"].shape[2], b["latents"].shape[3], b["latents"].shape[4], b["ctx_len"],
+                         b["context_in"].shape[1]) != shape:
+            self.prepare(*shape)
+        self.set_inputs(x, context, timestep)
+        return self.step().clone()
+
+    __call__ = forward
+
+    def hidden(self):
+        """This rank's slice of the hidden state after the last block (for tests)."""
+        return self._bufs["x"]

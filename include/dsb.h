@@ -76,11 +76,14 @@ int dsb_rmsnorm_rope_heads(void* buf, int64_t ld, int S, int H, int head_dim, in
                            const float* w_k, const float* rope, int rope_row0, float eps, void* stream);
 
 /*
- * In-place RMSNorm over the whole row (width D = heads*128, fp32 weight w[D]) followed by per-head RoPE
- * with the token's 64 (cos, sin) pairs (rope NULL = none).
+ * RMSNorm over the whole row (width D = heads*128, fp32 weight w[D]) followed by per-head RoPE with the token's
+ * 64 (cos, sin) pairs (rope NULL = none); out may equal x (in place).  With out_chunk_cols > 0 column c of row m is
+ * written to out[(c / out_chunk_cols) * out_chunk_stride + m * ld_out + c % out_chunk_cols], i.e. straight into the
+ * per-peer-contiguous send buffer [P][rows][D/P] of the sequence-parallel head exchange (0 = plain rows).
  * Replaces: models/wan/wan_dit.py:61-78 (RMSNorm over all heads) and :54-58 (rope_apply).
  */
-int dsb_rmsnorm_full(void* buf, int64_t ld, int M, int D, const float* w, const float* rope, int rope_row0,
+int dsb_rmsnorm_full(const void* x, int64_t ld_x, void* out, int64_t ld_out, int out_chunk_cols,
+                     int64_t out_chunk_stride, int M, int D, const float* w, const float* rope, int rope_row0,
                      float eps, void* stream);
 
 /*
@@ -90,6 +93,14 @@ int dsb_rmsnorm_full(void* buf, int64_t ld, int M, int D, const float* w, const 
  */
 int dsb_quant_rows(const void* x, int64_t ld_x, void* y, int64_t ld_y, float* row_scale, int M, int K, int out_fmt,
                    void* stream);
+
+/*
+ * dsb_quant_rows reading a chunked activation: column c of row m is x[(c / chunk_cols) * chunk_stride + m * ld_x +
+ * c % chunk_cols] - what the reverse head/sequence all-to-all delivers ([P][rows][K/P]); the output is plain rows.
+ * No reference counterpart (the reference has no sequence parallelism); arithmetic as dsb_quant_rows.
+ */
+int dsb_quant_rows_chunked(const void* x, int64_t ld_x, int chunk_cols, int64_t chunk_stride, void* y, int64_t ld_y,
+                           float* row_scale, int M, int K, int out_fmt, void* stream);
 
 /*
  * y[n] = act_out((sum_k W[n,k] * act_in(x[k])) * w_scale[n*w_scale_stride] + bias[n]) for one activation row

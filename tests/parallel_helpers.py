@@ -1,0 +1,48 @@
+"""Picklable worker models for the CPU (gloo) tests of the multi-GPU wrapper."""
+import os
+import sys
+
+import torch
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+
+def oracle_wan_attention(q, k, v, num_heads):
+    """``wan_dit.attention`` semantics ([B, S, H*D] in and out) on the CPU oracle."""
+    from oracle import ops as O
+    mh = lambda t: t.unflatten(2, (num_heads, t.shape[2] // num_heads)).transpose(1, 2)
+    return O.attention(mh(q), mh(k), mh(v)).transpose(1, 2).flatten(2)
+
+
+class SliceAttentionModel:
+    """Each rank attends with its slice of the tokens through the head exchange, then the slices are gathered."""
+
+    def __init__(self, payload, rank, group, device):
+        import torch.distributed as dist
+        from diffsynth_engine_b200.parallel import HeadExchangeAttention
+        self.dist, self.group = dist, group
+        self.P, self.r = dist.get_world_size(group), dist.get_rank(group)
+        self.num_heads = payload["num_heads"]
+        self.fail_rank = payload.get("fail_rank")
+        self.die_rank = payload.get("die_rank")
+        self.rank = rank
+        self.attn = HeadExchangeAttention(group, inner=oracle_wan_attention)
+
+    def __call__(self, q, k, v):
+        if self.fail_rank == self.rank:
+            raise RuntimeError("injected failure")
+        if self.die_rank == self.rank:
+            os._exit(17)
+        S = q.shape[1]
+        Sl = S // self.P
+        sl = slice(self.r * Sl, (self.r + 1) * Sl)
+        o = self.attn(q[:, sl].contiguous(), k[:, sl].contiguous(), v[:, sl].contiguous(), self.num_heads)
+        out = [torch.empty_like(o) for _ in range(self.P)]
+        self.dist.all_gather(out, o.contiguous(), group=self.group)
+        return torch.cat(out, dim=1)
+
+
+def slice_attention_factory(payload, rank, group, device):
+    return SliceAttentionModel(payload, rank, group, device)

@@ -1,0 +1,94 @@
+"""The multi-GPU wrapper on CPU ranks (gloo, world size 2 and 4): the head exchange reproduces full attention,
+the control plane (pipe, per-step broadcast, batch split + ordered gather, terminate) works, and failures made
+on the host (an exception in one worker, a worker that exits) surface as errors within the deadline instead of
+blocking the parent the way the reference's ``conn.recv()`` does (utils/parallel.py:181)."""
+import time
+
+import pytest
+import torch
+
+from tests.parallel_helpers import oracle_wan_attention, slice_attention_factory
+
+import diffsynth_engine_b200  # noqa: F401  (registers the package alias used by the worker processes)
+from diffsynth_engine_b200.parallel import ParallelWorkerError, UlyssesParallelModel, split_and_get
+
+_PORT = [29720]
+
+
+def _port():
+    _PORT[0] += 1
+    return _PORT[0]
+
+
+def _qkv(B, S, H, seed):
+    g = torch.Generator().manual_seed(seed)
+    return tuple(torch.randn(B, S, H * 16, generator=g) for _ in range(3))
+
+
+@pytest.mark.parametrize("sp", [2, 4])
+def test_head_exchange_matches_full_attention(sp):
+    H, S = 4, 24
+    q, k, v = _qkv(1, S, H, 1)
+    model = UlyssesParallelModel({"num_heads": H}, sp_degree=sp, batch_parallelism=1, master_port=_port(),
+                                 device="cpu", timeout_s=60, factory=slice_attention_factory)
+    try:
+        out = model(q=q, k=k, v=v)
+        ref = oracle_wan_attention(q, k, v, H)
+        assert out.shape == ref.shape
+        assert torch.allclose(out, ref, atol=1e-5, rtol=1e-5)
+        out2 = model(q=q * 2, k=k, v=v)          # a second step through the same workers
+        assert torch.allclose(out2, oracle_wan_attention(q * 2, k, v, H), atol=1e-5, rtol=1e-5)
+    finally:
+        model.close()
+
+
+def test_batch_parallel_split_and_ordered_gather():
+    """batch_parallelism=2 x sp_degree=2: positive/negative halves of a batch-2 input go to the two groups and come
+    back in order (the reference's CFG parallel, utils/parallel.py:123,127-132)."""
+    H, S = 2, 16
+    q, k, v = _qkv(2, S, H, 2)
+    model = UlyssesParallelModel({"num_heads": H}, sp_degree=2, batch_parallelism=2, master_port=_port(),
+                                 device="cpu", timeout_s=60, factory=slice_attention_factory)
+    try:
+        out = model(q=q, k=k, v=v)
+        ref = torch.cat([oracle_wan_attention(q[i:i + 1], k[i:i + 1], v[i:i + 1], H) for i in range(2)])
+        assert torch.allclose(out, ref, atol=1e-5, rtol=1e-5)
+    finally:
+        model.close()
+
+
+def test_worker_exception_reaches_the_parent():
+    q, k, v = _qkv(1, 8, 2, 3)
+    model = UlyssesParallelModel({"num_heads": 2, "fail_rank": 1}, sp_degree=2, master_port=_port(), device="cpu",
+                                 timeout_s=30, factory=slice_attention_factory)
+    t0 = time.time()
+    try:
+        with pytest.raises(ParallelWorkerError, match="injected failure"):
+            model(q=q, k=k, v=v)
+        assert time.time() - t0 < 25
+        with pytest.raises(ParallelWorkerError):   # the group is marked dead, no second hang
+            model(q=q, k=k, v=v)
+    finally:
+        model.close(grace_s=1.0)
+
+
+def test_worker_exit_is_detected():
+    q, k, v = _qkv(1, 8, 2, 4)
+    model = UlyssesParallelModel({"num_heads": 2, "die_rank": 1}, sp_degree=2, master_port=_port(), device="cpu",
+                                 timeout_s=30, factory=slice_attention_factory)
+    t0 = time.time()
+    try:
+        # either the parent sees the dead process first, or a surviving rank reports its broken collective
+        with pytest.raises(ParallelWorkerError, match="exited|closed by peer|failed"):
+            model(q=q, k=k, v=v)
+        assert time.time() - t0 < 25
+    finally:
+        model.close(grace_s=1.0)
+
+
+def test_split_and_get_matches_reference_contract():
+    d = {"a": torch.arange(8).reshape(4, 2), "b": [torch.zeros(2, 1), "keep"], "c": 3}
+    s = split_and_get(d, 2, 1)
+    assert s["a"].tolist() == [[4, 5], [6, 7]] and s["b"][0].shape == (1, 1) and s["b"][1] == "keep" and s["c"] == 3
+    with pytest.raises(ValueError, match="batch split failed"):
+        split_and_get(torch.zeros(1, 3), 2, 0)

@@ -1,0 +1,86 @@
+"""The Wan step engine against the CPU oracle (reduced width/depth), and its sequence-parallel form on two GPUs
+against the single-GPU result."""
+import os
+
+import pytest
+import torch
+
+from oracle import ops as O
+from oracle import wan as OW
+from oracle.flux import round_bf16
+from oracle.linear import LinearEval
+
+pytestmark = pytest.mark.gpu
+synth = __import__("importlib").import_module("diffsynth_engine_b200.synth")
+
+CFG = dict(d=256, ffn=512, num_layers=2, text_dim=64)
+H = 2
+
+
+def _case(seed=24, grid=(3, 8, 10), ctx=16):
+    w = synth.make_state_dict(synth.wan_dit_shapes(**CFG), seed=seed)
+    w = {k: v.bfloat16().float() for k, v in w.items()}
+    x = synth.randn((1, 16, *grid), seed + 1).bfloat16().float()
+    context = synth.randn((1, ctx, CFG["text_dim"]), seed + 2).bfloat16().float()
+    return w, x, context, torch.tensor([417.0])
+
+
+@pytest.mark.parametrize("fmt", ["fp8_channel", "fp8_tensor", "int8_channel", "bf16"])
+def test_wan_engine_matches_oracle(dsb, cuda_dev, fmt):
+    from diffsynth_engine_b200.wan import WanDiTEngine
+    w, x, context, t = _case()
+    ref = OW.wan_dit_forward(w, x, context, t, num_layers=2, H=H, lin=LinearEval(fmt), rt=round_bf16)
+    eng = WanDiTEngine(dict(w), fmt=fmt, device=cuda_dev, num_layers=2, num_heads=H)
+    out = eng(x.to(cuda_dev), context.to(cuda_dev), t.to(cuda_dev)).float().cpu()
+    dsb.ops.check_status(0)
+    err = O.rel_l2(out, ref)
+    exact = O.rel_l2(out, OW.wan_dit_forward(w, x, context, t, num_layers=2, H=H))
+    print(f"wan tiny model {fmt}: rel-L2 vs same-quantisation oracle {err:.3e}, vs exact fp32 {exact:.3e}")
+    assert out.shape == ref.shape
+    assert err < (4e-3 if fmt == "bf16" else 2e-2)
+
+
+def test_wan_rope_table_matches_oracle(dsb, cuda_dev):
+    from diffsynth_engine_b200.wan import wan_rope_table
+    assert torch.equal(wan_rope_table(3, 4, 5, device=cuda_dev).cpu(), O.wan_rope_table(3, 4, 5))
+
+
+def test_chunked_layout_kernels(dsb, cuda_dev):
+    """rmsnorm_full writing the [P][rows][D/P] send layout and quant_rows reading it back."""
+    g = torch.Generator().manual_seed(5)
+    M, Hh, P = 50, 4, 2
+    D = Hh * 128
+    x = torch.randn(M, D, generator=g).bfloat16()
+    wgt = 1 + 0.1 * torch.randn(D, generator=g)
+    table = O.wan_rope_table(2, 5, 5)
+    ref = O.apply_rope_pairs(O.rmsnorm(x, wgt).reshape(M, Hh, 128).transpose(0, 1), table[:M]).transpose(0, 1)
+    ref = ref.reshape(M, D)
+    out = torch.zeros(P, M, D // P, dtype=torch.bfloat16, device=cuda_dev)
+    dsb.ops.rmsnorm_full(x.to(cuda_dev), wgt.to(cuda_dev), table.to(cuda_dev), 0, 1e-6, out=out, chunks=P)
+    got = out.permute(1, 0, 2).reshape(M, D).float().cpu()
+    assert O.rel_l2(got, ref) < 3e-3
+    q, s = dsb.ops.quant_rows_chunked(out)
+    q_ref, s_ref = O.quant_rows_e4m3(out.permute(1, 0, 2).reshape(M, D).float().cpu())
+    assert torch.equal(s.cpu(), s_ref) and torch.equal(q.cpu().view(torch.uint8), q_ref.view(torch.uint8))
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+@pytest.mark.parametrize("fmt", ["fp8_channel", "bf16"])
+def test_sequence_parallel_two_gpus_matches_one(dsb, cuda_dev, fmt):
+    """UlyssesParallelModel (2 ranks, NCCL) against the single-GPU engine on the same weights and inputs."""
+    os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+    from diffsynth_engine_b200.parallel import UlyssesParallelModel
+    from diffsynth_engine_b200.wan import WanDiTEngine
+    w, x, context, t = _case(seed=30, grid=(3, 8, 10))
+    one = WanDiTEngine(dict(w), fmt=fmt, device=cuda_dev, num_layers=2, num_heads=H)
+    ref = one(x.to(cuda_dev), context.to(cuda_dev), t.to(cuda_dev)).float().cpu()
+    model = UlyssesParallelModel(dict(w), sp_degree=2, master_port=29641, device="cuda", timeout_s=120, fmt=fmt,
+                                 num_layers=2, num_heads=H)
+    try:
+        out = model(x=x, context=context, timestep=t).float().cpu()
+        out2 = model(x=x, context=context, timestep=t).float().cpu()
+    finally:
+        model.close()
+    # same kernels on the same numbers, only the attention tiling (heads per rank) differs
+    assert O.rel_l2(out, ref) < 3e-3
+    assert torch.equal(out, out2)
