@@ -26,6 +26,8 @@ PKG_DIR = os.path.join(ROOT, "diffsynth-engine_b200")
 sys.path.insert(0, ROOT)
 
 FLUX = dict(d=3072, H=24, n_double=19, n_single=38, S_txt=512, height=128, width=128, txt_dim=4096, pooled_dim=768)
+# Wan2.1-14B text-to-video at 81 frames x 480 x 832: latent 21 x 60 x 104, patch (1,2,2) -> 21*30*52 = 32760 tokens
+WAN = dict(d=5120, ffn=13824, num_layers=40, H=40, frames=21, height=60, width=104, ctx=512, text_dim=4096)
 
 
 def load_package():
@@ -152,6 +154,78 @@ def cpu_reference_arm(steps=1, warmup=0, budget_s=150.0):
                 ms_per_step=step_s * 1e3, samples=len(times))
 
 
+def wan_step_flops(c=WAN):
+    S, d, L = c["frames"] * (c["height"] // 2) * (c["width"] // 2), c["d"], c["num_layers"]
+    lin = L * (2 * S * d * (8 * d + 2 * c["ffn"]) + 2 * c["ctx"] * d * 2 * d)
+    attn = L * (4 * S * S * d + 4 * S * c["ctx"] * d)
+    return lin, attn
+
+
+def run_wan(args, torch, pkg, synth, dev, dist, rank, world, steps, warmup):
+    """Wan2.1-14B-architecture step, sequence-parallel (Ulysses) over all ranks: ONE video, strong scaling."""
+    wan = importlib.import_module("diffsynth_engine_b200.wan")
+    c = dict(WAN)
+    if args.wan_layers:
+        c["num_layers"] = args.wan_layers
+    shapes = synth.wan_dit_shapes(d=c["d"], ffn=c["ffn"], num_layers=c["num_layers"], text_dim=c["text_dim"])
+    sd = synth.make_state_dict(shapes, seed=1234, device=dev, dtype=torch.bfloat16)   # same weights on every rank
+    eng = wan.WanDiTEngine(sd, fmt=args.wan_fmt, device=dev, num_layers=c["num_layers"], num_heads=c["H"],
+                           group=(dist.group.WORLD if dist is not None else None), release_source=True)
+    del sd
+    torch.cuda.empty_cache()
+    eng.prepare(c["frames"], c["height"], c["width"], c["ctx"], c["text_dim"])
+    h_x = synth.randn((1, 16, c["frames"], c["height"], c["width"]), 7).bfloat16().pin_memory()
+    h_ctx = synth.randn((1, c["ctx"], c["text_dim"]), 8).bfloat16().pin_memory()
+    h_t = torch.tensor([500.0]).pin_memory()
+    h_out = torch.empty((1, 16, c["frames"], c["height"], c["width"]), dtype=torch.bfloat16).pin_memory()
+
+    def sync():
+        torch.cuda.synchronize()
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    eng.set_inputs(h_x, h_ctx, h_t)
+    n0 = pkg._lib.launches
+    for _ in range(max(1, warmup)):
+        eng.step()
+    launches = (pkg._lib.launches - n0) // max(1, warmup)
+    sync()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        eng.step()
+    e1.record()
+    sync()
+    ms = e0.elapsed_time(e1) / steps
+    e0.record()
+    for _ in range(steps):
+        eng.set_inputs(h_x, h_ctx, h_t)
+        out = eng.step()
+        if rank == 0:
+            h_out.copy_(out, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+    e1.record()
+    sync()
+    ms_e2e = e0.elapsed_time(e1) / steps
+    if dist is not None:
+        t = torch.tensor([ms, ms_e2e], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms, ms_e2e = float(t[0]), float(t[1])
+    pkg.ops.check_status(dev.index)
+    lin_f, attn_f = wan_step_flops(c)
+    peaks = measured_peaks()
+    fp8 = args.wan_fmt != "bf16"
+    roof_ms = (lin_f / (peaks["bf16"] * (2 if fp8 else 1) * 1e12) + attn_f / (peaks["bf16"] * 1e12)) * 1e3
+    return {"workload": f"wan2.1-14B-arch t2v DiT step, 81x480x832 (32760 tokens, 512 context tokens), batch 1, "
+                        f"{c['num_layers']} blocks, weights {args.wan_fmt}, Ulysses sequence parallel x{world}",
+            "steps_per_s": 1e3 / ms, "ms_per_step": ms, "e2e_steps_per_s": 1e3 / ms_e2e, "e2e_ms_per_step": ms_e2e,
+            "n_gpus": world, "scaling": "strong", "step_tflop": (lin_f + attn_f) / 1e12,
+            "frac_of_roofline_all_gpus": roof_ms / (ms * world), "gpu_launches_per_step": launches,
+            "h2d_bytes_per_step": sum(t.numel() * t.element_size() for t in (h_x, h_ctx, h_t)),
+            "d2h_bytes_per_step": h_out.numel() * h_out.element_size()}
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -161,6 +235,12 @@ def main():
     ap.add_argument("--fmt", default="fp8_tensor")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--blocks", default=None, help="n_double,n_single override (reduced-depth debugging; not a bench)")
+    ap.add_argument("--workload", default="flux", choices=["flux", "wan", "both"],
+                    help="flux: the headline line; wan: Wan-14B sequence-parallel step only; both: flux line with the "
+                         "wan result attached under 'wan'")
+    ap.add_argument("--wan-fmt", default="fp8_channel")
+    ap.add_argument("--wan-layers", type=int, default=0, help="reduced depth (debugging; not a bench)")
+    ap.add_argument("--wan-steps", type=int, default=2)
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -198,6 +278,23 @@ def main():
     if world > 1:
         import torch.distributed as dist
         dist.init_process_group("nccl", device_id=dev)
+
+    if args.workload == "wan":
+        r = run_wan(args, torch, pkg, synth, dev, dist, rank, world, max(1, args.steps), max(1, min(args.warmup, 3)))
+        if rank == 0:
+            line = {"metric": "DiT denoise steps/s", "value": r["steps_per_s"], "unit": "steps/s", "n_gpus": world,
+                    "steps": args.steps, "warmup": max(1, min(args.warmup, 3)), "ms_per_step": r["ms_per_step"],
+                    "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+                    "dtype": "fp8_e4m3 linear, bf16 attention" if args.wan_fmt != "bf16" else "bf16",
+                    "data": "synthetic", "config": {"workload": r["workload"], "parallelism": f"sp{world}"},
+                    "e2e": {"value": r["e2e_steps_per_s"], "unit": "steps/s",
+                            "h2d_bytes_per_step": r["h2d_bytes_per_step"], "d2h_bytes_per_step": r["d2h_bytes_per_step"]},
+                    "gpu_launches": r["gpu_launches_per_step"] * args.steps, "wan": r}
+            print(json.dumps(line), flush=True)
+        if dist is not None:
+            dist.barrier()
+            dist.destroy_process_group()
+        return
 
     # random-init weights of the architecture, drawn on the device, packed to FP8 layer by layer
     shapes = synth.flux_dit_shapes(d=cfg["d"], H=cfg["H"], n_double=cfg["n_double"], n_single=cfg["n_single"],
@@ -319,6 +416,10 @@ def main():
                     "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms, "wall_ms_per_step": e2e_wall_ms},
             "gpu_launches": launches_per_step * args.steps, "gpu_launches_per_step": launches_per_step,
             "roofline": roofline}
+    if args.workload == "both":
+        del eng
+        torch.cuda.empty_cache()
+        line["wan"] = run_wan(args, torch, pkg, synth, dev, dist, rank, world, args.wan_steps, 1)
     if rank == 0:
         if not args.no_cpu_baseline and world == 1:
             r = cpu_reference_arm(steps=1, warmup=0)

@@ -15,6 +15,7 @@
 // HBM layout: A and W are row-major with K contiguous, so both operands are
 // "K-major" for the tensor core and no transpose or repack is ever needed; the
 // FP8/INT8 payload is the plain [N,K] byte matrix produced by the prepack.
+#include <cstdlib>
 #include <mutex>
 
 #include "common.cuh"
@@ -50,30 +51,38 @@ constexpr int kEpiWarps = 8;               // two per TMEM lane quadrant, each d
 constexpr int kStageSlotBytes = 32 * 128;  // 32 rows x 64 bf16
 constexpr int kStageBytes = kEpiWarps * kStageSlotBytes;
 
-template <int BLOCK_N>
+// CTAS = 1: one CTA computes 128 x BLOCK_N.  CTAS = 2: a CTA pair computes 256 x BLOCK_N with one tcgen05.mma
+// (cta_group::2); each CTA stages 128 rows of A and BLOCK_N/2 rows of W, which halves the shared-memory bytes
+// per flop (the single-CTA kernel is bound by that traffic) and the L2 reads of W.
+template <int BLOCK_N, int CTAS>
 struct GemmSmem {
   static constexpr int kStageA = kBlockM * kSlabBytes;
-  static constexpr int kStageB = BLOCK_N * kSlabBytes;
+  static constexpr int kStageB = (BLOCK_N / CTAS) * kSlabBytes;
   static constexpr int kStage = kStageA + kStageB;
-  static constexpr int kStages = (BLOCK_N == 256) ? 4 : 6;
+  static constexpr int kStages = (kStage == 48 * 1024) ? 4 : 6;
   static constexpr int kBarBytes = 256;
   static constexpr int kTotal = kStages * kStage + kStageBytes + kBarBytes + 1024;  // + alignment slack
 };
 
-template <int KIND, int BLOCK_N>
+template <int KIND, int BLOCK_N, int CTAS>
 __global__ void __launch_bounds__(kGemmThreads, 1)
     gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                 const __grid_constant__ CUtensorMap tmap_o0, const __grid_constant__ CUtensorMap tmap_o1,
                 const __grid_constant__ CUtensorMap tmap_r, int M, int N, int K, GemmEpilogue ep) {
-  using SM = GemmSmem<BLOCK_N>;
+  using SM = GemmSmem<BLOCK_N, CTAS>;
   constexpr int kStages = SM::kStages;
   constexpr int kElemBytes = (KIND == KIND_F16) ? 2 : 1;
   constexpr int kSlabElems = kSlabBytes / kElemBytes;
   constexpr uint32_t kTmemCols = 2 * BLOCK_N;
+  constexpr int kTileM = kBlockM * CTAS;  // rows of one scheduled tile (both CTAs of a pair)
   constexpr uint32_t kIdesc =
-      (KIND == KIND_F16)  ? make_idesc(DFMT_F32, FMT_BF16, FMT_BF16, 0, 0, kBlockM, BLOCK_N)
-      : (KIND == KIND_F8) ? make_idesc(DFMT_F32, FMT_E4M3, FMT_E4M3, 0, 0, kBlockM, BLOCK_N)
-                          : make_idesc(DFMT_S32, FMT_S8, FMT_S8, 0, 0, kBlockM, BLOCK_N);
+      (KIND == KIND_F16)  ? make_idesc(DFMT_F32, FMT_BF16, FMT_BF16, 0, 0, kTileM, BLOCK_N)
+      : (KIND == KIND_F8) ? make_idesc(DFMT_F32, FMT_E4M3, FMT_E4M3, 0, 0, kTileM, BLOCK_N)
+                          : make_idesc(DFMT_S32, FMT_S8, FMT_S8, 0, 0, kTileM, BLOCK_N);
+  const uint32_t cta_rank = (CTAS == 2) ? cluster_ctarank() : 0u;
+  const bool leader = cta_rank == 0;
+  const int unit = blockIdx.x / CTAS;        // which CTA (pair) of the persistent grid
+  const int num_units = gridDim.x / CTAS;
 
   extern __shared__ uint8_t smem_raw[];
   // 1024-byte alignment: the 128-byte swizzle pattern repeats every 8 rows = 1024 bytes.
@@ -98,7 +107,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(&tmem_full[a], 1);
-      mbar_init(&tmem_empty[a], kEpiWarps * 32);
+      mbar_init(&tmem_empty[a], CTAS * kEpiWarps * 32);
     }
     for (int i = 0; i < kEpiWarps; ++i) mbar_init(&resid_bar[i], 1);
     *abort_flag = 0;
@@ -110,15 +119,21 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
     tma_prefetch_desc(&tmap_o0);
   }
   if (warp == 1) {
-    tmem_alloc(tmem_slot, kTmemCols);
-    tmem_relinquish();
+    if constexpr (CTAS == 2) {
+      tmem_alloc_cg2(tmem_slot, kTmemCols);
+      tmem_relinquish_cg2();
+    } else {
+      tmem_alloc(tmem_slot, kTmemCols);
+      tmem_relinquish();
+    }
   }
   tc_fence_before();
   __syncthreads();
+  if constexpr (CTAS == 2) cluster_sync_all();  // the peer's barriers are initialised before anyone signals them
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
-  const int tiles_m = (M + kBlockM - 1) / kBlockM;
+  const int tiles_m = (M + kTileM - 1) / kTileM;
   const int tiles_n = (N + BLOCK_N - 1) / BLOCK_N;
   const int num_tiles = tiles_m * tiles_n;
   const int num_kb = (K + kSlabElems - 1) / kSlabElems;
@@ -128,16 +143,24 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
     if (lane == 0) {
       int stage = 0;
       uint32_t phase = 0;
-      for (int t = blockIdx.x; t < num_tiles; t += gridDim.x) {
-        const int m0 = (t % tiles_m) * kBlockM;
-        const int n0 = (t / tiles_m) * BLOCK_N;
+      for (int t = unit; t < num_tiles; t += num_units) {
+        const int m0 = (t % tiles_m) * kTileM + static_cast<int>(cta_rank) * kBlockM;
+        const int n0 = (t / tiles_m) * BLOCK_N + static_cast<int>(cta_rank) * (BLOCK_N / CTAS);
         for (int kb = 0; kb < num_kb; ++kb) {
           if (!mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag)) goto producer_done;
           uint8_t* sa = smem + stage * SM::kStage;
           uint8_t* sb = sa + SM::kStageA;
-          mbar_expect_tx(&full_bar[stage], SM::kStage);
-          tma_load_2d(sa, &tmap_a, &full_bar[stage], kb * kSlabElems, m0);
-          tma_load_2d(sb, &tmap_b, &full_bar[stage], kb * kSlabElems, n0);
+          if constexpr (CTAS == 2) {
+            // both CTAs' bytes are counted on the leader's barrier, which the leader arms for the pair
+            if (leader) mbar_expect_tx(&full_bar[stage], 2 * SM::kStage);
+            const uint32_t bar = mapa_u32(smem_u32(&full_bar[stage]), 0);
+            tma_load_2d_cg2(sa, &tmap_a, bar, kb * kSlabElems, m0);
+            tma_load_2d_cg2(sb, &tmap_b, bar, kb * kSlabElems, n0);
+          } else {
+            mbar_expect_tx(&full_bar[stage], SM::kStage);
+            tma_load_2d(sa, &tmap_a, &full_bar[stage], kb * kSlabElems, m0);
+            tma_load_2d(sb, &tmap_b, &full_bar[stage], kb * kSlabElems, n0);
+          }
           if (++stage == kStages) {
             stage = 0;
             phase ^= 1;
@@ -148,11 +171,11 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
   producer_done:;
   } else if (warp == 1) {
     // -------------------------------------------------------------- MMA issuer
-    if (lane == 0) {
+    if (lane == 0 && leader) {
       int stage = 0;
       uint32_t phase = 0;
       int it = 0;
-      for (int t = blockIdx.x; t < num_tiles; t += gridDim.x, ++it) {
+      for (int t = unit; t < num_tiles; t += num_units, ++it) {
         const int acc = it & 1;
         const uint32_t acc_phase = (it >> 1) & 1;
         if (!mbar_wait(&tmem_empty[acc], acc_phase ^ 1, abort_flag)) goto mma_done;
@@ -167,15 +190,28 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
 #pragma unroll
           for (int k = 0; k < 4; ++k) {
             // advancing 32 bytes along K inside the swizzle row = +2 in the (addr >> 4) field
-            mma_ss<KIND>(d_tmem, adesc + 2 * k, bdesc + 2 * k, kIdesc, (kb | k) != 0 ? 1u : 0u);
+            if constexpr (CTAS == 2)
+              mma_ss_cg2<KIND>(d_tmem, adesc + 2 * k, bdesc + 2 * k, kIdesc, (kb | k) != 0 ? 1u : 0u);
+            else
+              mma_ss<KIND>(d_tmem, adesc + 2 * k, bdesc + 2 * k, kIdesc, (kb | k) != 0 ? 1u : 0u);
           }
-          tc_commit(&empty_bar[stage]);
+          if constexpr (CTAS == 2) {  // the stage is free in both CTAs once these MMAs have read it
+            tc_commit_cg2(smem_u32(&empty_bar[stage]));
+            tc_commit_cg2(mapa_u32(smem_u32(&empty_bar[stage]), 1));
+          } else {
+            tc_commit(&empty_bar[stage]);
+          }
           if (++stage == kStages) {
             stage = 0;
             phase ^= 1;
           }
         }
-        tc_commit(&tmem_full[acc]);
+        if constexpr (CTAS == 2) {
+          tc_commit_cg2(smem_u32(&tmem_full[acc]));
+          tc_commit_cg2(mapa_u32(smem_u32(&tmem_full[acc]), 1));
+        } else {
+          tc_commit(&tmem_full[acc]);
+        }
       }
     }
   mma_done:;
@@ -191,10 +227,10 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
     const uint32_t row_off = static_cast<uint32_t>(lane) * 128u;
     const uint32_t sw = static_cast<uint32_t>(lane & 7);
     int it = 0;
-    for (int t = blockIdx.x; t < num_tiles; t += gridDim.x, ++it) {
+    for (int t = unit; t < num_tiles; t += num_units, ++it) {
       const int acc = it & 1;
       const uint32_t acc_phase = (it >> 1) & 1;
-      const int m0 = (t % tiles_m) * kBlockM;
+      const int m0 = (t % tiles_m) * kTileM + static_cast<int>(cta_rank) * kBlockM;
       const int n0 = (t / tiles_m) * BLOCK_N;
       if (!mbar_wait(&tmem_full[acc], acc_phase, abort_flag)) break;
       tc_fence_after();
@@ -378,7 +414,12 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
         }
       }
       tc_fence_before();
-      mbar_arrive(&tmem_empty[acc]);
+      if constexpr (CTAS == 2) {  // the leader's MMA thread waits for the epilogues of both CTAs
+        if (leader) mbar_arrive(&tmem_empty[acc]);
+        else mbar_arrive_cluster(mapa_u32(smem_u32(&tmem_empty[acc]), 0));
+      } else {
+        mbar_arrive(&tmem_empty[acc]);
+      }
       if (!alive) break;
     }
     if (lane == 0) bulk_wait<0>();  // every store of this warp has left shared memory and been written
@@ -389,30 +430,75 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
   if (*abort_flag) __nanosleep(200000);
   tc_fence_before();
   __syncthreads();
+  if constexpr (CTAS == 2) cluster_sync_all();  // neither CTA leaves (or frees TMEM) while its peer may still use it
   if (warp == 1) {
     tc_fence_after();
-    tmem_dealloc(tmem_base, kTmemCols);
+    if constexpr (CTAS == 2) tmem_dealloc_cg2(tmem_base, kTmemCols);
+    else tmem_dealloc(tmem_base, kTmemCols);
   }
   if (threadIdx.x == 0 && *abort_flag && ep.status) atomicCAS(ep.status, 0, DSB_ERR_TIMEOUT);
 }
 
-template <int KIND, int BLOCK_N>
+template <int KIND, int BLOCK_N, int CTAS>
 static int launch_gemm(const void* A, int64_t lda, const void* W, int64_t ldw, int M, int N, int K,
                        const GemmEpilogue& ep, const CUtensorMap& to0, const CUtensorMap& to1, const CUtensorMap& tr,
                        cudaStream_t st) {
-  using SM = GemmSmem<BLOCK_N>;
+  using SM = GemmSmem<BLOCK_N, CTAS>;
   constexpr int esz = (KIND == KIND_F16) ? 2 : 1;
   constexpr int slab_elems = kSlabBytes / esz;
   const CUtensorMapDataType dt = (KIND == KIND_F16) ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_UINT8;
   CUtensorMap ta, tb;
   if (make_tmap_2d(&ta, dt, esz, A, M, K, lda * esz, kBlockM, slab_elems) != DSB_OK) return DSB_ERR_CUDA;
-  if (make_tmap_2d(&tb, dt, esz, W, N, K, ldw * esz, BLOCK_N, slab_elems) != DSB_OK) return DSB_ERR_CUDA;
-  auto kern = gemm_kernel<KIND, BLOCK_N>;
+  if (make_tmap_2d(&tb, dt, esz, W, N, K, ldw * esz, BLOCK_N / CTAS, slab_elems) != DSB_OK) return DSB_ERR_CUDA;
+  auto kern = gemm_kernel<KIND, BLOCK_N, CTAS>;
   DSB_ENSURE_SMEM(kern, SM::kTotal);
-  const int tiles = ((M + kBlockM - 1) / kBlockM) * ((N + BLOCK_N - 1) / BLOCK_N);
-  const int grid = tiles < sm_count() ? tiles : sm_count();
-  gemm_kernel<KIND, BLOCK_N><<<grid, kGemmThreads, SM::kTotal, st>>>(ta, tb, to0, to1, tr, M, N, K, ep);
+  const int tiles = ((M + kBlockM * CTAS - 1) / (kBlockM * CTAS)) * ((N + BLOCK_N - 1) / BLOCK_N);
+  if constexpr (CTAS == 1) {
+    const int grid = tiles < sm_count() ? tiles : sm_count();
+    kern<<<grid, kGemmThreads, SM::kTotal, st>>>(ta, tb, to0, to1, tr, M, N, K, ep);
+  } else {
+    // persistent grid = the CTA pairs the device can hold at once (GPCs with an odd SM count leave one SM out)
+    static int resident_pairs[64] = {0};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return DSB_ERR_CUDA;
+    cudaLaunchConfig_t cfg = {};
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    if (resident_pairs[dev] == 0) {
+      cfg.gridDim = dim3(sm_count() & ~1, 1, 1);
+      cfg.blockDim = dim3(kGemmThreads, 1, 1);
+      cfg.dynamicSmemBytes = SM::kTotal;
+      cfg.attrs = attr;
+      cfg.numAttrs = 1;
+      int n = 0;
+      if (cudaOccupancyMaxActiveClusters(&n, kern, &cfg) != cudaSuccess || n <= 0) n = sm_count() / 2;
+      resident_pairs[dev] = n;
+    }
+    const int units = resident_pairs[dev];
+    const int grid = (tiles < units ? tiles : units) * CTAS;
+    cfg.gridDim = dim3(grid, 1, 1);
+    cfg.blockDim = dim3(kGemmThreads, 1, 1);
+    cfg.dynamicSmemBytes = SM::kTotal;
+    cfg.stream = st;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    if (cudaLaunchKernelEx(&cfg, kern, ta, tb, to0, to1, tr, M, N, K, ep) != cudaSuccess) return DSB_ERR_CUDA;
+  }
   return cudaGetLastError() == cudaSuccess ? DSB_OK : DSB_ERR_CUDA;
+}
+
+// CTA pairs (256 x 256 tiles) are used when the problem has enough rows to fill them; DSB_GEMM_PAIR=0 in the
+// environment turns them off (single-CTA tiles only).
+static bool pair_mode_enabled() {
+  static int v = -1;
+  if (v < 0) {
+    const char* e = getenv("DSB_GEMM_PAIR");
+    v = (e && e[0] == '0') ? 0 : 1;
+  }
+  return v == 1;
 }
 
 // Tile width: 256 columns unless that leaves SMs idle that 128-wide tiles would fill.
@@ -494,9 +580,11 @@ static int gemm_common(const void* A, int64_t lda, const void* W, int64_t ldw, i
     return DSB_ERR_CUDA;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   const int bn = nq_w ? 256 : pick_block_n(M, N);  // the fused norm needs a whole head per epilogue warp
-#define DSB_GEMM_DISPATCH(KIND)                                                        \
-  (bn == 256 ? launch_gemm<KIND, 256>(A, lda, W, ldw, M, N, K, ep, to0, to1, tr, st)   \
-             : launch_gemm<KIND, 128>(A, lda, W, ldw, M, N, K, ep, to0, to1, tr, st))
+  const bool pair = pair_mode_enabled() && bn == 256 && M > 256 && N >= 256;
+#define DSB_GEMM_DISPATCH(KIND)                                                              \
+  (pair        ? launch_gemm<KIND, 256, 2>(A, lda, W, ldw, M, N, K, ep, to0, to1, tr, st)    \
+   : bn == 256 ? launch_gemm<KIND, 256, 1>(A, lda, W, ldw, M, N, K, ep, to0, to1, tr, st)    \
+               : launch_gemm<KIND, 128, 1>(A, lda, W, ldw, M, N, K, ep, to0, to1, tr, st))
   if (fmt == DSB_FMT_BF16) return DSB_GEMM_DISPATCH(KIND_F16);
   if (fmt == DSB_FMT_E4M3) return DSB_GEMM_DISPATCH(KIND_F8);
   return DSB_GEMM_DISPATCH(KIND_I8);
