@@ -9,6 +9,8 @@ Prints ONE JSON line.  `value` = whole-job denoise steps/s with inputs resident 
 step, CUDA events, max over ranks); `e2e` = the same through `FluxDiTEngine.forward`-style host buffers (pinned
 host -> device copies of every input and a device -> host read of the model output inside the timed region).
 With N > 1 every rank denoises its own latent (independent replicas, weak scaling, no data-path collective).
+By default the line also carries, under "wan", the Wan2.1-14B-architecture 480p step run sequence-parallel
+(Ulysses) over the same N GPUs on ONE video (strong scaling); `--workload flux|wan` runs one of the two.
 """
 import argparse
 import importlib
@@ -235,7 +237,7 @@ def main():
     ap.add_argument("--fmt", default="fp8_tensor")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--blocks", default=None, help="n_double,n_single override (reduced-depth debugging; not a bench)")
-    ap.add_argument("--workload", default="flux", choices=["flux", "wan", "both"],
+    ap.add_argument("--workload", default="both", choices=["flux", "wan", "both"],
                     help="flux: the headline line; wan: Wan-14B sequence-parallel step only; both: flux line with the "
                          "wan result attached under 'wan'")
     ap.add_argument("--wan-fmt", default="fp8_channel")
@@ -276,6 +278,8 @@ def main():
     dev = torch.device(f"cuda:{local_rank}")
     dist = None
     if world > 1:
+        if os.environ.get("NCCL_DEBUG", "").upper() == "VERSION":
+            os.environ["NCCL_DEBUG"] = "WARN"   # keep NCCL's version banner off stdout: one JSON line only
         import torch.distributed as dist
         dist.init_process_group("nccl", device_id=dev)
 
