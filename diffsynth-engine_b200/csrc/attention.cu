@@ -152,25 +152,33 @@ __global__ void __launch_bounds__(kAttnThreads, 1)
     if (lane == 0) {
       constexpr uint32_t idesc_qk = make_idesc(DFMT_F32, FMT_BF16, FMT_BF16, 0, 0, 128, 128);
       constexpr uint32_t idesc_pv = make_idesc(DFMT_F32, FMT_BF16, FMT_BF16, 0, 1, 128, 128);
+      // One tcgen05.mma here is only 64 tensor-core cycles of work, so the issuing thread must not spend more than
+      // a few instructions per MMA: every descriptor is a base computed once plus a compile-time offset in the
+      // low word (the address field, in 16-byte units, never carries into the upper word).
+      const uint64_t q_desc0 = make_desc_k_sw128(smem_u32(sQ));
+      const uint64_t k_desc0 = make_desc_k_sw128(smem_u32(sK));
+      const uint64_t v_desc0 = make_desc_mn_sw128(smem_u32(sV), kHalfBytes, 1024);
+      constexpr uint32_t kTile16 = kTileBytes >> 4, kHalf16 = kHalfBytes >> 4;
       auto issue_qk = [&](int q, int st) {
-        const uint32_t a_base = smem_u32(sQ + q * kTileBytes);
-        const uint32_t b_base = smem_u32(sK + st * kTileBytes);
+        const uint64_t ad0 = q_desc0 + static_cast<uint32_t>(q) * kTile16;
+        const uint64_t bd0 = k_desc0 + static_cast<uint32_t>(st) * kTile16;
+        const uint32_t d = tmem_base + q * 128;
 #pragma unroll
         for (int kk = 0; kk < 8; ++kk) {
-          const uint32_t off = (kk >> 2) * kHalfBytes;
-          const uint64_t ad = make_desc_k_sw128(a_base + off) + 2 * (kk & 3);
-          const uint64_t bd = make_desc_k_sw128(b_base + off) + 2 * (kk & 3);
-          mma_ss<KIND_F16>(tmem_base + q * 128, ad, bd, idesc_qk, kk > 0 ? 1u : 0u);
+          constexpr uint32_t dummy = 0;
+          (void)dummy;
+          const uint32_t off = (kk >> 2) * kHalf16 + 2 * (kk & 3);
+          mma_ss<KIND_F16>(d, ad0 + off, bd0 + off, idesc_qk, kk > 0 ? 1u : 0u);
         }
       };
       auto issue_pv = [&](int q, int st, bool accumulate) {
-        const uint32_t v_base = smem_u32(sV + st * kTileBytes);
+        const uint64_t bd0 = v_desc0 + static_cast<uint32_t>(st) * kTile16;
+        const uint32_t d = tmem_base + 256 + q * 128;
+        const uint32_t a = tmem_base + q * 128;
 #pragma unroll
         for (int kk = 0; kk < 8; ++kk) {
-          // 16 keys per instruction = 16 rows of 128 bytes; the two 64-column halves are kHalfBytes apart
-          const uint64_t bd = make_desc_mn_sw128(v_base + kk * 2048, kHalfBytes, 1024);
-          mma_ts_f16(tmem_base + 256 + q * 128, tmem_base + q * 128 + kk * 8, bd, idesc_pv,
-                     (accumulate || kk > 0) ? 1u : 0u);
+          // 16 keys per instruction = 16 rows of 128 bytes (2048 bytes = 128 units) further into the V tile
+          mma_ts_f16(d, a + kk * 8, bd0 + kk * 128u, idesc_pv, (accumulate || kk > 0) ? 1u : 0u);
         }
       };
       int kst = 0, vst = 0;
