@@ -27,6 +27,7 @@ c_i, c_i64, c_f, c_p = ctypes.c_int, ctypes.c_int64, ctypes.c_float, ctypes.c_vo
 _SIGS = {
     "dsb_version": [],
     "dsb_ln_modulate": [c_p, c_i64, c_p, c_p, c_p, c_i64, c_p, c_i, c_i, c_f, c_i, c_p],
+    "dsb_ln_modulate2": [c_p, c_i64, c_p, c_p, c_i, c_p, c_p, c_p, c_i64, c_p, c_i, c_i, c_f, c_i, c_p],
     "dsb_gate_residual": [c_p, c_i64, c_p, c_i64, c_p, c_p, c_i64, c_i, c_i, c_p],
     "dsb_rmsnorm_rope_heads": [c_p, c_i64, c_i, c_i, c_i, c_i, c_p, c_p, c_p, c_i, c_f, c_p],
     "dsb_rmsnorm_full": [c_p, c_i64, c_p, c_i64, c_i, c_i64, c_i, c_i, c_p, c_p, c_i, c_f, c_p],
@@ -43,6 +44,19 @@ _SIGS = {
     "dsb_pack_quant_weight": [c_p, c_i64, c_i, c_p, c_i64, c_p, c_i, c_i, c_i, c_i, c_p, c_p],
     "dsb_linear_static": [c_p, c_i64, c_p, c_i64, c_i, c_i, c_i, c_i, c_p, c_i, c_p, c_i, c_p, c_i64, c_p, c_p],
 }
+
+
+
+class GemmArgs(ctypes.Structure):
+    """``dsb_gemm_args`` of include/dsb.h."""
+    _fields_ = [("A", c_p), ("lda", c_i64), ("W", c_p), ("ldw", c_i64), ("M", c_i), ("N", c_i), ("K", c_i),
+                ("row_scale", c_p), ("col_scale", c_p), ("col_scale_stride", c_i), ("bias", c_p), ("act", c_i),
+                ("act_col0", c_i), ("gate", c_p), ("resid", c_p), ("ld_resid", c_i64), ("out0", c_p),
+                ("ld_out0", c_i64), ("out1", c_p), ("ld_out1", c_i64), ("split_col", c_i), ("nq_w", c_p),
+                ("nk_w", c_p), ("d_model", c_i), ("rope", c_p), ("rope_row0", c_i), ("norm_eps", c_f)]
+
+
+_SIGS["dsb_gemm_group"] = [ctypes.POINTER(GemmArgs), c_i, c_i, c_p, c_p]
 
 _lib = None
 

@@ -59,13 +59,19 @@ __device__ __forceinline__ float row_scale_from_amax(float amax, float qmax) {
 // OUT: 0 bf16, 1 e4m3 + row scale, 2 int8 + row scale.
 template <int NV, int OUT>
 __global__ void __launch_bounds__(kRowThreads) ln_modulate_kernel(const __nv_bfloat16* __restrict__ x, int64_t ld_x,
-                                                                  const float* __restrict__ shift,
-                                                                  const float* __restrict__ scale, void* __restrict__ y,
+                                                                  const float* __restrict__ shift_a,
+                                                                  const float* __restrict__ scale_a, int split_row,
+                                                                  const float* __restrict__ shift_b,
+                                                                  const float* __restrict__ scale_b, void* __restrict__ y,
                                                                   int64_t ld_y, float* __restrict__ row_scale, int M,
                                                                   int D, float eps) {
   __shared__ float red[4];
   const int row = blockIdx.x;
   if (row >= M) return;
+  // rows below split_row take the first modulation vectors, the rest the second (text rows precede image rows
+  // in the joint hidden-state buffer, each stream with its own AdaLN output)
+  const float* shift = row < split_row ? shift_a : shift_b;
+  const float* scale = row < split_row ? scale_a : scale_b;
   const int nvec = D >> 3;
   const __nv_bfloat16* xr = x + static_cast<int64_t>(row) * ld_x;
   float v[NV][8];
@@ -159,13 +165,15 @@ __global__ void __launch_bounds__(kRowThreads) ln_modulate_kernel(const __nv_bfl
 }
 
 template <int OUT>
-static int launch_ln_modulate(const void* x, int64_t ld_x, const float* shift, const float* scale, void* y,
-                              int64_t ld_y, float* row_scale, int M, int D, float eps, cudaStream_t st) {
+static int launch_ln_modulate(const void* x, int64_t ld_x, const float* shift, const float* scale, int split_row,
+                              const float* shift_b, const float* scale_b, void* y, int64_t ld_y, float* row_scale,
+                              int M, int D, float eps, cudaStream_t st) {
   const int nv = (D / 8 + kRowThreads - 1) / kRowThreads;
   const __nv_bfloat16* xp = reinterpret_cast<const __nv_bfloat16*>(x);
 #define DSB_LN_CASE(NV)                                                                                         \
   case NV:                                                                                                      \
-    ln_modulate_kernel<NV, OUT><<<M, kRowThreads, 0, st>>>(xp, ld_x, shift, scale, y, ld_y, row_scale, M, D, eps); \
+    ln_modulate_kernel<NV, OUT><<<M, kRowThreads, 0, st>>>(xp, ld_x, shift, scale, split_row, shift_b, scale_b, y, ld_y, \
+                                                           row_scale, M, D, eps);                                  \
     break;
   switch (nv) {
     DSB_LN_CASE(1) DSB_LN_CASE(2) DSB_LN_CASE(3) DSB_LN_CASE(4) DSB_LN_CASE(5) DSB_LN_CASE(6) DSB_LN_CASE(7)
@@ -545,7 +553,14 @@ extern "C" {
 
 int dsb_ln_modulate(const void* x, int64_t ld_x, const float* shift, const float* scale, void* y, int64_t ld_y,
                     float* row_scale, int M, int D, float eps, int out_fmt, void* stream) {
+  return dsb_ln_modulate2(x, ld_x, shift, scale, M, shift, scale, y, ld_y, row_scale, M, D, eps, out_fmt, stream);
+}
+
+int dsb_ln_modulate2(const void* x, int64_t ld_x, const float* shift, const float* scale, int split_row,
+                     const float* shift_b, const float* scale_b, void* y, int64_t ld_y, float* row_scale, int M, int D,
+                     float eps, int out_fmt, void* stream) {
   if (M == 0 && D > 0 && !(D & 7)) return DSB_OK;
+  if (!shift_b || !scale_b || !aligned16(shift_b) || !aligned16(scale_b)) return DSB_ERR_ARG;
   if (!x || !shift || !scale || !y || M < 0 || D <= 0 || (D & 7) || (ld_x & 7) || !aligned16(x) || !aligned16(y) ||
       !aligned16(shift) || !aligned16(scale))
     return DSB_ERR_ARG;
@@ -555,11 +570,11 @@ int dsb_ln_modulate(const void* x, int64_t ld_x, const float* shift, const float
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   switch (out_fmt) {
     case DSB_FMT_BF16:
-      return launch_ln_modulate<0>(x, ld_x, shift, scale, y, ld_y, row_scale, M, D, eps, st);
+      return launch_ln_modulate<0>(x, ld_x, shift, scale, split_row, shift_b, scale_b, y, ld_y, row_scale, M, D, eps, st);
     case DSB_FMT_E4M3:
-      return launch_ln_modulate<1>(x, ld_x, shift, scale, y, ld_y, row_scale, M, D, eps, st);
+      return launch_ln_modulate<1>(x, ld_x, shift, scale, split_row, shift_b, scale_b, y, ld_y, row_scale, M, D, eps, st);
     case DSB_FMT_INT8:
-      return launch_ln_modulate<2>(x, ld_x, shift, scale, y, ld_y, row_scale, M, D, eps, st);
+      return launch_ln_modulate<2>(x, ld_x, shift, scale, split_row, shift_b, scale_b, y, ld_y, row_scale, M, D, eps, st);
     default:
       return DSB_ERR_ARG;
   }

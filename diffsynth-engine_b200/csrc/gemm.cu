@@ -47,6 +47,19 @@ struct GemmEpilogue {
   float norm_eps;
 };
 
+struct alignas(64) GemmProblem {
+  CUtensorMap a, b, o0, o1, r;  // operands, the two output ranges, the residual
+  GemmEpilogue ep;
+  int M, N, K;
+  int tiles_m, num_tiles, num_kb;  // for the tile shape the launch uses
+};
+// Up to two independent problems (same format and tile shape) share one persistent launch: the tile list of the
+// second follows the first, so a small problem (the 512-row text stream) fills the SMs its big sibling leaves idle.
+struct alignas(64) GemmGroup {
+  GemmProblem p[2];
+  int count;
+};
+
 constexpr int kEpiWarps = 8;               // two per TMEM lane quadrant, each draining half of the tile's columns
 constexpr int kStageSlotBytes = 32 * 128;  // 32 rows x 64 bf16
 constexpr int kStageBytes = kEpiWarps * kStageSlotBytes;
@@ -66,9 +79,7 @@ struct GemmSmem {
 
 template <int KIND, int BLOCK_N, int CTAS>
 __global__ void __launch_bounds__(kGemmThreads, 1)
-    gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
-                const __grid_constant__ CUtensorMap tmap_o0, const __grid_constant__ CUtensorMap tmap_o1,
-                const __grid_constant__ CUtensorMap tmap_r, int M, int N, int K, GemmEpilogue ep) {
+    gemm_kernel(const __grid_constant__ GemmGroup g) {
   using SM = GemmSmem<BLOCK_N, CTAS>;
   constexpr int kStages = SM::kStages;
   constexpr int kElemBytes = (KIND == KIND_F16) ? 2 : 1;
@@ -114,9 +125,9 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
     fence_mbar_init();
   }
   if (warp == 0 && lane == 0) {
-    tma_prefetch_desc(&tmap_a);
-    tma_prefetch_desc(&tmap_b);
-    tma_prefetch_desc(&tmap_o0);
+    tma_prefetch_desc(&g.p[0].a);
+    tma_prefetch_desc(&g.p[0].b);
+    tma_prefetch_desc(&g.p[0].o0);
   }
   if (warp == 1) {
     if constexpr (CTAS == 2) {
@@ -133,10 +144,8 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
-  const int tiles_m = (M + kTileM - 1) / kTileM;
-  const int tiles_n = (N + BLOCK_N - 1) / BLOCK_N;
-  const int num_tiles = tiles_m * tiles_n;
-  const int num_kb = (K + kSlabElems - 1) / kSlabElems;
+  const int tiles_first = g.p[0].num_tiles;
+  const int num_tiles = tiles_first + (g.count > 1 ? g.p[1].num_tiles : 0);
 
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer
@@ -144,8 +153,11 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
       int stage = 0;
       uint32_t phase = 0;
       for (int t = unit; t < num_tiles; t += num_units) {
-        const int m0 = (t % tiles_m) * kTileM + static_cast<int>(cta_rank) * kBlockM;
-        const int n0 = (t / tiles_m) * BLOCK_N + static_cast<int>(cta_rank) * (BLOCK_N / CTAS);
+        const GemmProblem& P = g.p[t >= tiles_first ? 1 : 0];
+        const int tl = t >= tiles_first ? t - tiles_first : t;
+        const int m0 = (tl % P.tiles_m) * kTileM + static_cast<int>(cta_rank) * kBlockM;
+        const int n0 = (tl / P.tiles_m) * BLOCK_N + static_cast<int>(cta_rank) * (BLOCK_N / CTAS);
+        const int num_kb = P.num_kb;
         for (int kb = 0; kb < num_kb; ++kb) {
           if (!mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag)) goto producer_done;
           uint8_t* sa = smem + stage * SM::kStage;
@@ -154,12 +166,12 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
             // both CTAs' bytes are counted on the leader's barrier, which the leader arms for the pair
             if (leader) mbar_expect_tx(&full_bar[stage], 2 * SM::kStage);
             const uint32_t bar = mapa_u32(smem_u32(&full_bar[stage]), 0);
-            tma_load_2d_cg2(sa, &tmap_a, bar, kb * kSlabElems, m0);
-            tma_load_2d_cg2(sb, &tmap_b, bar, kb * kSlabElems, n0);
+            tma_load_2d_cg2(sa, &P.a, bar, kb * kSlabElems, m0);
+            tma_load_2d_cg2(sb, &P.b, bar, kb * kSlabElems, n0);
           } else {
             mbar_expect_tx(&full_bar[stage], SM::kStage);
-            tma_load_2d(sa, &tmap_a, &full_bar[stage], kb * kSlabElems, m0);
-            tma_load_2d(sb, &tmap_b, &full_bar[stage], kb * kSlabElems, n0);
+            tma_load_2d(sa, &P.a, &full_bar[stage], kb * kSlabElems, m0);
+            tma_load_2d(sb, &P.b, &full_bar[stage], kb * kSlabElems, n0);
           }
           if (++stage == kStages) {
             stage = 0;
@@ -181,6 +193,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
         if (!mbar_wait(&tmem_empty[acc], acc_phase ^ 1, abort_flag)) goto mma_done;
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * BLOCK_N;
+        const int num_kb = g.p[t >= tiles_first ? 1 : 0].num_kb;
         for (int kb = 0; kb < num_kb; ++kb) {
           if (!mbar_wait(&full_bar[stage], phase, abort_flag)) goto mma_done;
           tc_fence_after();
@@ -230,8 +243,12 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
     for (int t = unit; t < num_tiles; t += num_units, ++it) {
       const int acc = it & 1;
       const uint32_t acc_phase = (it >> 1) & 1;
-      const int m0 = (t % tiles_m) * kTileM + static_cast<int>(cta_rank) * kBlockM;
-      const int n0 = (t / tiles_m) * BLOCK_N;
+      const GemmProblem& P = g.p[t >= tiles_first ? 1 : 0];
+      const GemmEpilogue& ep = P.ep;
+      const int M = P.M, N = P.N;
+      const int tl = t >= tiles_first ? t - tiles_first : t;
+      const int m0 = (tl % P.tiles_m) * kTileM + static_cast<int>(cta_rank) * kBlockM;
+      const int n0 = (tl / P.tiles_m) * BLOCK_N;
       if (!mbar_wait(&tmem_full[acc], acc_phase, abort_flag)) break;
       tc_fence_after();
       const int r0 = m0 + quad * 32;
@@ -239,7 +256,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
       const float rs = (ep.row_scale && m < M) ? ep.row_scale[m] : 1.0f;
       const float rs_t = (ep.col_scale && !ep.col_scale_stride) ? rs * __ldg(ep.col_scale) : rs;  // per-tensor scale folded in
       const bool second = n0 >= ep.split_col;
-      const CUtensorMap* tmap_out = second ? &tmap_o1 : &tmap_o0;
+      const CUtensorMap* tmap_out = second ? &P.o1 : &P.o0;
       const int col_shift = second ? ep.split_col : 0;
       const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + acc * BLOCK_N;
       // Fused QK-RMSNorm (+RoPE): with 256-wide tiles this warp's 128 columns are exactly one head, one row per
@@ -301,7 +318,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
         if (ep.has_resid) {
           if (lane == 0) {
             mbar_expect_tx(rbar, kStageSlotBytes);
-            tma_load_2d(sbuf, &tmap_r, rbar, nb, r0);
+            tma_load_2d(sbuf, &P.r, rbar, nb, r0);
           }
           if (!mbar_wait(rbar, rphase, abort_flag)) {
             alive = false;
@@ -436,26 +453,19 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
     if constexpr (CTAS == 2) tmem_dealloc_cg2(tmem_base, kTmemCols);
     else tmem_dealloc(tmem_base, kTmemCols);
   }
-  if (threadIdx.x == 0 && *abort_flag && ep.status) atomicCAS(ep.status, 0, DSB_ERR_TIMEOUT);
+  if (threadIdx.x == 0 && *abort_flag && g.p[0].ep.status) atomicCAS(g.p[0].ep.status, 0, DSB_ERR_TIMEOUT);
 }
 
 template <int KIND, int BLOCK_N, int CTAS>
-static int launch_gemm(const void* A, int64_t lda, const void* W, int64_t ldw, int M, int N, int K,
-                       const GemmEpilogue& ep, const CUtensorMap& to0, const CUtensorMap& to1, const CUtensorMap& tr,
-                       cudaStream_t st) {
+static int launch_group(GemmGroup& grp, cudaStream_t st) {
   using SM = GemmSmem<BLOCK_N, CTAS>;
-  constexpr int esz = (KIND == KIND_F16) ? 2 : 1;
-  constexpr int slab_elems = kSlabBytes / esz;
-  const CUtensorMapDataType dt = (KIND == KIND_F16) ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_UINT8;
-  CUtensorMap ta, tb;
-  if (make_tmap_2d(&ta, dt, esz, A, M, K, lda * esz, kBlockM, slab_elems) != DSB_OK) return DSB_ERR_CUDA;
-  if (make_tmap_2d(&tb, dt, esz, W, N, K, ldw * esz, BLOCK_N / CTAS, slab_elems) != DSB_OK) return DSB_ERR_CUDA;
   auto kern = gemm_kernel<KIND, BLOCK_N, CTAS>;
   DSB_ENSURE_SMEM(kern, SM::kTotal);
-  const int tiles = ((M + kBlockM * CTAS - 1) / (kBlockM * CTAS)) * ((N + BLOCK_N - 1) / BLOCK_N);
+  int tiles = 0;
+  for (int i = 0; i < grp.count; ++i) tiles += grp.p[i].num_tiles;
   if constexpr (CTAS == 1) {
     const int grid = tiles < sm_count() ? tiles : sm_count();
-    kern<<<grid, kGemmThreads, SM::kTotal, st>>>(ta, tb, to0, to1, tr, M, N, K, ep);
+    kern<<<grid, kGemmThreads, SM::kTotal, st>>>(grp);
   } else {
     // persistent grid = the CTA pairs the device can hold at once (GPCs with an odd SM count leave one SM out)
     static int resident_pairs[64] = {0};
@@ -467,25 +477,20 @@ static int launch_gemm(const void* A, int64_t lda, const void* W, int64_t ldw, i
     attr[0].val.clusterDim.x = 2;
     attr[0].val.clusterDim.y = 1;
     attr[0].val.clusterDim.z = 1;
+    cfg.blockDim = dim3(kGemmThreads, 1, 1);
+    cfg.dynamicSmemBytes = SM::kTotal;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
     if (resident_pairs[dev] == 0) {
       cfg.gridDim = dim3(sm_count() & ~1, 1, 1);
-      cfg.blockDim = dim3(kGemmThreads, 1, 1);
-      cfg.dynamicSmemBytes = SM::kTotal;
-      cfg.attrs = attr;
-      cfg.numAttrs = 1;
       int n = 0;
       if (cudaOccupancyMaxActiveClusters(&n, kern, &cfg) != cudaSuccess || n <= 0) n = sm_count() / 2;
       resident_pairs[dev] = n;
     }
     const int units = resident_pairs[dev];
-    const int grid = (tiles < units ? tiles : units) * CTAS;
-    cfg.gridDim = dim3(grid, 1, 1);
-    cfg.blockDim = dim3(kGemmThreads, 1, 1);
-    cfg.dynamicSmemBytes = SM::kTotal;
+    cfg.gridDim = dim3((tiles < units ? tiles : units) * CTAS, 1, 1);
     cfg.stream = st;
-    cfg.attrs = attr;
-    cfg.numAttrs = 1;
-    if (cudaLaunchKernelEx(&cfg, kern, ta, tb, to0, to1, tr, M, N, K, ep) != cudaSuccess) return DSB_ERR_CUDA;
+    if (cudaLaunchKernelEx(&cfg, kern, grp) != cudaSuccess) return DSB_ERR_CUDA;
   }
   return cudaGetLastError() == cudaSuccess ? DSB_OK : DSB_ERR_CUDA;
 }
@@ -521,70 +526,107 @@ static int pick_block_n(int M, int N) {
 
 using namespace dsb;
 
-static int gemm_common(const void* A, int64_t lda, const void* W, int64_t ldw, int fmt, int M, int N, int K,
-                       const float* row_scale, const float* col_scale, int col_scale_stride, const float* bias,
-                       int act, int act_col0, const float* gate, const void* resid, int64_t ld_resid, void* out0,
-                       int64_t ld_out0, void* out1, int64_t ld_out1, int split_col, const float* nq_w,
-                       const float* nk_w, int d_model, const float* rope, int rope_row0, float norm_eps, int* status,
-                       void* stream) {
-  if (M < 0 || N < 0 || K <= 0 || (N & 7)) return DSB_ERR_ARG;
-  if (M == 0 || N == 0) return DSB_OK;  // an empty product: nothing to read or write
-  if (!A || !W || !out0) return DSB_ERR_ARG;
-  if (fmt != DSB_FMT_BF16 && fmt != DSB_FMT_E4M3 && fmt != DSB_FMT_INT8) return DSB_ERR_ARG;
+// Validates one problem and fills everything of it that does not depend on the tile shape.
+static int check_problem(const dsb_gemm_args& a, int fmt, int* status, GemmProblem* P) {
+  if (a.M < 0 || a.N < 0 || a.K <= 0 || (a.N & 7)) return DSB_ERR_ARG;
+  if (a.M == 0 || a.N == 0) return DSB_OK;
+  if (!a.A || !a.W || !a.out0) return DSB_ERR_ARG;
   const int esz = (fmt == DSB_FMT_BF16) ? 2 : 1;
   auto al16 = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; };
-  if (!al16(A) || !al16(W) || !al16(out0) || (out1 && !al16(out1)) || (resid && !al16(resid)) ||
-      (bias && !al16(bias)) || (gate && !al16(gate)) || (col_scale && col_scale_stride && !al16(col_scale)))
+  if (!al16(a.A) || !al16(a.W) || !al16(a.out0) || (a.out1 && !al16(a.out1)) || (a.resid && !al16(a.resid)) ||
+      (a.bias && !al16(a.bias)) || (a.gate && !al16(a.gate)) ||
+      (a.col_scale && a.col_scale_stride && !al16(a.col_scale)))
     return DSB_ERR_ARG;
-  if (((lda * esz) & 15) || ((ldw * esz) & 15) || (ld_out0 & 7) || (ld_resid & 7) || (ld_out1 & 7))
+  if (((a.lda * esz) & 15) || ((a.ldw * esz) & 15) || (a.ld_out0 & 7) || (a.ld_resid & 7) || (a.ld_out1 & 7))
     return DSB_ERR_ARG;
-  if (col_scale_stride != 0 && col_scale_stride != 1) return DSB_ERR_ARG;
-  if (act != DSB_ACT_NONE && act != DSB_ACT_GELU_TANH && act != DSB_ACT_SILU) return DSB_ERR_ARG;
-  if (!out1) split_col = INT32_MAX;
+  if (a.col_scale_stride != 0 && a.col_scale_stride != 1) return DSB_ERR_ARG;
+  if (a.act != DSB_ACT_NONE && a.act != DSB_ACT_GELU_TANH && a.act != DSB_ACT_SILU) return DSB_ERR_ARG;
+  int split_col = a.split_col;
+  if (!a.out1) split_col = INT32_MAX;
   else if (split_col < 0 || (split_col % 256) != 0) return DSB_ERR_ARG;
-  if (gate && !resid) return DSB_ERR_ARG;
-  if (resid && out1) return DSB_ERR_ARG;  // the residual form writes one output
-  if (nq_w) {
-    if (!nk_w || d_model <= 0 || (d_model % 128) || 2 * d_model > N || resid || !al16(nq_w) || !al16(nk_w) ||
-        (rope && !al16(rope)))
+  if (a.gate && !a.resid) return DSB_ERR_ARG;
+  if (a.resid && a.out1) return DSB_ERR_ARG;  // the residual form writes one output
+  if (a.nq_w) {
+    if (!a.nk_w || a.d_model <= 0 || (a.d_model % 128) || 2 * a.d_model > a.N || a.resid || !al16(a.nq_w) ||
+        !al16(a.nk_w) || (a.rope && !al16(a.rope)))
       return DSB_ERR_ARG;
   }
-  GemmEpilogue ep;
-  ep.row_scale = row_scale;
-  ep.col_scale = col_scale;
-  ep.col_scale_stride = col_scale_stride;
-  ep.bias = bias;
-  ep.act = act;
-  ep.act_col0 = act_col0;
-  ep.gate = gate;
-  ep.has_resid = resid ? 1 : 0;
+  GemmEpilogue& ep = P->ep;
+  ep.row_scale = a.row_scale;
+  ep.col_scale = a.col_scale;
+  ep.col_scale_stride = a.col_scale_stride;
+  ep.bias = a.bias;
+  ep.act = a.act;
+  ep.act_col0 = a.act_col0;
+  ep.gate = a.gate;
+  ep.has_resid = a.resid ? 1 : 0;
   ep.split_col = split_col;
   ep.status = status;
-  ep.nq_w = nq_w;
-  ep.nk_w = nk_w;
-  ep.rope = reinterpret_cast<const float2*>(rope);
-  ep.rope_row0 = rope_row0;
-  ep.d_model = d_model;
-  ep.norm_eps = norm_eps;
+  ep.nq_w = a.nq_w;
+  ep.nk_w = a.nk_w;
+  ep.rope = reinterpret_cast<const float2*>(a.rope);
+  ep.rope_row0 = a.rope_row0;
+  ep.d_model = a.d_model;
+  ep.norm_eps = a.norm_eps;
+  P->M = a.M, P->N = a.N, P->K = a.K;
   // bf16 output / residual tiles of 32 rows x 64 columns (128 bytes per row, 128-byte swizzle)
-  CUtensorMap to0, to1, tr;
-  const int n0cols = out1 ? (split_col < N ? split_col : N) : N;
-  if (make_tmap_2d(&to0, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, out0, M, n0cols, ld_out0 * 2, 32, 64) != DSB_OK)
+  const int n0cols = a.out1 ? (split_col < a.N ? split_col : a.N) : a.N;
+  if (make_tmap_2d(&P->o0, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, a.out0, a.M, n0cols, a.ld_out0 * 2, 32, 64) != DSB_OK)
     return DSB_ERR_CUDA;
-  to1 = to0;
-  if (out1 && split_col < N &&
-      make_tmap_2d(&to1, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, out1, M, N - split_col, ld_out1 * 2, 32, 64) != DSB_OK)
+  P->o1 = P->o0;
+  if (a.out1 && split_col < a.N &&
+      make_tmap_2d(&P->o1, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, a.out1, a.M, a.N - split_col, a.ld_out1 * 2, 32,
+                   64) != DSB_OK)
     return DSB_ERR_CUDA;
-  tr = to0;
-  if (resid && make_tmap_2d(&tr, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, resid, M, N, ld_resid * 2, 32, 64) != DSB_OK)
+  P->r = P->o0;
+  if (a.resid &&
+      make_tmap_2d(&P->r, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, a.resid, a.M, a.N, a.ld_resid * 2, 32, 64) != DSB_OK)
     return DSB_ERR_CUDA;
+  return DSB_OK;
+}
+
+// Operand maps and tile counts for the chosen tile shape.
+static int shape_problem(const dsb_gemm_args& a, int fmt, int bn, int ctas, GemmProblem* P) {
+  const int esz = (fmt == DSB_FMT_BF16) ? 2 : 1;
+  const int slab_elems = kSlabBytes / esz;
+  const CUtensorMapDataType dt =
+      (fmt == DSB_FMT_BF16) ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_UINT8;
+  if (make_tmap_2d(&P->a, dt, esz, a.A, a.M, a.K, a.lda * esz, kBlockM, slab_elems) != DSB_OK) return DSB_ERR_CUDA;
+  if (make_tmap_2d(&P->b, dt, esz, a.W, a.N, a.K, a.ldw * esz, bn / ctas, slab_elems) != DSB_OK) return DSB_ERR_CUDA;
+  P->tiles_m = (a.M + kBlockM * ctas - 1) / (kBlockM * ctas);
+  P->num_tiles = P->tiles_m * ((a.N + bn - 1) / bn);
+  P->num_kb = (a.K + slab_elems - 1) / slab_elems;
+  return DSB_OK;
+}
+
+extern "C" int dsb_gemm_group(const dsb_gemm_args* args, int count, int fmt, int* status, void* stream) {
+  if (!args || count < 1 || count > 2) return DSB_ERR_ARG;
+  if (fmt != DSB_FMT_BF16 && fmt != DSB_FMT_E4M3 && fmt != DSB_FMT_INT8) return DSB_ERR_ARG;
+  GemmGroup grp;
+  const dsb_gemm_args* live[2];
+  grp.count = 0;
+  for (int i = 0; i < count; ++i) {
+    const int rc = check_problem(args[i], fmt, status, &grp.p[grp.count]);
+    if (rc != DSB_OK) return rc;
+    if (args[i].M == 0 || args[i].N == 0) continue;  // an empty product: nothing to read or write
+    live[grp.count++] = &args[i];
+  }
+  if (grp.count == 0) return DSB_OK;
+  // one tile shape for the launch, chosen for the first (larger) problem; the fused norm needs a whole head per
+  // epilogue warp, i.e. 256-wide tiles
+  bool any_norm = false;
+  for (int i = 0; i < grp.count; ++i) any_norm = any_norm || live[i]->nq_w != nullptr;
+  const int bn = any_norm ? 256 : pick_block_n(live[0]->M, live[0]->N);
+  const bool pair = pair_mode_enabled() && bn == 256 && live[0]->M > 256 && live[0]->N >= 256;
+  for (int i = 0; i < grp.count; ++i) {
+    const int rc = shape_problem(*live[i], fmt, bn, pair ? 2 : 1, &grp.p[i]);
+    if (rc != DSB_OK) return rc;
+  }
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
-  const int bn = nq_w ? 256 : pick_block_n(M, N);  // the fused norm needs a whole head per epilogue warp
-  const bool pair = pair_mode_enabled() && bn == 256 && M > 256 && N >= 256;
-#define DSB_GEMM_DISPATCH(KIND)                                                              \
-  (pair        ? launch_gemm<KIND, 256, 2>(A, lda, W, ldw, M, N, K, ep, to0, to1, tr, st)    \
-   : bn == 256 ? launch_gemm<KIND, 256, 1>(A, lda, W, ldw, M, N, K, ep, to0, to1, tr, st)    \
-               : launch_gemm<KIND, 128, 1>(A, lda, W, ldw, M, N, K, ep, to0, to1, tr, st))
+#define DSB_GEMM_DISPATCH(KIND)                       \
+  (pair        ? launch_group<KIND, 256, 2>(grp, st)  \
+   : bn == 256 ? launch_group<KIND, 256, 1>(grp, st)  \
+               : launch_group<KIND, 128, 1>(grp, st))
   if (fmt == DSB_FMT_BF16) return DSB_GEMM_DISPATCH(KIND_F16);
   if (fmt == DSB_FMT_E4M3) return DSB_GEMM_DISPATCH(KIND_F8);
   return DSB_GEMM_DISPATCH(KIND_I8);
@@ -595,9 +637,12 @@ extern "C" int dsb_gemm(const void* A, int64_t lda, const void* W, int64_t ldw, 
                         const float* row_scale, const float* col_scale, int col_scale_stride, const float* bias,
                         int act, int act_col0, const float* gate, const void* resid, int64_t ld_resid, void* out0,
                         int64_t ld_out0, void* out1, int64_t ld_out1, int split_col, int* status, void* stream) {
-  return gemm_common(A, lda, W, ldw, fmt, M, N, K, row_scale, col_scale, col_scale_stride, bias, act, act_col0, gate,
-                     resid, ld_resid, out0, ld_out0, out1, ld_out1, split_col, nullptr, nullptr, 0, nullptr, 0, 0.f,
-                     status, stream);
+  dsb_gemm_args a = {};
+  a.A = A, a.lda = lda, a.W = W, a.ldw = ldw, a.M = M, a.N = N, a.K = K;
+  a.row_scale = row_scale, a.col_scale = col_scale, a.col_scale_stride = col_scale_stride, a.bias = bias;
+  a.act = act, a.act_col0 = act_col0, a.gate = gate, a.resid = resid, a.ld_resid = ld_resid;
+  a.out0 = out0, a.ld_out0 = ld_out0, a.out1 = out1, a.ld_out1 = ld_out1, a.split_col = split_col;
+  return dsb_gemm_group(&a, 1, fmt, status, stream);
 }
 
 extern "C" int dsb_gemm_qkv(const void* A, int64_t lda, const void* W, int64_t ldw, int fmt, int M, int N, int K,
@@ -606,7 +651,11 @@ extern "C" int dsb_gemm_qkv(const void* A, int64_t lda, const void* W, int64_t l
                             int split_col, const float* nq_w, const float* nk_w, int d_model, const float* rope,
                             int rope_row0, float norm_eps, int* status, void* stream) {
   if (!nq_w || !nk_w) return DSB_ERR_ARG;
-  return gemm_common(A, lda, W, ldw, fmt, M, N, K, row_scale, col_scale, col_scale_stride, bias, act, act_col0,
-                     nullptr, nullptr, 0, out0, ld_out0, out1, ld_out1, split_col, nq_w, nk_w, d_model, rope,
-                     rope_row0, norm_eps, status, stream);
+  dsb_gemm_args a = {};
+  a.A = A, a.lda = lda, a.W = W, a.ldw = ldw, a.M = M, a.N = N, a.K = K;
+  a.row_scale = row_scale, a.col_scale = col_scale, a.col_scale_stride = col_scale_stride, a.bias = bias;
+  a.act = act, a.act_col0 = act_col0;
+  a.out0 = out0, a.ld_out0 = ld_out0, a.out1 = out1, a.ld_out1 = ld_out1, a.split_col = split_col;
+  a.nq_w = nq_w, a.nk_w = nk_w, a.d_model = d_model, a.rope = rope, a.rope_row0 = rope_row0, a.norm_eps = norm_eps;
+  return dsb_gemm_group(&a, 1, fmt, status, stream);
 }

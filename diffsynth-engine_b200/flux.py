@@ -6,10 +6,11 @@ patchify/unpatchify reshapes at the model boundary):
 
   step start : sinusoid -> 6 GEMVs (time, guidance, pooled MLPs, summed in fp32) -> ONE GEMV over the stacked
                AdaLN weights of all blocks = every shift/scale/gate of the step
-  double     : per stream  ln_modulate(+quantise) -> qkv GEMM (+bias, per-head RMSNorm+RoPE of q and k in the
-               epilogue) into the joint [S, 3d] buffer (text rows first);   joint flash attention;
-               per stream  quantise -> out-proj GEMM with x += gate*(.) fused -> ln_modulate(+quantise)
-               -> FF1 GEMM (+GELU) -> quantise -> FF2 GEMM with x += gate*(.) fused
+  double     : ln_modulate(+quantise) of both streams in one launch (per-stream shift/scale) -> the two qkv GEMMs as
+               ONE grouped launch (+bias, per-head RMSNorm+RoPE of q and k in the epilogue) into the joint [S, 3d]
+               buffer (text rows first) -> joint flash attention -> quantise -> the two out-proj GEMMs (grouped, with
+               x += gate*(.) fused) -> ln_modulate(+quantise) -> the two FF1 GEMMs (grouped, +GELU) -> quantise
+               -> the two FF2 GEMMs (grouped, x += gate*(.) fused): 9 launches per block
   single     : ln_modulate(+quantise) -> ONE GEMM N=7d whose epilogue routes [q|k|v] to the attention buffer and
                GELU(mlp) next to where attention will write its output (no torch.cat), RMSNorm+RoPE applied to the
                q and k columns on the way -> flash attention -> quantise -> proj GEMM K=5d with x = x + gate*(.) fused
@@ -136,8 +137,8 @@ class FluxDiTEngine:
         ops.quant_rows(x, self.afmt, out=out, row_scale=rs)
         return out, rs
 
-    def _ln(self, x, shift, scale, out, rs):
-        y, s = ops.ln_modulate(x, shift, scale, 1e-6, self.afmt, out=out, row_scale=rs)
+    def _ln(self, x, shift, scale, out, rs, **split):
+        y, s = ops.ln_modulate(x, shift, scale, 1e-6, self.afmt, out=out, row_scale=rs, **split)
         return y, (s if self.afmt != ops.FMT_BF16 else None)
 
     def _gemm(self, a, rs, p: PackedLinear, **kw):
@@ -177,27 +178,35 @@ class FluxDiTEngine:
         v4 = qkv[:, 2 * d:].unflatten(1, (H, 128)).unsqueeze(0)
         o4 = attn_o.unflatten(1, (H, 128)).unsqueeze(0)
         off = 0
-        streams = ((slice(S_txt, S), "a", 0), (slice(0, S_txt), "b", 6 * d))
+        img, txt = slice(S_txt, S), slice(0, S_txt)
+        hid_all, hidq_all = cat[:, d:5 * d], catq[:, d:5 * d]
+
+        def pl(p, rows, a, sc, **kw):   # one problem of a grouped launch on a stream's row range
+            return dict(a=a[rows], w=p.w, row_scale=None if sc is None else sc[rows], col_scale=p.scale, bias=p.bias,
+                        **kw)
+
         for blk in self.double:
-            m = mv[off:off + 12 * d]
+            m = mv[off:off + 12 * d]          # [image: shift,scale,gate (msa), shift,scale,gate (mlp) | text: same]
             off += 12 * d
-            for rows, s_, mo in streams:
-                sh_msa, sc_msa = m[mo:mo + d], m[mo + d:mo + 2 * d]
-                a, sc = self._ln(x[rows], sh_msa, sc_msa, xq_d[rows], rs[rows])
-                p = blk["qkv_" + s_]
-                ops.gemm_qkv(a, p.w, blk["nq_" + s_], blk["nk_" + s_], d, rope, rows.start, 1e-6, row_scale=sc,
-                             col_scale=p.scale, bias=p.bias, out=qkv[rows])
+            mi, mt = m[:6 * d], m[6 * d:]
+            # both streams through one LayerNorm+modulate+quantise launch (text rows first in x)
+            a, sc = self._ln(x, mt[:d], mt[d:2 * d], xq_d, rs, split_row=S_txt, shift_b=mi[:d], scale_b=mi[d:2 * d])
+            ops.gemm_group([
+                pl(blk["qkv_a"], img, a, sc, out=qkv[img], nq_w=blk["nq_a"], nk_w=blk["nk_a"], d_model=d, rope=rope,
+                   rope_row0=S_txt),
+                pl(blk["qkv_b"], txt, a, sc, out=qkv[txt], nq_w=blk["nq_b"], nk_w=blk["nk_b"], d_model=d, rope=rope,
+                   rope_row0=0)])
             ops.flash_attn(q4, k4, v4, out=o4)
-            for rows, s_, mo in streams:
-                g_msa = m[mo + 2 * d:mo + 3 * d]
-                sh_mlp, sc_mlp, g_mlp = m[mo + 3 * d:mo + 4 * d], m[mo + 4 * d:mo + 5 * d], m[mo + 5 * d:mo + 6 * d]
-                a, sc = self._quant(attn_o[rows], catq[rows, :d], rs[rows])
-                self._gemm(a, sc, blk["out_" + s_], gate=g_msa, resid=x[rows], out=x[rows])
-                a, sc = self._ln(x[rows], sh_mlp, sc_mlp, xq_d[rows], rs[rows])
-                hid = cat[rows, d:5 * d]
-                self._gemm(a, sc, blk["ff0_" + s_], act=ops.ACT_GELU_TANH, out=hid)
-                a, sc = self._quant(hid, catq[rows, d:5 * d], rs[rows])
-                self._gemm(a, sc, blk["ff2_" + s_], gate=g_mlp, resid=x[rows], out=x[rows])
+            a, sc = self._quant(attn_o, catq[:, :d], rs)
+            ops.gemm_group([pl(blk["out_a"], img, a, sc, gate=mi[2 * d:3 * d], resid=x[img], out=x[img]),
+                            pl(blk["out_b"], txt, a, sc, gate=mt[2 * d:3 * d], resid=x[txt], out=x[txt])])
+            a, sc = self._ln(x, mt[3 * d:4 * d], mt[4 * d:5 * d], xq_d, rs, split_row=S_txt, shift_b=mi[3 * d:4 * d],
+                             scale_b=mi[4 * d:5 * d])
+            ops.gemm_group([pl(blk["ff0_a"], img, a, sc, act=ops.ACT_GELU_TANH, out=hid_all[img]),
+                            pl(blk["ff0_b"], txt, a, sc, act=ops.ACT_GELU_TANH, out=hid_all[txt])])
+            a, sc = self._quant(hid_all, hidq_all, rs)
+            ops.gemm_group([pl(blk["ff2_a"], img, a, sc, gate=mi[5 * d:6 * d], resid=x[img], out=x[img]),
+                            pl(blk["ff2_b"], txt, a, sc, gate=mt[5 * d:6 * d], resid=x[txt], out=x[txt])])
         for blk in self.single:
             m = mv[off:off + 3 * d]
             off += 3 * d
@@ -281,8 +290,7 @@ class FluxDiTEngine:
 
     def kernel_launches_per_step(self) -> int:
         """Launches of this library's kernels in one step (the count of the dataflow above)."""
-        per_stream = 2 + (2 if self.afmt != ops.FMT_BF16 else 0) + 4
-        dbl = 2 * per_stream + 1
+        dbl = 2 + 4 + 1 + (2 if self.afmt != ops.FMT_BF16 else 0)   # 2 LN, 4 grouped GEMMs, attention, 2 quantisers
         sgl = 3 + (1 if self.afmt != ops.FMT_BF16 else 0) + 1
         pre = 1 + (6 if self.use_guidance else 4) + 1 + 2 + (2 if self.afmt != ops.FMT_BF16 else 0)
         return pre + self.n_double * dbl + self.n_single * sgl + 2

@@ -63,17 +63,24 @@ def _rows(t: torch.Tensor) -> Tuple[int, int, int]:
     return t.shape[0], t.shape[1], t.stride(0)
 
 
-def ln_modulate(x, shift, scale, eps=1e-6, out_fmt=FMT_BF16, out=None, row_scale=None):
-    """LayerNorm (no affine) then ``* (1 + scale) + shift``; optionally quantised per row.
-    Returns ``(y, row_scale)`` (row_scale is None for bf16 output)."""
-    _require_cuda(x, shift, scale)
+def ln_modulate(x, shift, scale, eps=1e-6, out_fmt=FMT_BF16, out=None, row_scale=None, split_row=None,
+                shift_b=None, scale_b=None):
+    """LayerNorm (no affine) then ``* (1 + scale) + shift``; optionally quantised per row.  With ``split_row``
+    rows from that index on use ``(shift_b, scale_b)`` instead.  Returns ``(y, row_scale)`` (row_scale is None
+    for bf16 output)."""
+    _require_cuda(x, shift, scale, shift_b, scale_b)
     M, D, ld_x = _rows(x)
     if out is None:
         out = torch.empty((M, D), dtype=_OUT_DTYPE[out_fmt], device=x.device)
     if out_fmt != FMT_BF16 and row_scale is None:
         row_scale = torch.empty(M, dtype=torch.float32, device=x.device)
-    rc = _lib.lib().dsb_ln_modulate(_ptr(x), ld_x, _ptr(shift), _ptr(scale), _ptr(out), out.stride(0),
-                                    _ptr(row_scale), M, D, eps, out_fmt, _stream())
+    if split_row is None:
+        rc = _lib.lib().dsb_ln_modulate(_ptr(x), ld_x, _ptr(shift), _ptr(scale), _ptr(out), out.stride(0),
+                                        _ptr(row_scale), M, D, eps, out_fmt, _stream())
+    else:
+        rc = _lib.lib().dsb_ln_modulate2(_ptr(x), ld_x, _ptr(shift), _ptr(scale), split_row, _ptr(shift_b),
+                                         _ptr(scale_b), _ptr(out), out.stride(0), _ptr(row_scale), M, D, eps, out_fmt,
+                                         _stream())
     check(rc, "dsb_ln_modulate")
     return out, row_scale
 
@@ -222,6 +229,42 @@ def gemm_qkv(a, w, nq_w, nk_w, d_model, rope=None, rope_row0=0, eps=1e-6, row_sc
         _ptr(status_word(a.device)), _stream())
     check(rc, "dsb_gemm_qkv")
     return out
+
+
+def gemm_group(problems):
+    """``dsb_gemm_group``: one persistent launch for up to two GEMMs of one format.  Each problem is a dict with
+    the keyword arguments of :func:`gemm` / :func:`gemm_qkv` (``a``, ``w``, ``out`` required; ``nq_w`` present
+    selects the fused QK-RMSNorm/RoPE epilogue).  Outputs must be preallocated."""
+    if not 1 <= len(problems) <= 2:
+        raise _lib.DsbError("gemm_group takes one or two problems")
+    arr = (_lib.GemmArgs * len(problems))()
+    fmt = _fmt_of(problems[0]["a"])
+    keep = []
+    for i, pr in enumerate(problems):
+        a, w, out = pr["a"], pr["w"], pr["out"]
+        out1, resid = pr.get("out1"), pr.get("resid")
+        _require_cuda(a, w, out, out1, resid)
+        M, K, lda = _rows(a)
+        N, Kw, ldw = _rows(w)
+        if K != Kw or _fmt_of(a) != fmt or _fmt_of(w) != fmt:
+            raise _lib.DsbError("gemm_group operands disagree in K or format")
+        cs = pr.get("col_scale")
+        g = arr[i]
+        g.A, g.lda, g.W, g.ldw, g.M, g.N, g.K = a.data_ptr(), lda, w.data_ptr(), ldw, M, N, K
+        for name, key in (("row_scale", "row_scale"), ("col_scale", "col_scale"), ("bias", "bias"), ("gate", "gate"),
+                          ("resid", "resid"), ("out1", "out1"), ("nq_w", "nq_w"), ("nk_w", "nk_w"), ("rope", "rope")):
+            t = pr.get(key)
+            setattr(g, name, None if t is None else t.data_ptr())
+            keep.append(t)
+        g.col_scale_stride = 0 if (cs is None or cs.numel() == 1) else 1
+        g.act, g.act_col0 = pr.get("act", ACT_NONE), pr.get("act_col0", 0)
+        g.ld_resid = 0 if resid is None else resid.stride(0)
+        g.out0, g.ld_out0 = out.data_ptr(), out.stride(0)
+        g.ld_out1 = 0 if out1 is None else out1.stride(0)
+        g.split_col = N if pr.get("split_col") is None else pr["split_col"]
+        g.d_model, g.rope_row0, g.norm_eps = pr.get("d_model", 0), pr.get("rope_row0", 0), float(pr.get("eps", 1e-6))
+    rc = _lib.lib().dsb_gemm_group(arr, len(problems), fmt, _ptr(status_word(problems[0]["a"].device)), _stream())
+    check(rc, "dsb_gemm_group")
 
 
 def flash_attn(q, k, v, out=None, sm_scale=None):

@@ -60,6 +60,15 @@ int dsb_ln_modulate(const void* x, int64_t ld_x, const float* shift, const float
                     float* row_scale, int M, int D, float eps, int out_fmt, void* stream);
 
 /*
+ * dsb_ln_modulate with two modulation sets: rows [0, split_row) use (shift, scale), rows [split_row, M) use
+ * (shift_b, scale_b) - the text rows and the image rows of the joint hidden-state buffer, each with its own AdaLN
+ * output (models/flux/flux_dit.py:220-221,228,233), normalised in one launch.
+ */
+int dsb_ln_modulate2(const void* x, int64_t ld_x, const float* shift, const float* scale, int split_row,
+                     const float* shift_b, const float* scale_b, void* y, int64_t ld_y, float* row_scale, int M, int D,
+                     float eps, int out_fmt, void* stream);
+
+/*
  * out = x + gate[d] * y (gate NULL: out = x + y); bf16 in/out, fp32 gate.
  * Replaces: models/flux/flux_dit.py:227,229,232,234,318-319; models/wan/wan_dit.py:189,190,192.
  */
@@ -163,6 +172,36 @@ int dsb_gemm_qkv(const void* A, int64_t lda, const void* W, int64_t ldw, int fmt
                  int act_col0, void* out0, int64_t ld_out0, void* out1, int64_t ld_out1, int split_col,
                  const float* nq_w, const float* nk_w, int d_model, const float* rope, int rope_row0, float norm_eps,
                  int* status, void* stream);
+
+/*
+ * One problem of a grouped launch: the arguments of dsb_gemm / dsb_gemm_qkv as a struct (nq_w NULL = no fused
+ * QK-RMSNorm/RoPE; resid NULL = no residual form; out1 NULL = one output).
+ */
+typedef struct dsb_gemm_args {
+  const void* A; int64_t lda;
+  const void* W; int64_t ldw;
+  int M, N, K;
+  const float* row_scale;
+  const float* col_scale; int col_scale_stride;
+  const float* bias;
+  int act, act_col0;
+  const float* gate;
+  const void* resid; int64_t ld_resid;
+  void* out0; int64_t ld_out0;
+  void* out1; int64_t ld_out1;
+  int split_col;
+  const float* nq_w; const float* nk_w; int d_model;
+  const float* rope; int rope_row0; float norm_eps;
+} dsb_gemm_args;
+
+/*
+ * count (1 or 2) independent GEMMs of one format in ONE persistent launch: the tile list of the second problem
+ * follows the first, so the 512-row text-stream Linear of a double-stream block runs on the SMs that the
+ * 4096-row image-stream Linear leaves idle in its last wave (models/flux/flux_dit.py:165-174,189-193,229,234 issue
+ * them one after the other).  Arithmetic per problem exactly as dsb_gemm / dsb_gemm_qkv; the tile shape is chosen
+ * for args[0].
+ */
+int dsb_gemm_group(const dsb_gemm_args* args, int count, int fmt, int* status, void* stream);
 
 /*
  * Attention without mask: o[b,s,h,:] = softmax(q[b,s,h,:] . k[b,:,h,:]^T * sm_scale) v[b,:,h,:], head_dim 128,
