@@ -28,6 +28,9 @@ PKG_DIR = os.path.join(ROOT, "diffsynth-engine_b200")
 sys.path.insert(0, ROOT)
 
 FLUX = dict(d=3072, H=24, n_double=19, n_single=38, S_txt=512, height=128, width=128, txt_dim=4096, pooled_dim=768)
+# Qwen-Image-architecture stand-in (the reference snapshot has no Qwen-Image code): 60 Flux-style double-stream
+# blocks, 1328x1328 -> latent 166x166 -> 83*83 = 6889 image tokens + 256 text tokens of width 3584
+QWEN = dict(d=3072, H=24, n_double=60, n_single=0, S_txt=256, height=166, width=166, txt_dim=3584, pooled_dim=768)
 # Wan2.1-14B text-to-video at 81 frames x 480 x 832: latent 21 x 60 x 104, patch (1,2,2) -> 21*30*52 = 32760 tokens
 WAN = dict(d=5120, ffn=13824, num_layers=40, H=40, frames=21, height=60, width=104, ctx=512, text_dim=4096)
 
@@ -228,6 +231,54 @@ def run_wan(args, torch, pkg, synth, dev, dist, rank, world, steps, warmup):
             "d2h_bytes_per_step": h_out.numel() * h_out.element_size()}
 
 
+def run_sweeps(torch, pkg, dev):
+    """Isolated kernel sweeps: FP8 e4m3 Linear (per-tensor and per-channel weight scale, bf16 out, fused
+    bias + GELU-tanh) and joint attention (bf16, head_dim 128), N(0,1) values from a seed."""
+    ops = pkg.ops
+    peaks = measured_peaks()
+    gen = torch.Generator(device=dev).manual_seed(0)
+
+    def timeit(fn, n=10, warm=3):
+        for _ in range(warm):
+            fn()
+        torch.cuda.synchronize()
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s.record()
+        for _ in range(n):
+            fn()
+        e.record()
+        torch.cuda.synchronize()
+        return s.elapsed_time(e) / n
+
+    linear, attn = [], []
+    for (K, N) in [(3072, 3072), (3072, 12288), (12288, 3072), (5120, 13824), (3072, 9216)]:
+        w = torch.randn(N, K, generator=gen, device=dev) * 0.02
+        bias = torch.randn(N, generator=gen, device=dev) * 0.02
+        packs = {"per_tensor": ops.pack_quant_weight(w, ops.FMT_E4M3, False),
+                 "per_channel": ops.pack_quant_weight(w, ops.FMT_E4M3, True)}
+        for M in (1024, 4096, 8192, 32760):
+            x = torch.randn(M, K, generator=gen, device=dev).to(torch.bfloat16)
+            xq, rs = ops.quant_rows(x)
+            out = torch.empty(M, N, dtype=torch.bfloat16, device=dev)
+            for mode, (wq, ws) in packs.items():
+                ms = timeit(lambda: ops.gemm(xq, wq, row_scale=rs, col_scale=ws, bias=bias, act=ops.ACT_GELU_TANH,
+                                             out=out))
+                tf = 2.0 * M * N * K / ms / 1e9
+                linear.append({"M": M, "K": K, "N": N, "scale": mode, "us": ms * 1e3, "tflops": tf,
+                               "frac_of_2x_bf16_peak": tf / (2 * peaks["bf16"])})
+    for H in (24, 40):
+        for S in (1536, 4608, 7145, 32760):
+            q, k, v = (torch.randn(1, S, H, 128, generator=gen, device=dev).to(torch.bfloat16) for _ in range(3))
+            o = torch.empty_like(q)
+            ms = timeit(lambda: ops.flash_attn(q, k, v, out=o), n=5 if S > 8192 else 10)
+            tf = 4.0 * S * S * H * 128 / ms / 1e9
+            attn.append({"H": H, "S": S, "us": ms * 1e3, "tflops": tf, "frac_of_bf16_peak": tf / peaks["bf16"]})
+    ops.check_status(dev.index)
+    return {"metric": "isolated kernel sweeps", "unit": "TFLOP/s", "data": "synthetic",
+            "peak_source": f"MEASURED_PEAKS.json ({peaks['source']}): bf16 {peaks['bf16']} TFLOP/s; FP8 taken as 2x",
+            "fp8_linear_bias_gelu": linear, "joint_attention": attn}
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -237,7 +288,7 @@ def main():
     ap.add_argument("--fmt", default="fp8_tensor")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--blocks", default=None, help="n_double,n_single override (reduced-depth debugging; not a bench)")
-    ap.add_argument("--workload", default="both", choices=["flux", "wan", "both"],
+    ap.add_argument("--workload", default="both", choices=["flux", "wan", "both", "qwen", "sweeps"],
                     help="flux: the headline line; wan: Wan-14B sequence-parallel step only; both: flux line with the "
                          "wan result attached under 'wan'")
     ap.add_argument("--wan-fmt", default="fp8_channel")
@@ -247,11 +298,16 @@ def main():
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
-    cfg = dict(FLUX)
+    cfg = dict(QWEN if args.workload == "qwen" else FLUX)
     if args.blocks:
         cfg["n_double"], cfg["n_single"] = (int(v) for v in args.blocks.split(","))
-    config = {"workload": "flux1-dev-arch DiT step, 1024x1024 (4096 image + 512 text tokens), batch 1, "
-                          f"{cfg['n_double']} double + {cfg['n_single']} single blocks, weights {args.fmt}, bf16 activations",
+    if args.workload == "qwen":
+        wl = ("qwen-image-arch stand-in (Flux-style double-stream blocks), 1328x1328 (6889 image + 256 text tokens of "
+              f"width 3584), batch 1, {cfg['n_double']} double blocks, weights {args.fmt}, bf16 activations")
+    else:
+        wl = ("flux1-dev-arch DiT step, 1024x1024 (4096 image + 512 text tokens), batch 1, "
+              f"{cfg['n_double']} double + {cfg['n_single']} single blocks, weights {args.fmt}, bf16 activations")
+    config = {"workload": wl,
               "parallelism": f"replicas x{world}" if world > 1 else "single GPU",
               "l2": "per-step working set (11.9 GB of weights) exceeds the 126 MB L2; no flush between steps"}
 
@@ -283,6 +339,10 @@ def main():
         import torch.distributed as dist
         dist.init_process_group("nccl", device_id=dev)
 
+    if args.workload == "sweeps":
+        if rank == 0:
+            print(json.dumps(run_sweeps(torch, pkg, dev)), flush=True)
+        return
     if args.workload == "wan":
         r = run_wan(args, torch, pkg, synth, dev, dist, rank, world, max(1, args.steps), max(1, min(args.warmup, 3)))
         if rank == 0:

@@ -35,6 +35,7 @@ _SIGS = {
     "dsb_quant_rows": [c_p, c_i64, c_p, c_i64, c_p, c_i, c_i, c_i, c_p],
     "dsb_gemv": [c_p, c_i64, c_i, c_p, c_p, c_i, c_p, c_p, c_i, c_i, c_i, c_i, c_i, c_p],
     "dsb_timestep_embedding": [c_p, c_i, c_i, c_f, c_i, c_i, c_p, c_p],
+    "dsb_cfg_euler_step": [c_p, c_p, c_p, c_f, c_f, c_p, c_i64, c_i, c_p],
     "dsb_euler_step": [c_p, c_p, c_p, c_p, c_f, c_p, c_i64, c_i, c_p],
     "dsb_gemm": [c_p, c_i64, c_p, c_i64, c_i, c_i, c_i, c_i, c_p, c_p, c_i, c_p, c_i, c_i, c_p, c_p, c_i64, c_p,
                  c_i64, c_p, c_i64, c_i, c_p, c_p],

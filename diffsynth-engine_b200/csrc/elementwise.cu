@@ -543,6 +543,32 @@ __global__ void timestep_embedding_kernel(const float* __restrict__ t, int n, in
   out[r * dim + half + i] = s;
 }
 
+// ------------------------------------------------- CFG combine + euler step
+// model_out = neg + cfg * (pos - neg), then the flow-match Euler update, in one pass.  The bf16 form rounds where
+// the reference's tensor expression rounds (each elementwise op yields a bf16 tensor).
+__device__ __forceinline__ float rbf(float v) { return __bfloat162float(__float2bfloat16(v)); }
+__global__ void __launch_bounds__(256) cfg_euler_step_kernel(const __nv_bfloat16* __restrict__ latents,
+                                                             const __nv_bfloat16* __restrict__ pos,
+                                                             const __nv_bfloat16* __restrict__ neg, float cfg, float dt,
+                                                             __nv_bfloat16* __restrict__ out, int64_t n) {
+  for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < n;
+       i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const float p = __bfloat162float(pos[i]), q = __bfloat162float(neg[i]);
+    const float m = rbf(q + rbf(cfg * rbf(p - q)));
+    out[i] = __float2bfloat16(__bfloat162float(latents[i]) + rbf(m * dt));
+  }
+}
+__global__ void __launch_bounds__(256) cfg_euler_step_f32_kernel(const float* __restrict__ latents,
+                                                                 const float* __restrict__ pos,
+                                                                 const float* __restrict__ neg, float cfg, float dt,
+                                                                 float* __restrict__ out, int64_t n) {
+  for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < n;
+       i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const float m = neg[i] + cfg * (pos[i] - neg[i]);
+    out[i] = latents[i] + m * dt;
+  }
+}
+
 static bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
 }  // namespace dsb
@@ -713,6 +739,26 @@ int dsb_timestep_embedding(const float* t, int n, int dim, float t_scale, int mo
   const int total = n * (dim / 2);
   timestep_embedding_kernel<<<(total + 127) / 128, 128, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
       t, n, dim, t_scale, mode, round_bf16, out);
+  return cudaGetLastError() == cudaSuccess ? DSB_OK : DSB_ERR_CUDA;
+}
+
+int dsb_cfg_euler_step(const void* latents, const void* pos, const void* neg, float cfg_scale, float dt, void* out,
+                       int64_t n, int is_f32, void* stream) {
+  if (!latents || !pos || !neg || !out || n < 0) return DSB_ERR_ARG;
+  if (n == 0) return DSB_OK;
+  int blocks = static_cast<int>((n + 255) / 256);
+  const int cap = sm_count() * 8;
+  if (blocks > cap) blocks = cap;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  if (is_f32)
+    cfg_euler_step_f32_kernel<<<blocks, 256, 0, st>>>(reinterpret_cast<const float*>(latents),
+                                                      reinterpret_cast<const float*>(pos),
+                                                      reinterpret_cast<const float*>(neg), cfg_scale, dt,
+                                                      reinterpret_cast<float*>(out), n);
+  else
+    cfg_euler_step_kernel<<<blocks, 256, 0, st>>>(
+        reinterpret_cast<const __nv_bfloat16*>(latents), reinterpret_cast<const __nv_bfloat16*>(pos),
+        reinterpret_cast<const __nv_bfloat16*>(neg), cfg_scale, dt, reinterpret_cast<__nv_bfloat16*>(out), n);
   return cudaGetLastError() == cudaSuccess ? DSB_OK : DSB_ERR_CUDA;
 }
 

@@ -190,6 +190,17 @@ def euler_step(latents, model_out, dt: float, init=None, mask=None, out=None):
     return out
 
 
+def cfg_euler_step(latents, pos, neg, cfg_scale: float, dt: float, out=None):
+    """``latents + (neg + cfg_scale * (pos - neg)) * dt`` in one pass (CFG combine + flow-match Euler update)."""
+    _require_cuda(latents, pos, neg)
+    if out is None:
+        out = torch.empty_like(pos)
+    rc = _lib.lib().dsb_cfg_euler_step(_ptr(latents), _ptr(pos), _ptr(neg), float(cfg_scale), float(dt), _ptr(out),
+                                       latents.numel(), 1 if pos.dtype == torch.float32 else 0, _stream())
+    check(rc, "dsb_cfg_euler_step")
+    return out
+
+
 def gemm(a, w, row_scale=None, col_scale=None, bias=None, act=ACT_NONE, act_col0=0, gate=None, resid=None, out=None,
          out1=None, split_col=None):
     """out = epilogue(a @ w.T): see ``dsb_gemm`` in include/dsb.h.  a: [M,K], w: [N,K] of one format."""

@@ -141,6 +141,16 @@ int dsb_euler_step(const void* latents, const void* model_out, const void* init,
                    void* out, int64_t n, int is_f32, void* stream);
 
 /*
+ * Classifier-free-guidance combine fused with the sampler update:
+ *   model_out = neg + cfg_scale * (pos - neg);   out = cast(latents + model_out * dt)
+ * Replaces: pipelines/wan_video.py:230,248 and pipelines/flux_image.py:387,398 (noise_pred = negative + cfg_scale *
+ * (positive - negative)) followed by algorithm/sampler/flow_match/flow_match_euler.py:11-19; bit-identical to that
+ * tensor expression for bf16 (same rounding points) and fp32.
+ */
+int dsb_cfg_euler_step(const void* latents, const void* pos, const void* neg, float cfg_scale, float dt, void* out,
+                       int64_t n, int is_f32, void* stream);
+
+/*
  * Quantised / bf16 Linear on the tensor cores:
  *   acc[m,n]  = sum_k A[m,k] * W[n,k]                      (fp32 accumulate; int32 for INT8)
  *   v         = acc * row_scale[m] * col_scale[n*col_scale_stride] + bias[n]

@@ -164,6 +164,12 @@ def euler_step(latents, model_out, sigmas, i, init=None, mask=None):
     return out.to(model_out.dtype)
 
 
+def cfg_combine(pos, neg, cfg_scale):
+    """noise_pred = negative + cfg_scale * (positive - negative): pipelines/wan_video.py:230,248;
+    pipelines/flux_image.py:387,398 (evaluated in the tensors' own dtype, as PyTorch does)."""
+    return neg + cfg_scale * (pos - neg)
+
+
 def rectified_flow_schedule(num_steps, shift=1.0, sigma_min=0.001, sigma_max=1.0, num_train_timesteps=1000,
                             mu=None):
     """algorithm/noise_scheduler/flow_match/recifited_flow.py:34-50 (mu given = dynamic shifting, as Flux uses)."""

@@ -90,3 +90,24 @@ def test_small_model_end_to_end(dsb, cuda_dev, fmt):
     eng._graph = None
     eng.step()
     assert dsb._lib.launches - n0 == eng.kernel_launches_per_step()
+
+
+@pytest.mark.parametrize("fmt", ["int8_channel", "fp8_tensor"])
+def test_double_stream_only_model_with_ragged_token_counts(dsb, cuda_dev, fmt):
+    """The Qwen-Image-architecture stand-in (double-stream blocks only, text width != 4096) at a reduced size with
+    token counts that are no tile multiple: 9x7 = 63 image tokens, 20 text tokens."""
+    d, H, nd = 256, 2, 3
+    shapes = synth.flux_dit_shapes(d=d, H=H, n_double=nd, n_single=0, txt_dim=448, pooled_dim=64)
+    w = {k: v.bfloat16().float() for k, v in synth.make_state_dict(shapes, seed=12).items()}
+    lat = synth.randn((1, 16, 18, 14), 13).bfloat16().float()
+    pe, pooled = synth.randn((1, 20, 448), 14).bfloat16().float(), synth.randn((1, 64), 15)
+    t, g = torch.tensor([250.0]), torch.tensor([1.0])
+    ref = OF.flux_dit_forward(w, lat, t, pe, pooled, g, n_double=nd, n_single=0, H=H, lin=LinearEval(fmt),
+                              rt=OF.round_bf16)
+    from diffsynth_engine_b200.flux import FluxDiTEngine
+    eng = FluxDiTEngine(dict(w), fmt=fmt, device=cuda_dev, n_double=nd, n_single=0, num_heads=H)
+    out = eng(lat.to(cuda_dev), t.to(cuda_dev), pe.to(cuda_dev), pooled.to(cuda_dev), g.to(cuda_dev)).float().cpu()
+    err = O.rel_l2(out, ref)
+    print(f"double-stream-only model {fmt}: rel-L2 {err:.3e}")
+    assert out.shape == (1, 16, 18, 14)
+    assert err < 2e-2

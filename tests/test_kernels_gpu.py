@@ -192,6 +192,21 @@ def test_euler_step(dsb, cuda_dev):
     assert torch.equal(outb.cpu(), refb)
 
 
+def test_cfg_euler_step(dsb, cuda_dev):
+    """CFG combine + Euler update in one kernel, bit-identical to the reference's two tensor expressions."""
+    g = _gen(18)
+    lat, pos, neg = (torch.randn(1, 16, 21, 30, 52, generator=g) for _ in range(3))
+    sig = torch.linspace(0.999, 0.001, 51)
+    for cast in (lambda t: t, _bf):
+        l, p, n = cast(lat), cast(pos), cast(neg)
+        ref = O.euler_step(l, O.cfg_combine(p, n, 5.0), sig, 7)
+        out = dsb.ops.cfg_euler_step(l.to(cuda_dev), p.to(cuda_dev), n.to(cuda_dev), 5.0, float(sig[8] - sig[7]))
+        if l.dtype == torch.float32:
+            assert torch.allclose(out.cpu(), ref, rtol=1e-6, atol=1e-6)
+        else:
+            assert torch.equal(out.cpu(), ref)
+
+
 # ---------------------------------------------------------------------------------- gemm
 def _gemm_case(dsb, dev, fmt, M, N, K, per_channel, bias, act, gated, seed=11):
     g = _gen(seed)
