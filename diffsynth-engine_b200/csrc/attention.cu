@@ -7,15 +7,21 @@
 //               (plain tiled loads, 128-byte swizzle, two 64-column halves)
 //   warp 1      MMA issuer:   S_q = Q_q K_j^T  (SS, both operands K-major)
 //                             O_q += P_q V_j   (TS: P read from TMEM, V MN-major)
-//   warps 4-7   softmax of query tile 0 (one thread per query row)
-//   warps 8-11  softmax of query tile 1
-// TMEM (512 columns): S_0 | S_1 | O_0 | O_1, 128 fp32 columns each; the bf16
-// probabilities P_q overwrite the first 64 columns of S_q, so S_q(j+1) is issued
-// only after O_q += P_q(j) V_j, and the two query tiles ping-pong on the tensor
-// core while the other one is in its softmax.
-// The running maximum is refreshed lazily (only when it grows by more than 2^8),
-// which keeps O's rescale out of the common path; it is exact because O and the
-// row sum carry the same reference maximum.
+//   warps 4-11  softmax of query tile 0, two threads per query row: warps 4-7 own key columns [0,64) of the
+//               score tile, warps 8-11 own [64,128)
+//   warps 12-19 softmax of query tile 1, same split
+// TMEM (512 columns): S_0 | S_1 | O_0 | O_1, 128 fp32 columns each.  Each softmax thread turns its 64 scores into
+// 32 columns of packed bf16 probabilities written over the FIRST half of its own 64 score columns, so P_q sits in
+// columns [0,32) and [64,96) of S_q and no thread ever writes where another thread still has scores to read.
+// S_q(j+1) is issued only after O_q += P_q(j) V_j, and the two query tiles ping-pong on the tensor core.
+//
+// The exponentials use a REFERENCE maximum that is one tile stale: p = exp2(s*c - m_ref) with m_ref = the row's
+// maximum over all earlier key tiles.  Row sums and O carry the same reference, so the result is exact; entries of
+// the current tile that exceed m_ref simply give p > 1 (fp32/bf16 have the range).  That takes the row-maximum
+// reduction - and the exchange of it between the two threads of a row - off the S -> P -> MMA critical path: the
+// threads publish their running maxima after they hand P over, and pick the partner's value up one tile later.
+// Only the first tile computes its maximum before exponentiating.  m_ref is refreshed (O and the sums rescaled)
+// when the running maximum has grown by more than 2^8.
 #include <algorithm>
 #include <mutex>
 
@@ -24,16 +30,15 @@
 
 namespace dsb {
 
-constexpr int kAttnThreads = 384;
+constexpr int kAttnThreads = 640;  // 4 control warps + 16 softmax warps
 constexpr int kTileQ = 128;
 constexpr int kTileKV = 128;
 constexpr int kNQ = 2;
 constexpr int kKVStages = 2;
 constexpr int kTileBytes = 128 * 128 * 2;  // 32 KiB: one 128 x 128 bf16 tile as two 64-column halves
 constexpr int kHalfBytes = kTileBytes / 2;
-constexpr int kCtrlRegs = 72;      // registers per thread kept by the control warps
-constexpr int kSoftmaxRegs = 208;  // registers per thread of the softmax warps
-constexpr int kAttnSmem = (kNQ + 2 * kKVStages) * kTileBytes + 256 + 1024;
+constexpr int kXchgSlots = 2 * 2 * 128 * 3;  // [q][half][row] x {running maximum (even tile, odd tile), row sum}
+constexpr int kAttnSmem = (kNQ + 2 * kKVStages) * kTileBytes + 256 + kXchgSlots * 8 + 1024;
 
 struct AttnParams {
   __nv_bfloat16* o;
@@ -52,6 +57,32 @@ __device__ __forceinline__ void reg_alloc() {
 template <int N>
 __device__ __forceinline__ void reg_dealloc() {
   asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(N));
+}
+
+// Hand-over of one float between the two threads of a query row: a 64-bit slot {sequence number, value} written with
+// one store; the reader spins (bounded) until the sequence number it expects is there.
+__device__ __forceinline__ void xchg_publish(unsigned long long* slot, uint32_t seq, float v) {
+  *reinterpret_cast<volatile unsigned long long*>(slot) =
+      (static_cast<unsigned long long>(seq) << 32) | static_cast<unsigned long long>(__float_as_uint(v));
+}
+__device__ __forceinline__ bool xchg_read(const unsigned long long* slot, uint32_t seq, float* v,
+                                          volatile int* abort_flag) {
+  const long long t0 = clock64();
+  uint32_t spins = 0;
+  for (;;) {
+    const unsigned long long w = *reinterpret_cast<const volatile unsigned long long*>(slot);
+    if (static_cast<uint32_t>(w >> 32) == seq) {
+      *v = __uint_as_float(static_cast<uint32_t>(w));
+      return true;
+    }
+    if (((++spins) & 0xffu) == 0) {
+      if (*abort_flag) return false;
+      if (clock64() - t0 > kWaitLimitCycles) {
+        *abort_flag = 1;
+        return false;
+      }
+    }
+  }
 }
 
 __device__ __forceinline__ void load_tile(uint8_t* dst, const CUtensorMap* m, uint64_t* bar, const int (&pos)[3], int s0,
@@ -83,6 +114,7 @@ __global__ void __launch_bounds__(kAttnThreads, 1)
   uint64_t* o_full = p_full + kNQ;          // kNQ
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(o_full + kNQ);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  unsigned long long* xchg = reinterpret_cast<unsigned long long*>(reinterpret_cast<uint8_t*>(bars) + 256);
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -101,12 +133,13 @@ __global__ void __launch_bounds__(kAttnThreads, 1)
     }
     for (int q = 0; q < kNQ; ++q) {
       mbar_init(&s_full[q], 1);
-      mbar_init(&p_full[q], 128);
+      mbar_init(&p_full[q], 256);
       mbar_init(&o_full[q], 1);
     }
     *abort_flag = 0;
     fence_mbar_init();
   }
+  for (int i = threadIdx.x; i < kXchgSlots; i += blockDim.x) xchg[i] = 0ull;  // sequence 0 = nothing published
   if (warp == 0 && lane == 0) {
     tma_prefetch_desc(&tmap_q);
     tma_prefetch_desc(&tmap_k);
@@ -121,12 +154,6 @@ __global__ void __launch_bounds__(kAttnThreads, 1)
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
-  // Registers move from the four control warps (TMA, MMA, two idle) to the softmax warps, which hold a whole
-  // 128-wide score row per thread.  The kernel launches with 168 registers per thread (384 threads); the 128
-  // control threads give back 168-72 = 96 each (12288), the 256 softmax threads take 208-168 = 40 each (10240).
-  // The increase must never ask for more than was released: setmaxnreg.inc blocks until it is satisfied.
-  static_assert((168 - kCtrlRegs) * 128 >= (kSoftmaxRegs - 168) * 256, "setmaxnreg.inc could never be satisfied");
-  if (warp < 4) reg_dealloc<kCtrlRegs>();
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer
     if (lane == 0) {
@@ -178,7 +205,8 @@ __global__ void __launch_bounds__(kAttnThreads, 1)
 #pragma unroll
         for (int kk = 0; kk < 8; ++kk) {
           // 16 keys per instruction = 16 rows of 128 bytes (2048 bytes = 128 units) further into the V tile
-          mma_ts_f16(d, a + kk * 8, bd0 + kk * 128u, idesc_pv, (accumulate || kk > 0) ? 1u : 0u);
+          // P of keys [0,64) lives in columns [0,32) of S_q, P of keys [64,128) in columns [64,96)
+          mma_ts_f16(d, a + (kk >> 2) * 64 + (kk & 3) * 8, bd0 + kk * 128u, idesc_pv, (accumulate || kk > 0) ? 1u : 0u);
         }
       };
       int kst = 0, vst = 0;
@@ -218,15 +246,20 @@ __global__ void __launch_bounds__(kAttnThreads, 1)
   mma_done:;
   } else if (warp >= 4) {
     // ----------------------------------------------------------------- softmax
-    reg_alloc<kSoftmaxRegs>();
-    const int q = (warp - 4) >> 2;
+    const int ws = warp - 4;
+    const int q = ws >> 3;
+    const int half = (ws >> 2) & 1;
     const int quad = warp & 3;
     const int row = quad * 32 + lane;
     const uint32_t lane_off = static_cast<uint32_t>(quad * 32) << 16;
-    const uint32_t t_s = tmem_base + lane_off + q * 128;
-    const uint32_t t_o = tmem_base + lane_off + 256 + q * 128;
+    const uint32_t t_s = tmem_base + lane_off + q * 128 + half * 64;        // my 64 score columns; P goes to the first 32
+    const uint32_t t_o = tmem_base + lane_off + 256 + q * 128 + half * 64;  // my half of the output columns
+    unsigned long long* slot_mine = xchg + ((q * 2 + half) * 128 + row) * 3;  // {max even tile, max odd tile, sum}
+    const unsigned long long* slot_other = xchg + ((q * 2 + (half ^ 1)) * 128 + row) * 3;
     const float cs = p.scale_log2;
-    float m = 0.f, l = 0.f;
+    float m_ref = 0.f;       // reference maximum (log2 units) the exponentials, the row sum and O currently use
+    float run_max = -INFINITY;  // this thread's running maximum of raw scores over its columns, all tiles so far
+    float l = 0.f;
     bool ok = true;
     for (int j = 0; j < nkv; ++j) {
       if (!mbar_wait(&s_full[q], j & 1, abort_flag)) {
@@ -234,73 +267,130 @@ __global__ void __launch_bounds__(kAttnThreads, 1)
         break;
       }
       tc_fence_after();
-      const int valid = min(kTileKV, p.Sk - j * kTileKV);
-      // the whole score row (128 fp32) in registers: four loads in flight, one wait
-      uint32_t s[128];
-#pragma unroll
-      for (int c = 0; c < 4; ++c) tmem_ld32(t_s + c * 32, reinterpret_cast<uint32_t(&)[32]>(s[c * 32]));
-      tc_wait_ld();
-      if (valid != kTileKV) {
-#pragma unroll
-        for (int i = 0; i < 128; ++i)
-          if (i >= valid) s[i] = 0xff800000u;  // -inf: masked keys of the last tile
-      }
-      float mx[8];
-#pragma unroll
-      for (int a = 0; a < 8; ++a) mx[a] = __uint_as_float(s[a]);
-#pragma unroll
-      for (int i = 8; i < 128; ++i) mx[i & 7] = fmaxf(mx[i & 7], __uint_as_float(s[i]));
-      const float mrow = fmaxf(fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])),
-                               fmaxf(fmaxf(mx[4], mx[5]), fmaxf(mx[6], mx[7])));
-      const float m_new = mrow * cs;
+      const int valid = min(kTileKV, p.Sk - j * kTileKV) - half * 64;  // valid columns among my 64 (may be <= 0)
       if (j == 0) {
-        m = m_new;
-      } else if (__any_sync(0xffffffffu, m_new > m + 8.0f)) {
-        const float m_upd = fmaxf(m, m_new);
-        const float alpha = fast_exp2(m - m_upd);
-        m = m_upd;
-        l *= alpha;
-#pragma unroll 1
-        for (int c = 0; c < 4; ++c) {
-          uint32_t r[32];
-          tmem_ld32(t_o + c * 32, r);
-          tc_wait_ld();
+        // first tile: the row maximum must be known before anything is exponentiated
+        uint32_t s0[32], s1[32];
+        tmem_ld32(t_s, s0);
+        tmem_ld32(t_s + 32, s1);
+        tc_wait_ld();
+        float mx = -INFINITY;
 #pragma unroll
-          for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
-          tmem_st32(t_o + c * 32, r);
+        for (int i = 0; i < 32; ++i) {
+          if (i < valid) mx = fmaxf(mx, __uint_as_float(s0[i]));
+          if (32 + i < valid) mx = fmaxf(mx, __uint_as_float(s1[i]));
         }
-      }
-      // probabilities, written over S as packed bf16 (64 columns)
-      float ls[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll
-      for (int c = 0; c < 4; ++c) {
+        run_max = mx;
+        xchg_publish(&slot_mine[0], 1u, mx);
+        float mo;
+        if (!xchg_read(&slot_other[0], 1u, &mo, abort_flag)) {
+          ok = false;
+          break;
+        }
+        m_ref = fmaxf(mx, mo) * cs;  // at least one key of the tile is valid, so this is finite
+        float ls = 0.f;
         uint32_t pk[16];
 #pragma unroll
         for (int i = 0; i < 16; ++i) {
-          const float p0 = fast_exp2(fmaf(__uint_as_float(s[c * 32 + 2 * i]), cs, -m));
-          const float p1 = fast_exp2(fmaf(__uint_as_float(s[c * 32 + 2 * i + 1]), cs, -m));
-          ls[i & 3] += p0 + p1;
+          const float p0 = (2 * i < valid) ? fast_exp2(fmaf(__uint_as_float(s0[2 * i]), cs, -m_ref)) : 0.f;
+          const float p1 = (2 * i + 1 < valid) ? fast_exp2(fmaf(__uint_as_float(s0[2 * i + 1]), cs, -m_ref)) : 0.f;
+          ls += p0 + p1;
           pk[i] = pack_bf16x2(p0, p1);
         }
-        tmem_st16(t_s + c * 16, pk);
+        tmem_st16(t_s, pk);
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+          const float p0 = (32 + 2 * i < valid) ? fast_exp2(fmaf(__uint_as_float(s1[2 * i]), cs, -m_ref)) : 0.f;
+          const float p1 = (33 + 2 * i < valid) ? fast_exp2(fmaf(__uint_as_float(s1[2 * i + 1]), cs, -m_ref)) : 0.f;
+          ls += p0 + p1;
+          pk[i] = pack_bf16x2(p0, p1);
+        }
+        tmem_st16(t_s + 16, pk);
+        l = ls;
+      } else {
+        // pick up the partner's running maximum of the tiles before this one (published after the previous tile)
+        float mo;
+        if (!xchg_read(&slot_other[(j - 1) & 1], static_cast<uint32_t>(j), &mo, abort_flag)) {
+          ok = false;
+          break;
+        }
+        const float m_run = fmaxf(run_max, mo) * cs;
+        if (__any_sync(0xffffffffu, m_run > m_ref + 8.0f)) {
+          // both warps of these rows see the same values, so both take this branch.  O is idle: S_q(j) is only
+          // signalled after O_q += P_q(j-1) V has completed.
+          const float m_upd = fmaxf(m_ref, m_run);
+          const float alpha = fast_exp2(m_ref - m_upd);
+          m_ref = m_upd;
+          l *= alpha;
+#pragma unroll 1
+          for (int c = 0; c < 2; ++c) {
+            uint32_t r[32];
+            tmem_ld32(t_o + c * 32, r);
+            tc_wait_ld();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
+            tmem_st32(t_o + c * 32, r);
+          }
+        }
+        float mx[4] = {run_max, run_max, run_max, run_max};
+        float ls[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+        for (int c = 0; c < 2; ++c) {
+          uint32_t sc[32];
+          tmem_ld32(t_s + c * 32, sc);
+          tc_wait_ld();
+          uint32_t pk[16];
+          if (valid >= 64) {
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+              const float a0 = __uint_as_float(sc[2 * i]), a1 = __uint_as_float(sc[2 * i + 1]);
+              // the clamp only matters for rows whose scores jump by more than 2^100 from one key tile to the next
+              const float p0 = fast_exp2(fminf(fmaf(a0, cs, -m_ref), 100.f));
+              const float p1 = fast_exp2(fminf(fmaf(a1, cs, -m_ref), 100.f));
+              mx[i & 3] = fmaxf(mx[i & 3], fmaxf(a0, a1));
+              ls[i & 3] += p0 + p1;
+              pk[i] = pack_bf16x2(p0, p1);
+            }
+          } else {
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+              const int c0 = c * 32 + 2 * i;
+              const float a0 = __uint_as_float(sc[2 * i]), a1 = __uint_as_float(sc[2 * i + 1]);
+              const float p0 = (c0 < valid) ? fast_exp2(fminf(fmaf(a0, cs, -m_ref), 100.f)) : 0.f;
+              const float p1 = (c0 + 1 < valid) ? fast_exp2(fminf(fmaf(a1, cs, -m_ref), 100.f)) : 0.f;
+              if (c0 < valid) mx[i & 3] = fmaxf(mx[i & 3], a0);
+              if (c0 + 1 < valid) mx[i & 3] = fmaxf(mx[i & 3], a1);
+              ls[i & 3] += p0 + p1;
+              pk[i] = pack_bf16x2(p0, p1);
+            }
+          }
+          tmem_st16(t_s + c * 16, pk);
+        }
+        run_max = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
+        l += (ls[0] + ls[1]) + (ls[2] + ls[3]);
       }
-      l += (ls[0] + ls[1]) + (ls[2] + ls[3]);
       tc_wait_st();
       tc_fence_before();
       mbar_arrive(&p_full[q]);
+      // off the critical path: publish my running maximum for the partner to use at the next tile (slot by tile
+      // parity: the partner cannot be two tiles ahead, S_q(j+2) needs this thread's P_q(j+1))
+      if (j > 0) xchg_publish(&slot_mine[j & 1], static_cast<uint32_t>(j + 1), run_max);
     }
     if (ok && mbar_wait(&o_full[q], 0, abort_flag)) {
       tc_fence_after();
+      xchg_publish(&slot_mine[2], 0x7fffffffu, l);
+      float lo = 0.f;
+      ok = xchg_read(&slot_other[2], 0x7fffffffu, &lo, abort_flag);
+      const float inv = 1.0f / (l + lo);
       const int sq = q0 + q * kTileQ + row;
-      const float inv = 1.0f / l;
       __nv_bfloat16* orow = p.o + static_cast<int64_t>(b) * p.o_stride_b + static_cast<int64_t>(sq) * p.o_stride_s +
-                            static_cast<int64_t>(h) * p.o_stride_h;
+                            static_cast<int64_t>(h) * p.o_stride_h + half * 64;
 #pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
+      for (int c = 0; c < 2; ++c) {
         uint32_t r[32];
         tmem_ld32(t_o + c * 32, r);
         tc_wait_ld();
-        if (sq < p.Sq) {
+        if (ok && sq < p.Sq) {
 #pragma unroll
           for (int g = 0; g < 4; ++g) {
             uint4 o;
