@@ -469,7 +469,7 @@ def main():
                 else "gemm_kernel<bf16>", "bound": "tensor",
                 "achieved": ach_tf, "peak": peak_tf, "unit": "TFLOP/s", "frac": ach_tf / peak_tf,
                 # DRAM read+write bytes per GEMM launch: ncu capture of the 1+1-block case scaled by the block counts
-                # (profiles/flux_step_dram_traffic.md); only meaningful for the full 19+38-block FP8 model
+                # (the ncu summary of per-kernel DRAM traffic under profiles/); only meaningful for the full 19+38-block FP8 model
                 "traffic": (30.8e9 / 231 if (fp8 and not args.blocks) else None),
                 "peak_source": (f"2 x bf16_tflops of MEASURED_PEAKS.json ({peaks['source']}); no FP8 peak was measured"
                                 if fp8 else f"bf16_tflops of MEASURED_PEAKS.json ({peaks['source']})"),

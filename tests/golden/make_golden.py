@@ -1,7 +1,7 @@
 """Generates the fixtures in this directory by EXECUTING THE REFERENCE (modelscope/DiffSynth-Engine
 v0.1.1, imported from its source tree) on seeded inputs.  Run where the reference is mounted:
 
-    python tests/golden/make_golden.py /root/reference
+    python tests/golden/make_golden.py <path to the DiffSynth-Engine source tree>
 
 Only outputs (and small inputs) are stored; weights and large inputs are regenerated from their seeds by
 ``diffsynth-engine_b200/synth.py``, which the reference run, the oracle and the CUDA path all share.
@@ -166,4 +166,4 @@ def main(ref_root):
 
 
 if __name__ == "__main__":
-    main(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    main(sys.argv[1] if len(sys.argv) > 1 else os.path.join(os.path.expanduser("~"), "reference"))

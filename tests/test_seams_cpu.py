@@ -40,7 +40,7 @@ def test_synth_is_deterministic():
     assert 11.8e9 < n < 12.0e9  # Flux.1-dev has 11.9 G parameters
 
 
-REF = os.environ.get("DSB_REFERENCE_ROOT", "/root/reference")
+REF = os.environ.get("DSB_REFERENCE_ROOT", os.path.join(os.path.expanduser("~"), "reference"))
 
 
 @pytest.mark.skipif(not os.path.isdir(os.path.join(REF, "diffsynth_engine")), reason="reference tree not mounted")
