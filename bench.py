@@ -294,6 +294,9 @@ def main():
     ap.add_argument("--wan-fmt", default="fp8_channel")
     ap.add_argument("--wan-layers", type=int, default=0, help="reduced depth (debugging; not a bench)")
     ap.add_argument("--wan-steps", type=int, default=2)
+    ap.add_argument("--sp", action="store_true",
+                    help="flux/qwen workloads under torchrun: ONE image, its token sequence split over all ranks (Ulysses, "
+                         "strong scaling) instead of one replica per GPU")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -307,8 +310,10 @@ def main():
     else:
         wl = ("flux1-dev-arch DiT step, 1024x1024 (4096 image + 512 text tokens), batch 1, "
               f"{cfg['n_double']} double + {cfg['n_single']} single blocks, weights {args.fmt}, bf16 activations")
+    sp = args.sp and world > 1
     config = {"workload": wl,
-              "parallelism": f"replicas x{world}" if world > 1 else "single GPU",
+              "parallelism": (f"sp{world} (Ulysses, one image)" if sp else f"replicas x{world}") if world > 1
+              else "single GPU",
               "l2": "per-step working set (11.9 GB of weights) exceeds the 126 MB L2; no flush between steps"}
 
     if args.impl == "reference":
@@ -363,16 +368,17 @@ def main():
     # random-init weights of the architecture, drawn on the device, packed to FP8 layer by layer
     shapes = synth.flux_dit_shapes(d=cfg["d"], H=cfg["H"], n_double=cfg["n_double"], n_single=cfg["n_single"],
                                    txt_dim=cfg["txt_dim"], pooled_dim=cfg["pooled_dim"])
-    sd = synth.make_state_dict(shapes, seed=rank, device=dev, dtype=torch.bfloat16)
+    seed = 0 if sp else rank            # sequence parallel: every rank holds the same model and the same inputs
+    sd = synth.make_state_dict(shapes, seed=seed, device=dev, dtype=torch.bfloat16)
     eng = flux.FluxDiTEngine(sd, fmt=args.fmt, device=dev, n_double=cfg["n_double"], n_single=cfg["n_single"],
-                             num_heads=cfg["H"], release_source=True)
+                             num_heads=cfg["H"], release_source=True, group=dist.group.WORLD if sp else None)
     del sd
     torch.cuda.empty_cache()
     eng.prepare(cfg["S_txt"], cfg["height"], cfg["width"], cfg["txt_dim"], cfg["pooled_dim"])
     # inputs on the host (pinned), as a pipeline would hold them between steps
-    h_lat = synth.randn((1, 16, cfg["height"], cfg["width"]), 100 + rank).bfloat16().pin_memory()
-    h_pe = synth.randn((1, cfg["S_txt"], cfg["txt_dim"]), 200 + rank).bfloat16().pin_memory()
-    h_pool = synth.randn((1, cfg["pooled_dim"]), 300 + rank).pin_memory()
+    h_lat = synth.randn((1, 16, cfg["height"], cfg["width"]), 100 + seed).bfloat16().pin_memory()
+    h_pe = synth.randn((1, cfg["S_txt"], cfg["txt_dim"]), 200 + seed).bfloat16().pin_memory()
+    h_pool = synth.randn((1, cfg["pooled_dim"]), 300 + seed).pin_memory()
     h_t, h_g = torch.tensor([500.0]).pin_memory(), torch.tensor([3.5]).pin_memory()
     h_out = torch.empty((1, 16, cfg["height"], cfg["width"]), dtype=torch.bfloat16).pin_memory()
     h2d = sum(t.numel() * t.element_size() for t in (h_lat, h_pe, h_pool, h_t, h_g))
@@ -414,7 +420,7 @@ def main():
     ms_total = max_over_ranks(e0.elapsed_time(e1))
     clocks = sampler.stop() if sampler else None
     ms_per_step = ms_total / args.steps
-    value = world * 1e3 / ms_per_step
+    value = (1 if sp else world) * 1e3 / ms_per_step
 
     # ---- end to end: host buffers in, host buffer out, every step
     def e2e_step():
@@ -439,25 +445,27 @@ def main():
     # ---- roofline of the dominant kernel (the FP8 GEMM): CUDA events around every launch of one eager step
     peaks = measured_peaks()
     recs = []
-    real_gemm, real_gemm_qkv = ops.gemm, ops.gemm_qkv
+    real_gemm, real_gemm_qkv, real_group = ops.gemm, ops.gemm_qkv, ops.gemm_group
 
-    def timed(fn):
-        def wrapper(a, w, *rest, **kw):
+    def timed(fn, grouped=False):
+        def wrapper(a, *rest, **kw):
             s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             s.record()
-            r = fn(a, w, *rest, **kw)
+            r = fn(a, *rest, **kw)
             e.record()
-            recs.append((2.0 * a.shape[0] * a.shape[1] * w.shape[0], s, e))
+            probs = a if grouped else [dict(a=a, w=rest[0])]
+            recs.append((sum(2.0 * p["a"].shape[0] * p["a"].shape[1] * p["w"].shape[0] for p in probs), s, e))
             return r
         return wrapper
 
     eng._graph_saved, eng._graph = eng._graph, None
-    ops.gemm, ops.gemm_qkv = timed(real_gemm), timed(real_gemm_qkv)   # both entry points launch gemm_kernel
+    # all three entry points launch gemm_kernel (a grouped launch runs two problems in one persistent grid)
+    ops.gemm, ops.gemm_qkv, ops.gemm_group = timed(real_gemm), timed(real_gemm_qkv), timed(real_group, True)
     try:
         eng.step()
         torch.cuda.synchronize()
     finally:
-        ops.gemm, ops.gemm_qkv = real_gemm, real_gemm_qkv
+        ops.gemm, ops.gemm_qkv, ops.gemm_group = real_gemm, real_gemm_qkv, real_group
         eng._graph = eng._graph_saved
     gemm_flops = sum(r[0] for r in recs)
     gemm_ms = sum(r[1].elapsed_time(r[2]) for r in recs)
@@ -470,19 +478,20 @@ def main():
                 "achieved": ach_tf, "peak": peak_tf, "unit": "TFLOP/s", "frac": ach_tf / peak_tf,
                 # DRAM read+write bytes per GEMM launch: ncu capture of the 1+1-block case scaled by the block counts
                 # (the ncu summary of per-kernel DRAM traffic under profiles/); only meaningful for the full 19+38-block FP8 model
-                "traffic": (30.8e9 / 231 if (fp8 and not args.blocks) else None),
+                "traffic": (30.8e9 / 231 if (fp8 and not args.blocks and args.workload != "qwen" and not sp) else None),
                 "peak_source": (f"2 x bf16_tflops of MEASURED_PEAKS.json ({peaks['source']}); no FP8 peak was measured"
                                 if fp8 else f"bf16_tflops of MEASURED_PEAKS.json ({peaks['source']})"),
                 "launches_per_step": len(recs), "gemm_ms_per_step": gemm_ms,
                 "method": "CUDA events around each GEMM launch of one eager (un-graphed) step; 2MNK per launch",
                 "step_tflop": (lin_f + attn_f) / 1e12,
-                "step_frac_of_roofline": ((lin_f / (peak_tf * 1e12) + attn_f / (peaks["bf16"] * 1e12)) * 1e3) / ms_per_step}
+                "step_frac_of_roofline": ((lin_f / (peak_tf * 1e12) + attn_f / (peaks["bf16"] * 1e12)) * 1e3) / (ms_per_step * (world if sp else 1))}
 
     line = {"metric": "DiT denoise steps/s", "value": value, "unit": "steps/s", "n_gpus": world, "steps": args.steps,
-            "warmup": max(3, args.warmup), "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
+            "warmup": max(3, args.warmup), "ms_per_step": ms_per_step, "higher_is_better": True,
+            "scaling": "strong" if sp else "weak",
             "vs_baseline": None, "dtype": "fp8_e4m3 x fp8_e4m3 -> fp32 (linear), bf16 (attention)" if fp8 else "bf16",
             "data": "synthetic", "config": config, "clocks": clocks,
-            "e2e": {"value": world * 1e3 / e2e_ms, "unit": "steps/s", "h2d_bytes_per_step": h2d,
+            "e2e": {"value": (1 if sp else world) * 1e3 / e2e_ms, "unit": "steps/s", "h2d_bytes_per_step": h2d,
                     "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms, "wall_ms_per_step": e2e_wall_ms},
             "gpu_launches": launches_per_step * args.steps, "gpu_launches_per_step": launches_per_step,
             "roofline": roofline}

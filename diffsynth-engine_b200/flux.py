@@ -40,7 +40,17 @@ def flux_rope_table(ids: torch.Tensor, axes_dim=(16, 56, 56), theta=10000) -> to
 class FluxDiTEngine:
     def __init__(self, state_dict: Dict[str, torch.Tensor], fmt: str = "fp8_tensor", device="cuda:0",
                  n_double: int = 19, n_single: int = 38, num_heads: int = 24, use_guidance: bool = True,
-                 release_source: bool = False):
+                 release_source: bool = False, group=None):
+        """``group``: a ``torch.distributed`` process group to run the step sequence-parallel over (Ulysses): every
+        rank then owns a contiguous slice of the joint text+image token sequence (padded to a multiple of the group
+        size) for all token-wise kernels, and the joint attention exchanges heads for tokens; weights are
+        replicated (pass ``torch.distributed.group.WORLD`` for all ranks).  ``None`` = one GPU."""
+        from .wan import HeadExchange
+        self.xchg = HeadExchange(group)
+        # without a group the engine is a one-GPU replica even inside an initialised process group
+        self.P, self.rank = (self.xchg.world, self.xchg.rank) if group is not None else (1, 0)
+        if num_heads % self.P:
+            raise ValueError(f"{num_heads} heads do not split over {self.P} ranks")
         self.dev = torch.device(device)
         self.fmt = fmt
         self.afmt = act_format(fmt)
@@ -97,13 +107,20 @@ class FluxDiTEngine:
 
     # ------------------------------------------------------------------ buffers
     def _alloc(self, S_txt: int, height: int, width: int, txt_dim: int, pooled_dim: int):
-        d, dev = self.d, self.dev
+        d, dev, P = self.d, self.dev, self.P
         S_img = (height // 2) * (width // 2)
         S = S_txt + S_img
+        S_pad = (S + P - 1) // P * P            # joint sequence padded so that every rank owns Sl rows
+        Sl = S_pad // P
+        g0 = self.rank * Sl                     # global index of this rank's first row
+        t_loc = min(max(S_txt - g0, 0), Sl)     # local rows [0, t_loc) are text, [t_loc, Sl) image (+ padding)
+        n_loc = min(max(S - g0, 0), Sl)         # local rows below n_loc exist in the unpadded sequence
         qdt = {ops.FMT_BF16: torch.bfloat16, ops.FMT_E4M3: torch.float8_e4m3fn, ops.FMT_INT8: torch.int8}[self.afmt]
         bf = torch.bfloat16
-        b = dict(S_txt=S_txt, S_img=S_img, S=S, height=height, width=width)
-        # static inputs
+        C = d // P
+        b = dict(S_txt=S_txt, S_img=S_img, S=S, S_pad=S_pad, Sl=Sl, g0=g0, t_loc=t_loc, n_loc=n_loc, height=height,
+                 width=width)
+        # static inputs (replicated on every rank)
         b["latents"] = torch.zeros(1, self.in_ch // 4, height, width, dtype=bf, device=dev)
         b["prompt"] = torch.zeros(S_txt, txt_dim, dtype=bf, device=dev)
         b["pooled"] = torch.zeros(pooled_dim, dtype=torch.float32, device=dev)
@@ -112,15 +129,20 @@ class FluxDiTEngine:
         b["hid"] = torch.zeros(d, dtype=torch.float32, device=dev)
         b["cond"] = torch.zeros(d, dtype=torch.float32, device=dev)
         b["modv"] = torch.zeros(self.mod.out_features, dtype=torch.float32, device=dev)
-        b["x"] = torch.zeros(S, d, dtype=bf, device=dev)
-        b["xq"] = torch.zeros(S, max(d, txt_dim), dtype=qdt, device=dev)       # quantised LN output / embedder input
-        b["rs"] = torch.zeros(S, dtype=torch.float32, device=dev)
-        b["qkv"] = torch.zeros(S, 3 * d, dtype=bf, device=dev)
-        b["cat"] = torch.zeros(S, 5 * d, dtype=bf, device=dev)                 # [attention out | gelu(mlp)]
-        b["catq"] = torch.zeros(S if self.afmt != ops.FMT_BF16 else 1, 5 * d, dtype=qdt, device=dev)
+        b["x"] = torch.zeros(Sl, d, dtype=bf, device=dev)
+        b["xq"] = torch.zeros(Sl, max(d, txt_dim), dtype=qdt, device=dev)      # quantised LN output / embedder input
+        b["rs"] = torch.zeros(Sl, dtype=torch.float32, device=dev)
+        b["qkv"] = torch.zeros(Sl, 3 * d, dtype=bf, device=dev)
+        b["cat"] = torch.zeros(Sl, 5 * d, dtype=bf, device=dev)                # [attention out | gelu(mlp)]
+        b["catq"] = torch.zeros(Sl if self.afmt != ops.FMT_BF16 else 1, 5 * d, dtype=qdt, device=dev)
         b["patches"] = torch.zeros(S_img, self.in_ch, dtype=bf, device=dev)
-        b["out_tok"] = torch.zeros(S_img, self.in_ch, dtype=bf, device=dev)
-        b["ids_key"] = None
+        b["out_tok"] = torch.zeros(Sl, self.in_ch, dtype=bf, device=dev)
+        if P > 1:   # head exchange: [P][Sl][q|k|v][d/P] out and back, attention output [S_pad, d/P] and its return
+            b["send"] = torch.zeros(P, Sl, 3, C, dtype=bf, device=dev)
+            b["recv"] = torch.zeros(P, Sl, 3, C, dtype=bf, device=dev)
+            b["ao"] = torch.zeros(P, Sl, C, dtype=bf, device=dev)
+            b["ao_back"] = torch.zeros(P, Sl, C, dtype=bf, device=dev)
+            b["out_all"] = torch.zeros(S_pad, self.in_ch, dtype=bf, device=dev)
         b["rope"] = None
         self._bufs = b
         self._graph = None
@@ -145,9 +167,28 @@ class FluxDiTEngine:
         return ops.gemm(a, p.w, row_scale=rs, col_scale=p.scale, bias=p.bias, **kw)
 
     # ---------------------------------------------------------------------- step
+    def _attention(self, q4, k4, v4, o4):
+        """Joint attention over the whole (unpadded) sequence.  One GPU: straight from the projection buffer.
+        Sequence parallel: q, k, v of the own token slice go out as [P][Sl][3][heads/P], all tokens of the own head
+        group come back, attention runs with the padded rows masked as keys, and the output returns the same way;
+        the result is left in ``ao_back`` as [P][Sl][d/P]."""
+        b, P = self._bufs, self.P
+        if P == 1:
+            ops.flash_attn(q4, k4, v4, out=o4)
+            return
+        d, Sl, C, S, S_pad, Hl = self.d, b["Sl"], self.d // P, b["S"], b["S_pad"], self.H // P
+        send, recv = b["send"], b["recv"]
+        # one copy and one all-to-all for q, k and v together: chunk p = [Sl rows][q | k | v of head group p]
+        send.copy_(b["qkv"].view(Sl, 3, P, C).permute(2, 0, 1, 3))
+        self.xchg(send, recv)
+        rows = recv.view(S_pad, 3, Hl, 128)                       # all tokens, own head group
+        ops.flash_attn(rows[:, 0].unsqueeze(0), rows[:S, 1].unsqueeze(0), rows[:S, 2].unsqueeze(0),   # real keys only
+                       out=b["ao"].view(1, S_pad, Hl, 128))
+        self.xchg(b["ao"], b["ao_back"])
+
     def _run(self):
-        b, d, H = self._bufs, self.d, self.H
-        S_txt, S = b["S_txt"], b["S"]
+        b, d, H, P = self._bufs, self.d, self.H, self.P
+        S_txt, S, Sl, g0, t_loc, n_loc = b["S_txt"], b["S"], b["Sl"], b["g0"], b["t_loc"], b["n_loc"]
         x, qkv, cat, catq, xq, rs = b["x"], b["qkv"], b["cat"], b["catq"], b["xq"], b["rs"]
         xq_d = xq[:, :d]
         # conditioning (flux_dit.py:409-415): time + guidance + pooled, fp32
@@ -162,14 +203,20 @@ class FluxDiTEngine:
         # every AdaLN shift/scale/gate of the step in one launch (they all read SiLU(cond))
         self._gemv(self.mod, b["cond"], b["modv"], act_in=ops.ACT_SILU)
         mv = b["modv"]
-        # token embedders (flux_dit.py:416,419-421)
+        # token embedders (flux_dit.py:416,419-421) on this rank's rows: text rows first, then image rows
+        img, txt = slice(t_loc, Sl), slice(0, t_loc)
         txt_dim = b["prompt"].shape[1]
-        a, s = self._quant(b["prompt"], xq[:S_txt, :txt_dim], rs[:S_txt])
-        self._gemm(a, s, self.ctx_emb, out=x[:S_txt])
+        if t_loc > 0:
+            a, s = self._quant(b["prompt"][g0:g0 + t_loc], xq[txt, :txt_dim], rs[txt])
+            self._gemm(a, s, self.ctx_emb, out=x[txt])
         b["patches"].copy_(b["latents"].reshape(self.in_ch // 4, b["height"] // 2, 2, b["width"] // 2, 2)
                            .permute(1, 3, 0, 2, 4).reshape(b["S_img"], self.in_ch))
-        a, s = self._quant(b["patches"], xq[S_txt:, :self.in_ch], rs[S_txt:])
-        self._gemm(a, s, self.x_emb, out=x[S_txt:])
+        n_img = n_loc - t_loc                    # image rows of this rank that exist (the rest is padding)
+        if n_img > 0:
+            p0 = g0 + t_loc - S_txt              # first image token of this rank
+            rows = slice(t_loc, n_loc)
+            a, s = self._quant(b["patches"][p0:p0 + n_img], xq[rows, :self.in_ch], rs[rows])
+            self._gemm(a, s, self.x_emb, out=x[rows])
 
         rope = b["rope"]
         attn_o = cat[:, :d]                      # attention output lands in the first d columns of `cat`
@@ -178,29 +225,37 @@ class FluxDiTEngine:
         v4 = qkv[:, 2 * d:].unflatten(1, (H, 128)).unsqueeze(0)
         o4 = attn_o.unflatten(1, (H, 128)).unsqueeze(0)
         off = 0
-        img, txt = slice(S_txt, S), slice(0, S_txt)
         hid_all, hidq_all = cat[:, d:5 * d], catq[:, d:5 * d]
 
         def pl(p, rows, a, sc, **kw):   # one problem of a grouped launch on a stream's row range
             return dict(a=a[rows], w=p.w, row_scale=None if sc is None else sc[rows], col_scale=p.scale, bias=p.bias,
                         **kw)
 
+        def attn_operand():
+            """The attention output as the next GEMM's activation operand (quantised rows)."""
+            if P == 1:
+                return self._quant(attn_o, catq[:, :d], rs)
+            if self.afmt == ops.FMT_BF16:
+                attn_o.copy_(b["ao_back"].permute(1, 0, 2).reshape(Sl, d))
+                return attn_o, None
+            return ops.quant_rows_chunked(b["ao_back"], self.afmt, out=catq[:, :d], row_scale=rs)
+
         for blk in self.double:
             m = mv[off:off + 12 * d]          # [image: shift,scale,gate (msa), shift,scale,gate (mlp) | text: same]
             off += 12 * d
             mi, mt = m[:6 * d], m[6 * d:]
             # both streams through one LayerNorm+modulate+quantise launch (text rows first in x)
-            a, sc = self._ln(x, mt[:d], mt[d:2 * d], xq_d, rs, split_row=S_txt, shift_b=mi[:d], scale_b=mi[d:2 * d])
+            a, sc = self._ln(x, mt[:d], mt[d:2 * d], xq_d, rs, split_row=t_loc, shift_b=mi[:d], scale_b=mi[d:2 * d])
             ops.gemm_group([
                 pl(blk["qkv_a"], img, a, sc, out=qkv[img], nq_w=blk["nq_a"], nk_w=blk["nk_a"], d_model=d, rope=rope,
-                   rope_row0=S_txt),
+                   rope_row0=g0 + t_loc),
                 pl(blk["qkv_b"], txt, a, sc, out=qkv[txt], nq_w=blk["nq_b"], nk_w=blk["nk_b"], d_model=d, rope=rope,
-                   rope_row0=0)])
-            ops.flash_attn(q4, k4, v4, out=o4)
-            a, sc = self._quant(attn_o, catq[:, :d], rs)
+                   rope_row0=g0)])
+            self._attention(q4, k4, v4, o4)
+            a, sc = attn_operand()
             ops.gemm_group([pl(blk["out_a"], img, a, sc, gate=mi[2 * d:3 * d], resid=x[img], out=x[img]),
                             pl(blk["out_b"], txt, a, sc, gate=mt[2 * d:3 * d], resid=x[txt], out=x[txt])])
-            a, sc = self._ln(x, mt[3 * d:4 * d], mt[4 * d:5 * d], xq_d, rs, split_row=S_txt, shift_b=mi[3 * d:4 * d],
+            a, sc = self._ln(x, mt[3 * d:4 * d], mt[4 * d:5 * d], xq_d, rs, split_row=t_loc, shift_b=mi[3 * d:4 * d],
                              scale_b=mi[4 * d:5 * d])
             ops.gemm_group([pl(blk["ff0_a"], img, a, sc, act=ops.ACT_GELU_TANH, out=hid_all[img]),
                             pl(blk["ff0_b"], txt, a, sc, act=ops.ACT_GELU_TANH, out=hid_all[txt])])
@@ -212,17 +267,21 @@ class FluxDiTEngine:
             off += 3 * d
             a, sc = self._ln(x, m[:d], m[d:2 * d], xq_d, rs)
             p = blk["qkv_mlp"]
-            ops.gemm_qkv(a, p.w, blk["nq"], blk["nk"], d, rope, 0, 1e-6, row_scale=sc, col_scale=p.scale, bias=p.bias,
+            ops.gemm_qkv(a, p.w, blk["nq"], blk["nk"], d, rope, g0, 1e-6, row_scale=sc, col_scale=p.scale, bias=p.bias,
                          act=ops.ACT_GELU_TANH, act_col0=3 * d, out=qkv, out1=cat[:, d:], split_col=3 * d)
-            ops.flash_attn(q4, k4, v4, out=o4)
+            self._attention(q4, k4, v4, o4)
+            if P > 1:   # bring the returned [P][Sl][d/P] layout back to rows next to gelu(mlp)
+                attn_o.copy_(b["ao_back"].permute(1, 0, 2).reshape(Sl, d))
             a, sc = self._quant(cat, catq, rs)
             self._gemm(a, sc, blk["proj"], gate=m[2 * d:3 * d], resid=x, out=x)
-        # final AdaLN (scale first, flux_dit.py:333) + projection on the image tokens
+        # final AdaLN (scale first, flux_dit.py:333) + projection; all local rows, the image rows are picked below
         m = mv[off:off + 2 * d]
-        rows = slice(S_txt, S)
-        a, sc = self._ln(x[rows], m[d:2 * d], m[:d], xq_d[rows], rs[rows])
+        a, sc = self._ln(x, m[d:2 * d], m[:d], xq_d, rs)
         self._gemm(a, sc, self.final_proj, out=b["out_tok"])
-        return b["out_tok"]
+        if P > 1:
+            self.xchg.dist.all_gather_into_tensor(b["out_all"], b["out_tok"], group=self.xchg.group)
+            return b["out_all"][S_txt:S]
+        return b["out_tok"][S_txt:S]
 
     def prepare(self, S_txt: int, height: int, width: int, txt_dim: int = 4096, pooled_dim: int = 768,
                 text_ids: Optional[torch.Tensor] = None, image_ids: Optional[torch.Tensor] = None):
@@ -237,7 +296,8 @@ class FluxDiTEngine:
             image_ids = image_ids.reshape(-1, 3)
         if text_ids is None:
             text_ids = torch.zeros(S_txt, 3, device=self.dev)
-        ids = torch.cat([text_ids.reshape(-1, 3).float().to(self.dev), image_ids.reshape(-1, 3).float().to(self.dev)])
+        ids = torch.cat([text_ids.reshape(-1, 3).float().to(self.dev), image_ids.reshape(-1, 3).float().to(self.dev),
+                         torch.zeros(b["S_pad"] - b["S"], 3, device=self.dev)])   # padding rows: position 0
         b["rope"] = flux_rope_table(ids)
         return self
 
@@ -251,7 +311,11 @@ class FluxDiTEngine:
         b["tg"][1:2].copy_(guidance.reshape(1).float() * 1000.0, non_blocking=True)  # flux_dit.py:413
 
     def capture(self):
-        """Record the step into a CUDA graph (inputs must be set once before)."""
+        """Record the step into a CUDA graph (inputs must be set once before).  One GPU only: the sequence-parallel
+        step holds NCCL collectives and always runs eagerly (recording them into a graph did not return on a
+        two-GPU trial, so that path is not offered)."""
+        if self.P > 1:
+            return self
         torch.cuda.synchronize(self.dev)
         side = torch.cuda.Stream(self.dev)
         with torch.cuda.stream(side):
@@ -266,13 +330,14 @@ class FluxDiTEngine:
     def step(self):
         """Run the DiT forward on the current inputs; returns the [1, C, h, w] model output (a view of a
         static buffer)."""
+        b = self._bufs
         if self._graph is not None:
             self._graph.replay()
+            tok = (b["out_all"] if self.P > 1 else b["out_tok"])[b["S_txt"]:b["S"]]
         else:
-            self._run()
-        b = self._bufs
+            tok = self._run()
         C = self.in_ch // 4
-        return (b["out_tok"].reshape(b["height"] // 2, b["width"] // 2, C, 2, 2).permute(2, 0, 3, 1, 4)
+        return (tok.reshape(b["height"] // 2, b["width"] // 2, C, 2, 2).permute(2, 0, 3, 1, 4)
                 .reshape(1, C, b["height"], b["width"]))
 
     def forward(self, hidden_states, timestep, prompt_emb, pooled_prompt_emb, guidance, text_ids=None,

@@ -61,6 +61,13 @@ def wan_engine_factory(state_dict, rank, sp_group, device, **engine_kwargs):
     return WanDiTEngine(state_dict, device=device, group=sp_group, **engine_kwargs)
 
 
+def flux_engine_factory(state_dict, rank, sp_group, device, **engine_kwargs):
+    """Worker model for the Flux / MMDiT step: a sequence-parallel ``FluxDiTEngine`` over ``sp_group``; called with
+    the keyword arguments of ``FluxDiT.forward``."""
+    from .flux import FluxDiTEngine
+    return FluxDiTEngine(state_dict, device=device, group=sp_group, **engine_kwargs)
+
+
 def _worker_loop(rank: int, world_size: int, conn, payload, factory: Callable, sp_degree: int, batch_parallelism: int,
                  master_port: int, device: str, backend: str, timeout_s: float, engine_kwargs: dict):
     model = None
@@ -202,7 +209,8 @@ class UlyssesParallelModel(nn.Module):
             pass
 
 
-__all__ = ["UlyssesParallelModel", "ParallelWorkerError", "HeadExchangeAttention"]
+__all__ = ["UlyssesParallelModel", "ParallelWorkerError", "HeadExchangeAttention", "wan_engine_factory",
+           "flux_engine_factory"]
 
 
 class HeadExchangeAttention:

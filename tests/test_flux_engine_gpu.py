@@ -111,3 +111,35 @@ def test_double_stream_only_model_with_ragged_token_counts(dsb, cuda_dev, fmt):
     print(f"double-stream-only model {fmt}: rel-L2 {err:.3e}")
     assert out.shape == (1, 16, 18, 14)
     assert err < 2e-2
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+@pytest.mark.parametrize("fmt,S_txt,hw", [("fp8_tensor", 41, (24, 14)), ("bf16", 72, (18, 12)), ("int8_channel", 8, (16, 16))])
+def test_sequence_parallel_two_gpus_matches_one(dsb, cuda_dev, fmt, S_txt, hw):
+    """The joint text+image sequence split over two ranks (NCCL) against the one-GPU engine on the same weights and
+    inputs.  Cases: 41 + 84 = 125 tokens (odd: one padded row that must not act as a key); 72 + 54 tokens, where
+    rank 0 owns text rows only and the text/image boundary lies inside rank 1; 8 + 64, boundary inside rank 0."""
+    import os
+    os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+    from diffsynth_engine_b200.flux import FluxDiTEngine
+    from diffsynth_engine_b200.parallel import UlyssesParallelModel, flux_engine_factory
+    d, H, nd, ns = 512, 4, 2, 2
+    shapes = synth.flux_dit_shapes(d=d, H=H, n_double=nd, n_single=ns, txt_dim=256, pooled_dim=64)
+    w = {k: v.bfloat16().float() for k, v in synth.make_state_dict(shapes, seed=21).items()}
+    lat = synth.randn((1, 16, *hw), 22).bfloat16()
+    pe, pooled = synth.randn((1, S_txt, 256), 23).bfloat16(), synth.randn((1, 64), 24)
+    t, g = torch.tensor([400.0]), torch.tensor([3.5])
+    one = FluxDiTEngine(dict(w), fmt=fmt, device=cuda_dev, n_double=nd, n_single=ns, num_heads=H)
+    ref = one(lat.to(cuda_dev), t.to(cuda_dev), pe.to(cuda_dev), pooled.to(cuda_dev), g.to(cuda_dev)).float().cpu()
+    model = UlyssesParallelModel(dict(w), sp_degree=2, master_port=29651, device="cuda", timeout_s=120,
+                                 factory=flux_engine_factory, fmt=fmt, n_double=nd, n_single=ns, num_heads=H)
+    try:
+        kw = dict(hidden_states=lat, timestep=t, prompt_emb=pe, pooled_prompt_emb=pooled, guidance=g)
+        out = model(**kw).float().cpu()
+        out2 = model(**kw).float().cpu()
+    finally:
+        model.close()
+    assert out.shape == ref.shape
+    # same kernels on the same numbers; only the attention's head grouping and key-tile boundaries differ
+    assert O.rel_l2(out, ref) < 3e-3
+    assert torch.equal(out, out2)
