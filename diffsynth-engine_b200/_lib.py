@@ -10,7 +10,7 @@ HEADER = os.path.join(os.path.dirname(HERE), "include", "dsb.h")
 
 OK, ERR_ARG, ERR_CUDA, ERR_TIMEOUT, ERR_UNSUPPORTED, ERR_TOO_LARGE = 0, -1, -2, -3, -4, -5
 FMT_BF16, FMT_E4M3, FMT_INT8 = 0, 1, 2
-ACT_NONE, ACT_GELU_TANH, ACT_SILU = 0, 1, 2
+ACT_NONE, ACT_GELU_TANH, ACT_SILU, ACT_GELU = 0, 1, 2, 3
 
 _ERR_NAMES = {
     ERR_ARG: "DSB_ERR_ARG (bad pointer, size, alignment or flag combination)",

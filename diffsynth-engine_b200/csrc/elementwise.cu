@@ -475,6 +475,7 @@ __global__ void __launch_bounds__(256) gemv_kernel(const void* __restrict__ W, i
       float o = a * sc + (bias ? bias[n] : 0.f);
       if (act_out == DSB_ACT_SILU) o = silu(o);
       if (act_out == DSB_ACT_GELU_TANH) o = gelu_tanh(o);
+      if (act_out == DSB_ACT_GELU) o = gelu_erf(o);
       y[n] = accumulate ? y[n] + o : o;
     }
   }

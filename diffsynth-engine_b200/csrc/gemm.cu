@@ -389,9 +389,12 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
                 if (ep.act == DSB_ACT_GELU_TANH) {
 #pragma unroll
                   for (int j = 0; j < 8; ++j) v[j] = gelu_tanh(v[j]);
-                } else {
+                } else if (ep.act == DSB_ACT_SILU) {
 #pragma unroll
                   for (int j = 0; j < 8; ++j) v[j] = silu(v[j]);
+                } else {
+#pragma unroll
+                  for (int j = 0; j < 8; ++j) v[j] = gelu_erf(v[j]);
                 }
               }
               if (ep.has_resid) {
@@ -540,7 +543,7 @@ static int check_problem(const dsb_gemm_args& a, int fmt, int* status, GemmProbl
   if (((a.lda * esz) & 15) || ((a.ldw * esz) & 15) || (a.ld_out0 & 7) || (a.ld_resid & 7) || (a.ld_out1 & 7))
     return DSB_ERR_ARG;
   if (a.col_scale_stride != 0 && a.col_scale_stride != 1) return DSB_ERR_ARG;
-  if (a.act != DSB_ACT_NONE && a.act != DSB_ACT_GELU_TANH && a.act != DSB_ACT_SILU) return DSB_ERR_ARG;
+  if (a.act < DSB_ACT_NONE || a.act > DSB_ACT_GELU) return DSB_ERR_ARG;
   int split_col = a.split_col;
   if (!a.out1) split_col = INT32_MAX;
   else if (split_col < 0 || (split_col % 256) != 0) return DSB_ERR_ARG;

@@ -7,7 +7,7 @@ from typing import Optional, Tuple
 import torch
 
 from . import _lib
-from ._lib import ACT_GELU_TANH, ACT_NONE, ACT_SILU, FMT_BF16, FMT_E4M3, FMT_INT8, check  # noqa: F401
+from ._lib import ACT_GELU, ACT_GELU_TANH, ACT_NONE, ACT_SILU, FMT_BF16, FMT_E4M3, FMT_INT8, check  # noqa: F401
 
 _status = {}
 

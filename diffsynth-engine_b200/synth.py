@@ -17,7 +17,8 @@ def init_param(name: str, shape, gen, device="cpu", dtype=torch.float32):
     Wan ``modulation`` tables (as models/wan/wan_dit.py:183,232 initialises them)."""
     if name.endswith("modulation"):
         return _normal(shape, 1.0 / shape[-1] ** 0.5, gen, device, dtype)
-    is_norm = (".norm_q" in name or ".norm_k" in name or "norm3" in name) and name.endswith("weight")
+    is_norm = (".norm_q" in name or ".norm_k" in name or "norm3" in name or name.startswith("img_emb.proj.0")
+               or name.startswith("img_emb.proj.4")) and name.endswith("weight")
     t = _normal(shape, 0.02, gen, device, dtype)
     return t + 1.0 if is_norm else t
 
@@ -74,7 +75,7 @@ def flux_dit_shapes(d=3072, H=24, n_double=19, n_single=38, in_ch=64, txt_dim=40
     return s
 
 
-def wan_block_shapes(pre: str, d: int, ffn: int) -> Dict[str, Tuple[int, ...]]:
+def wan_block_shapes(pre: str, d: int, ffn: int, has_image_input: bool = False) -> Dict[str, Tuple[int, ...]]:
     s = {}
     def lin(n, o, i):
         s[pre + n + ".weight"] = (o, i)
@@ -89,11 +90,17 @@ def wan_block_shapes(pre: str, d: int, ffn: int) -> Dict[str, Tuple[int, ...]]:
     lin("ffn.0", ffn, d)
     lin("ffn.2", d, ffn)
     s[pre + "modulation"] = (1, 6, d)
+    if has_image_input:   # image-to-video: second key/value projection for the CLIP tokens (wan_dit.py:131-134)
+        lin("cross_attn.k_img", d, d)
+        lin("cross_attn.v_img", d, d)
+        s[pre + "cross_attn.norm_k_img.weight"] = (d,)
     return s
 
 
 def wan_dit_shapes(d=5120, ffn=13824, num_layers=40, in_dim=16, out_dim=16, text_dim=4096,
-                   freq_dim=256) -> Dict[str, Tuple[int, ...]]:
+                   freq_dim=256, has_image_input: bool = False, clip_dim: int = 1280) -> Dict[str, Tuple[int, ...]]:
+    """``has_image_input``: the image-to-video variant (``in_dim`` is then 36 in the released models: 16 latent +
+    20 conditioning channels) with the CLIP-feature MLP ``img_emb`` (wan_dit.py:196-216,297-298)."""
     s = {"patch_embedding.weight": (d, in_dim, 1, 2, 2), "patch_embedding.bias": (d,)}
     def lin(n, o, i):
         s[n + ".weight"] = (o, i)
@@ -104,9 +111,14 @@ def wan_dit_shapes(d=5120, ffn=13824, num_layers=40, in_dim=16, out_dim=16, text
     lin("time_embedding.2", d, d)
     lin("time_projection.1", 6 * d, d)
     for i in range(num_layers):
-        s.update(wan_block_shapes(f"blocks.{i}.", d, ffn))
+        s.update(wan_block_shapes(f"blocks.{i}.", d, ffn, has_image_input))
     lin("head.head", out_dim * 4, d)
     s["head.modulation"] = (1, 2, d)
+    if has_image_input:
+        s["img_emb.proj.0.weight"], s["img_emb.proj.0.bias"] = (clip_dim,), (clip_dim,)
+        lin("img_emb.proj.1", clip_dim, clip_dim)
+        lin("img_emb.proj.3", d, clip_dim)
+        s["img_emb.proj.4.weight"], s["img_emb.proj.4.bias"] = (d,), (d,)
     return s
 
 

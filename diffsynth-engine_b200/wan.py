@@ -44,6 +44,9 @@ def wan_rope_table(f: int, h: int, w: int, head_dim: int = 128, theta: float = 1
     return torch.stack([torch.cos(ang), torch.sin(ang)], dim=-1).float().contiguous()
 
 
+IMG_TOKENS = 257   # CLIP tokens at the head of an image-to-video context (wan_dit.py:138-139)
+
+
 class HeadExchange:
     """The Ulysses all-to-all.  ``send`` is ``[P, rows, C]``: chunk p goes to rank p; the result's chunk r came from
     rank r.  Forward (tokens -> heads): rows = S/P own tokens, chunk p = head group p; result = all S tokens of the
@@ -111,6 +114,15 @@ class WanDiTEngine:
                 cnk=V(pre + "cross_attn.norm_k.weight"),
                 n3_scale=V(pre + "norm3.weight") - 1.0, n3_shift=V(pre + "norm3.bias"),
                 f0=P_(pre + "ffn.0"), f2=P_(pre + "ffn.2")))
+        # image-to-video models: CLIP-feature MLP and a second key/value projection per block (wan_dit.py:131-134,297)
+        self.has_image = "img_emb.proj.1.weight" in sd
+        if self.has_image:
+            self.img_ln0 = (V("img_emb.proj.0.bias"), V("img_emb.proj.0.weight") - 1.0)   # affine LN as shift, scale
+            self.img1, self.img3 = P_("img_emb.proj.1"), P_("img_emb.proj.3")
+            self.img_ln4 = (V("img_emb.proj.4.bias"), V("img_emb.proj.4.weight") - 1.0)
+            for i, blk in enumerate(self.blocks):
+                pre = f"blocks.{i}.cross_attn."
+                blk.update(ck_img=P_(pre + "k_img"), cv_img=P_(pre + "v_img"), cnk_img=V(pre + "norm_k_img.weight"))
         self.mod = torch.stack(mods).contiguous()          # [L, 6, d]
         self.head = P_("head.head")
         self.head_mod = V("head.modulation").reshape(2, self.d)
@@ -144,18 +156,24 @@ class WanDiTEngine:
         b["patches"] = torch.zeros(Sl, self.patch.in_features, dtype=bf, device=dev)
         b["x"] = torch.zeros(Sl, d, dtype=bf, device=dev)
         b["xq"] = torch.zeros(Sl, max(d, ffn), dtype=qdt, device=dev)
-        b["rs"] = torch.zeros(max(Sl, ctx_len), dtype=f32, device=dev)
+        b["rs"] = torch.zeros(max(Sl, ctx_len, IMG_TOKENS), dtype=f32, device=dev)
         b["proj"] = torch.zeros(3, Sl, d, dtype=bf, device=dev)              # q, k, v projections of the slice
         b["send"] = torch.zeros(3, P, Sl, C, dtype=bf, device=dev) if P > 1 else None
         b["recv"] = torch.zeros(3, P, Sl, C, dtype=bf, device=dev) if P > 1 else None
         b["ao"] = torch.zeros(P, Sl, C, dtype=bf, device=dev)                # attention out: [S, H/P*128]
         b["ao_back"] = torch.zeros(P, Sl, C, dtype=bf, device=dev) if P > 1 else None
         b["hid"] = torch.zeros(Sl, ffn, dtype=bf, device=dev)
-        b["ctx"] = torch.zeros(ctx_len, d, dtype=bf, device=dev)
-        b["ctx_h"] = torch.zeros(ctx_len, d, dtype=bf, device=dev)
-        b["ctxq"] = torch.zeros(ctx_len, max(d, text_dim), dtype=qdt, device=dev)
-        b["ctx_rs"] = torch.zeros(ctx_len, dtype=f32, device=dev)
-        b["ck"], b["cv"] = torch.zeros(ctx_len, d, dtype=bf, device=dev), torch.zeros(ctx_len, d, dtype=bf, device=dev)
+        # context rows: [CLIP tokens (image-to-video only) | text tokens], as the reference concatenates them
+        n_img = IMG_TOKENS if self.has_image else 0
+        L_all = n_img + ctx_len
+        b["n_img"] = n_img
+        b["ctx"] = torch.zeros(L_all, d, dtype=bf, device=dev)
+        b["ctx_h"] = torch.zeros(max(ctx_len, n_img), max(d, 1280 if n_img else 0), dtype=bf, device=dev)
+        b["ctxq"] = torch.zeros(L_all, max(d, text_dim, 1280 if n_img else 0), dtype=qdt, device=dev)
+        b["ctx_rs"] = torch.zeros(L_all, dtype=f32, device=dev)
+        b["ck"], b["cv"] = torch.zeros(L_all, d, dtype=bf, device=dev), torch.zeros(L_all, d, dtype=bf, device=dev)
+        if n_img:
+            b["clip_in"] = torch.zeros(n_img, 1280, dtype=bf, device=dev)
         b["out_tok"] = torch.zeros(Sl, self.head.out_features, dtype=bf, device=dev)
         b["out_all"] = torch.zeros(S, self.head.out_features, dtype=bf, device=dev) if P > 1 else None
         self._bufs = b
@@ -178,9 +196,19 @@ class WanDiTEngine:
     def _gemm(self, a, rs, p: PackedLinear, **kw):
         return ops.gemm(a, p.w, row_scale=rs, col_scale=p.scale, bias=p.bias, **kw)
 
-    def set_inputs(self, x, context, timestep):
+    def set_inputs(self, x, context, timestep, clip_feature=None, y=None):
         b = self._bufs
-        b["latents"].copy_(x.reshape(b["latents"].shape), non_blocking=True)
+        if self.has_image:
+            if clip_feature is None or y is None:
+                raise ValueError("an image-to-video model needs clip_feature and y")
+            nx = x.shape[1]
+            b["latents"][:, :nx].copy_(x, non_blocking=True)          # torch.cat([x, y], dim=1), wan_dit.py:331
+            b["latents"][:, nx:].copy_(y, non_blocking=True)
+            b["clip_in"].copy_(clip_feature.reshape(b["clip_in"].shape), non_blocking=True)
+        else:
+            if clip_feature is not None or y is not None:
+                raise ValueError("this model has no image branch (no img_emb / k_img / v_img weights)")
+            b["latents"].copy_(x.reshape(b["latents"].shape), non_blocking=True)
         b["context_in"].copy_(context.reshape(b["context_in"].shape), non_blocking=True)
         b["t"].copy_(timestep.reshape(1), non_blocking=True)
 
@@ -216,10 +244,22 @@ class WanDiTEngine:
         torch.add(self.head_mod, b["tvec"].view(1, d), out=b["headmod"])       # wan_dit.py:235
         # text embedding (wan_dit.py:329), replicated on every rank
         tdim = b["context_in"].shape[1]
-        a, s = self._quant(b["context_in"], b["ctxq"][:, :tdim], b["ctx_rs"])
-        self._gemm(a, s, self.text0, act=ops.ACT_GELU_TANH, out=b["ctx_h"])
-        a, s = self._quant(b["ctx_h"], b["ctxq"][:, :d], b["ctx_rs"])
-        self._gemm(a, s, self.text2, out=b["ctx"])
+        n_img, L = b["n_img"], b["ctx_len"]
+        txt_rows = slice(n_img, n_img + L)
+        ctxq_t, crs_t, ctx_h = b["ctxq"][txt_rows], b["ctx_rs"][txt_rows], b["ctx_h"]
+        a, s = self._quant(b["context_in"], ctxq_t[:, :tdim], crs_t)
+        self._gemm(a, s, self.text0, act=ops.ACT_GELU_TANH, out=ctx_h[:L, :d])
+        a, s = self._quant(ctx_h[:L, :d], ctxq_t[:, :d], crs_t)
+        self._gemm(a, s, self.text2, out=b["ctx"][txt_rows])
+        if n_img:   # CLIP tokens through img_emb (LN -> Linear -> GELU -> Linear -> LN, wan_dit.py:196-216), eps 1e-5
+            ctxq_i, crs_i = b["ctxq"][:n_img], b["ctx_rs"][:n_img]
+            a, s = ops.ln_modulate(b["clip_in"], self.img_ln0[0], self.img_ln0[1], 1e-5, self.afmt,
+                                   out=ctxq_i[:, :1280], row_scale=crs_i)
+            s = s if self.afmt != ops.FMT_BF16 else None
+            self._gemm(a, s, self.img1, act=ops.ACT_GELU, out=ctx_h[:n_img, :1280])
+            a, s = self._quant(ctx_h[:n_img, :1280], ctxq_i[:, :1280], crs_i)
+            self._gemm(a, s, self.img3, out=b["ck"][:n_img])                   # ck is free until the first block
+            ops.ln_modulate(b["ck"][:n_img], self.img_ln4[0], self.img_ln4[1], 1e-5, ops.FMT_BF16, out=b["ctx"][:n_img])
         cq_, cs_ = self._quant(b["ctx"], b["ctxq"][:, :d], b["ctx_rs"])        # quantised context, reused by all blocks
         # patch embedding: Conv3d with kernel = stride = (1,2,2) is a Linear over (c, y, z) patches (wan_dit.py:271-273)
         fr, gh, gw = b["grid"]
@@ -277,12 +317,22 @@ class WanDiTEngine:
             a, sc = self._ln(x, blk["n3_shift"], blk["n3_scale"], xq_d, rs[:Sl])
             self._gemm(a, sc, blk["cq"], out=proj[0])
             ops.rmsnorm_full(proj[0], blk["cnq"], None, 0, self.eps)
-            self._gemm(cq_, cs_, blk["ck"], out=b["ck"])
-            ops.rmsnorm_full(b["ck"], blk["cnk"], None, 0, self.eps)
-            self._gemm(cq_, cs_, blk["cv"], out=b["cv"])
-            L = b["ctx_len"]
-            ops.flash_attn(proj[0].view(1, Sl, H, 128), b["ck"].view(1, L, H, 128), b["cv"].view(1, L, H, 128),
+            cq_t, cs_t = cq_[txt_rows], (None if cs_ is None else cs_[txt_rows])
+            ck_t, cv_t = b["ck"][txt_rows], b["cv"][txt_rows]
+            self._gemm(cq_t, cs_t, blk["ck"], out=ck_t)
+            ops.rmsnorm_full(ck_t, blk["cnk"], None, 0, self.eps)
+            self._gemm(cq_t, cs_t, blk["cv"], out=cv_t)
+            ops.flash_attn(proj[0].view(1, Sl, H, 128), ck_t.view(1, L, H, 128), cv_t.view(1, L, H, 128),
                            out=proj[1].view(1, Sl, H, 128))
+            if n_img:   # the CLIP tokens have their own k/v projection; the two attention outputs add (wan_dit.py:147-151)
+                cq_i, cs_i = cq_[:n_img], (None if cs_ is None else cs_[:n_img])
+                ck_i, cv_i = b["ck"][:n_img], b["cv"][:n_img]
+                self._gemm(cq_i, cs_i, blk["ck_img"], out=ck_i)
+                ops.rmsnorm_full(ck_i, blk["cnk_img"], None, 0, self.eps)
+                self._gemm(cq_i, cs_i, blk["cv_img"], out=cv_i)
+                ops.flash_attn(proj[0].view(1, Sl, H, 128), ck_i.view(1, n_img, H, 128), cv_i.view(1, n_img, H, 128),
+                               out=proj[2].view(1, Sl, H, 128))
+                ops.gate_residual(proj[1], proj[2], None, out=proj[1])         # bf16(x + y)
             a, sc = self._quant(proj[1], xq_d, rs[:Sl])
             self._gemm(a, sc, blk["co"], resid=x, out=x)
             # ---- FFN (wan_dit.py:179-182,191-192)
@@ -303,15 +353,14 @@ class WanDiTEngine:
         return tok.reshape(fr, gh, gw, 1, 2, 2, od).permute(6, 0, 3, 1, 4, 2, 5).reshape(1, od, fr, gh * 2, gw * 2)
 
     def forward(self, x, context, timestep, clip_feature=None, y=None):
-        """Signature of ``WanDiT.forward`` (wan_dit.py:319-326); text-to-video only (no image branch)."""
-        if clip_feature is not None or y is not None:
-            raise NotImplementedError("the image-to-video branch (clip_feature / y) is not part of this engine")
+        """Signature of ``WanDiT.forward`` (wan_dit.py:319-326).  ``clip_feature`` [1,257,1280] and ``y`` (conditioning
+        latents on the grid of ``x``) are required by image-to-video weights and rejected by text-to-video ones."""
         b = self._bufs
         shape = (x.shape[2], x.shape[3], x.shape[4], context.shape[1], context.shape[2])
         if b is None or (b["latents"].shape[2], b["latents"].shape[3], b["latents"].shape[4], b["ctx_len"],
                          b["context_in"].shape[1]) != shape:
             self.prepare(*shape)
-        self.set_inputs(x, context, timestep)
+        self.set_inputs(x, context, timestep, clip_feature, y)
         return self.step().clone()
 
     __call__ = forward

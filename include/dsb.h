@@ -44,6 +44,7 @@ extern "C" {
 #define DSB_ACT_NONE 0
 #define DSB_ACT_GELU_TANH 1
 #define DSB_ACT_SILU 2
+#define DSB_ACT_GELU 3 /* exact (erf) GELU: torch.nn.GELU() of the Wan image-embedding MLP, wan_dit.py:208 */
 
 /* Library/ABI version (major*100 + minor). */
 int dsb_version(void);

@@ -7,6 +7,9 @@ from . import ops as O
 from .linear import LinearEval
 
 
+IMG_TOKENS = 257   # CLIP tokens at the head of the context of image-to-video models (wan_dit.py:138-139)
+
+
 def _ident(x):
     return x
 
@@ -39,12 +42,21 @@ def wan_block(x, context, t_mod, table, w, pre, H, lin: LinearEval, rt=_ident, e
     v = rt(L(n, "self_attn.v"))
     q, k = rt(_rope(q, table, H)), rt(_rope(k, table, H))
     x = rt(x.float() + g_msa * L(rt(_attend(q, k, v, H)), "self_attn.o"))
-    # cross-attention (t2v: no image branch), wan_dit.py:136-152; norm3 is an affine LayerNorm (:178,190)
+    # cross-attention, wan_dit.py:136-152; norm3 is an affine LayerNorm (:178,190).  Image-to-video models carry
+    # k_img/v_img: the first 257 context rows are CLIP tokens with their own key/value projection, attended
+    # separately, and the two attention outputs are summed before the output projection (:137-152).
+    has_img = (pre + "cross_attn.k_img.weight") in w
+    img, ctx = (context[:IMG_TOKENS], context[IMG_TOKENS:]) if has_img else (None, context)
     n3 = O.layer_norm(x, eps) * w[pre + "norm3.weight"].float() + w[pre + "norm3.bias"].float()
     q = rt(O.rmsnorm(rt(L(n3, "cross_attn.q")), w[pre + "cross_attn.norm_q.weight"], eps))
-    k = rt(O.rmsnorm(rt(L(context, "cross_attn.k")), w[pre + "cross_attn.norm_k.weight"], eps))
-    v = rt(L(context, "cross_attn.v"))
-    x = rt(x + L(rt(_attend(q, k, v, H)), "cross_attn.o"))
+    k = rt(O.rmsnorm(rt(L(ctx, "cross_attn.k")), w[pre + "cross_attn.norm_k.weight"], eps))
+    v = rt(L(ctx, "cross_attn.v"))
+    att = rt(_attend(q, k, v, H))
+    if has_img:
+        k_i = rt(O.rmsnorm(rt(L(img, "cross_attn.k_img")), w[pre + "cross_attn.norm_k_img.weight"], eps))
+        v_i = rt(L(img, "cross_attn.v_img"))
+        att = rt(att + rt(_attend(q, k_i, v_i, H)))
+    x = rt(x + L(att, "cross_attn.o"))
     # FFN, wan_dit.py:179-182,191-192
     n2 = O.ln_modulate(x, sh_mlp, sc_mlp, eps)
     hid = rt(O.gelu_tanh(L(n2, "ffn.0")))
@@ -66,9 +78,19 @@ def unpatchify(x, grid, out_dim):
     return x.reshape(f, h, ww, 1, 2, 2, out_dim).permute(6, 0, 3, 1, 4, 2, 5).reshape(1, out_dim, f, h * 2, ww * 2)
 
 
+def img_emb(clip_feature, w, lin, rt=_ident):
+    """MLP of wan_dit.py:196-216 on the CLIP feature [257, 1280]: LayerNorm (eps 1e-5, affine) -> Linear -> exact
+    GELU -> Linear -> LayerNorm."""
+    def ln(t, i):
+        return O.layer_norm(t, 1e-5) * w[f"img_emb.proj.{i}.weight"].float() + w[f"img_emb.proj.{i}.bias"].float()
+    h = rt(F.gelu(lin(ln(clip_feature, 0), w["img_emb.proj.1.weight"], w["img_emb.proj.1.bias"])))
+    return rt(ln(rt(lin(h, w["img_emb.proj.3.weight"], w["img_emb.proj.3.bias"])), 4))
+
+
 def wan_dit_forward(w, x, context, timestep, num_layers, H, freq_dim=256, eps=1e-6, lin: LinearEval = None,
-                    rt=_ident):
-    """WanDiT.forward (t2v), wan_dit.py:319-351, batch 1."""
+                    rt=_ident, clip_feature=None, y=None):
+    """WanDiT.forward, wan_dit.py:319-351, batch 1.  With ``clip_feature`` [1,257,1280] and ``y`` (conditioning
+    latents, concatenated to x on the channel axis) the image-to-video branch (:330-333)."""
     lin = lin or LinearEval("fp32")
     d = w["time_embedding.0.weight"].shape[0]
     def L(inp, name, **kw):
@@ -77,6 +99,9 @@ def wan_dit_forward(w, x, context, timestep, num_layers, H, freq_dim=256, eps=1e
     t = L(F.silu(L(sin, "time_embedding.0", act_quant=False)), "time_embedding.2", act_quant=False)   # [1,d]
     t_mod = L(F.silu(t), "time_projection.1", act_quant=False).reshape(6, d)
     ctx = rt(L(rt(O.gelu_tanh(L(context[0], "text_embedding.0"))), "text_embedding.2"))
+    if clip_feature is not None:
+        x = torch.cat([x, y], dim=1)
+        ctx = torch.cat([img_emb(clip_feature[0].float(), w, lin, rt), ctx], dim=0)
     h, grid = patchify(x, w, lin)
     h = rt(h)
     table = O.wan_rope_table(*grid, head_dim=d // H)

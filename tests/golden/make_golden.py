@@ -139,6 +139,15 @@ def main(ref_root):
     out["wan_dit_tiny.out"] = model(synth.randn((1, 16, 3, 8, 10), 25), synth.randn((1, 16, 64), 26),
                                     torch.tensor([417.0]))
 
+    # ---- the image-to-video variant of the same tiny model (CLIP-token branch of the cross-attention, img_emb MLP)
+    cfg_i2v = dict(cfg, in_dim=36, has_image_input=True)
+    sd = synth.make_state_dict(synth.wan_dit_shapes(d=256, ffn=512, num_layers=2, text_dim=64, in_dim=36,
+                                                    has_image_input=True), seed=27)
+    model = load_into(wan_dit.WanDiT(**cfg_i2v, device="cpu", dtype=torch.float32), sd).eval()
+    out["wan_dit_tiny_i2v.out"] = model(synth.randn((1, 16, 3, 8, 10), 25), synth.randn((1, 16, 64), 26),
+                                        torch.tensor([417.0]), clip_feature=synth.randn((1, 257, 1280), 28),
+                                        y=synth.randn((1, 20, 3, 8, 10), 29))
+
     # ---- the reference's FP8 Linear as shipped (unit scales) on a small case, for the drop-in patch
     lin = torch.nn.Linear(256, 128)
     lin.weight.copy_(synth.randn((128, 256), 30) * 0.5)

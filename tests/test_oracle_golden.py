@@ -102,6 +102,15 @@ def test_wan_dit_tiny():
     assert O.rel_l2(y, G["wan_dit_tiny.out"]) < TOL
 
 
+def test_wan_dit_tiny_image_to_video():
+    w = synth.make_state_dict(synth.wan_dit_shapes(d=256, ffn=512, num_layers=2, text_dim=64, in_dim=36,
+                                                   has_image_input=True), seed=27)
+    y = OW.wan_dit_forward(w, synth.randn((1, 16, 3, 8, 10), 25), synth.randn((1, 16, 64), 26),
+                           torch.tensor([417.0]), num_layers=2, H=2, clip_feature=synth.randn((1, 257, 1280), 28),
+                           y=synth.randn((1, 20, 3, 8, 10), 29))
+    assert O.rel_l2(y, G["wan_dit_tiny_i2v.out"]) < TOL
+
+
 def test_reference_suite_sampler_fixture():
     """tests/test_algorithm/test_sampler.py:22-42 of the reference, on a row subsample of its fixture."""
     mu = (1024 // 16 * 1024 // 16) * ((1.15 - 0.5) / (4096 - 256)) + (0.5 - ((1.15 - 0.5) / (4096 - 256)) * 256)

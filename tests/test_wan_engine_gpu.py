@@ -40,6 +40,36 @@ def test_wan_engine_matches_oracle(dsb, cuda_dev, fmt):
     assert err < (4e-3 if fmt == "bf16" else 2e-2)
 
 
+def _i2v_case(seed=40, grid=(3, 8, 10), ctx=16):
+    w = synth.make_state_dict(synth.wan_dit_shapes(**CFG, in_dim=36, has_image_input=True), seed=seed)
+    w = {k: v.bfloat16().float() for k, v in w.items()}
+    x = synth.randn((1, 16, *grid), seed + 1).bfloat16().float()
+    y = synth.randn((1, 20, *grid), seed + 2).bfloat16().float()
+    clip = synth.randn((1, 257, 1280), seed + 3).bfloat16().float()
+    context = synth.randn((1, ctx, CFG["text_dim"]), seed + 4).bfloat16().float()
+    return w, x, context, torch.tensor([417.0]), clip, y
+
+
+@pytest.mark.parametrize("fmt", ["fp8_channel", "bf16"])
+def test_wan_image_to_video_engine_matches_oracle(dsb, cuda_dev, fmt):
+    """Image-to-video weights: 36 input channels (x | y), the CLIP-feature MLP (exact GELU, LayerNorm eps 1e-5) and
+    the second key/value projection of every cross-attention over the 257 CLIP tokens."""
+    from diffsynth_engine_b200.wan import WanDiTEngine
+    w, x, context, t, clip, y = _i2v_case()
+    ref = OW.wan_dit_forward(w, x, context, t, num_layers=2, H=H, lin=LinearEval(fmt), rt=round_bf16,
+                             clip_feature=clip, y=y)
+    eng = WanDiTEngine(dict(w), fmt=fmt, device=cuda_dev, num_layers=2, num_heads=H)
+    dev = cuda_dev
+    out = eng(x.to(dev), context.to(dev), t.to(dev), clip_feature=clip.to(dev), y=y.to(dev)).float().cpu()
+    dsb.ops.check_status(0)
+    err = O.rel_l2(out, ref)
+    print(f"wan tiny image-to-video model {fmt}: rel-L2 vs same-quantisation oracle {err:.3e}")
+    assert out.shape == ref.shape
+    assert err < (4e-3 if fmt == "bf16" else 2e-2)
+    with pytest.raises(ValueError):
+        eng(x.to(dev), context.to(dev), t.to(dev))       # image-to-video weights without the image inputs
+
+
 def test_wan_rope_table_matches_oracle(dsb, cuda_dev):
     from diffsynth_engine_b200.wan import wan_rope_table
     assert torch.equal(wan_rope_table(3, 4, 5, device=cuda_dev).cpu(), O.wan_rope_table(3, 4, 5))
@@ -84,3 +114,21 @@ def test_sequence_parallel_two_gpus_matches_one(dsb, cuda_dev, fmt):
     # same kernels on the same numbers, only the attention tiling (heads per rank) differs
     assert O.rel_l2(out, ref) < 3e-3
     assert torch.equal(out, out2)
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_sequence_parallel_image_to_video_two_gpus_matches_one(dsb, cuda_dev):
+    os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+    from diffsynth_engine_b200.parallel import UlyssesParallelModel
+    from diffsynth_engine_b200.wan import WanDiTEngine
+    w, x, context, t, clip, y = _i2v_case(seed=50)
+    dev = cuda_dev
+    one = WanDiTEngine(dict(w), fmt="fp8_channel", device=dev, num_layers=2, num_heads=H)
+    ref = one(x.to(dev), context.to(dev), t.to(dev), clip_feature=clip.to(dev), y=y.to(dev)).float().cpu()
+    model = UlyssesParallelModel(dict(w), sp_degree=2, master_port=29643, device="cuda", timeout_s=120,
+                                 fmt="fp8_channel", num_layers=2, num_heads=H)
+    try:
+        out = model(x=x, context=context, timestep=t, clip_feature=clip, y=y).float().cpu()
+    finally:
+        model.close()
+    assert O.rel_l2(out, ref) < 3e-3
