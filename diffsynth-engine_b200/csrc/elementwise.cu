@@ -386,6 +386,56 @@ __global__ void __launch_bounds__(256) quant_rows_kernel(const __nv_bfloat16* __
   }
 }
 
+// ------------------------------------------------------------- cast_quant
+// bf16 [M, D] -> e4m3 (saturating, round-to-nearest-even) or int8 (round-half-even, clamp +-127) with no scale:
+// the values are already in the operand's units.  Fills the K-extension columns of a quantised activation
+// buffer with the LoRA down-projection.  SPLIT (e4m3 only): writes [head | remainder | head] at column offsets
+// 0, D, 2D, where head = e4m3(x) and remainder = e4m3(x - head), so that the pair carries about 7 mantissa bits.
+__device__ __forceinline__ float e4m3_value(float v) {
+  const __nv_fp8_storage_t q = __nv_cvt_float_to_fp8(v, __NV_SATFINITE, __NV_E4M3);
+  const __half_raw h = __nv_cvt_fp8_to_halfraw(q, __NV_E4M3);
+  return __half2float(*reinterpret_cast<const __half*>(&h));
+}
+
+template <int OUT, bool SPLIT>
+__global__ void __launch_bounds__(256) cast_quant_kernel(const __nv_bfloat16* __restrict__ x, int64_t ld_x,
+                                                         uint8_t* __restrict__ y, int64_t ld_y, int M, int D) {
+  const int nvec = D >> 3;
+  const int64_t total = static_cast<int64_t>(M) * nvec;
+  for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < total;
+       i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const int64_t r = i / nvec;
+    const int c = static_cast<int>(i - r * nvec) * 8;
+    bf16x8 p = *reinterpret_cast<const bf16x8*>(x + r * ld_x + c);
+    float f[8];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      float2 t = unpack_bf16x2(p.u[j]);
+      f[2 * j] = t.x, f[2 * j + 1] = t.y;
+    }
+    uint2 o;
+    if constexpr (OUT == 1) {
+      o.x = pack_e4m3x4(f[0], f[1], f[2], f[3]);
+      o.y = pack_e4m3x4(f[4], f[5], f[6], f[7]);
+    } else {
+      o.x = pack_s8x4(f[0], f[1], f[2], f[3]);
+      o.y = pack_s8x4(f[4], f[5], f[6], f[7]);
+    }
+    uint8_t* dst = y + r * ld_y + c;
+    *reinterpret_cast<uint2*>(dst) = o;
+    if constexpr (SPLIT) {
+      *reinterpret_cast<uint2*>(dst + 2 * D) = o;
+      float g[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) g[j] = f[j] - e4m3_value(f[j]);
+      uint2 lo;
+      lo.x = pack_e4m3x4(g[0], g[1], g[2], g[3]);
+      lo.y = pack_e4m3x4(g[4], g[5], g[6], g[7]);
+      *reinterpret_cast<uint2*>(dst + D) = lo;
+    }
+  }
+}
+
 // ------------------------------------------------------------------- gemv
 // y[n] = (sum_k W[n,k] * f(x[k])) * w_scale[n or 0] + bias[n].  The activation vector is staged once per CTA
 // in shared memory; each warp walks groups of four consecutive rows so that every 64-byte read of the
@@ -703,6 +753,30 @@ static int quant_rows_impl(const void* x, int64_t ld_x, int chunk_cols, int64_t 
 }
 
 extern "C" {
+
+int dsb_cast_quant(const void* x, int64_t ld_x, void* y, int64_t ld_y, int M, int D, int out_fmt, int split,
+                   void* stream) {
+  if (M < 0 || D <= 0 || (D & 7) || (ld_x & 7) || (ld_y & 7)) return DSB_ERR_ARG;
+  if (split && out_fmt != DSB_FMT_E4M3) return DSB_ERR_ARG;
+  if (M == 0) return DSB_OK;
+  if (!x || !y || !aligned16(x) || (reinterpret_cast<uintptr_t>(y) & 7u)) return DSB_ERR_ARG;
+  const int64_t total = static_cast<int64_t>(M) * (D >> 3);
+  int blocks = static_cast<int>((total + 255) / 256);
+  const int cap = sm_count() * 8;
+  if (blocks > cap) blocks = cap;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  const __nv_bfloat16* xp = reinterpret_cast<const __nv_bfloat16*>(x);
+  uint8_t* yp = reinterpret_cast<uint8_t*>(y);
+  if (out_fmt == DSB_FMT_E4M3 && split)
+    cast_quant_kernel<1, true><<<blocks, 256, 0, st>>>(xp, ld_x, yp, ld_y, M, D);
+  else if (out_fmt == DSB_FMT_E4M3)
+    cast_quant_kernel<1, false><<<blocks, 256, 0, st>>>(xp, ld_x, yp, ld_y, M, D);
+  else if (out_fmt == DSB_FMT_INT8)
+    cast_quant_kernel<2, false><<<blocks, 256, 0, st>>>(xp, ld_x, yp, ld_y, M, D);
+  else
+    return DSB_ERR_ARG;
+  return cudaGetLastError() == cudaSuccess ? DSB_OK : DSB_ERR_CUDA;
+}
 
 int dsb_gemv(const void* W, int64_t ld_w, int w_fmt, const float* x, const float* w_scale, int w_scale_stride,
              const float* bias, float* y, int N, int K, int act_in, int act_out, int accumulate, void* stream) {

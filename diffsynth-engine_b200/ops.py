@@ -154,6 +154,18 @@ def quant_rows_chunked(x3, out_fmt=FMT_E4M3, out=None, row_scale=None):
     return out, row_scale
 
 
+def cast_quant(x, out, out_fmt=FMT_E4M3, split=False):
+    """Saturating cast of bf16 ``x [M, D]`` into the 8-bit window ``out`` (may be a column slice): ``[M, D]``, or
+    with ``split`` (e4m3) ``[M, 3D]`` = [head | remainder | head]."""
+    _require_cuda(x, out)
+    M, D, ld_x = _rows(x)
+    if out.shape[0] != M or out.shape[1] != (3 * D if split else D):
+        raise _lib.DsbError("cast_quant: output window has the wrong shape")
+    rc = _lib.lib().dsb_cast_quant(_ptr(x), ld_x, _ptr(out), out.stride(0), M, D, out_fmt, int(split), _stream())
+    check(rc, "dsb_cast_quant")
+    return out
+
+
 def gemv(W, x, w_scale=None, bias=None, act_in=ACT_NONE, act_out=ACT_NONE, out=None, accumulate=False):
     """y = act_out((W @ act_in(x)) * w_scale + bias) for one fp32 activation row."""
     _require_cuda(W, x, w_scale, bias)

@@ -12,7 +12,7 @@ weights that need metadata travel as a ``Parameter`` subclass (``GGUFParameter``
         dit(...)                                      # every Linear whose weight is a QuantLinearWeight runs here
 
 Anything that is not a ``QuantLinearWeight`` (VAE, text encoders, LoRA side matrices) falls through to the
-original ``F.linear`` untouched.  Unlike the reference's context manager this one restores ``F.linear`` in a
+original ``F.linear`` untouched; ``lora.fuse_lora(dit)`` folds loaded-but-unfused LoRAs into the quantised GEMM.  Unlike the reference's context manager this one restores ``F.linear`` in a
 ``finally`` block.
 """
 from contextlib import contextmanager
@@ -34,6 +34,8 @@ class QuantLinearWeight(nn.Parameter):
         self.scale = scale
         self.fmt = fmt
         self._bias_f32 = None
+        self.lora_ext = None      # unfused LoRAs riding in the GEMM as extra K columns (lora.fuse_lora)
+        self._lora_sig = None
         return self
 
     __torch_function__ = torch._C._disabled_torch_function_impl
@@ -88,6 +90,13 @@ def b200_linear(input: torch.Tensor, weight: torch.Tensor, bias=None, _origin=F.
     M = x.shape[0]
     b32 = weight.bias_f32(bias)
     payload = weight.data
+    ext = getattr(weight, "lora_ext", None)
+    if ext is not None:
+        from .lora import linear_lora
+        xb = x if x.dtype == torch.bfloat16 else x.to(torch.bfloat16)
+        if xb.stride(-1) != 1 or (xb.stride(0) % 8) or (xb.data_ptr() % 16):
+            xb = xb.contiguous()
+        return linear_lora(xb, payload, weight.scale, b32, ext).to(input.dtype).reshape(*lead, N)
     if M <= 4:  # conditioning vectors: bandwidth-bound GEMV on fp32 activations, weights dequantised on the fly
         xf = x.float().contiguous()
         rows = [ops.gemv(payload, xf[i], weight.scale, b32) for i in range(M)]

@@ -113,6 +113,17 @@ int dsb_quant_rows_chunked(const void* x, int64_t ld_x, int chunk_cols, int64_t 
                            float* row_scale, int M, int K, int out_fmt, void* stream);
 
 /*
+ * y = saturating cast of bf16 x [M, ld_x] (D columns, D % 8 == 0) to e4m3 (round-to-nearest-even, +-448) or int8
+ * (round-half-even, +-127), no scale: the values are already in operand units.  y may be a column window of a wider
+ * 8-bit buffer (ld_y in elements, 8-byte aligned start).  split != 0 (e4m3 only) writes three windows of D columns,
+ * [head | remainder | head] with head = e4m3(x), remainder = e4m3(x - head).  Used to place the LoRA
+ * down-projection next to the quantised activations so that the side matrices ride in the main GEMM as extra K
+ * columns; replaces the separate up(down(x)) GEMMs and the scaled add of models/basic/lora.py:29-32,137-141.
+ */
+int dsb_cast_quant(const void* x, int64_t ld_x, void* y, int64_t ld_y, int M, int D, int out_fmt, int split,
+                   void* stream);
+
+/*
  * y[n] = act_out((sum_k W[n,k] * act_in(x[k])) * w_scale[n*w_scale_stride] + bias[n]) for one activation row
  * (fp32 x, fp32 y).  W is [N, ld_w] in w_fmt.  act_in: 0 none, DSB_ACT_SILU; act_out: DSB_ACT_*;
  * accumulate != 0 adds the result to y instead of overwriting it.

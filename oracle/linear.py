@@ -42,3 +42,74 @@ class LinearEval:
             else:
                 y = x @ (q.float() * sd).t()
         return y if b is None else y + b.float()
+
+
+# ------------------------------------------------------------------ LoRA side matrices
+def lora_reference(x, W, b, loras):
+    """``LoRALinear.forward`` (models/basic/lora.py:137-141 with ``LoRA.forward`` :29-32) in exact fp32:
+    ``x W^T + b + sum_i scale_i * alpha_i / rank_i * (x down_i^T) up_i^T``.  ``loras``: (coef, up [N,r], down [r,K])
+    with coef = scale * alpha / rank."""
+    y = x.float() @ W.float().t()
+    if b is not None:
+        y = y + b.float()
+    for coef, up, down in loras:
+        y = y + coef * ((x.float() @ down.float().t()) @ up.float().t())
+    return y
+
+
+def _e4m3(t):
+    return torch.clamp(t, -448, 448).to(torch.float8_e4m3fn).float()
+
+
+def lora_extension(W_q, W_s, mode, loras, pad=64):
+    """The library's K-extension of a quantised weight by unfused LoRAs (no reference counterpart: the reference
+    runs the side matrices as two more bf16 Linears).  Stacks ``D = cat(down_i)`` [R, K] and
+    ``U = cat(coef_i * up_i)`` [N, R] (R padded with zeros to a multiple of ``pad``), quantises D per row, and
+    returns (W_ext_q [N, K+E], D_q, D_colscale [R]) such that
+    ``(x_q W_q^T + t_ext U_ext^T) * s_m * s_n`` with ``t = bf16(x_q D_q^T * D_colscale)`` reproduces the LoRA sum;
+    tau balances the ranges of the two 8-bit factors per rank column.  FP8: both factors are split into an e4m3
+    head and an e4m3 remainder, t_ext = [t_hi | t_lo | t_hi] against U_ext = [U_hi | U_hi | U_lo] (E = 3R), which
+    leaves only the remainder-times-remainder term out.  INT8: single columns (E = R)."""
+    qmax = 127.0 if mode == "int8_channel" else 448.0
+    N, K = W_q.shape
+    D = torch.cat([d.float() for _, _, d in loras], dim=0)
+    U = torch.cat([c * u.float() for c, u, _ in loras], dim=1)
+    R = D.shape[0]
+    Rp = (R + pad - 1) // pad * pad
+    D = torch.cat([D, torch.zeros(Rp - R, K)], dim=0)
+    U = torch.cat([U, torch.zeros(N, Rp - R)], dim=1)
+    D_q, D_s = O.quant_weight(D, "int8_channel" if mode == "int8_channel" else "fp8_channel")
+    s_n = W_s.float().reshape(-1, 1) if W_s.numel() > 1 else W_s.float().reshape(1, 1)
+    a = qmax * D.norm(dim=1)                                  # 4-sigma bound of |x_q . D_j| for rows with amax qmax
+    bmax = (U / s_n).abs().amax(dim=0)
+    tau = torch.sqrt(a / bmax.clamp_min(1e-30)).clamp_min(1e-30)
+    tau = torch.where((a > 0) & (bmax > 0), tau, torch.ones_like(tau))
+    Up = U * tau[None, :] / s_n
+    assert float(Up.abs().amax()) <= qmax, "LoRA column beyond the quantised weight's range: the library keeps it unfused"
+    if mode == "int8_channel":
+        U_ext = torch.clamp(torch.round(Up), -127, 127).to(torch.int8)
+    else:
+        U_hi = _e4m3(Up)
+        U_lo = _e4m3(Up - U_hi)
+        U_ext = torch.cat([U_hi, U_hi, U_lo], dim=1).to(torch.float8_e4m3fn)
+    return torch.cat([W_q, U_ext], dim=1), D_q, (D_s.float() / tau).contiguous()
+
+
+def lora_linear_quant(x, W, b, loras, mode):
+    """Same-quantisation restatement of the library's fused LoRA Linear for ``mode`` in fp8_tensor / fp8_channel /
+    int8_channel (bf16 activations in, fp32 out before the final bf16 rounding)."""
+    W_q, W_s = O.quant_weight(W, mode)
+    W_ext, D_q, D_cs = lora_extension(W_q, W_s, mode, loras)
+    int8 = mode == "int8_channel"
+    x_q, x_s = (O.quant_rows_int8 if int8 else O.quant_rows_e4m3)(x.bfloat16())
+    t = (x_q.float() @ D_q.float().t()) * D_cs[None, :]
+    t = t.bfloat16().float()
+    if int8:
+        t_ext = torch.clamp(torch.round(t), -127, 127)
+    else:
+        t_hi = _e4m3(t)
+        t_ext = torch.cat([t_hi, _e4m3(t - t_hi), t_hi], dim=1)
+    acc = torch.cat([x_q.float(), t_ext], dim=1) @ W_ext.float().t()
+    s_n = W_s.float().reshape(1, -1) if W_s.numel() > 1 else W_s.float().reshape(1, 1)
+    y = acc * x_s.float().reshape(-1, 1) * s_n
+    return y if b is None else y + b.float()

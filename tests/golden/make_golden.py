@@ -148,6 +148,15 @@ def main(ref_root):
                                         torch.tensor([417.0]), clip_feature=synth.randn((1, 257, 1280), 28),
                                         y=synth.randn((1, 20, 3, 8, 10), 29))
 
+    # ---- LoRALinear with two unfused adapters (models/basic/lora.py:137-141), fp32
+    from diffsynth_engine.models.basic.lora import LoRALinear
+    ll = LoRALinear(256, 192)
+    ll.weight.copy_(synth.randn((192, 256), 60) * 0.05)
+    ll.bias.copy_(synth.randn((192,), 61) * 0.1)
+    ll.add_lora("a", 0.8, 8, 16, synth.randn((192, 8), 62) * 0.02, synth.randn((8, 256), 63) * 0.06, "cpu", torch.float32)
+    ll.add_lora("b", 1.0, 4, 4, synth.randn((192, 4), 64) * 0.02, synth.randn((4, 256), 65) * 0.06, "cpu", torch.float32)
+    out["lora_linear.out"] = ll(synth.randn((40, 256), 66))
+
     # ---- the reference's FP8 Linear as shipped (unit scales) on a small case, for the drop-in patch
     lin = torch.nn.Linear(256, 128)
     lin.weight.copy_(synth.randn((128, 256), 30) * 0.5)

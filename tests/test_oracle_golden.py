@@ -136,3 +136,26 @@ def test_fp8_unit_scale_linear_matches_reference_path():
     y = (xq @ W.to(torch.float8_e4m3fn).float().t() + b.bfloat16().float()).bfloat16().float().reshape(2, 24, 128)
     # cuBLAS-free CPU fallback of _scaled_mm rounds once to bf16, like this restatement; allow one bf16 ulp
     assert O.rel_l2(y, G["fp8_linear_unit_scale.out"]) < 4e-3
+
+
+def lora_case():
+    """Inputs of the ``lora_linear.out`` fixture: (x, W, b, [(coef, up, down)])."""
+    W, b = synth.randn((192, 256), 60) * 0.05, synth.randn((192,), 61) * 0.1
+    loras = [(0.8 * 16 / 8, synth.randn((192, 8), 62) * 0.02, synth.randn((8, 256), 63) * 0.06),
+             (1.0 * 4 / 4, synth.randn((192, 4), 64) * 0.02, synth.randn((4, 256), 65) * 0.06)]
+    return synth.randn((40, 256), 66), W, b, loras
+
+
+def test_lora_linear_restatement_and_quantised_extension():
+    from oracle.linear import lora_linear_quant, lora_reference
+    x, W, b, loras = lora_case()
+    ref = lora_reference(x, W, b, loras)
+    assert O.rel_l2(ref, G["lora_linear.out"]) < TOL
+    # the K-extension form reproduces the LoRA sum to quantisation accuracy, and the LoRA part itself (not just the
+    # main product) is resolved: its error is small against the size of the LoRA contribution
+    delta = ref - (x @ W.t() + b)
+    for mode in ("fp8_tensor", "fp8_channel", "int8_channel"):
+        y = lora_linear_quant(x, W, b, loras, mode)
+        base = LinearEval(mode)(x, W, b)
+        assert O.rel_l2(y, ref) < 5e-2
+        assert O.rel_l2(y - base, delta) < 5e-2, mode

@@ -100,3 +100,29 @@ def test_reference_modules_use_the_seams():
     finally:
         F.linear = origin
     assert calls == [((2, 3, 8), (4, 8))]                 # nn.Linear resolves F.linear at call time, [N,K] weight
+
+
+@pytest.mark.skipif(not os.path.isdir(os.path.join(REF, "diffsynth_engine")), reason="reference tree not mounted")
+def test_reference_lora_linear_has_what_the_fused_path_reads(dsb):
+    """The fused-LoRA seam reads ``_lora_dict`` adapters (scale, alpha, rank, up.weight, down.weight) off the
+    reference's LoRALinear and swaps its forward; check that against the real class, on the CPU."""
+    m = types.ModuleType("diffsynth_engine")
+    m.__path__ = [os.path.join(REF, "diffsynth_engine")]
+    saved = sys.modules.get("diffsynth_engine")
+    sys.modules["diffsynth_engine"] = m
+    try:
+        from diffsynth_engine.models.basic.lora import LoRALinear
+        lora = __import__("importlib").import_module("diffsynth_engine_b200.lora")
+        lin = LoRALinear(32, 16)
+        lin.add_lora("a", 0.5, 4, 8, torch.randn(16, 4), torch.randn(4, 32), "cpu", torch.float32)
+        (coef, up, down), = lora._adapters(lin)
+        assert coef == 0.5 * 8 / 4 and up.shape == (16, 4) and down.shape == (4, 32)
+        sig = lora._signature(lin)
+        lin.modify_scale("a", 0.25)
+        assert lora._signature(lin) != sig                      # a scale change invalidates the built extension
+        assert lora.fuse_lora(lin) == 0                         # not prepacked: left alone
+    finally:
+        if saved is None:
+            sys.modules.pop("diffsynth_engine", None)
+        else:
+            sys.modules["diffsynth_engine"] = saved
