@@ -41,7 +41,7 @@ struct GemmEpilogue {
   // fused per-head QK-RMSNorm + RoPE on the projection's q and k column ranges (nq_w == nullptr: off)
   const float* nq_w;   // [128] weights of the q heads (columns [0, d_model))
   const float* nk_w;   // [128] weights of the k heads (columns [d_model, 2 d_model))
-  const float2* rope;  // [(rope_row0 + m) * 64 + pair] = (cos, sin); nullptr: no rotation
+  int has_rope;  // RoPE table (fp16 [rows][64] (cos, sin)) is reached through the problem's staging-load tensor map
   int rope_row0;
   int d_model;
   float norm_eps;
@@ -315,10 +315,17 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
         // this warp's previous store must have read the staging slot out
         if (lane == 0) bulk_wait_read<0>();
         __syncwarp();
-        if (ep.has_resid) {
+        // Tile-shaped epilogue input, fetched by TMA into this warp's staging slot (32 rows x 128 bytes, the slot the
+        // output block is then written over cell by cell): the residual block, or for a normalised head the RoPE
+        // factors of these rows - 32 pairs of fp16 (cos, sin) are the same 128 bytes per row as 64 bf16 outputs.
+        const bool do_rope = fuse_norm && ep.has_rope;
+        if (ep.has_resid || do_rope) {
           if (lane == 0) {
             mbar_expect_tx(rbar, kStageSlotBytes);
-            tma_load_2d(sbuf, &P.r, rbar, nb, r0);
+            if (do_rope)
+              tma_load_2d(sbuf, &P.r, rbar, nb - head_col0, ep.rope_row0 + r0);
+            else
+              tma_load_2d(sbuf, &P.r, rbar, nb, r0);
           }
           if (!mbar_wait(rbar, rphase, abort_flag)) {
             alive = false;
@@ -371,17 +378,19 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
                 const float4 w1 = __ldg(reinterpret_cast<const float4*>(head_w + ch + 4));
                 v[0] *= rnorm * w0.x, v[1] *= rnorm * w0.y, v[2] *= rnorm * w0.z, v[3] *= rnorm * w0.w;
                 v[4] *= rnorm * w1.x, v[5] *= rnorm * w1.y, v[6] *= rnorm * w1.z, v[7] *= rnorm * w1.w;
-                if (ep.rope && m < M) {
-                  const float4* rp = reinterpret_cast<const float4*>(
-                      ep.rope + (static_cast<int64_t>(ep.rope_row0) + m) * 64 + (ch >> 1));
-                  const float4 c01 = __ldg(rp), c23 = __ldg(rp + 1);  // (cos, sin) of four pairs
-                  float t0 = c01.x * v[0] - c01.y * v[1], t1 = c01.y * v[0] + c01.x * v[1];
+                if (do_rope) {
+                  const uint4 cs4 = *reinterpret_cast<const uint4*>(cell);  // (cos, sin) of the four pairs, fp16
+                  const float2 f0 = __half22float2(*reinterpret_cast<const __half2*>(&cs4.x));
+                  const float2 f1 = __half22float2(*reinterpret_cast<const __half2*>(&cs4.y));
+                  const float2 f2 = __half22float2(*reinterpret_cast<const __half2*>(&cs4.z));
+                  const float2 f3 = __half22float2(*reinterpret_cast<const __half2*>(&cs4.w));
+                  float t0 = f0.x * v[0] - f0.y * v[1], t1 = f0.y * v[0] + f0.x * v[1];
                   v[0] = t0, v[1] = t1;
-                  t0 = c01.z * v[2] - c01.w * v[3], t1 = c01.w * v[2] + c01.z * v[3];
+                  t0 = f1.x * v[2] - f1.y * v[3], t1 = f1.y * v[2] + f1.x * v[3];
                   v[2] = t0, v[3] = t1;
-                  t0 = c23.x * v[4] - c23.y * v[5], t1 = c23.y * v[4] + c23.x * v[5];
+                  t0 = f2.x * v[4] - f2.y * v[5], t1 = f2.y * v[4] + f2.x * v[5];
                   v[4] = t0, v[5] = t1;
-                  t0 = c23.z * v[6] - c23.w * v[7], t1 = c23.w * v[6] + c23.z * v[7];
+                  t0 = f3.x * v[6] - f3.y * v[7], t1 = f3.y * v[6] + f3.x * v[7];
                   v[6] = t0, v[7] = t1;
                 }
               }
@@ -567,7 +576,7 @@ static int check_problem(const dsb_gemm_args& a, int fmt, int* status, GemmProbl
   ep.status = status;
   ep.nq_w = a.nq_w;
   ep.nk_w = a.nk_w;
-  ep.rope = reinterpret_cast<const float2*>(a.rope);
+  ep.has_rope = (a.nq_w && a.rope) ? 1 : 0;
   ep.rope_row0 = a.rope_row0;
   ep.d_model = a.d_model;
   ep.norm_eps = a.norm_eps;
@@ -584,6 +593,10 @@ static int check_problem(const dsb_gemm_args& a, int fmt, int* status, GemmProbl
   P->r = P->o0;
   if (a.resid &&
       make_tmap_2d(&P->r, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, a.resid, a.M, a.N, a.ld_resid * 2, 32, 64) != DSB_OK)
+    return DSB_ERR_CUDA;
+  // RoPE table rows [0, rope_row0 + M) of 64 (cos, sin) fp16 pairs = 128 halves = 256 bytes per row
+  if (ep.has_rope && make_tmap_2d(&P->r, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, a.rope,
+                                  static_cast<int64_t>(a.rope_row0) + a.M, 128, 256, 32, 64) != DSB_OK)
     return DSB_ERR_CUDA;
   return DSB_OK;
 }
@@ -651,7 +664,7 @@ extern "C" int dsb_gemm(const void* A, int64_t lda, const void* W, int64_t ldw, 
 extern "C" int dsb_gemm_qkv(const void* A, int64_t lda, const void* W, int64_t ldw, int fmt, int M, int N, int K,
                             const float* row_scale, const float* col_scale, int col_scale_stride, const float* bias,
                             int act, int act_col0, void* out0, int64_t ld_out0, void* out1, int64_t ld_out1,
-                            int split_col, const float* nq_w, const float* nk_w, int d_model, const float* rope,
+                            int split_col, const float* nq_w, const float* nk_w, int d_model, const void* rope,
                             int rope_row0, float norm_eps, int* status, void* stream) {
   if (!nq_w || !nk_w) return DSB_ERR_ARG;
   dsb_gemm_args a = {};

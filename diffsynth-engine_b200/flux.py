@@ -218,7 +218,7 @@ class FluxDiTEngine:
             a, s = self._quant(b["patches"][p0:p0 + n_img], xq[rows, :self.in_ch], rs[rows])
             self._gemm(a, s, self.x_emb, out=x[rows])
 
-        rope = b["rope"]
+        rope = b["rope_h"]
         attn_o = cat[:, :d]                      # attention output lands in the first d columns of `cat`
         q4 = qkv[:, :d].unflatten(1, (H, 128)).unsqueeze(0)
         k4 = qkv[:, d:2 * d].unflatten(1, (H, 128)).unsqueeze(0)
@@ -299,6 +299,8 @@ class FluxDiTEngine:
         ids = torch.cat([text_ids.reshape(-1, 3).float().to(self.dev), image_ids.reshape(-1, 3).float().to(self.dev),
                          torch.zeros(b["S_pad"] - b["S"], 3, device=self.dev)])   # padding rows: position 0
         b["rope"] = flux_rope_table(ids)
+        # fp16 (cos, sin) copy for the projection GEMMs' epilogue, which fetches it by TMA (exact to 2^-12)
+        b["rope_h"] = b["rope"].reshape(-1, 64, 2).to(torch.float16).contiguous()
         return self
 
     def set_inputs(self, latents, timestep, prompt_emb, pooled, guidance):

@@ -234,10 +234,20 @@ def gemm(a, w, row_scale=None, col_scale=None, bias=None, act=ACT_NONE, act_col0
     return out
 
 
+def _check_rope_table(rope, rows_needed):
+    """The GEMM epilogue reads the RoPE table through a TMA map: fp16 [rows, 64, 2] (cos, sin), contiguous."""
+    if rope is None:
+        return
+    if rope.dtype != torch.float16 or not rope.is_contiguous() or rope.numel() % 128 or rope.numel() // 128 < rows_needed:
+        raise _lib.DsbError("the fused-RoPE GEMM takes a contiguous float16 [rows, 64, 2] table covering rope_row0 + M rows")
+
+
 def gemm_qkv(a, w, nq_w, nk_w, d_model, rope=None, rope_row0=0, eps=1e-6, row_scale=None, col_scale=None, bias=None,
              act=ACT_NONE, act_col0=0, out=None, out1=None, split_col=None):
-    """``dsb_gemm_qkv``: the fused q|k|v(|mlp) projection with per-head RMSNorm + RoPE on the q and k columns."""
+    """``dsb_gemm_qkv``: the fused q|k|v(|mlp) projection with per-head RMSNorm + RoPE on the q and k columns.
+    ``rope``: float16 [rows, 64, 2] (cos, sin)."""
     _require_cuda(a, w, nq_w, nk_w, rope, row_scale, col_scale, bias, out, out1)
+    _check_rope_table(rope, rope_row0 + a.shape[0])
     M, K, lda = _rows(a)
     N, Kw, ldw = _rows(w)
     if K != Kw or _fmt_of(a) != _fmt_of(w):
@@ -271,6 +281,8 @@ def gemm_group(problems):
         N, Kw, ldw = _rows(w)
         if K != Kw or _fmt_of(a) != fmt or _fmt_of(w) != fmt:
             raise _lib.DsbError("gemm_group operands disagree in K or format")
+        if pr.get("nq_w") is not None:
+            _check_rope_table(pr.get("rope"), pr.get("rope_row0", 0) + M)
         cs = pr.get("col_scale")
         g = arr[i]
         g.A, g.lda, g.W, g.ldw, g.M, g.N, g.K = a.data_ptr(), lda, w.data_ptr(), ldw, M, N, K

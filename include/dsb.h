@@ -185,14 +185,17 @@ int dsb_gemm(const void* A, int64_t lda, const void* W, int64_t ldw, int fmt, in
  * dsb_gemm for a fused q|k|v (|mlp) projection, with the per-head QK-RMSNorm and RoPE applied in the epilogue:
  * columns [0, d_model) are q heads (weights nq_w[128]), [d_model, 2 d_model) k heads (nk_w[128]); each head's 128
  * columns are scaled by rsqrt(mean(v^2) + norm_eps) * w and then rotated pairwise with rope[(rope_row0 + m)*64 + j]
- * = (cos, sin) (rope NULL: no rotation).  Columns from 2 d_model on follow dsb_gemm (bias, activation from act_col0,
+ * = (cos, sin) (rope NULL: no rotation).  Here the table is FP16, [rows >= rope_row0 + M][64][2], 16-byte aligned:
+ * the epilogue fetches it with TMA tile loads, 128 bytes per row and 64 output columns, like a residual block
+ * (per-thread loads of an fp32 table cost the 4096x3072->9216 projection 40 % of its time).  fp16 cos/sin are
+ * exact to 2^-12, an eighth of the bf16 rounding of the result.  Columns from 2 d_model on follow dsb_gemm (bias, activation from act_col0,
  * split output).  Replaces, on top of dsb_gemm: models/basic/transformer_helper.py:73-78 (RMSNorm) and
  * models/flux/flux_dit.py:154-159 (apply_rope) as used at flux_dit.py:165-180 and :297-301.
  */
 int dsb_gemm_qkv(const void* A, int64_t lda, const void* W, int64_t ldw, int fmt, int M, int N, int K,
                  const float* row_scale, const float* col_scale, int col_scale_stride, const float* bias, int act,
                  int act_col0, void* out0, int64_t ld_out0, void* out1, int64_t ld_out1, int split_col,
-                 const float* nq_w, const float* nk_w, int d_model, const float* rope, int rope_row0, float norm_eps,
+                 const float* nq_w, const float* nk_w, int d_model, const void* rope, int rope_row0, float norm_eps,
                  int* status, void* stream);
 
 /*
@@ -213,7 +216,7 @@ typedef struct dsb_gemm_args {
   void* out1; int64_t ld_out1;
   int split_col;
   const float* nq_w; const float* nk_w; int d_model;
-  const float* rope; int rope_row0; float norm_eps;
+  const void* rope; /* fp16 (cos, sin) table, see dsb_gemm_qkv */ int rope_row0; float norm_eps;
 } dsb_gemm_args;
 
 /*
