@@ -249,20 +249,37 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
       const int tl = t >= tiles_first ? t - tiles_first : t;
       const int m0 = (tl % P.tiles_m) * kTileM + static_cast<int>(cta_rank) * kBlockM;
       const int n0 = (tl / P.tiles_m) * BLOCK_N;
-      if (!mbar_wait(&tmem_full[acc], acc_phase, abort_flag)) break;
-      tc_fence_after();
       const int r0 = m0 + quad * 32;
       const int m = r0 + lane;
+      // Fused QK-RMSNorm (+RoPE): with 256-wide tiles this warp's 128 columns are exactly one head, one row per
+      // thread, so the row's sum of squares needs no cross-thread traffic - just a first pass over TMEM.
+      const int head_col0 = n0 + half * 128;
+      const bool fuse_norm = (BLOCK_N == 256) && ep.nq_w != nullptr && head_col0 < 2 * ep.d_model && head_col0 < N;
+      const bool rope_tile = fuse_norm && ep.has_rope;
+      // The tile-shaped epilogue input of this warp's FIRST 64-column block (residual rows, or RoPE factors) does not
+      // depend on the accumulator: request it before waiting for the MMAs, so its L2 round trip runs under them.
+      // The staging slot must first have been read out by the previous tile's store.
+      const int pre_nb = n0 + half * kBlocksPerWarp * 64;
+      const bool pre_issued = (ep.has_resid || rope_tile) && pre_nb < N;
+      if (pre_issued) {
+        if (lane == 0) {
+          bulk_wait_read<0>();
+          mbar_expect_tx(rbar, kStageSlotBytes);
+          if (rope_tile)
+            tma_load_2d(sbuf, &P.r, rbar, pre_nb - head_col0, ep.rope_row0 + r0);
+          else
+            tma_load_2d(sbuf, &P.r, rbar, pre_nb, r0);
+        }
+        __syncwarp();
+      }
+      if (!mbar_wait(&tmem_full[acc], acc_phase, abort_flag)) break;
+      tc_fence_after();
       const float rs = (ep.row_scale && m < M) ? ep.row_scale[m] : 1.0f;
       const float rs_t = (ep.col_scale && !ep.col_scale_stride) ? rs * __ldg(ep.col_scale) : rs;  // per-tensor scale folded in
       const bool second = n0 >= ep.split_col;
       const CUtensorMap* tmap_out = second ? &P.o1 : &P.o0;
       const int col_shift = second ? ep.split_col : 0;
       const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + acc * BLOCK_N;
-      // Fused QK-RMSNorm (+RoPE): with 256-wide tiles this warp's 128 columns are exactly one head, one row per
-      // thread, so the row's sum of squares needs no cross-thread traffic - just a first pass over TMEM.
-      const int head_col0 = n0 + half * 128;
-      const bool fuse_norm = (BLOCK_N == 256) && ep.nq_w != nullptr && head_col0 < 2 * ep.d_model && head_col0 < N;
       const float* head_w = head_col0 < ep.d_model ? ep.nq_w : ep.nk_w;
       float rnorm = 1.0f;
       if (fuse_norm) {
@@ -318,9 +335,9 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
         // Tile-shaped epilogue input, fetched by TMA into this warp's staging slot (32 rows x 128 bytes, the slot the
         // output block is then written over cell by cell): the residual block, or for a normalised head the RoPE
         // factors of these rows - 32 pairs of fp16 (cos, sin) are the same 128 bytes per row as 64 bf16 outputs.
-        const bool do_rope = fuse_norm && ep.has_rope;
+        const bool do_rope = rope_tile;
         if (ep.has_resid || do_rope) {
-          if (lane == 0) {
+          if (lane == 0 && !(pre_issued && nb == pre_nb)) {  // the first block's input is already on its way
             mbar_expect_tx(rbar, kStageSlotBytes);
             if (do_rope)
               tma_load_2d(sbuf, &P.r, rbar, nb - head_col0, ep.rope_row0 + r0);
