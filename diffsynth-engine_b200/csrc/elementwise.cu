@@ -436,6 +436,35 @@ __global__ void __launch_bounds__(256) cast_quant_kernel(const __nv_bfloat16* __
   }
 }
 
+// ---------------------------------------------------------- dequant_q8_0
+// GGUF Q8_0 -> bf16: one thread per block of 32 weights (34 bytes: fp16 d, 32 x int8).  A block is only 2-byte
+// aligned, so it is read as 17 halfwords; the thread writes 64 contiguous bytes.  out = bf16(bf16(d) * q), the
+// product the reference forms when its compute dtype is bf16.
+__global__ void __launch_bounds__(256) dequant_q8_0_kernel(const uint16_t* __restrict__ raw, int64_t row_halfwords,
+                                                           __nv_bfloat16* __restrict__ out, int64_t ld_out, int N,
+                                                           int blocks_per_row) {
+  const int64_t total = static_cast<int64_t>(N) * blocks_per_row;
+  for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < total;
+       i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const int64_t n = i / blocks_per_row;
+    const int kb = static_cast<int>(i - n * blocks_per_row);
+    const uint16_t* src = raw + n * row_halfwords + static_cast<int64_t>(kb) * 17;
+    const __half_raw hr = {__ldg(src)};
+    const float d = __bfloat162float(__float2bfloat16_rn(__half2float(*reinterpret_cast<const __half*>(&hr))));
+    uint32_t o[16];
+#pragma unroll
+    for (int j = 0; j < 16; ++j) {
+      const uint16_t w = __ldg(src + 1 + j);
+      const float q0 = static_cast<float>(static_cast<int8_t>(w & 0xffu));
+      const float q1 = static_cast<float>(static_cast<int8_t>(w >> 8));
+      o[j] = pack_bf16x2(d * q0, d * q1);
+    }
+    uint4* dst = reinterpret_cast<uint4*>(out + n * ld_out + static_cast<int64_t>(kb) * 32);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) dst[j] = make_uint4(o[4 * j], o[4 * j + 1], o[4 * j + 2], o[4 * j + 3]);
+  }
+}
+
 // ------------------------------------------------------------------- gemv
 // y[n] = (sum_k W[n,k] * f(x[k])) * w_scale[n or 0] + bias[n].  The activation vector is staged once per CTA
 // in shared memory; each warp walks groups of four consecutive rows so that every 64-byte read of the
@@ -753,6 +782,21 @@ static int quant_rows_impl(const void* x, int64_t ld_x, int chunk_cols, int64_t 
 }
 
 extern "C" {
+
+int dsb_dequant_q8_0(const void* blocks, int64_t row_bytes, int N, int K, void* out, int64_t ld_out, void* stream) {
+  if (N < 0 || K <= 0 || (K & 31) || (row_bytes & 1) || row_bytes < static_cast<int64_t>(K / 32) * 34 || (ld_out & 7))
+    return DSB_ERR_ARG;
+  if (N == 0) return DSB_OK;
+  if (!blocks || !out || (reinterpret_cast<uintptr_t>(blocks) & 1u) || !aligned16(out)) return DSB_ERR_ARG;
+  const int bpr = K / 32;
+  const int64_t total = static_cast<int64_t>(N) * bpr;
+  int nblk = static_cast<int>((total + 255) / 256);
+  const int cap = sm_count() * 16;
+  if (nblk > cap) nblk = cap;
+  dequant_q8_0_kernel<<<nblk, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      reinterpret_cast<const uint16_t*>(blocks), row_bytes / 2, reinterpret_cast<__nv_bfloat16*>(out), ld_out, N, bpr);
+  return cudaGetLastError() == cudaSuccess ? DSB_OK : DSB_ERR_CUDA;
+}
 
 int dsb_cast_quant(const void* x, int64_t ld_x, void* y, int64_t ld_y, int M, int D, int out_fmt, int split,
                    void* stream) {

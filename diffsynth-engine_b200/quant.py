@@ -50,8 +50,32 @@ class QuantLinearWeight(nn.Parameter):
         return self._bias_f32[1]
 
 
+def _is_gguf_q8_0(weight) -> bool:
+    """A ``GGUFParameter`` (utils/gguf.py:9-59) holding Q8_0 blocks: raw uint8 rows plus a ``quant_dtype`` tag."""
+    qd = getattr(weight, "quant_dtype", None)
+    return qd is not None and getattr(qd, "name", str(qd)) == "Q8_0"
+
+
+def _raw_bytes(weight) -> torch.Tensor:
+    """The stored bytes of a GGUFParameter (its ``shape``/``dtype`` properties describe the dequantised weight)."""
+    t = torch.Tensor._make_subclass(torch.Tensor, weight.detach(), False)
+    return t.view(torch.uint8) if t.dtype != torch.uint8 else t
+
+
 def _enable_b200_linear(module: nn.Module, fmt: str):
-    if isinstance(module, nn.Linear) and torch.is_floating_point(module.weight.data) \
+    if isinstance(module, nn.Linear) and _is_gguf_q8_0(module.weight):
+        # GGUF Q8_0: dequantise ONCE, exactly as the reference does per call, then prepack like any other weight
+        raw = _raw_bytes(module.weight)
+        if not raw.is_cuda:
+            raise ops._lib.DsbError("enable_b200_linear: move the module to the GPU first (no CPU path exists)")
+        w = ops.dequant_q8_0(raw.reshape(raw.shape[0], -1).contiguous())
+        if fmt == "bf16":
+            payload, scale = w, None
+        else:
+            code = ops.FMT_INT8 if fmt == "int8_channel" else ops.FMT_E4M3
+            payload, scale = ops.pack_quant_weight(w, code, per_channel=(fmt != "fp8_tensor"))
+        module.weight = QuantLinearWeight(payload, scale, fmt)
+    elif isinstance(module, nn.Linear) and torch.is_floating_point(module.weight.data) \
             and not isinstance(module.weight, QuantLinearWeight):
         w = module.weight.data
         if not w.is_cuda:
@@ -70,7 +94,9 @@ def _enable_b200_linear(module: nn.Module, fmt: str):
 
 def enable_b200_linear(module: nn.Module, fmt: str = "fp8_tensor"):
     """Counterpart of ``enable_fp8_linear`` (utils/fp8_linear.py:7-17): prepack every floating ``nn.Linear``
-    weight below ``module`` and mark the module."""
+    weight below ``module`` and mark the module.  GGUF Q8_0 weights (``GGUFParameter``) are dequantised once on the
+    device (``fmt="bf16"`` keeps exactly the values the reference's ``gguf_linear`` multiplies with) and then take
+    the same path, so they no longer depend on ``gguf_inference`` re-materialising them in every call."""
     if fmt not in FORMATS:
         raise ValueError(f"fmt must be one of {FORMATS}, but got '{fmt}'")
     _enable_b200_linear(module, fmt)

@@ -113,6 +113,16 @@ int dsb_quant_rows_chunked(const void* x, int64_t ld_x, int chunk_cols, int64_t 
                            float* row_scale, int M, int K, int out_fmt, void* stream);
 
 /*
+ * GGUF Q8_0 -> bf16: blocks [N, row_bytes] of raw bytes (K/32 blocks of 34 bytes per row: fp16 d, 32 x int8 q; 2-byte
+ * aligned), out[n, k] = bf16(bf16(d) * q), bit-identical to dequantize_blocks_Q8_0 with a bf16 compute dtype
+ * (utils/gguf.py:171-175).  Meant to run ONCE per weight when a GGUF checkpoint is attached (the reference
+ * dequantises the whole weight inside every Linear call, utils/gguf.py:77-84): with 180 GB of HBM the bf16 (or
+ * re-quantised FP8/INT8) copy stays resident, and a compute-bound GEMM gains nothing from converting its operand on
+ * every one of its M/128 passes over the weight.  K % 32 == 0.
+ */
+int dsb_dequant_q8_0(const void* blocks, int64_t row_bytes, int N, int K, void* out, int64_t ld_out, void* stream);
+
+/*
  * y = saturating cast of bf16 x [M, ld_x] (D columns, D % 8 == 0) to e4m3 (round-to-nearest-even, +-448) or int8
  * (round-half-even, +-127), no scale: the values are already in operand units.  y may be a column window of a wider
  * 8-bit buffer (ld_y in elements, 8-byte aligned start).  split != 0 (e4m3 only) writes three windows of D columns,

@@ -127,6 +127,27 @@ def quant_weight(W, fmt="fp8_tensor"):
     return q, s
 
 
+def q8_0_quantize(W):
+    """GGUF Q8_0 as published (ggml): blocks of 32 along the last axis, each ``fp16 d = amax / 127`` followed by 32
+    ``int8 q = round(x / d)``; returns the raw bytes ``[N, K / 32 * 34]`` (uint8).  Only used to make test inputs."""
+    N, K = W.shape
+    blk = W.float().reshape(N, K // 32, 32)
+    d = (blk.abs().amax(dim=-1, keepdim=True) / 127.0)
+    q = torch.where(d > 0, blk / d, torch.zeros_like(blk)).round().clamp(-127, 127).to(torch.int8)
+    raw = torch.cat([d.to(torch.float16).view(torch.uint8), q.view(torch.uint8)], dim=-1)     # [N, K/32, 2 + 32]
+    return raw.reshape(N, K // 32 * 34).contiguous()
+
+
+def q8_0_dequantize(raw, dtype=torch.bfloat16):
+    """``dequantize_blocks_Q8_0`` (utils/gguf.py:171-175): ``d.view(fp16).to(dtype) * q.view(int8)``, the product
+    taken in ``dtype``.  raw: uint8 ``[N, K / 32 * 34]`` -> ``[N, K]``."""
+    N = raw.shape[0]
+    blocks = raw.reshape(-1, 34)
+    d = blocks[:, :2].contiguous().view(torch.float16).to(dtype)
+    q = blocks[:, 2:].contiguous().view(torch.int8)
+    return (d * q).reshape(N, -1)
+
+
 def linear_quant(x_q, x_s, W_q, W_s, bias=None):
     """Quantised Linear with fp32 accumulation: ((x_q W_q^T) * x_s[m] * W_s[n]) + bias.
     Dataflow of utils/fp8_linear.py:33-50 with scales added; products of e4m3 (or int8) values are exact in fp32

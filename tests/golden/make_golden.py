@@ -157,6 +157,17 @@ def main(ref_root):
     ll.add_lora("b", 1.0, 4, 4, synth.randn((192, 4), 64) * 0.02, synth.randn((4, 256), 65) * 0.06, "cpu", torch.float32)
     out["lora_linear.out"] = ll(synth.randn((40, 256), 66))
 
+    # ---- GGUF Q8_0 block dequantisation (utils/gguf.py:113-135,171-175) on seeded raw bytes
+    import gguf as gguf_pkg
+    from diffsynth_engine.utils import gguf as ref_gguf
+    from oracle.ops import q8_0_quantize
+    raw = q8_0_quantize(synth.randn((24, 128), 67) * 0.05)
+    out["q8_0.raw"] = raw
+    out["q8_0.dequant_bf16"] = ref_gguf.dequantize(raw, quant_dtype=gguf_pkg.GGMLQuantizationType.Q8_0,
+                                                   compute_dtype=torch.bfloat16).float()
+    out["q8_0.dequant_f32"] = ref_gguf.dequantize(raw, quant_dtype=gguf_pkg.GGMLQuantizationType.Q8_0,
+                                                  compute_dtype=torch.float32)
+
     # ---- the reference's FP8 Linear as shipped (unit scales) on a small case, for the drop-in patch
     lin = torch.nn.Linear(256, 128)
     lin.weight.copy_(synth.randn((128, 256), 30) * 0.5)

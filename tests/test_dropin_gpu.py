@@ -111,3 +111,39 @@ def test_set_attn_implementation_names(dsb):
     assert fake_flux._attn_func is A.b200_attn and fake_wan.attention is A.b200_wan_attention
     A.set_attn_implementation("sdpa", fake_flux, fake_wan)
     assert fake_flux._attn_func is F.scaled_dot_product_attention and fake_wan.attention is not A.b200_wan_attention
+
+
+class _Q8Param(torch.nn.Parameter):
+    """Stand-in for the reference's GGUFParameter: raw bytes plus a ``quant_dtype`` tag with a ``name``."""
+
+    def __new__(cls, data):
+        self = torch.Tensor._make_subclass(cls, data, False)
+        self.quant_dtype = type("QT", (), {"name": "Q8_0"})()
+        return self
+
+    __torch_function__ = torch._C._disabled_torch_function_impl
+
+
+def test_gguf_q8_0_dequantisation_and_linear(dsb, cuda_dev):
+    """Q8_0 bytes -> bf16 on the device, bit-identical to the reference's dequantisation; a Linear holding such a
+    weight is prepacked once (bf16 = the reference's numbers; FP8 = re-quantised) and then runs like any other."""
+    from oracle import ops as O
+    from oracle.linear import LinearEval
+    from diffsynth_engine_b200.quant import b200_inference, enable_b200_linear
+    synth = __import__("importlib").import_module("diffsynth_engine_b200.synth")
+    N, K = 200, 512
+    W = synth.randn((N, K), 120) * 0.05
+    raw = O.q8_0_quantize(W)
+    ref_w = O.q8_0_dequantize(raw, torch.bfloat16)
+    got = dsb.ops.dequant_q8_0(raw.to(cuda_dev)).cpu()
+    assert torch.equal(got.view(torch.int16), ref_w.view(torch.int16))
+    x = synth.randn((96, K), 121).bfloat16()
+    for fmt, tol in (("bf16", 3e-3), ("fp8_channel", 1e-2)):
+        lin = torch.nn.Linear(K, N).to(cuda_dev).bfloat16()
+        bias = lin.bias.detach().float().cpu()
+        lin.weight = _Q8Param(raw.to(cuda_dev))
+        enable_b200_linear(lin, fmt)
+        with b200_inference():
+            y = lin(x.to(cuda_dev)).float().cpu()
+        ref = LinearEval(fmt)(x.float(), ref_w.float(), bias)
+        assert O.rel_l2(y, ref) < tol, fmt

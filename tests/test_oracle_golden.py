@@ -159,3 +159,12 @@ def test_lora_linear_restatement_and_quantised_extension():
         base = LinearEval(mode)(x, W, b)
         assert O.rel_l2(y, ref) < 5e-2
         assert O.rel_l2(y - base, delta) < 5e-2, mode
+
+
+def test_q8_0_dequantisation_matches_reference():
+    raw = G["q8_0.raw"]
+    assert torch.equal(raw, O.q8_0_quantize(synth.randn((24, 128), 67) * 0.05))
+    assert torch.equal(O.q8_0_dequantize(raw, torch.bfloat16).float(), G["q8_0.dequant_bf16"])
+    assert torch.equal(O.q8_0_dequantize(raw, torch.float32), G["q8_0.dequant_f32"])
+    w = synth.randn((24, 128), 67) * 0.05
+    assert O.rel_l2(G["q8_0.dequant_f32"], w) < 1e-2     # Q8_0 itself: 8-bit blocks of 32

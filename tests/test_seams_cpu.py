@@ -126,3 +126,30 @@ def test_reference_lora_linear_has_what_the_fused_path_reads(dsb):
             sys.modules.pop("diffsynth_engine", None)
         else:
             sys.modules["diffsynth_engine"] = saved
+
+
+@pytest.mark.skipif(not os.path.isdir(os.path.join(REF, "diffsynth_engine")), reason="reference tree not mounted")
+def test_reference_gguf_parameter_is_recognised(dsb):
+    """``enable_b200_linear`` finds Q8_0 weights by the ``quant_dtype`` tag of the reference's GGUFParameter and reads
+    their stored bytes, not the dequantised ``shape``/``dtype`` the class reports."""
+    import gguf
+    m = types.ModuleType("diffsynth_engine")
+    m.__path__ = [os.path.join(REF, "diffsynth_engine")]
+    saved = sys.modules.get("diffsynth_engine")
+    sys.modules["diffsynth_engine"] = m
+    try:
+        from diffsynth_engine.utils.gguf import GGUFParameter
+        quant = __import__("importlib").import_module("diffsynth_engine_b200.quant")
+        raw = torch.zeros(8, 2 * 34, dtype=torch.uint8)
+        p = GGUFParameter(raw, quant_dtype=gguf.GGMLQuantizationType.Q8_0, compute_dtype=torch.bfloat16)
+        assert tuple(p.shape) == (8, 64) and p.dtype == torch.bfloat16      # what the class reports
+        assert quant._is_gguf_q8_0(p)
+        assert tuple(quant._raw_bytes(p).shape) == (8, 68) and quant._raw_bytes(p).dtype == torch.uint8
+        q4 = GGUFParameter(raw, quant_dtype=gguf.GGMLQuantizationType.Q4_K, compute_dtype=torch.bfloat16)
+        assert not quant._is_gguf_q8_0(q4)
+        assert not quant._is_gguf_q8_0(torch.nn.Parameter(torch.zeros(2, 2)))
+    finally:
+        if saved is None:
+            sys.modules.pop("diffsynth_engine", None)
+        else:
+            sys.modules["diffsynth_engine"] = saved
