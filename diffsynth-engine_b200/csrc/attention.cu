@@ -67,6 +67,13 @@ __device__ __forceinline__ void xchg_publish(unsigned long long* slot, uint32_t 
 }
 __device__ __forceinline__ bool xchg_read(const unsigned long long* slot, uint32_t seq, float* v,
                                           volatile int* abort_flag) {
+  {
+    const unsigned long long w = *reinterpret_cast<const volatile unsigned long long*>(slot);
+    if (static_cast<uint32_t>(w >> 32) == seq) {  // the usual case: published long ago
+      *v = __uint_as_float(static_cast<uint32_t>(w));
+      return true;
+    }
+  }
   const long long t0 = clock64();
   uint32_t spins = 0;
   for (;;) {
@@ -176,7 +183,9 @@ __global__ void __launch_bounds__(kAttnThreads, 1)
     }
   } else if (warp == 1) {
     // -------------------------------------------------------------- MMA issuer
-    if (lane == 0) {
+    {
+      // the whole warp runs this loop so that descriptors and addresses stay warp-uniform; one elected lane issues
+      const uint32_t leader = elect_one();
       constexpr uint32_t idesc_qk = make_idesc(DFMT_F32, FMT_BF16, FMT_BF16, 0, 0, 128, 128);
       constexpr uint32_t idesc_pv = make_idesc(DFMT_F32, FMT_BF16, FMT_BF16, 0, 1, 128, 128);
       // One tcgen05.mma here is only 64 tensor-core cycles of work, so the issuing thread must not spend more than
@@ -192,10 +201,8 @@ __global__ void __launch_bounds__(kAttnThreads, 1)
         const uint32_t d = tmem_base + q * 128;
 #pragma unroll
         for (int kk = 0; kk < 8; ++kk) {
-          constexpr uint32_t dummy = 0;
-          (void)dummy;
           const uint32_t off = (kk >> 2) * kHalf16 + 2 * (kk & 3);
-          mma_ss<KIND_F16>(d, ad0 + off, bd0 + off, idesc_qk, kk > 0 ? 1u : 0u);
+          mma_ss_f16_elect(d, ad0 + off, bd0 + off, idesc_qk, kk > 0 ? 1u : 0u, leader);
         }
       };
       auto issue_pv = [&](int q, int st, bool accumulate) {
@@ -206,7 +213,8 @@ __global__ void __launch_bounds__(kAttnThreads, 1)
         for (int kk = 0; kk < 8; ++kk) {
           // 16 keys per instruction = 16 rows of 128 bytes (2048 bytes = 128 units) further into the V tile
           // P of keys [0,64) lives in columns [0,32) of S_q, P of keys [64,128) in columns [64,96)
-          mma_ts_f16(d, a + (kk >> 2) * 64 + (kk & 3) * 8, bd0 + kk * 128u, idesc_pv, (accumulate || kk > 0) ? 1u : 0u);
+          mma_ts_f16_elect(d, a + (kk >> 2) * 64 + (kk & 3) * 8, bd0 + kk * 128u, idesc_pv, (accumulate || kk > 0) ? 1u : 0u,
+                           leader);
         }
       };
       int kst = 0, vst = 0;
@@ -216,9 +224,9 @@ __global__ void __launch_bounds__(kAttnThreads, 1)
       tc_fence_after();
       for (int q = 0; q < kNQ; ++q) {
         issue_qk(q, kst);
-        tc_commit(&s_full[q]);
+        tc_commit_elect(&s_full[q], leader);
       }
-      tc_commit(&k_empty[kst]);
+      tc_commit_elect(&k_empty[kst], leader);
       if (++kst == kKVStages) kst = 0, kph ^= 1;
       for (int j = 0; j < nkv; ++j) {
         const bool has_next = (j + 1) < nkv;
@@ -230,15 +238,15 @@ __global__ void __launch_bounds__(kAttnThreads, 1)
           issue_pv(q, vst, j > 0);
           if (has_next) {
             issue_qk(q, kst);
-            tc_commit(&s_full[q]);
+            tc_commit_elect(&s_full[q], leader);
           } else {
-            tc_commit(&o_full[q]);
+            tc_commit_elect(&o_full[q], leader);
           }
         }
-        tc_commit(&v_empty[vst]);
+        tc_commit_elect(&v_empty[vst], leader);
         if (++vst == kKVStages) vst = 0, vph ^= 1;
         if (has_next) {
-          tc_commit(&k_empty[kst]);
+          tc_commit_elect(&k_empty[kst], leader);
           if (++kst == kKVStages) kst = 0, kph ^= 1;
         }
       }
@@ -259,7 +267,10 @@ __global__ void __launch_bounds__(kAttnThreads, 1)
     const float cs = p.scale_log2;
     float m_ref = 0.f;       // reference maximum (log2 units) the exponentials, the row sum and O currently use
     float run_max = -INFINITY;  // this thread's running maximum of raw scores over its columns, all tiles so far
-    float l = 0.f;
+    // four running maxima and four partial row sums live across the key tiles (folded only when published / at the
+    // end), so no per-tile reduction chain sits between the last exponential and the hand-over of P
+    float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+    float2 ls2[2] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
     bool ok = true;
     for (int j = 0; j < nkv; ++j) {
       if (!mbar_wait(&s_full[q], j & 1, abort_flag)) {
@@ -274,20 +285,20 @@ __global__ void __launch_bounds__(kAttnThreads, 1)
         tmem_ld32(t_s, s0);
         tmem_ld32(t_s + 32, s1);
         tc_wait_ld();
-        float mx = -INFINITY;
+        float m0 = -INFINITY;
 #pragma unroll
         for (int i = 0; i < 32; ++i) {
-          if (i < valid) mx = fmaxf(mx, __uint_as_float(s0[i]));
-          if (32 + i < valid) mx = fmaxf(mx, __uint_as_float(s1[i]));
+          if (i < valid) m0 = fmaxf(m0, __uint_as_float(s0[i]));
+          if (32 + i < valid) m0 = fmaxf(m0, __uint_as_float(s1[i]));
         }
-        run_max = mx;
-        xchg_publish(&slot_mine[0], 1u, mx);
+        run_max = m0;
+        xchg_publish(&slot_mine[0], 1u, m0);
         float mo;
         if (!xchg_read(&slot_other[0], 1u, &mo, abort_flag)) {
           ok = false;
           break;
         }
-        m_ref = fmaxf(mx, mo) * cs;  // at least one key of the tile is valid, so this is finite
+        m_ref = fmaxf(m0, mo) * cs;  // at least one key of the tile is valid, so this is finite
         float ls = 0.f;
         uint32_t pk[16];
 #pragma unroll
@@ -306,9 +317,12 @@ __global__ void __launch_bounds__(kAttnThreads, 1)
           pk[i] = pack_bf16x2(p0, p1);
         }
         tmem_st16(t_s + 16, pk);
-        l = ls;
+        ls2[0].x = ls;
+        mx[0] = m0;
       } else {
-        // pick up the partner's running maximum of the tiles before this one (published after the previous tile)
+        // first score chunk on its way from TMEM while the (already published) partner maximum is read
+        uint32_t sc[32];
+        tmem_ld32(t_s, sc);
         float mo;
         if (!xchg_read(&slot_other[(j - 1) & 1], static_cast<uint32_t>(j), &mo, abort_flag)) {
           ok = false;
@@ -321,7 +335,8 @@ __global__ void __launch_bounds__(kAttnThreads, 1)
           const float m_upd = fmaxf(m_ref, m_run);
           const float alpha = fast_exp2(m_ref - m_upd);
           m_ref = m_upd;
-          l *= alpha;
+          ls2[0].x *= alpha, ls2[0].y *= alpha, ls2[1].x *= alpha, ls2[1].y *= alpha;
+          tc_wait_ld();
 #pragma unroll 1
           for (int c = 0; c < 2; ++c) {
             uint32_t r[32];
@@ -332,24 +347,22 @@ __global__ void __launch_bounds__(kAttnThreads, 1)
             tmem_st32(t_o + c * 32, r);
           }
         }
-        float mx[4] = {run_max, run_max, run_max, run_max};
-        float ls[4] = {0.f, 0.f, 0.f, 0.f};
+        const float2 cs2 = make_float2(cs, cs), nm2 = make_float2(-m_ref, -m_ref);
 #pragma unroll
         for (int c = 0; c < 2; ++c) {
-          uint32_t sc[32];
-          tmem_ld32(t_s + c * 32, sc);
+          if (c == 1) tmem_ld32(t_s + 32, sc);
           tc_wait_ld();
           uint32_t pk[16];
           if (valid >= 64) {
 #pragma unroll
             for (int i = 0; i < 16; ++i) {
-              const float a0 = __uint_as_float(sc[2 * i]), a1 = __uint_as_float(sc[2 * i + 1]);
+              const float2 a = make_float2(__uint_as_float(sc[2 * i]), __uint_as_float(sc[2 * i + 1]));
+              const float2 x = __ffma2_rn(a, cs2, nm2);
               // the clamp only matters for rows whose scores jump by more than 2^100 from one key tile to the next
-              const float p0 = fast_exp2(fminf(fmaf(a0, cs, -m_ref), 100.f));
-              const float p1 = fast_exp2(fminf(fmaf(a1, cs, -m_ref), 100.f));
-              mx[i & 3] = fmaxf(mx[i & 3], fmaxf(a0, a1));
-              ls[i & 3] += p0 + p1;
-              pk[i] = pack_bf16x2(p0, p1);
+              const float2 pp = make_float2(fast_exp2(fminf(x.x, 100.f)), fast_exp2(fminf(x.y, 100.f)));
+              mx[i & 3] = max3f(mx[i & 3], a.x, a.y);
+              ls2[i & 1] = __fadd2_rn(ls2[i & 1], pp);
+              pk[i] = pack_bf16x2(pp.x, pp.y);
             }
           } else {
 #pragma unroll
@@ -360,24 +373,27 @@ __global__ void __launch_bounds__(kAttnThreads, 1)
               const float p1 = (c0 + 1 < valid) ? fast_exp2(fminf(fmaf(a1, cs, -m_ref), 100.f)) : 0.f;
               if (c0 < valid) mx[i & 3] = fmaxf(mx[i & 3], a0);
               if (c0 + 1 < valid) mx[i & 3] = fmaxf(mx[i & 3], a1);
-              ls[i & 3] += p0 + p1;
+              ls2[i & 1].x += p0;
+              ls2[i & 1].y += p1;
               pk[i] = pack_bf16x2(p0, p1);
             }
           }
           tmem_st16(t_s + c * 16, pk);
         }
-        run_max = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
-        l += (ls[0] + ls[1]) + (ls[2] + ls[3]);
       }
       tc_wait_st();
       tc_fence_before();
       mbar_arrive(&p_full[q]);
       // off the critical path: publish my running maximum for the partner to use at the next tile (slot by tile
       // parity: the partner cannot be two tiles ahead, S_q(j+2) needs this thread's P_q(j+1))
-      if (j > 0) xchg_publish(&slot_mine[j & 1], static_cast<uint32_t>(j + 1), run_max);
+      if (j > 0) {
+        run_max = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
+        xchg_publish(&slot_mine[j & 1], static_cast<uint32_t>(j + 1), run_max);
+      }
     }
     if (ok && mbar_wait(&o_full[q], 0, abort_flag)) {
       tc_fence_after();
+      const float l = (ls2[0].x + ls2[0].y) + (ls2[1].x + ls2[1].y);
       xchg_publish(&slot_mine[2], 0x7fffffffu, l);
       float lo = 0.f;
       ok = xchg_read(&slot_other[2], 0x7fffffffu, &lo, abort_flag);
