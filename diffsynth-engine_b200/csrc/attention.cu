@@ -35,6 +35,7 @@ constexpr int kTileQ = 128;
 constexpr int kTileKV = 128;
 constexpr int kNQ = 2;
 constexpr int kKVStages = 2;
+constexpr int kRefresh = 1;  // the reference maximum is re-examined every kRefresh key tiles (power of two)
 constexpr int kTileBytes = 128 * 128 * 2;  // 32 KiB: one 128 x 128 bf16 tile as two 64-column halves
 constexpr int kHalfBytes = kTileBytes / 2;
 constexpr int kXchgSlots = 2 * 2 * 128 * 3;  // [q][half][row] x {running maximum (even tile, odd tile), row sum}
@@ -117,8 +118,9 @@ __global__ void __launch_bounds__(kAttnThreads, 1)
   uint64_t* v_full = k_empty + kKVStages;   // kKVStages
   uint64_t* v_empty = v_full + kKVStages;   // kKVStages
   uint64_t* s_full = v_empty + kKVStages;   // kNQ
-  uint64_t* p_full = s_full + kNQ;          // kNQ
-  uint64_t* o_full = p_full + kNQ;          // kNQ
+  uint64_t* p_full = s_full + kNQ;          // kNQ: P of the first 32 keys of both key halves is in TMEM
+  uint64_t* p_rest = p_full + kNQ;          // kNQ: ... and of the other 32
+  uint64_t* o_full = p_rest + kNQ;          // kNQ
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(o_full + kNQ);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   unsigned long long* xchg = reinterpret_cast<unsigned long long*>(reinterpret_cast<uint8_t*>(bars) + 256);
@@ -141,6 +143,7 @@ __global__ void __launch_bounds__(kAttnThreads, 1)
     for (int q = 0; q < kNQ; ++q) {
       mbar_init(&s_full[q], 1);
       mbar_init(&p_full[q], 256);
+      mbar_init(&p_rest[q], 256);
       mbar_init(&o_full[q], 1);
     }
     *abort_flag = 0;
@@ -205,15 +208,18 @@ __global__ void __launch_bounds__(kAttnThreads, 1)
           mma_ss_f16_elect(d, ad0 + off, bd0 + off, idesc_qk, kk > 0 ? 1u : 0u, leader);
         }
       };
-      auto issue_pv = [&](int q, int st, bool accumulate) {
+      // O_q += P_q V for the 16-key groups kk in {g, g+1, g+4, g+5}: g = 0 are the keys whose probabilities every
+      // softmax thread writes first (its first 32 of 64 columns), g = 2 the rest
+      auto issue_pv = [&](int q, int st, int g, bool accumulate) {
         const uint64_t bd0 = v_desc0 + static_cast<uint32_t>(st) * kTile16;
         const uint32_t d = tmem_base + 256 + q * 128;
         const uint32_t a = tmem_base + q * 128;
 #pragma unroll
-        for (int kk = 0; kk < 8; ++kk) {
+        for (int i = 0; i < 4; ++i) {
+          const int kk = g + (i & 1) + (i >> 1) * 4;
           // 16 keys per instruction = 16 rows of 128 bytes (2048 bytes = 128 units) further into the V tile
           // P of keys [0,64) lives in columns [0,32) of S_q, P of keys [64,128) in columns [64,96)
-          mma_ts_f16_elect(d, a + (kk >> 2) * 64 + (kk & 3) * 8, bd0 + kk * 128u, idesc_pv, (accumulate || kk > 0) ? 1u : 0u,
+          mma_ts_f16_elect(d, a + (kk >> 2) * 64 + (kk & 3) * 8, bd0 + kk * 128u, idesc_pv, (accumulate || i > 0) ? 1u : 0u,
                            leader);
         }
       };
@@ -233,9 +239,12 @@ __global__ void __launch_bounds__(kAttnThreads, 1)
         if (!mbar_wait(&v_full[vst], vph, abort_flag)) goto mma_done;
         if (has_next && !mbar_wait(&k_full[kst], kph, abort_flag)) goto mma_done;
         for (int q = 0; q < kNQ; ++q) {
-          if (!mbar_wait(&p_full[q], j & 1, abort_flag)) goto mma_done;
+          if (!mbar_wait_spin(&p_full[q], j & 1, abort_flag)) goto mma_done;
           tc_fence_after();
-          issue_pv(q, vst, j > 0);
+          issue_pv(q, vst, 0, j > 0);
+          if (!mbar_wait_spin(&p_rest[q], j & 1, abort_flag)) goto mma_done;
+          tc_fence_after();
+          issue_pv(q, vst, 2, true);
           if (has_next) {
             issue_qk(q, kst);
             tc_commit_elect(&s_full[q], leader);
@@ -279,6 +288,7 @@ __global__ void __launch_bounds__(kAttnThreads, 1)
       }
       tc_fence_after();
       const int valid = min(kTileKV, p.Sk - j * kTileKV) - half * 64;  // valid columns among my 64 (may be <= 0)
+      bool handed = false;  // p_full already signalled for this tile
       if (j == 0) {
         // first tile: the row maximum must be known before anything is exponentiated
         uint32_t s0[32], s1[32];
@@ -323,28 +333,32 @@ __global__ void __launch_bounds__(kAttnThreads, 1)
         // first score chunk on its way from TMEM while the (already published) partner maximum is read
         uint32_t sc[32];
         tmem_ld32(t_s, sc);
-        float mo;
-        if (!xchg_read(&slot_other[(j - 1) & 1], static_cast<uint32_t>(j), &mo, abort_flag)) {
-          ok = false;
-          break;
-        }
-        const float m_run = fmaxf(run_max, mo) * cs;
-        if (__any_sync(0xffffffffu, m_run > m_ref + 8.0f)) {
-          // both warps of these rows see the same values, so both take this branch.  O is idle: S_q(j) is only
-          // signalled after O_q += P_q(j-1) V has completed.
-          const float m_upd = fmaxf(m_ref, m_run);
-          const float alpha = fast_exp2(m_ref - m_upd);
-          m_ref = m_upd;
-          ls2[0].x *= alpha, ls2[0].y *= alpha, ls2[1].x *= alpha, ls2[1].y *= alpha;
-          tc_wait_ld();
-#pragma unroll 1
-          for (int c = 0; c < 2; ++c) {
-            uint32_t r[32];
-            tmem_ld32(t_o + c * 32, r);
+        if (kRefresh == 1 || (j & (kRefresh - 1)) == 1) {
+          // every kRefresh-th tile: is the reference maximum still close enough to the running maximum of the row?
+          // (the partner published its running maximum after tile j-1)
+          float mo;
+          if (!xchg_read(&slot_other[((j - 1) / kRefresh) & 1], static_cast<uint32_t>(j), &mo, abort_flag)) {
+            ok = false;
+            break;
+          }
+          const float m_run = fmaxf(run_max, mo) * cs;
+          if (__any_sync(0xffffffffu, m_run > m_ref + 8.0f)) {
+            // both warps of these rows see the same values, so both take this branch.  O is idle: S_q(j) is only
+            // signalled after O_q += P_q(j-1) V has completed.
+            const float m_upd = fmaxf(m_ref, m_run);
+            const float alpha = fast_exp2(m_ref - m_upd);
+            m_ref = m_upd;
+            ls2[0].x *= alpha, ls2[0].y *= alpha, ls2[1].x *= alpha, ls2[1].y *= alpha;
             tc_wait_ld();
+#pragma unroll 1
+            for (int c = 0; c < 2; ++c) {
+              uint32_t r[32];
+              tmem_ld32(t_o + c * 32, r);
+              tc_wait_ld();
 #pragma unroll
-            for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
-            tmem_st32(t_o + c * 32, r);
+              for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
+              tmem_st32(t_o + c * 32, r);
+            }
           }
         }
         const float2 cs2 = make_float2(cs, cs), nm2 = make_float2(-m_ref, -m_ref);
@@ -356,6 +370,13 @@ __global__ void __launch_bounds__(kAttnThreads, 1)
           if (valid >= 64) {
 #pragma unroll
             for (int i = 0; i < 16; ++i) {
+              if (c == 1 && i == 8) {
+                // the first chunk's P store has had half a chunk of arithmetic to land: hand the first 32 keys over
+                tc_wait_st();
+                tc_fence_before();
+                mbar_arrive(&p_full[q]);
+                handed = true;
+              }
               const float2 a = make_float2(__uint_as_float(sc[2 * i]), __uint_as_float(sc[2 * i + 1]));
               const float2 x = __ffma2_rn(a, cs2, nm2);
               // the clamp only matters for rows whose scores jump by more than 2^100 from one key tile to the next
@@ -383,12 +404,13 @@ __global__ void __launch_bounds__(kAttnThreads, 1)
       }
       tc_wait_st();
       tc_fence_before();
-      mbar_arrive(&p_full[q]);
+      if (!handed) mbar_arrive(&p_full[q]);
+      mbar_arrive(&p_rest[q]);
       // off the critical path: publish my running maximum for the partner to use at the next tile (slot by tile
       // parity: the partner cannot be two tiles ahead, S_q(j+2) needs this thread's P_q(j+1))
-      if (j > 0) {
+      if (j > 0 && (j & (kRefresh - 1)) == 0) {
         run_max = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
-        xchg_publish(&slot_mine[j & 1], static_cast<uint32_t>(j + 1), run_max);
+        xchg_publish(&slot_mine[(j / kRefresh) & 1], static_cast<uint32_t>(j + 1), run_max);
       }
     }
     if (ok && mbar_wait(&o_full[q], 0, abort_flag)) {

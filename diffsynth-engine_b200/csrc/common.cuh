@@ -93,6 +93,38 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
   return true;
 }
 
+// Latency-critical variant: polls with the non-suspending test_wait, so the waiter notices the phase flip within a
+// few cycles instead of after try_wait's suspend window (measured in the attention kernel: ~285 cycles from the last
+// arrival to the waiter's next instruction with try_wait).  Only for a warp that has nothing else to run.
+__device__ __forceinline__ uint32_t mbar_test_wait(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n"
+      " .reg .pred p;\n"
+      " mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+      " selp.u32 %0, 1, 0, p;\n"
+      "}\n"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok;
+}
+__device__ __forceinline__ bool mbar_wait_spin(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
+  if (mbar_test_wait(bar, parity)) return true;
+  const long long t0 = clock64();
+  uint32_t spins = 0;
+  while (!mbar_test_wait(bar, parity)) {
+    if (((++spins) & 0x3ffu) == 0) {
+      if (*abort_flag) return false;
+      if (clock64() - t0 > kWaitLimitCycles) {
+        *abort_flag = 1;
+        return false;
+      }
+    }
+  }
+  return true;
+}
+
 // --------------------------------------------------------------------- TMA
 // Plain (non-multicast) tiled loads only: each CTA fetches its own tiles.
 __device__ __forceinline__ void tma_prefetch_desc(const CUtensorMap* m) {
