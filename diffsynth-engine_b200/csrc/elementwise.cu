@@ -465,6 +465,59 @@ __global__ void __launch_bounds__(256) dequant_q8_0_kernel(const uint16_t* __res
   }
 }
 
+// ---------------------------------------------------------- dequant_q4_k
+// GGUF Q4_K -> bf16: super-blocks of 256 weights in 144 bytes (fp16 d, fp16 dmin, 12 bytes of eight 6-bit scales and
+// eight 6-bit mins, 128 bytes of 4-bit quants).  One thread per sub-block of 32 weights.  The arithmetic repeats the
+// reference's bf16 evaluation order: (bf16(d) * sc) rounded, (bf16(dmin) * m) rounded, (that * q) rounded, minus.
+__device__ __forceinline__ float rbf(float v) { return __bfloat162float(__float2bfloat16_rn(v)); }
+
+__global__ void __launch_bounds__(256) dequant_q4_k_kernel(const uint8_t* __restrict__ raw, int64_t row_bytes,
+                                                           __nv_bfloat16* __restrict__ out, int64_t ld_out, int N,
+                                                           int subs_per_row) {
+  const int64_t total = static_cast<int64_t>(N) * subs_per_row;
+  for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < total;
+       i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const int64_t n = i / subs_per_row;
+    const int sb = static_cast<int>(i - n * subs_per_row);  // sub-block inside the row
+    const int j = sb & 7;
+    const uint8_t* blk = raw + n * row_bytes + static_cast<int64_t>(sb >> 3) * 144;
+    const uint4 head = __ldg(reinterpret_cast<const uint4*>(blk));  // d, dmin, 12 scale bytes
+    const __half_raw hd = {static_cast<unsigned short>(head.x & 0xffffu)};
+    const __half_raw hm = {static_cast<unsigned short>(head.x >> 16)};
+    const float d = rbf(__half2float(*reinterpret_cast<const __half*>(&hd)));
+    const float dmin = rbf(__half2float(*reinterpret_cast<const __half*>(&hm)));
+    const uint32_t w[3] = {head.y, head.z, head.w};
+    auto sbyte = [&](int k) { return (w[k >> 2] >> ((k & 3) * 8)) & 0xffu; };
+    uint32_t sc, mn;
+    if (j < 4) {
+      sc = sbyte(j) & 63u;
+      mn = sbyte(j + 4) & 63u;
+    } else {
+      sc = (sbyte(j + 4) & 15u) | ((sbyte(j - 4) >> 6) << 4);
+      mn = (sbyte(j + 4) >> 4) | ((sbyte(j) >> 6) << 4);
+    }
+    const float dsc = rbf(d * static_cast<float>(sc));
+    const float dm = rbf(dmin * static_cast<float>(mn));
+    const uint4* qp = reinterpret_cast<const uint4*>(blk + 16 + (j >> 1) * 32);
+    const int shift = (j & 1) * 4;
+    uint4* dst = reinterpret_cast<uint4*>(out + n * ld_out + static_cast<int64_t>(sb) * 32);
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      const uint4 qv = __ldg(qp + h);
+      const uint32_t qw[4] = {qv.x, qv.y, qv.z, qv.w};
+      uint32_t o[8];
+#pragma unroll
+      for (int k = 0; k < 8; ++k) {
+        const uint32_t b0 = (qw[k >> 1] >> ((k & 1) * 16)) & 0xffu, b1 = (qw[k >> 1] >> ((k & 1) * 16 + 8)) & 0xffu;
+        const float q0 = static_cast<float>((b0 >> shift) & 15u), q1 = static_cast<float>((b1 >> shift) & 15u);
+        o[k] = pack_bf16x2(rbf(dsc * q0) - dm, rbf(dsc * q1) - dm);
+      }
+      dst[2 * h] = make_uint4(o[0], o[1], o[2], o[3]);
+      dst[2 * h + 1] = make_uint4(o[4], o[5], o[6], o[7]);
+    }
+  }
+}
+
 // ------------------------------------------------------------------- gemv
 // y[n] = (sum_k W[n,k] * f(x[k])) * w_scale[n or 0] + bias[n].  The activation vector is staged once per CTA
 // in shared memory; each warp walks groups of four consecutive rows so that every 64-byte read of the
@@ -626,7 +679,6 @@ __global__ void timestep_embedding_kernel(const float* __restrict__ t, int n, in
 // ------------------------------------------------- CFG combine + euler step
 // model_out = neg + cfg * (pos - neg), then the flow-match Euler update, in one pass.  The bf16 form rounds where
 // the reference's tensor expression rounds (each elementwise op yields a bf16 tensor).
-__device__ __forceinline__ float rbf(float v) { return __bfloat162float(__float2bfloat16(v)); }
 __global__ void __launch_bounds__(256) cfg_euler_step_kernel(const __nv_bfloat16* __restrict__ latents,
                                                              const __nv_bfloat16* __restrict__ pos,
                                                              const __nv_bfloat16* __restrict__ neg, float cfg, float dt,
@@ -795,6 +847,21 @@ int dsb_dequant_q8_0(const void* blocks, int64_t row_bytes, int N, int K, void* 
   if (nblk > cap) nblk = cap;
   dequant_q8_0_kernel<<<nblk, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
       reinterpret_cast<const uint16_t*>(blocks), row_bytes / 2, reinterpret_cast<__nv_bfloat16*>(out), ld_out, N, bpr);
+  return cudaGetLastError() == cudaSuccess ? DSB_OK : DSB_ERR_CUDA;
+}
+
+int dsb_dequant_q4_k(const void* blocks, int64_t row_bytes, int N, int K, void* out, int64_t ld_out, void* stream) {
+  if (N < 0 || K <= 0 || (K & 255) || (row_bytes & 15) || row_bytes < static_cast<int64_t>(K / 256) * 144 || (ld_out & 7))
+    return DSB_ERR_ARG;
+  if (N == 0) return DSB_OK;
+  if (!blocks || !out || !aligned16(blocks) || !aligned16(out)) return DSB_ERR_ARG;
+  const int spr = K / 32;
+  const int64_t total = static_cast<int64_t>(N) * spr;
+  int nblk = static_cast<int>((total + 255) / 256);
+  const int cap = sm_count() * 16;
+  if (nblk > cap) nblk = cap;
+  dequant_q4_k_kernel<<<nblk, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      reinterpret_cast<const uint8_t*>(blocks), row_bytes, reinterpret_cast<__nv_bfloat16*>(out), ld_out, N, spr);
   return cudaGetLastError() == cudaSuccess ? DSB_OK : DSB_ERR_CUDA;
 }
 

@@ -167,6 +167,19 @@ def dequant_q8_0(raw, out=None):
     return out
 
 
+def dequant_q4_k(raw, out=None):
+    """GGUF Q4_K bytes ``[N, K/256*144]`` (uint8) -> bf16 ``[N, K]``."""
+    _require_cuda(raw, out)
+    if raw.dtype != torch.uint8 or raw.dim() != 2 or raw.stride(1) != 1 or raw.shape[1] % 144:
+        raise _lib.DsbError("dequant_q4_k takes uint8 rows of 144-byte super-blocks")
+    N, K = raw.shape[0], raw.shape[1] // 144 * 256
+    if out is None:
+        out = torch.empty((N, K), dtype=torch.bfloat16, device=raw.device)
+    rc = _lib.lib().dsb_dequant_q4_k(_ptr(raw), raw.stride(0), N, K, _ptr(out), out.stride(0), _stream())
+    check(rc, "dsb_dequant_q4_k")
+    return out
+
+
 def cast_quant(x, out, out_fmt=FMT_E4M3, split=False):
     """Saturating cast of bf16 ``x [M, D]`` into the 8-bit window ``out`` (may be a column slice): ``[M, D]``, or
     with ``split`` (e4m3) ``[M, 3D]`` = [head | remainder | head]."""

@@ -50,10 +50,16 @@ class QuantLinearWeight(nn.Parameter):
         return self._bias_f32[1]
 
 
-def _is_gguf_q8_0(weight) -> bool:
-    """A ``GGUFParameter`` (utils/gguf.py:9-59) holding Q8_0 blocks: raw uint8 rows plus a ``quant_dtype`` tag."""
+def _gguf_type(weight):
+    """"Q8_0" / "Q4_K" for a ``GGUFParameter`` (utils/gguf.py:9-59: raw uint8 rows plus a ``quant_dtype`` tag) of a
+    type this library dequantises itself, else None."""
     qd = getattr(weight, "quant_dtype", None)
-    return qd is not None and getattr(qd, "name", str(qd)) == "Q8_0"
+    name = None if qd is None else getattr(qd, "name", str(qd))
+    return name if name in ("Q8_0", "Q4_K") else None
+
+
+def _is_gguf_q8_0(weight) -> bool:
+    return _gguf_type(weight) == "Q8_0"
 
 
 def _raw_bytes(weight) -> torch.Tensor:
@@ -63,12 +69,13 @@ def _raw_bytes(weight) -> torch.Tensor:
 
 
 def _enable_b200_linear(module: nn.Module, fmt: str):
-    if isinstance(module, nn.Linear) and _is_gguf_q8_0(module.weight):
-        # GGUF Q8_0: dequantise ONCE, exactly as the reference does per call, then prepack like any other weight
+    if isinstance(module, nn.Linear) and _gguf_type(module.weight) is not None:
+        # GGUF Q8_0 / Q4_K: dequantise ONCE, exactly as the reference does per call, then prepack like any other weight
         raw = _raw_bytes(module.weight)
         if not raw.is_cuda:
             raise ops._lib.DsbError("enable_b200_linear: move the module to the GPU first (no CPU path exists)")
-        w = ops.dequant_q8_0(raw.reshape(raw.shape[0], -1).contiguous())
+        raw = raw.reshape(raw.shape[0], -1).contiguous()
+        w = ops.dequant_q8_0(raw) if _gguf_type(module.weight) == "Q8_0" else ops.dequant_q4_k(raw)
         if fmt == "bf16":
             payload, scale = w, None
         else:
@@ -94,7 +101,7 @@ def _enable_b200_linear(module: nn.Module, fmt: str):
 
 def enable_b200_linear(module: nn.Module, fmt: str = "fp8_tensor"):
     """Counterpart of ``enable_fp8_linear`` (utils/fp8_linear.py:7-17): prepack every floating ``nn.Linear``
-    weight below ``module`` and mark the module.  GGUF Q8_0 weights (``GGUFParameter``) are dequantised once on the
+    weight below ``module`` and mark the module.  GGUF Q8_0 and Q4_K weights (``GGUFParameter``) are dequantised once on the
     device (``fmt="bf16"`` keeps exactly the values the reference's ``gguf_linear`` multiplies with) and then take
     the same path, so they no longer depend on ``gguf_inference`` re-materialising them in every call."""
     if fmt not in FORMATS:

@@ -123,6 +123,13 @@ int dsb_quant_rows_chunked(const void* x, int64_t ld_x, int chunk_cols, int64_t 
 int dsb_dequant_q8_0(const void* blocks, int64_t row_bytes, int N, int K, void* out, int64_t ld_out, void* stream);
 
 /*
+ * GGUF Q4_K -> bf16, same role as dsb_dequant_q8_0: blocks [N, row_bytes] with K/256 super-blocks of 144 bytes per row
+ * (16-byte aligned rows), out bit-identical to dequantize_blocks_Q4_K with a bf16 compute dtype
+ * (utils/gguf.py:158-168,298-315), including its bf16 rounding after every product.  K % 256 == 0.
+ */
+int dsb_dequant_q4_k(const void* blocks, int64_t row_bytes, int N, int K, void* out, int64_t ld_out, void* stream);
+
+/*
  * y = saturating cast of bf16 x [M, ld_x] (D columns, D % 8 == 0) to e4m3 (round-to-nearest-even, +-448) or int8
  * (round-half-even, +-127), no scale: the values are already in operand units.  y may be a column window of a wider
  * 8-bit buffer (ld_y in elements, 8-byte aligned start).  split != 0 (e4m3 only) writes three windows of D columns,

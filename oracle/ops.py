@@ -148,6 +148,43 @@ def q8_0_dequantize(raw, dtype=torch.bfloat16):
     return (d * q).reshape(N, -1)
 
 
+def q4_k_random_blocks(N, K, seed):
+    """Well-formed random GGUF Q4_K bytes ``[N, K / 256 * 144]`` (test input only): per 256 weights an fp16 d, an fp16
+    dmin, 12 bytes holding eight 6-bit scales and eight 6-bit mins, and 128 bytes of 4-bit quants (ggml's layout)."""
+    g = torch.Generator().manual_seed(seed)
+    nb = N * (K // 256)
+    d = (torch.rand(nb, 1, generator=g) * 0.01 + 0.001).to(torch.float16).view(torch.uint8)
+    dmin = (torch.rand(nb, 1, generator=g) * 0.02).to(torch.float16).view(torch.uint8)
+    rest = torch.randint(0, 256, (nb, 12 + 128), generator=g, dtype=torch.uint8)
+    return torch.cat([d, dmin, rest], dim=1).reshape(N, (K // 256) * 144).contiguous()
+
+
+def q4_k_dequantize(raw, dtype=torch.bfloat16):
+    """``dequantize_blocks_Q4_K`` with ``get_scale_min`` (utils/gguf.py:158-168,298-315): sub-block j of 32 weights is
+    ``(d * sc_j) * q - (dmin * m_j)``, every product and the difference taken in ``dtype``.  Scales and mins are
+    6-bit: j < 4: sc = s[j] & 63, m = s[j+4] & 63; j >= 4: sc = (s[j+4] & 15) | ((s[j-4] >> 6) << 4),
+    m = (s[j+4] >> 4) | ((s[j] >> 6) << 4).  Quants: bytes [32g, 32g+32) carry sub-block 2g in their low and sub-block
+    2g+1 in their high nibbles."""
+    N = raw.shape[0]
+    blk = raw.reshape(-1, 144)
+    nb = blk.shape[0]
+    d = blk[:, 0:2].contiguous().view(torch.float16).to(dtype)
+    dmin = blk[:, 2:4].contiguous().view(torch.float16).to(dtype)
+    s = blk[:, 4:16].to(torch.int32)
+    sc = torch.empty(nb, 8, dtype=torch.int32)
+    mn = torch.empty(nb, 8, dtype=torch.int32)
+    for j in range(4):
+        sc[:, j] = s[:, j] & 63
+        mn[:, j] = s[:, j + 4] & 63
+        sc[:, j + 4] = (s[:, j + 8] & 15) | ((s[:, j] >> 6) << 4)
+        mn[:, j + 4] = (s[:, j + 8] >> 4) | ((s[:, j + 4] >> 6) << 4)
+    dsc = (d * sc.to(torch.uint8)).reshape(nb, 8, 1)
+    dm = (dmin * mn.to(torch.uint8)).reshape(nb, 8, 1)
+    qs = blk[:, 16:].reshape(nb, 4, 32)
+    q = torch.stack([qs & 0x0F, qs >> 4], dim=2).reshape(nb, 8, 32)
+    return (dsc * q - dm).reshape(N, -1)
+
+
 def linear_quant(x_q, x_s, W_q, W_s, bias=None):
     """Quantised Linear with fp32 accumulation: ((x_q W_q^T) * x_s[m] * W_s[n]) + bias.
     Dataflow of utils/fp8_linear.py:33-50 with scales added; products of e4m3 (or int8) values are exact in fp32

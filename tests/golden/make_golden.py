@@ -168,6 +168,14 @@ def main(ref_root):
     out["q8_0.dequant_f32"] = ref_gguf.dequantize(raw, quant_dtype=gguf_pkg.GGMLQuantizationType.Q8_0,
                                                   compute_dtype=torch.float32)
 
+    from oracle.ops import q4_k_random_blocks
+    raw4 = q4_k_random_blocks(6, 512, 68)
+    out["q4_k.raw"] = raw4
+    out["q4_k.dequant_bf16"] = ref_gguf.dequantize(raw4, quant_dtype=gguf_pkg.GGMLQuantizationType.Q4_K,
+                                                   compute_dtype=torch.bfloat16).float()
+    out["q4_k.dequant_f32"] = ref_gguf.dequantize(raw4, quant_dtype=gguf_pkg.GGMLQuantizationType.Q4_K,
+                                                  compute_dtype=torch.float32)
+
     # ---- the reference's FP8 Linear as shipped (unit scales) on a small case, for the drop-in patch
     lin = torch.nn.Linear(256, 128)
     lin.weight.copy_(synth.randn((128, 256), 30) * 0.5)

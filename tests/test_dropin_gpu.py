@@ -147,3 +147,23 @@ def test_gguf_q8_0_dequantisation_and_linear(dsb, cuda_dev):
             y = lin(x.to(cuda_dev)).float().cpu()
         ref = LinearEval(fmt)(x.float(), ref_w.float(), bias)
         assert O.rel_l2(y, ref) < tol, fmt
+
+
+def test_gguf_q4_k_dequantisation_is_bit_exact(dsb, cuda_dev):
+    """Q4_K super-blocks -> bf16 on the device against the oracle's restatement of the reference's evaluation order
+    (itself pinned bit-exactly by a reference-generated fixture), and the Linear seam on such a weight."""
+    from oracle import ops as O
+    from diffsynth_engine_b200.quant import b200_inference, enable_b200_linear
+    raw = O.q4_k_random_blocks(70, 1024, 130)
+    ref_w = O.q4_k_dequantize(raw, torch.bfloat16)
+    got = dsb.ops.dequant_q4_k(raw.to(cuda_dev)).cpu()
+    assert torch.equal(got.view(torch.int16), ref_w.view(torch.int16))
+    lin = torch.nn.Linear(1024, 70, bias=False).to(cuda_dev).bfloat16()
+    p = _Q8Param(raw.to(cuda_dev))
+    p.quant_dtype = type("QT", (), {"name": "Q4_K"})()
+    lin.weight = p
+    enable_b200_linear(lin, "bf16")
+    x = torch.randn(40, 1024, generator=torch.Generator().manual_seed(3)).bfloat16()
+    with b200_inference():
+        y = lin(x.to(cuda_dev)).float().cpu()
+    assert O.rel_l2(y, x.float() @ ref_w.float().t()) < 3e-3

@@ -168,3 +168,10 @@ def test_q8_0_dequantisation_matches_reference():
     assert torch.equal(O.q8_0_dequantize(raw, torch.float32), G["q8_0.dequant_f32"])
     w = synth.randn((24, 128), 67) * 0.05
     assert O.rel_l2(G["q8_0.dequant_f32"], w) < 1e-2     # Q8_0 itself: 8-bit blocks of 32
+
+
+def test_q4_k_dequantisation_matches_reference():
+    raw = G["q4_k.raw"]
+    assert torch.equal(raw, O.q4_k_random_blocks(6, 512, 68))
+    assert torch.equal(O.q4_k_dequantize(raw, torch.bfloat16).float(), G["q4_k.dequant_bf16"])
+    assert torch.equal(O.q4_k_dequantize(raw, torch.float32), G["q4_k.dequant_f32"])

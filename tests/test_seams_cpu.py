@@ -145,8 +145,11 @@ def test_reference_gguf_parameter_is_recognised(dsb):
         assert tuple(p.shape) == (8, 64) and p.dtype == torch.bfloat16      # what the class reports
         assert quant._is_gguf_q8_0(p)
         assert tuple(quant._raw_bytes(p).shape) == (8, 68) and quant._raw_bytes(p).dtype == torch.uint8
-        q4 = GGUFParameter(raw, quant_dtype=gguf.GGMLQuantizationType.Q4_K, compute_dtype=torch.bfloat16)
-        assert not quant._is_gguf_q8_0(q4)
+        q4 = GGUFParameter(torch.zeros(8, 144, dtype=torch.uint8), quant_dtype=gguf.GGMLQuantizationType.Q4_K,
+                           compute_dtype=torch.bfloat16)
+        assert not quant._is_gguf_q8_0(q4) and quant._gguf_type(q4) == "Q4_K"
+        q6 = GGUFParameter(raw, quant_dtype=gguf.GGMLQuantizationType.Q6_K, compute_dtype=torch.bfloat16)
+        assert quant._gguf_type(q6) is None                                   # left to the reference's gguf_inference
         assert not quant._is_gguf_q8_0(torch.nn.Parameter(torch.zeros(2, 2)))
     finally:
         if saved is None:
