@@ -154,11 +154,11 @@ def test_gguf_q4_k_dequantisation_is_bit_exact(dsb, cuda_dev):
     (itself pinned bit-exactly by a reference-generated fixture), and the Linear seam on such a weight."""
     from oracle import ops as O
     from diffsynth_engine_b200.quant import b200_inference, enable_b200_linear
-    raw = O.q4_k_random_blocks(70, 1024, 130)
+    raw = O.q4_k_random_blocks(72, 1024, 130)
     ref_w = O.q4_k_dequantize(raw, torch.bfloat16)
     got = dsb.ops.dequant_q4_k(raw.to(cuda_dev)).cpu()
     assert torch.equal(got.view(torch.int16), ref_w.view(torch.int16))
-    lin = torch.nn.Linear(1024, 70, bias=False).to(cuda_dev).bfloat16()
+    lin = torch.nn.Linear(1024, 72, bias=False).to(cuda_dev).bfloat16()
     p = _Q8Param(raw.to(cuda_dev))
     p.quant_dtype = type("QT", (), {"name": "Q4_K"})()
     lin.weight = p
