@@ -37,6 +37,17 @@ def flux_rope_table(ids: torch.Tensor, axes_dim=(16, 56, 56), theta=10000) -> to
     return torch.cat(cols, dim=1).float().contiguous()
 
 
+def sequence_slice(S_txt: int, S_img: int, world: int, rank: int) -> Dict[str, int]:
+    """This rank's contiguous slice of the joint [text | image] token sequence under sequence parallelism: the
+    sequence is padded to ``S_pad`` (a multiple of ``world``), rank r owns rows ``[g0, g0 + Sl)``; of its local rows
+    ``[0, t_loc)`` are text, ``[t_loc, n_loc)`` image and ``[n_loc, Sl)`` padding."""
+    S = S_txt + S_img
+    S_pad = (S + world - 1) // world * world
+    Sl = S_pad // world
+    g0 = rank * Sl
+    return dict(S=S, S_pad=S_pad, Sl=Sl, g0=g0, t_loc=min(max(S_txt - g0, 0), Sl), n_loc=min(max(S - g0, 0), Sl))
+
+
 class FluxDiTEngine:
     def __init__(self, state_dict: Dict[str, torch.Tensor], fmt: str = "fp8_tensor", device="cuda:0",
                  n_double: int = 19, n_single: int = 38, num_heads: int = 24, use_guidance: bool = True,
@@ -109,12 +120,8 @@ class FluxDiTEngine:
     def _alloc(self, S_txt: int, height: int, width: int, txt_dim: int, pooled_dim: int):
         d, dev, P = self.d, self.dev, self.P
         S_img = (height // 2) * (width // 2)
-        S = S_txt + S_img
-        S_pad = (S + P - 1) // P * P            # joint sequence padded so that every rank owns Sl rows
-        Sl = S_pad // P
-        g0 = self.rank * Sl                     # global index of this rank's first row
-        t_loc = min(max(S_txt - g0, 0), Sl)     # local rows [0, t_loc) are text, [t_loc, Sl) image (+ padding)
-        n_loc = min(max(S - g0, 0), Sl)         # local rows below n_loc exist in the unpadded sequence
+        sl = sequence_slice(S_txt, S_img, P, self.rank)
+        S, S_pad, Sl, g0, t_loc, n_loc = (sl[k] for k in ("S", "S_pad", "Sl", "g0", "t_loc", "n_loc"))
         qdt = {ops.FMT_BF16: torch.bfloat16, ops.FMT_E4M3: torch.float8_e4m3fn, ops.FMT_INT8: torch.int8}[self.afmt]
         bf = torch.bfloat16
         C = d // P

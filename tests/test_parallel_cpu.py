@@ -92,3 +92,23 @@ def test_split_and_get_matches_reference_contract():
     assert s["a"].tolist() == [[4, 5], [6, 7]] and s["b"][0].shape == (1, 1) and s["b"][1] == "keep" and s["c"] == 3
     with pytest.raises(ValueError, match="batch split failed"):
         split_and_get(torch.zeros(1, 3), 2, 0)
+
+
+def test_joint_sequence_slices_cover_every_token_once():
+    """The text+image split of the sequence-parallel MMDiT step: for every group size the ranks' text and image rows
+    tile the unpadded sequence exactly, padding only at the end of the last ranks."""
+    flux = __import__("importlib").import_module("diffsynth_engine_b200.flux")
+    for S_txt, S_img in ((256, 6889), (512, 4096), (41, 84), (72, 54), (8, 64), (1, 1), (5, 0)):
+        for world in (1, 2, 3, 4, 8):
+            text_rows, image_rows, pad = [], [], 0
+            for rank in range(world):
+                sl = flux.sequence_slice(S_txt, S_img, world, rank)
+                assert sl["S_pad"] % world == 0 and 0 <= sl["S_pad"] - sl["S"] < world
+                assert 0 <= sl["t_loc"] <= sl["n_loc"] <= sl["Sl"]
+                g0 = sl["g0"]
+                text_rows += list(range(g0, g0 + sl["t_loc"]))
+                image_rows += list(range(g0 + sl["t_loc"], g0 + sl["n_loc"]))
+                pad += sl["Sl"] - sl["n_loc"]
+            assert text_rows == list(range(S_txt))
+            assert image_rows == list(range(S_txt, S_txt + S_img))
+            assert pad == sl["S_pad"] - sl["S"]
