@@ -13,7 +13,6 @@ The optional 2-way "CFG/batch parallel" of the reference (parallel.py:105-109,12
 ``batch_parallelism = 2`` the batch dimension of every tensor input is split over two groups of ``sp_degree`` ranks
 and the two results are gathered in order.
 """
-import copy
 import datetime
 import os
 import time
@@ -68,6 +67,48 @@ def flux_engine_factory(state_dict, rank, sp_group, device, **engine_kwargs):
     return FluxDiTEngine(state_dict, device=device, group=sp_group, **engine_kwargs)
 
 
+def _share_step_inputs(kwargs, rank: int, dev):
+    """Rank 0 hands one step's keyword arguments to every rank.  The reference pickles the whole dict, tensors
+    included, through ``broadcast_object_list`` every step (utils/parallel.py:112-116); here only the structure is
+    pickled (names, shapes, dtypes, non-tensor values) and each tensor leaf travels as one collective broadcast on the
+    workers' device (NCCL on GPUs, gloo on CPU ranks).  Returns the dict with tensors on ``dev`` (or TERMINATE)."""
+    leaves = []
+
+    def strip(v):
+        if isinstance(v, dict):
+            return {k: strip(x) for k, x in v.items()}
+        if isinstance(v, (tuple, list)):
+            return [strip(x) for x in v]
+        if isinstance(v, torch.Tensor):
+            leaves.append(v)
+            return ("__tensor__", len(leaves) - 1, tuple(v.shape), v.dtype)
+        return v
+
+    def fill(v):
+        if isinstance(v, dict):
+            return {k: fill(x) for k, x in v.items()}
+        if isinstance(v, tuple) and len(v) == 4 and v[0] == "__tensor__":
+            return leaves[v[1]]
+        if isinstance(v, list):
+            return [fill(x) for x in v]
+        return v
+
+    meta = [strip(kwargs) if rank == 0 else None, None]
+    if rank == 0:
+        meta[1] = [(tuple(t.shape), t.dtype) for t in leaves]
+    dist.broadcast_object_list(meta, src=0)
+    skeleton, specs = meta
+    if isinstance(skeleton, str) and skeleton == TERMINATE:
+        return TERMINATE
+    if rank == 0:
+        leaves = [t.to(dev).contiguous() for t in leaves]
+    else:
+        leaves = [torch.empty(shape, dtype=dtype, device=dev) for shape, dtype in specs]
+    for t in leaves:
+        dist.broadcast(t, src=0)
+    return fill(skeleton)
+
+
 def _worker_loop(rank: int, world_size: int, conn, payload, factory: Callable, sp_degree: int, batch_parallelism: int,
                  master_port: int, device: str, backend: str, timeout_s: float, engine_kwargs: dict):
     model = None
@@ -91,12 +132,9 @@ def _worker_loop(rank: int, world_size: int, conn, payload, factory: Callable, s
         if rank == 0:
             conn.send(("READY", None))
         while True:
-            data = [conn.recv() if rank == 0 else None]
-            dist.broadcast_object_list(data, src=0)
-            kwargs = data[0]
+            kwargs = _share_step_inputs(conn.recv() if rank == 0 else None, rank, dev)
             if isinstance(kwargs, str) and kwargs == TERMINATE:
                 break
-            kwargs = to_device(copy.deepcopy(kwargs), dev)
             kwargs = split_and_get(kwargs, batch_parallelism, bp_row)
             with torch.no_grad():
                 result = model(**kwargs)

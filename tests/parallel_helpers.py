@@ -46,3 +46,23 @@ class SliceAttentionModel:
 
 def slice_attention_factory(payload, rank, group, device):
     return SliceAttentionModel(payload, rank, group, device)
+
+
+class EchoModel:
+    """Returns a checksum of everything it was given: checks that nested keyword arguments (lists of tensors,
+    dtypes, plain Python values) reach every rank intact."""
+
+    def __init__(self, payload, rank, group, device):
+        import torch.distributed as dist
+        self.dist, self.group = dist, group
+
+    def __call__(self, x, extras, flag=None, scale=1.0):
+        acc = x.double().sum() * scale + sum(t.double().sum() for t in extras["list"]) + extras["k"]
+        acc = acc + (1000.0 if flag == "on" else 0.0) + (1.0 if extras["list"][1].dtype == torch.int64 else 0.0)
+        t = torch.tensor([[float(acc)]], dtype=torch.float64)
+        self.dist.all_reduce(t, group=self.group)      # every rank must have computed the same number
+        return t / self.dist.get_world_size(self.group)
+
+
+def echo_factory(payload, rank, group, device):
+    return EchoModel(payload, rank, group, device)

@@ -57,6 +57,21 @@ def test_batch_parallel_split_and_ordered_gather():
         model.close()
 
 
+def test_step_inputs_reach_every_rank_with_structure_and_dtypes():
+    """Per step only the structure of the keyword arguments is pickled; every tensor leaf is broadcast as a tensor.
+    Nested containers, integer tensors and non-tensor values must arrive unchanged on all ranks."""
+    from tests.parallel_helpers import echo_factory
+    model = UlyssesParallelModel({}, sp_degree=3, batch_parallelism=1, master_port=_port(), device="cpu", timeout_s=60,
+                                 factory=echo_factory)
+    try:
+        x = torch.arange(12, dtype=torch.float32).reshape(1, 3, 4)
+        extras = {"list": [torch.ones(2, 2, dtype=torch.bfloat16), torch.tensor([[5, 6]], dtype=torch.int64)], "k": 7}
+        out = model(x=x, extras=extras, flag="on", scale=2.0)
+        assert float(out) == 66.0 * 2 + 4 + 11 + 7 + 1000 + 1
+    finally:
+        model.close()
+
+
 def test_worker_exception_reaches_the_parent():
     q, k, v = _qkv(1, 8, 2, 3)
     model = UlyssesParallelModel({"num_heads": 2, "fail_rank": 1}, sp_degree=2, master_port=_port(), device="cpu",
