@@ -476,9 +476,10 @@ def main():
     roofline = {"kernel": "gemm_kernel<fp8> (256x256 CTA-pair tiles; 128x128 for the text stream)" if fp8
                 else "gemm_kernel<bf16>", "bound": "tensor",
                 "achieved": ach_tf, "peak": peak_tf, "unit": "TFLOP/s", "frac": ach_tf / peak_tf,
-                # DRAM read+write bytes per GEMM launch: ncu capture of the 1+1-block case scaled by the block counts
+                # DRAM read+write bytes per GEMM launch: ncu capture of the 1+1-block case scaled by the block counts to the
+                # step's 30.8 GB of GEMM traffic, over this step's GEMM launches
                 # (the ncu summary of per-kernel DRAM traffic under profiles/); only meaningful for the full 19+38-block FP8 model
-                "traffic": (30.8e9 / 231 if (fp8 and not args.blocks and args.workload != "qwen" and not sp) else None),
+                "traffic": (30.8e9 / max(1, len(recs)) if (fp8 and not args.blocks and args.workload != "qwen" and not sp) else None),
                 "peak_source": (f"2 x bf16_tflops of MEASURED_PEAKS.json ({peaks['source']}); no FP8 peak was measured"
                                 if fp8 else f"bf16_tflops of MEASURED_PEAKS.json ({peaks['source']})"),
                 "launches_per_step": len(recs), "gemm_ms_per_step": gemm_ms,
