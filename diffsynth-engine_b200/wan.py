@@ -272,8 +272,23 @@ class WanDiTEngine:
         rope = b["rope"]
         proj = b["proj"]
         ao = b["ao"]
+        def context_kv(blk):
+            """Keys and values of the cross-attention (wan_dit.py:143-145,148-149) from the quantised context."""
+            cq_t, cs_t = cq_[txt_rows], (None if cs_ is None else cs_[txt_rows])
+            ck_t, cv_t = b["ck"][txt_rows], b["cv"][txt_rows]
+            self._gemm(cq_t, cs_t, blk["ck"], out=ck_t)
+            ops.rmsnorm_full(ck_t, blk["cnk"], None, 0, self.eps)
+            self._gemm(cq_t, cs_t, blk["cv"], out=cv_t)
+            if n_img:
+                cq_i, cs_i = cq_[:n_img], (None if cs_ is None else cs_[:n_img])
+                ck_i, cv_i = b["ck"][:n_img], b["cv"][:n_img]
+                self._gemm(cq_i, cs_i, blk["ck_img"], out=ck_i)
+                ops.rmsnorm_full(ck_i, blk["cnk_img"], None, 0, self.eps)
+                self._gemm(cq_i, cs_i, blk["cv_img"], out=cv_i)
+
         for li, blk in enumerate(self.blocks):
             m = b["modall"][li]
+            kv_done = False
             # ---- self-attention (wan_dit.py:101-107) with the head exchange around it
             a, sc = self._ln(x, m[0], m[1], xq_d, rs[:Sl])
             if P == 1:
@@ -302,6 +317,10 @@ class WanDiTEngine:
                 q4, k4, v4 = (recv[i].view(1, S, Hl, 128) for i in range(3))
                 ops.flash_attn(q4, k4, v4, out=ao.view(1, S, Hl, 128))
                 e3 = self._exchange(ao, b["ao_back"])
+                # the cross-attention keys/values depend on the context only: they run while the attention output
+                # travels back
+                context_kv(blk)
+                kv_done = True
                 if e3 is not None:
                     cur.wait_event(e3)
                 att3 = b["ao_back"]
@@ -317,19 +336,13 @@ class WanDiTEngine:
             a, sc = self._ln(x, blk["n3_shift"], blk["n3_scale"], xq_d, rs[:Sl])
             self._gemm(a, sc, blk["cq"], out=proj[0])
             ops.rmsnorm_full(proj[0], blk["cnq"], None, 0, self.eps)
-            cq_t, cs_t = cq_[txt_rows], (None if cs_ is None else cs_[txt_rows])
+            if not kv_done:
+                context_kv(blk)
             ck_t, cv_t = b["ck"][txt_rows], b["cv"][txt_rows]
-            self._gemm(cq_t, cs_t, blk["ck"], out=ck_t)
-            ops.rmsnorm_full(ck_t, blk["cnk"], None, 0, self.eps)
-            self._gemm(cq_t, cs_t, blk["cv"], out=cv_t)
             ops.flash_attn(proj[0].view(1, Sl, H, 128), ck_t.view(1, L, H, 128), cv_t.view(1, L, H, 128),
                            out=proj[1].view(1, Sl, H, 128))
             if n_img:   # the CLIP tokens have their own k/v projection; the two attention outputs add (wan_dit.py:147-151)
-                cq_i, cs_i = cq_[:n_img], (None if cs_ is None else cs_[:n_img])
                 ck_i, cv_i = b["ck"][:n_img], b["cv"][:n_img]
-                self._gemm(cq_i, cs_i, blk["ck_img"], out=ck_i)
-                ops.rmsnorm_full(ck_i, blk["cnk_img"], None, 0, self.eps)
-                self._gemm(cq_i, cs_i, blk["cv_img"], out=cv_i)
                 ops.flash_attn(proj[0].view(1, Sl, H, 128), ck_i.view(1, n_img, H, 128), cv_i.view(1, n_img, H, 128),
                                out=proj[2].view(1, Sl, H, 128))
                 ops.gate_residual(proj[1], proj[2], None, out=proj[1])         # bf16(x + y)
