@@ -57,7 +57,8 @@ class GemmArgs(ctypes.Structure):
                 ("row_scale", c_p), ("col_scale", c_p), ("col_scale_stride", c_i), ("bias", c_p), ("act", c_i),
                 ("act_col0", c_i), ("gate", c_p), ("resid", c_p), ("ld_resid", c_i64), ("out0", c_p),
                 ("ld_out0", c_i64), ("out1", c_p), ("ld_out1", c_i64), ("split_col", c_i), ("nq_w", c_p),
-                ("nk_w", c_p), ("d_model", c_i), ("rope", c_p), ("rope_row0", c_i), ("norm_eps", c_f)]
+                ("nk_w", c_p), ("d_model", c_i), ("rope", c_p), ("rope_row0", c_i), ("norm_eps", c_f),
+                ("out0_fmt", c_i), ("out1_fmt", c_i)]
 
 
 _SIGS["dsb_gemm_group"] = [ctypes.POINTER(GemmArgs), c_i, c_i, c_p, c_p]

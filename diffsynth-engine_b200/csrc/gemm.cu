@@ -27,6 +27,12 @@ constexpr int kBlockM = 128;
 constexpr int kSlabBytes = 128;  // bytes of K per stage row (one swizzle row)
 constexpr int kGemmThreads = 320;  // TMA warp, MMA warp, 8 epilogue warps
 
+__device__ __forceinline__ uint32_t pack_e4m3x4_sat(float a, float b, float c, float d) {
+  const __nv_fp8x2_storage_t lo = __nv_cvt_float2_to_fp8x2(make_float2(a, b), __NV_SATFINITE, __NV_E4M3);
+  const __nv_fp8x2_storage_t hi = __nv_cvt_float2_to_fp8x2(make_float2(c, d), __NV_SATFINITE, __NV_E4M3);
+  return static_cast<uint32_t>(lo) | (static_cast<uint32_t>(hi) << 16);
+}
+
 struct GemmEpilogue {
   const float* row_scale;
   const float* col_scale;
@@ -45,6 +51,9 @@ struct GemmEpilogue {
   int rope_row0;
   int d_model;
   float norm_eps;
+  // e4m3 output (unit scale, saturating) instead of bf16 for the first / second output range: the consumer GEMM then
+  // needs no row quantiser.  Only with 256-wide tiles: a warp's two 64-column blocks share one 128-byte staging row.
+  int out0_e4m3, out1_e4m3;
 };
 
 struct alignas(64) GemmProblem {
@@ -278,6 +287,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
       const float rs_t = (ep.col_scale && !ep.col_scale_stride) ? rs * __ldg(ep.col_scale) : rs;  // per-tensor scale folded in
       const bool second = n0 >= ep.split_col;
       const CUtensorMap* tmap_out = second ? &P.o1 : &P.o0;
+      const bool out8 = (BLOCK_N == 256) && (second ? ep.out1_e4m3 : ep.out0_e4m3);
       const int col_shift = second ? ep.split_col : 0;
       const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + acc * BLOCK_N;
       const float* head_w = head_col0 < ep.d_model ? ep.nq_w : ep.nk_w;
@@ -329,9 +339,13 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
       for (int cb = half * kBlocksPerWarp; cb < (half + 1) * kBlocksPerWarp && alive; ++cb) {
         const int nb = n0 + cb * 64;
         if (nb >= N) break;  // uniform across the warp
-        // this warp's previous store must have read the staging slot out
-        if (lane == 0) bulk_wait_read<0>();
-        __syncwarp();
+        // this warp's previous store must have read the staging slot out (an e4m3 tile fills the slot with both of
+        // the warp's blocks, 64 bytes per row each, before it is stored)
+        const int cb_local = cb - half * kBlocksPerWarp;
+        if (!(out8 && cb_local > 0)) {
+          if (lane == 0) bulk_wait_read<0>();
+          __syncwarp();
+        }
         // Tile-shaped epilogue input, fetched by TMA into this warp's staging slot (32 rows x 128 bytes, the slot the
         // output block is then written over cell by cell): the residual block, or for a normalised head the RoPE
         // factors of these rows - 32 pairs of fp16 (cos, sin) are the same 128 bytes per row as 64 bf16 outputs.
@@ -444,19 +458,34 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
                 }
               }
             }
-            uint4 o;
-            o.x = pack_bf16x2(v[0], v[1]);
-            o.y = pack_bf16x2(v[2], v[3]);
-            o.z = pack_bf16x2(v[4], v[5]);
-            o.w = pack_bf16x2(v[6], v[7]);
-            *reinterpret_cast<uint4*>(cell) = o;
+            if (out8) {
+              // eight e4m3 values = half a 16-byte chunk of the 128-byte row that holds the warp's 128 columns
+              uint8_t* cell8 = sbuf + row_off + (((static_cast<uint32_t>(cb_local * 4 + h * 2 + (g >> 1))) ^ sw) << 4) +
+                               (g & 1) * 8;
+              uint2 o8;
+              o8.x = pack_e4m3x4_sat(v[0], v[1], v[2], v[3]);
+              o8.y = pack_e4m3x4_sat(v[4], v[5], v[6], v[7]);
+              *reinterpret_cast<uint2*>(cell8) = o8;
+            } else {
+              uint4 o;
+              o.x = pack_bf16x2(v[0], v[1]);
+              o.y = pack_bf16x2(v[2], v[3]);
+              o.z = pack_bf16x2(v[4], v[5]);
+              o.w = pack_bf16x2(v[6], v[7]);
+              *reinterpret_cast<uint4*>(cell) = o;
+            }
           }
         }
         fence_proxy_async();
         __syncwarp();
         if (lane == 0) {
-          tma_store_2d(tmap_out, sbuf, nb - col_shift, r0);
-          bulk_commit();
+          if (!out8) {
+            tma_store_2d(tmap_out, sbuf, nb - col_shift, r0);
+            bulk_commit();
+          } else if (cb_local + 1 == kBlocksPerWarp || nb + 64 >= N) {
+            tma_store_2d(tmap_out, sbuf, n0 + half * 128 - col_shift, r0);
+            bulk_commit();
+          }
         }
       }
       tc_fence_before();
@@ -574,6 +603,11 @@ static int check_problem(const dsb_gemm_args& a, int fmt, int* status, GemmProbl
   if (!a.out1) split_col = INT32_MAX;
   else if (split_col < 0 || (split_col % 256) != 0) return DSB_ERR_ARG;
   if (a.gate && !a.resid) return DSB_ERR_ARG;
+  const bool o0_8 = a.out0_fmt == DSB_FMT_E4M3, o1_8 = a.out1 && a.out1_fmt == DSB_FMT_E4M3;
+  if ((a.out0_fmt != DSB_FMT_BF16 && !o0_8) || (a.out1 && a.out1_fmt != DSB_FMT_BF16 && !o1_8)) return DSB_ERR_ARG;
+  if ((o0_8 || o1_8) && a.resid) return DSB_ERR_ARG;                      // the residual form writes bf16
+  if (o0_8 && (a.nq_w || (a.ld_out0 & 15))) return DSB_ERR_ARG;           // normalised heads stay bf16
+  if (o1_8 && (a.ld_out1 & 15)) return DSB_ERR_ARG;
   if (a.resid && a.out1) return DSB_ERR_ARG;  // the residual form writes one output
   if (a.nq_w) {
     if (!a.nk_w || a.d_model <= 0 || (a.d_model % 128) || 2 * a.d_model > a.N || a.resid || !al16(a.nq_w) ||
@@ -597,15 +631,21 @@ static int check_problem(const dsb_gemm_args& a, int fmt, int* status, GemmProbl
   ep.rope_row0 = a.rope_row0;
   ep.d_model = a.d_model;
   ep.norm_eps = a.norm_eps;
+  ep.out0_e4m3 = o0_8 ? 1 : 0;
+  ep.out1_e4m3 = o1_8 ? 1 : 0;
   P->M = a.M, P->N = a.N, P->K = a.K;
   // bf16 output / residual tiles of 32 rows x 64 columns (128 bytes per row, 128-byte swizzle)
   const int n0cols = a.out1 ? (split_col < a.N ? split_col : a.N) : a.N;
-  if (make_tmap_2d(&P->o0, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, a.out0, a.M, n0cols, a.ld_out0 * 2, 32, 64) != DSB_OK)
+  // bf16 ranges: blocks of 32 rows x 64 columns; e4m3 ranges: 32 rows x 128 columns (128 bytes per row either way)
+  if ((o0_8 ? make_tmap_2d(&P->o0, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, a.out0, a.M, n0cols, a.ld_out0, 32, 128)
+            : make_tmap_2d(&P->o0, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, a.out0, a.M, n0cols, a.ld_out0 * 2, 32, 64)) !=
+      DSB_OK)
     return DSB_ERR_CUDA;
   P->o1 = P->o0;
   if (a.out1 && split_col < a.N &&
-      make_tmap_2d(&P->o1, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, a.out1, a.M, a.N - split_col, a.ld_out1 * 2, 32,
-                   64) != DSB_OK)
+      (o1_8 ? make_tmap_2d(&P->o1, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, a.out1, a.M, a.N - split_col, a.ld_out1, 32, 128)
+            : make_tmap_2d(&P->o1, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, a.out1, a.M, a.N - split_col, a.ld_out1 * 2, 32,
+                           64)) != DSB_OK)
     return DSB_ERR_CUDA;
   P->r = P->o0;
   if (a.resid &&
@@ -648,7 +688,9 @@ extern "C" int dsb_gemm_group(const dsb_gemm_args* args, int count, int fmt, int
   // one tile shape for the launch, chosen for the first (larger) problem; the fused norm needs a whole head per
   // epilogue warp, i.e. 256-wide tiles
   bool any_norm = false;
-  for (int i = 0; i < grp.count; ++i) any_norm = any_norm || live[i]->nq_w != nullptr;
+  for (int i = 0; i < grp.count; ++i)
+    any_norm = any_norm || live[i]->nq_w != nullptr || live[i]->out0_fmt == DSB_FMT_E4M3 ||
+               (live[i]->out1 && live[i]->out1_fmt == DSB_FMT_E4M3);  // both need a warp's full 128 columns
   const int bn = any_norm ? 256 : pick_block_n(live[0]->M, live[0]->N);
   const bool pair = pair_mode_enabled() && bn == 256 && live[0]->M > 256 && live[0]->N >= 256;
   for (int i = 0; i < grp.count; ++i) {

@@ -226,6 +226,9 @@ class FluxDiTEngine:
             self._gemm(a, s, self.x_emb, out=x[rows])
 
         rope = b["rope_h"]
+        # FP8 weights: the post-GELU activations (and, in single blocks, the attention output) feed their Linear as
+        # e4m3 with unit scale, the reference's own activation rule, written by the producing kernel's epilogue
+        unit8 = self.afmt == ops.FMT_E4M3
         attn_o = cat[:, :d]                      # attention output lands in the first d columns of `cat`
         q4 = qkv[:, :d].unflatten(1, (H, 128)).unsqueeze(0)
         k4 = qkv[:, d:2 * d].unflatten(1, (H, 128)).unsqueeze(0)
@@ -264,9 +267,14 @@ class FluxDiTEngine:
                             pl(blk["out_b"], txt, a, sc, gate=mt[2 * d:3 * d], resid=x[txt], out=x[txt])])
             a, sc = self._ln(x, mt[3 * d:4 * d], mt[4 * d:5 * d], xq_d, rs, split_row=t_loc, shift_b=mi[3 * d:4 * d],
                              scale_b=mi[4 * d:5 * d])
-            ops.gemm_group([pl(blk["ff0_a"], img, a, sc, act=ops.ACT_GELU_TANH, out=hid_all[img]),
-                            pl(blk["ff0_b"], txt, a, sc, act=ops.ACT_GELU_TANH, out=hid_all[txt])])
-            a, sc = self._quant(hid_all, hidq_all, rs)
+            if unit8:   # GELU(hidden) leaves the epilogue as e4m3 with unit scale: no row quantiser before FF2
+                ops.gemm_group([pl(blk["ff0_a"], img, a, sc, act=ops.ACT_GELU_TANH, out=hidq_all[img]),
+                                pl(blk["ff0_b"], txt, a, sc, act=ops.ACT_GELU_TANH, out=hidq_all[txt])])
+                a, sc = hidq_all, None
+            else:
+                ops.gemm_group([pl(blk["ff0_a"], img, a, sc, act=ops.ACT_GELU_TANH, out=hid_all[img]),
+                                pl(blk["ff0_b"], txt, a, sc, act=ops.ACT_GELU_TANH, out=hid_all[txt])])
+                a, sc = self._quant(hid_all, hidq_all, rs)
             ops.gemm_group([pl(blk["ff2_a"], img, a, sc, gate=mi[5 * d:6 * d], resid=x[img], out=x[img]),
                             pl(blk["ff2_b"], txt, a, sc, gate=mt[5 * d:6 * d], resid=x[txt], out=x[txt])])
         for blk in self.single:
@@ -274,12 +282,17 @@ class FluxDiTEngine:
             off += 3 * d
             a, sc = self._ln(x, m[:d], m[d:2 * d], xq_d, rs)
             p = blk["qkv_mlp"]
-            ops.gemm_qkv(a, p.w, blk["nq"], blk["nk"], d, rope, g0, 1e-6, row_scale=sc, col_scale=p.scale, bias=p.bias,
-                         act=ops.ACT_GELU_TANH, act_col0=3 * d, out=qkv, out1=cat[:, d:], split_col=3 * d)
+            ops.gemm_group([dict(a=a, w=p.w, row_scale=sc, col_scale=p.scale, bias=p.bias, nq_w=blk["nq"], nk_w=blk["nk"],
+                                 d_model=d, rope=rope, rope_row0=g0, act=ops.ACT_GELU_TANH, act_col0=3 * d, out=qkv,
+                                 out1=(catq if unit8 else cat)[:, d:], split_col=3 * d)])
             self._attention(q4, k4, v4, o4)
             if P > 1:   # bring the returned [P][Sl][d/P] layout back to rows next to gelu(mlp)
                 attn_o.copy_(b["ao_back"].permute(1, 0, 2).reshape(Sl, d))
-            a, sc = self._quant(cat, catq, rs)
+            if unit8:   # gelu(mlp) is already e4m3 (unit scale) in catq; the attention output joins it by a plain cast
+                ops.cast_quant(attn_o, catq[:, :d], ops.FMT_E4M3)
+                a, sc = catq, None
+            else:
+                a, sc = self._quant(cat, catq, rs)
             self._gemm(a, sc, blk["proj"], gate=m[2 * d:3 * d], resid=x, out=x)
         # final AdaLN (scale first, flux_dit.py:333) + projection; all local rows, the image rows are picked below
         m = mv[off:off + 2 * d]
@@ -364,7 +377,10 @@ class FluxDiTEngine:
 
     def kernel_launches_per_step(self) -> int:
         """Launches of this library's kernels in one step (the count of the dataflow above)."""
-        dbl = 2 + 4 + 1 + (2 if self.afmt != ops.FMT_BF16 else 0)   # 2 LN, 4 grouped GEMMs, attention, 2 quantisers
+        # double: 2 LN, 4 grouped GEMMs, attention, row quantisers (attention output; GELU output unless it leaves the
+        # GEMM as e4m3); single: LN, 2 GEMMs, attention, one quantiser or cast
+        nq = {ops.FMT_BF16: 0, ops.FMT_E4M3: 1, ops.FMT_INT8: 2}[self.afmt]
+        dbl = 2 + 4 + 1 + nq
         sgl = 3 + (1 if self.afmt != ops.FMT_BF16 else 0) + 1
         pre = 1 + (6 if self.use_guidance else 4) + 1 + 2 + (2 if self.afmt != ops.FMT_BF16 else 0)
         return pre + self.n_double * dbl + self.n_single * sgl + 2

@@ -293,7 +293,8 @@ def gemm_qkv(a, w, nq_w, nk_w, d_model, rope=None, rope_row0=0, eps=1e-6, row_sc
 def gemm_group(problems):
     """``dsb_gemm_group``: one persistent launch for up to two GEMMs of one format.  Each problem is a dict with
     the keyword arguments of :func:`gemm` / :func:`gemm_qkv` (``a``, ``w``, ``out`` required; ``nq_w`` present
-    selects the fused QK-RMSNorm/RoPE epilogue).  Outputs must be preallocated."""
+    selects the fused QK-RMSNorm/RoPE epilogue).  Outputs must be preallocated; an output of dtype float8_e4m3fn is
+    written as the saturating e4m3 cast of the epilogue value (unit scale)."""
     if not 1 <= len(problems) <= 2:
         raise _lib.DsbError("gemm_group takes one or two problems")
     arr = (_lib.GemmArgs * len(problems))()
@@ -322,6 +323,9 @@ def gemm_group(problems):
         g.ld_resid = 0 if resid is None else resid.stride(0)
         g.out0, g.ld_out0 = out.data_ptr(), out.stride(0)
         g.ld_out1 = 0 if out1 is None else out1.stride(0)
+        # an e4m3 output tensor selects the unit-scale 8-bit epilogue for that column range
+        g.out0_fmt = FMT_E4M3 if out.dtype == torch.float8_e4m3fn else FMT_BF16
+        g.out1_fmt = FMT_E4M3 if (out1 is not None and out1.dtype == torch.float8_e4m3fn) else FMT_BF16
         g.split_col = N if pr.get("split_col") is None else pr["split_col"]
         g.d_model, g.rope_row0, g.norm_eps = pr.get("d_model", 0), pr.get("rope_row0", 0), float(pr.get("eps", 1e-6))
     rc = _lib.lib().dsb_gemm_group(arr, len(problems), fmt, _ptr(status_word(problems[0]["a"].device)), _stream())

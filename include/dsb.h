@@ -234,6 +234,11 @@ typedef struct dsb_gemm_args {
   int split_col;
   const float* nq_w; const float* nk_w; int d_model;
   const void* rope; /* fp16 (cos, sin) table, see dsb_gemm_qkv */ int rope_row0; float norm_eps;
+  /* DSB_FMT_BF16 (0) or DSB_FMT_E4M3: out0 / out1 written as e4m3 with unit scale (saturating cast of the fp32
+   * epilogue value; ld in elements = bytes, multiple of 16), which is the reference's own activation rule
+   * (utils/fp8_linear.py:35), so that the Linear consuming it needs no row quantiser.  Not with resid; normalised
+   * head columns (nq_w) stay bf16. */
+  int out0_fmt, out1_fmt;
 } dsb_gemm_args;
 
 /*

@@ -11,6 +11,9 @@ from . import ops as O
 from .linear import LinearEval
 
 
+UNIT_SCALE = True   # see LinearEval.unit_scale_acts (False restores per-row scales everywhere, for comparison)
+
+
 def _ident(x):
     return x
 
@@ -60,8 +63,11 @@ def double_block(xa, xb, temb, table, w, pre, H, lin: LinearEval, rt=_ident):
     def tail(x, att_x, g_msa, sh_mlp, sc_mlp, g_mlp, s):
         x = rt(x.float() + g_msa * lin(att_x, w[pre + f"attn.{s}_to_out.weight"], w[pre + f"attn.{s}_to_out.bias"]))
         n = O.ln_modulate(x, sh_mlp, sc_mlp)
-        hid = rt(O.gelu_tanh(lin(n, w[pre + f"ff_{s}.0.weight"], w[pre + f"ff_{s}.0.bias"])))
-        return rt(x + g_mlp * lin(hid, w[pre + f"ff_{s}.2.weight"], w[pre + f"ff_{s}.2.bias"]))
+        hid = O.gelu_tanh(lin(n, w[pre + f"ff_{s}.0.weight"], w[pre + f"ff_{s}.0.bias"]))
+        if not getattr(lin, "unit_scale_acts", False) or not UNIT_SCALE:
+            hid = rt(hid)    # otherwise the projection's epilogue emits e4m3 straight from its fp32 values
+        return rt(x + g_mlp * lin(hid, w[pre + f"ff_{s}.2.weight"], w[pre + f"ff_{s}.2.bias"],
+                                  act_quant="unit" if UNIT_SCALE else True))
     xa = tail(xa, att_a, g_msa_a, sh_mlp_a, sc_mlp_a, g_mlp_a, "a")
     xb = tail(xb, att_b, g_msa_b, sh_mlp_b, sc_mlp_b, g_mlp_b, "b")
     return xa, xb
@@ -75,9 +81,12 @@ def single_block(x, temb, table, w, pre, H, lin: LinearEval, rt=_ident):
     shift, scale, gate = emb.chunk(3)  # transformer_helper.py:32-36
     n = O.ln_modulate(x, shift, scale)
     h = lin(n, w[pre + "to_qkv_mlp.weight"], w[pre + "to_qkv_mlp.bias"])
-    qkv, mlp = rt(h[:, :3 * d]), rt(O.gelu_tanh(h[:, 3 * d:]))
+    qkv, mlp = rt(h[:, :3 * d]), O.gelu_tanh(h[:, 3 * d:])
+    if not getattr(lin, "unit_scale_acts", False) or not UNIT_SCALE:
+        mlp = rt(mlp)
     att = joint_attention(None, qkv, w, pre, H, table, rt)
-    out = lin(torch.cat([att, mlp], dim=1), w[pre + "proj_out.weight"], w[pre + "proj_out.bias"])
+    out = lin(torch.cat([att, mlp], dim=1), w[pre + "proj_out.weight"], w[pre + "proj_out.bias"],
+              act_quant="unit" if UNIT_SCALE else True)
     return rt(x.float() + gate * out)
 
 

@@ -27,7 +27,15 @@ class LinearEval:
             self._cache[key] = O.quant_weight(W, self.mode)
         return self._cache[key]
 
+    @property
+    def unit_scale_acts(self):
+        """FP8 weights: the post-GELU hidden and (single blocks) the attention output reach their Linear as e4m3 with
+        unit scale - the reference's own activation rule (utils/fp8_linear.py:35) - because the producing kernels
+        emit e4m3 directly; a per-row scale would need the finished row."""
+        return self.mode in ("fp8_tensor", "fp8_channel")
+
     def __call__(self, x, W, b=None, act_quant=True):
+        """``act_quant``: True = per-row dynamic scale, False = fp32 activations, "unit" = e4m3 cast with scale 1."""
         x = x.float()
         if self.mode == "fp32":
             y = x @ W.float().t()
@@ -36,7 +44,10 @@ class LinearEval:
         else:
             q, s = self._wq(W)
             sd = s if s.numel() == 1 else s[:, None]
-            if act_quant:
+            if act_quant == "unit" and self.unit_scale_acts:
+                xq = x.clamp(-448, 448).to(torch.float8_e4m3fn)
+                y = O.linear_quant(xq, torch.ones(x.shape[0]), q, s)
+            elif act_quant:
                 xq, xs = (O.quant_rows_int8 if self.mode == "int8_channel" else O.quant_rows_e4m3)(x.bfloat16())
                 y = O.linear_quant(xq, xs, q, s)
             else:

@@ -385,3 +385,35 @@ def test_gemm_qkv_fused_norm_rope(dsb, cuda_dev, fmt, M, H):
     assert O.rel_l2(qkv.float().cpu(), ref_qkv) < 4e-3
     assert O.rel_l2(cat[:, d:].float().cpu(), ref_mlp) < 4e-3
     assert float(cat[:, :d].abs().max()) == 0.0
+
+
+@pytest.mark.parametrize("M,N,K", [(300, 512, 256), (1000, 1280, 384), (129, 264, 128)])
+def test_gemm_e4m3_output_is_the_cast_of_the_epilogue_value(dsb, cuda_dev, M, N, K):
+    """An e4m3 output range: GELU(acc * scales + bias) cast to e4m3 with unit scale (saturating).  Next to a bf16 first
+    range (split output) and alone; N = 264 leaves the second 64-column block of the last warp pair out of range."""
+    g = _gen(55)
+    x = _bf(torch.randn(M, K, generator=g))
+    W = torch.randn(N, K, generator=g) * 0.05
+    b = torch.randn(N, generator=g) * 0.1
+    xq, xs = O.quant_rows_e4m3(x)
+    wq, ws = O.quant_weight(W, "fp8_tensor")
+    acc = O.linear_quant(xq, xs, wq, ws, b)
+    to = lambda t: t.to(cuda_dev)
+    # alone
+    out8 = torch.zeros(M, (N + 15) // 16 * 16, dtype=torch.float8_e4m3fn, device=cuda_dev)[:, :N]   # row pitch % 16 == 0
+    dsb.ops.gemm_group([dict(a=to(xq), w=to(wq), row_scale=to(xs), col_scale=to(ws), bias=to(b),
+                             act=dsb.ops.ACT_GELU_TANH, out=out8)])
+    ref = O.gelu_tanh(acc)
+    got = out8.float().cpu()
+    # e4m3 of nearly equal fp32 values: identical except where the two sides' fp32 values straddle a rounding boundary
+    close = (got - ref.clamp(-448, 448).to(torch.float8_e4m3fn).float()).abs() <= 0.0626 * ref.abs() + 2e-3
+    assert close.float().mean() > 0.999 and O.rel_l2(got, ref) < 4e-2
+    if N % 256 == 0:
+        split = (N // 512) * 256
+        o0 = torch.zeros(M, split, dtype=torch.bfloat16, device=cuda_dev)
+        o1 = torch.zeros(M, N - split, dtype=torch.float8_e4m3fn, device=cuda_dev)
+        dsb.ops.gemm_group([dict(a=to(xq), w=to(wq), row_scale=to(xs), col_scale=to(ws), bias=to(b),
+                                 act=dsb.ops.ACT_GELU_TANH, act_col0=split, out=o0, out1=o1, split_col=split)])
+        assert O.rel_l2(o0.float().cpu(), acc[:, :split]) < 4e-3
+        assert torch.equal(o1.view(torch.uint8).cpu(), out8[:, split:].contiguous().view(torch.uint8).cpu())
+    dsb.ops.check_status(0)
