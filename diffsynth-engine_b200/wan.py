@@ -155,14 +155,16 @@ class WanDiTEngine:
         b["headmod"] = torch.zeros(2, d, dtype=f32, device=dev)
         b["patches"] = torch.zeros(Sl, self.patch.in_features, dtype=bf, device=dev)
         b["x"] = torch.zeros(Sl, d, dtype=bf, device=dev)
-        b["xq"] = torch.zeros(Sl, max(d, ffn), dtype=qdt, device=dev)
+        b["xq"] = torch.zeros(Sl, d if self.afmt == ops.FMT_E4M3 else max(d, ffn), dtype=qdt, device=dev)
         b["rs"] = torch.zeros(max(Sl, ctx_len, IMG_TOKENS), dtype=f32, device=dev)
         b["proj"] = torch.zeros(3, Sl, d, dtype=bf, device=dev)              # q, k, v projections of the slice
         b["send"] = torch.zeros(3, P, Sl, C, dtype=bf, device=dev) if P > 1 else None
         b["recv"] = torch.zeros(3, P, Sl, C, dtype=bf, device=dev) if P > 1 else None
         b["ao"] = torch.zeros(P, Sl, C, dtype=bf, device=dev)                # attention out: [S, H/P*128]
         b["ao_back"] = torch.zeros(P, Sl, C, dtype=bf, device=dev) if P > 1 else None
-        b["hid"] = torch.zeros(Sl, ffn, dtype=bf, device=dev)
+        # FFN hidden: bf16 (then row-quantised into xq) - or, with FP8 weights, e4m3 written by the first FFN GEMM itself
+        # (its own buffer: that GEMM still reads its operand from xq)
+        b["hid"] = torch.zeros(Sl, ffn, dtype=qdt if self.afmt == ops.FMT_E4M3 else bf, device=dev)
         # context rows: [CLIP tokens (image-to-video only) | text tokens], as the reference concatenates them
         n_img = IMG_TOKENS if self.has_image else 0
         L_all = n_img + ctx_len
@@ -350,8 +352,17 @@ class WanDiTEngine:
             self._gemm(a, sc, blk["co"], resid=x, out=x)
             # ---- FFN (wan_dit.py:179-182,191-192)
             a, sc = self._ln(x, m[3], m[4], xq_d, rs[:Sl])
-            self._gemm(a, sc, blk["f0"], act=ops.ACT_GELU_TANH, out=b["hid"])
-            a, sc = self._quant(b["hid"], xq[:, :b["hid"].shape[1]], rs[:Sl])
+            if self.afmt == ops.FMT_E4M3:
+                # GELU(hidden) leaves the GEMM as e4m3 with unit scale (the reference's own activation rule,
+                # utils/fp8_linear.py:35): no row quantiser in front of the second FFN Linear
+                hq = b["hid"]
+                p0 = blk["f0"]
+                ops.gemm_group([dict(a=a, w=p0.w, row_scale=sc, col_scale=p0.scale, bias=p0.bias,
+                                     act=ops.ACT_GELU_TANH, out=hq)])
+                a, sc = hq, None
+            else:
+                self._gemm(a, sc, blk["f0"], act=ops.ACT_GELU_TANH, out=b["hid"])
+                a, sc = self._quant(b["hid"], xq[:, :b["hid"].shape[1]], rs[:Sl])
             self._gemm(a, sc, blk["f2"], gate=m[5], resid=x, out=x)
         # ---- head (wan_dit.py:234-237) and unpatchify (:307-317)
         hm = b["headmod"]

@@ -59,8 +59,10 @@ def wan_block(x, context, t_mod, table, w, pre, H, lin: LinearEval, rt=_ident, e
     x = rt(x + L(att, "cross_attn.o"))
     # FFN, wan_dit.py:179-182,191-192
     n2 = O.ln_modulate(x, sh_mlp, sc_mlp, eps)
-    hid = rt(O.gelu_tanh(L(n2, "ffn.0")))
-    return rt(x + g_mlp * L(hid, "ffn.2"))
+    hid = O.gelu_tanh(L(n2, "ffn.0"))
+    if getattr(lin, "unit_scale_acts", False):   # FP8 weights: the first FFN GEMM emits e4m3 (unit scale) directly
+        return rt(x + g_mlp * L(hid, "ffn.2", act_quant="unit"))
+    return rt(x + g_mlp * L(rt(hid), "ffn.2"))
 
 
 def patchify(x, w, lin):
