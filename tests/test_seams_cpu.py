@@ -156,3 +156,43 @@ def test_reference_gguf_parameter_is_recognised(dsb):
             sys.modules.pop("diffsynth_engine", None)
         else:
             sys.modules["diffsynth_engine"] = saved
+
+
+def test_entry_points_reject_bad_arguments_without_a_gpu(dsb):
+    """Every entry point validates its arguments before it touches CUDA and answers with DSB_ERR_ARG (-1) or
+    DSB_ERR_UNSUPPORTED (-4); none of these calls launches anything, so they run on a machine without a GPU."""
+    import ctypes
+    lib = dsb._lib.lib()
+    buf = (ctypes.c_char * 4096)()
+    p = ctypes.addressof(buf)
+    p16 = (p + 15) // 16 * 16
+    # Q8_0: K must be a multiple of 32, rows 2-byte aligned and long enough
+    assert lib.dsb_dequant_q8_0(p16, 68, 4, 48, p16, 64, None) == -1
+    assert lib.dsb_dequant_q8_0(p16, 33, 4, 64, p16, 64, None) == -1
+    assert lib.dsb_dequant_q8_0(p16, 34, 4, 64, p16, 64, None) == -1          # 64 weights need 68 bytes per row
+    assert lib.dsb_dequant_q8_0(None, 68, 0, 64, None, 64, None) == 0         # no rows: nothing to do
+    # Q4_K: K a multiple of 256, 16-byte aligned rows of 144-byte super-blocks
+    assert lib.dsb_dequant_q4_k(p16, 144, 2, 128, p16, 128, None) == -1
+    assert lib.dsb_dequant_q4_k(p16 + 8, 144, 2, 256, p16, 256, None) == -1
+    assert lib.dsb_dequant_q4_k(p16, 100, 2, 256, p16, 256, None) == -1
+    # cast: split form only for e4m3; widths in multiples of 8
+    assert lib.dsb_cast_quant(p16, 64, p16, 64, 4, 64, 2, 1, None) == -1
+    assert lib.dsb_cast_quant(p16, 64, p16, 64, 4, 60, 1, 0, None) == -1
+    # attention: head_dim 128 only, strides in multiples of 8 elements
+    st = [128 * 4, 128, 128 * 4 * 0 + 128] * 4
+    assert lib.dsb_flash_attn(p16, p16, p16, p16, 1, 1, 4, 4, 64, *st, 1.0, None, None) == -4
+    bad = list(st)
+    bad[1] = 12
+    assert lib.dsb_flash_attn(p16, p16, p16, p16, 1, 1, 4, 4, 128, *bad, 1.0, None, None) == -1
+    # GEMM group: 1 or 2 problems; e4m3 output cannot be combined with the residual form or a misaligned pitch
+    g = (dsb._lib.GemmArgs * 1)()
+    a = g[0]
+    a.A, a.lda, a.W, a.ldw, a.M, a.N, a.K = p16, 64, p16, 64, 8, 64, 64
+    a.out0, a.ld_out0, a.split_col = p16, 64, 64
+    assert lib.dsb_gemm_group(g, 3, 1, None, None) == -1
+    a.out0_fmt, a.resid, a.ld_resid = 1, p16, 64
+    assert lib.dsb_gemm_group(g, 1, 1, None, None) == -1
+    a.resid, a.ld_resid, a.ld_out0 = None, 0, 72
+    assert lib.dsb_gemm_group(g, 1, 1, None, None) == -1
+    a.out0_fmt, a.ld_out0, a.N = 0, 64, 60                                     # N must be a multiple of 8
+    assert lib.dsb_gemm_group(g, 1, 1, None, None) == -1
