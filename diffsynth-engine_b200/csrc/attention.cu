@@ -7,6 +7,8 @@
 //               (plain tiled loads, 128-byte swizzle, two 64-column halves)
 //   warp 1      MMA issuer:   S_q = Q_q K_j^T  (SS, both operands K-major)
 //                             O_q += P_q V_j   (TS: P read from TMEM, V MN-major)
+//               The whole warp runs the issue loop, so descriptors stay warp-uniform, and one elected lane issues;
+//               it polls the P barriers without suspending (a hand-over then costs a few cycles, not a wake-up).
 //   warps 4-11  softmax of query tile 0, two threads per query row: warps 4-7 own key columns [0,64) of the
 //               score tile, warps 8-11 own [64,128)
 //   warps 12-19 softmax of query tile 1, same split
@@ -14,6 +16,8 @@
 // 32 columns of packed bf16 probabilities written over the FIRST half of its own 64 score columns, so P_q sits in
 // columns [0,32) and [64,96) of S_q and no thread ever writes where another thread still has scores to read.
 // S_q(j+1) is issued only after O_q += P_q(j) V_j, and the two query tiles ping-pong on the tensor core.
+// P is handed over in two parts: the first 32 keys of each 64-key half as soon as their store has landed (a quarter
+// of the way into the second chunk's exponentials), the rest at the end, so half of P.V runs under the softmax.
 //
 // The exponentials use a REFERENCE maximum that is one tile stale: p = exp2(s*c - m_ref) with m_ref = the row's
 // maximum over all earlier key tiles.  Row sums and O carry the same reference, so the result is exact; entries of
