@@ -2,15 +2,16 @@
 //
 //   out[m,n] = epilogue( sum_k A[m,k] * W[n,k] )      A: [M,K], W: [N,K], K contiguous in both
 //
-// One CTA per SM walks output tiles of 128 x BLOCK_N.  Warp 0 feeds a ring of
-// shared-memory stages with plain TMA loads (128-byte swizzle, one 128-byte
-// K-slab per stage), warp 1 issues tcgen05.mma (M=128, N=BLOCK_N, 32 bytes of K
-// per instruction) into one of two TMEM accumulators, and warps 2..5 drain the
-// other accumulator with tcgen05.ld, apply the fused epilogue (dequant scales,
-// bias, GELU-tanh, gate-residual, output routing) and hand bf16 tiles of
-// 32 rows x 64 columns to TMA stores through a swizzled staging buffer, so every
-// global write (and every residual read, a TMA load into the same buffer) moves
-// whole 128-byte lines instead of 16 bytes per row.
+// One CTA per SM walks output tiles of 128 x BLOCK_N - or one CTA pair per two SMs tiles of 256 x 256 with one
+// cta_group::2 MMA, each CTA staging 128 rows of A and half of the W rows (no multicast).  Up to two problems
+// share a launch (their tile lists are concatenated).  Warp 0 feeds a ring of shared-memory stages with plain TMA
+// loads (128-byte swizzle, one 128-byte K-slab per stage), warp 1 issues tcgen05.mma (32 bytes of K per
+// instruction) into one of two TMEM accumulators, and eight epilogue warps (two per TMEM lane quadrant, half of the
+// tile's columns each) drain the other accumulator with tcgen05.ld and apply the fused epilogue: dequantisation
+// scales, bias, per-head RMSNorm + RoPE on q/k columns, GELU / SiLU, gate-residual, routing of column ranges to two
+// outputs.  Tiles of 32 rows x 128 bytes (64 bf16 columns, or 128 e4m3 columns for an 8-bit output range) go to TMA
+// stores through a swizzled staging slot per warp; per-row epilogue inputs - the residual block, the RoPE factors -
+// come into the same slot by TMA loads, so every global access of the epilogue moves whole 128-byte lines.
 //
 // HBM layout: A and W are row-major with K contiguous, so both operands are
 // "K-major" for the tensor core and no transpose or repack is ever needed; the
