@@ -55,15 +55,6 @@ struct AttnParams {
   int* status;
 };
 
-template <int N>
-__device__ __forceinline__ void reg_alloc() {
-  asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(N));
-}
-template <int N>
-__device__ __forceinline__ void reg_dealloc() {
-  asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(N));
-}
-
 // Hand-over of one float between the two threads of a query row: a 64-bit slot {sequence number, value} written with
 // one store; the reader spins (bounded) until the sequence number it expects is there.
 __device__ __forceinline__ void xchg_publish(unsigned long long* slot, uint32_t seq, float v) {
