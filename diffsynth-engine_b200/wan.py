@@ -136,15 +136,18 @@ class WanDiTEngine:
         d, dev, P = self.d, self.dev, self.P
         gh, gw = height // 2, width // 2
         S = frames * gh * gw
-        if S % P:
-            raise ValueError(f"{S} tokens do not split over {P} ranks (pad the grid)")
-        Sl = S // P
+        S_pad = (S + P - 1) // P * P     # a token count that does not split evenly is padded; the padded rows are
+        Sl = S_pad // P                  # ordinary rows whose results are dropped and that never act as keys
         ffn = self.blocks[0]["f0"].out_features if self.blocks else 4 * d
         qdt = {ops.FMT_BF16: torch.bfloat16, ops.FMT_E4M3: torch.float8_e4m3fn, ops.FMT_INT8: torch.int8}[self.afmt]
         bf, f32 = torch.bfloat16, torch.float32
         C = d // P
-        b = dict(S=S, Sl=Sl, grid=(frames, gh, gw), ctx_len=ctx_len, in_ch=self.patch.in_features // 4)
+        b = dict(S=S, S_pad=S_pad, Sl=Sl, grid=(frames, gh, gw), ctx_len=ctx_len, in_ch=self.patch.in_features // 4)
         b["rope"] = wan_rope_table(frames, gh, gw, device=dev)
+        if S_pad > S:   # identity rotation for the padded rows
+            pad = torch.zeros(S_pad - S, 64, 2, dtype=b["rope"].dtype, device=dev)
+            pad[..., 0] = 1.0
+            b["rope"] = torch.cat([b["rope"], pad]).contiguous()
         b["latents"] = torch.zeros(1, b["in_ch"], frames, height, width, dtype=bf, device=dev)
         b["context_in"] = torch.zeros(ctx_len, text_dim, dtype=bf, device=dev)
         b["t"] = torch.zeros(1, dtype=f32, device=dev)
@@ -177,7 +180,7 @@ class WanDiTEngine:
         if n_img:
             b["clip_in"] = torch.zeros(n_img, 1280, dtype=bf, device=dev)
         b["out_tok"] = torch.zeros(Sl, self.head.out_features, dtype=bf, device=dev)
-        b["out_all"] = torch.zeros(S, self.head.out_features, dtype=bf, device=dev) if P > 1 else None
+        b["out_all"] = torch.zeros(S_pad, self.head.out_features, dtype=bf, device=dev) if P > 1 else None
         self._bufs = b
         return self
 
@@ -267,7 +270,8 @@ class WanDiTEngine:
         fr, gh, gw = b["grid"]
         Cin = b["in_ch"]
         pat = (b["latents"][0].reshape(Cin, fr, gh, 2, gw, 2).permute(1, 2, 4, 0, 3, 5).reshape(S, Cin * 4))
-        b["patches"].copy_(pat[row0:row0 + Sl])
+        n_own = max(0, min(Sl, S - row0))            # rows of this rank that exist (the rest of the buffer stays zero)
+        b["patches"][:n_own].copy_(pat[row0:row0 + n_own])
         a, s = self._quant(b["patches"], xq[:, :Cin * 4], rs[:Sl])
         self._gemm(a, s, self.patch, out=x)
 
@@ -316,8 +320,10 @@ class WanDiTEngine:
                 for e in (e0, e1, e2):
                     if e is not None:
                         cur.wait_event(e)
-                q4, k4, v4 = (recv[i].view(1, S, Hl, 128) for i in range(3))
-                ops.flash_attn(q4, k4, v4, out=ao.view(1, S, Hl, 128))
+                S_pad = b["S_pad"]
+                q4 = recv[0].view(1, S_pad, Hl, 128)
+                k4, v4 = (recv[i].view(S_pad, Hl, 128)[:S].unsqueeze(0) for i in (1, 2))   # real tokens only as keys
+                ops.flash_attn(q4, k4, v4, out=ao.view(1, S_pad, Hl, 128))
                 e3 = self._exchange(ao, b["ao_back"])
                 # the cross-attention keys/values depend on the context only: they run while the attention output
                 # travels back
@@ -370,7 +376,7 @@ class WanDiTEngine:
         self._gemm(a, sc, self.head, out=b["out_tok"])
         if P > 1:
             self.xchg.dist.all_gather_into_tensor(b["out_all"], b["out_tok"], group=self.xchg.group)
-            tok = b["out_all"]
+            tok = b["out_all"][:S]
         else:
             tok = b["out_tok"]
         od = self.out_dim

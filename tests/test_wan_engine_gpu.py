@@ -136,3 +136,24 @@ def test_sequence_parallel_image_to_video_two_gpus_matches_one(dsb, cuda_dev):
     finally:
         model.close()
     assert O.rel_l2(out, ref) < 3e-3
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_sequence_parallel_pads_a_token_count_that_does_not_split(dsb, cuda_dev):
+    """3 x 7 x 5 = 105 tokens over two ranks: one padded row on the second rank, which must not act as a key and
+    whose output is dropped."""
+    os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+    from diffsynth_engine_b200.parallel import UlyssesParallelModel
+    from diffsynth_engine_b200.wan import WanDiTEngine
+    w, x, context, t = _case(seed=60, grid=(3, 14, 10))
+    dev = cuda_dev
+    one = WanDiTEngine(dict(w), fmt="fp8_channel", device=dev, num_layers=2, num_heads=H)
+    ref = one(x.to(dev), context.to(dev), t.to(dev)).float().cpu()
+    model = UlyssesParallelModel(dict(w), sp_degree=2, master_port=29645, device="cuda", timeout_s=120,
+                                 fmt="fp8_channel", num_layers=2, num_heads=H)
+    try:
+        out = model(x=x, context=context, timestep=t).float().cpu()
+    finally:
+        model.close()
+    assert out.shape == ref.shape
+    assert O.rel_l2(out, ref) < 3e-3
