@@ -239,6 +239,7 @@ def run_sweeps(torch, pkg, dev):
     gen = torch.Generator(device=dev).manual_seed(0)
 
     def timeit(fn, n=10, warm=3):
+        time.sleep(0.3)     # let the board leave its power cap: each case is timed as an isolated burst
         for _ in range(warm):
             fn()
         torch.cuda.synchronize()
