@@ -282,6 +282,32 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
         }
         __syncwarp();
       }
+      // Per-column epilogue parameters (bias, per-channel scale, gate, head-norm weight) of this warp's column range:
+      // lane l keeps kPer consecutive columns' values in registers, fetched once per tile before the accumulator is
+      // ready, and the 8-column groups below pick theirs up by warp shuffles.  (Loading them group by group, right
+      // where they are used, cost a serial L2 round trip per group: 20.8k cycles of epilogue per 256x256 tile
+      // against 16k of mainloop at K = 3072.)
+      constexpr int kWarpCols = BLOCK_N / 2, kPer = kWarpCols / 32;
+      const int wcol0 = n0 + half * kWarpCols;
+      float p_bias[kPer], p_cs[kPer], p_gate[kPer], p_hw[kPer];
+      {
+        const int c = wcol0 + lane * kPer;
+        const bool in = c < N;
+        const bool chan = ep.col_scale && ep.col_scale_stride;
+        const float* hw = (wcol0 < ep.d_model) ? ep.nq_w : ep.nk_w;
+#pragma unroll
+        for (int j = 0; j < kPer; ++j) {
+          p_bias[j] = (in && ep.bias) ? __ldg(ep.bias + c + j) : 0.f;
+          p_cs[j] = (in && chan) ? __ldg(ep.col_scale + c + j) : 1.f;
+          p_gate[j] = (in && ep.gate) ? __ldg(ep.gate + c + j) : 1.f;
+          p_hw[j] = (fuse_norm && hw) ? __ldg(hw + ((lane * kPer + j) & 127)) : 1.f;
+        }
+      }
+      // the 8 values of the column group that starts at column c8 (a multiple of 8) of the warp's range
+      auto pick8 = [&](const float (&mine)[kPer], int c8, float (&out)[8]) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) out[j] = __shfl_sync(0xffffffffu, mine[j % kPer], c8 / kPer + j / kPer);
+      };
       if (!mbar_wait(&tmem_full[acc], acc_phase, abort_flag)) break;
       tc_fence_after();
       const float rs = (ep.row_scale && m < M) ? ep.row_scale[m] : 1.0f;
@@ -291,7 +317,6 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
       const bool out8 = (BLOCK_N == 256) && (second ? ep.out1_e4m3 : ep.out0_e4m3);
       const int col_shift = second ? ep.split_col : 0;
       const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + acc * BLOCK_N;
-      const float* head_w = head_col0 < ep.d_model ? ep.nq_w : ep.nk_w;
       float rnorm = 1.0f;
       if (fuse_norm) {
         float ss = 0.f;
@@ -302,25 +327,11 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
           tc_wait_ld();
 #pragma unroll
           for (int g = 0; g < 4; ++g) {
-            const int n = head_col0 + c * 32 + g * 8;
             float cs8[8], b8[8];
-            if (ep.col_scale && ep.col_scale_stride) {
-              const float4 c0 = __ldg(reinterpret_cast<const float4*>(ep.col_scale + n));
-              const float4 c1 = __ldg(reinterpret_cast<const float4*>(ep.col_scale + n + 4));
-              cs8[0] = c0.x * rs, cs8[1] = c0.y * rs, cs8[2] = c0.z * rs, cs8[3] = c0.w * rs;
-              cs8[4] = c1.x * rs, cs8[5] = c1.y * rs, cs8[6] = c1.z * rs, cs8[7] = c1.w * rs;
-            } else {
+            pick8(p_cs, c * 32 + g * 8, cs8);
+            pick8(p_bias, c * 32 + g * 8, b8);
 #pragma unroll
-              for (int j = 0; j < 8; ++j) cs8[j] = rs_t;
-            }
-            if (ep.bias) {
-              const float4 b0 = __ldg(reinterpret_cast<const float4*>(ep.bias + n));
-              const float4 b1 = __ldg(reinterpret_cast<const float4*>(ep.bias + n + 4));
-              b8[0] = b0.x, b8[1] = b0.y, b8[2] = b0.z, b8[3] = b0.w, b8[4] = b1.x, b8[5] = b1.y, b8[6] = b1.z, b8[7] = b1.w;
-            } else {
-#pragma unroll
-              for (int j = 0; j < 8; ++j) b8[j] = 0.f;
-            }
+            for (int j = 0; j < 8; ++j) cs8[j] *= rs_t;   // rs_t = row scale x per-tensor scale (1 if per-channel)
 #pragma unroll
             for (int j = 0; j < 8; ++j) {
               float a;
@@ -384,32 +395,19 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
                 v[j] = __uint_as_float(r[g * 8 + j]);
             }
             if (n < N) {
-              if (ep.col_scale) {
-                if (ep.col_scale_stride) {
-                  const float4 c0 = __ldg(reinterpret_cast<const float4*>(ep.col_scale + n));
-                  const float4 c1 = __ldg(reinterpret_cast<const float4*>(ep.col_scale + n + 4));
-                  v[0] *= c0.x * rs, v[1] *= c0.y * rs, v[2] *= c0.z * rs, v[3] *= c0.w * rs;
-                  v[4] *= c1.x * rs, v[5] *= c1.y * rs, v[6] *= c1.z * rs, v[7] *= c1.w * rs;
-                } else {
+              const int c8 = cb_local * 64 + h * 32 + g * 8;   // first column of the group inside the warp's range
+              {
+                float cs8[8], b8[8];
+                pick8(p_cs, c8, cs8);
+                pick8(p_bias, c8, b8);
 #pragma unroll
-                  for (int j = 0; j < 8; ++j) v[j] *= rs_t;
-                }
-              } else if (ep.row_scale) {
-#pragma unroll
-                for (int j = 0; j < 8; ++j) v[j] *= rs;
-              }
-              if (ep.bias) {
-                const float4 b0 = __ldg(reinterpret_cast<const float4*>(ep.bias + n));
-                const float4 b1 = __ldg(reinterpret_cast<const float4*>(ep.bias + n + 4));
-                v[0] += b0.x, v[1] += b0.y, v[2] += b0.z, v[3] += b0.w;
-                v[4] += b1.x, v[5] += b1.y, v[6] += b1.z, v[7] += b1.w;
+                for (int j = 0; j < 8; ++j) v[j] = fmaf(v[j], cs8[j] * rs_t, b8[j]);
               }
               if (fuse_norm) {
-                const int ch = n - head_col0;  // column inside the head
-                const float4 w0 = __ldg(reinterpret_cast<const float4*>(head_w + ch));
-                const float4 w1 = __ldg(reinterpret_cast<const float4*>(head_w + ch + 4));
-                v[0] *= rnorm * w0.x, v[1] *= rnorm * w0.y, v[2] *= rnorm * w0.z, v[3] *= rnorm * w0.w;
-                v[4] *= rnorm * w1.x, v[5] *= rnorm * w1.y, v[6] *= rnorm * w1.z, v[7] *= rnorm * w1.w;
+                float w8[8];
+                pick8(p_hw, c8, w8);
+#pragma unroll
+                for (int j = 0; j < 8; ++j) v[j] *= rnorm * w8[j];
                 if (do_rope) {
                   const uint4 cs4 = *reinterpret_cast<const uint4*>(cell);  // (cos, sin) of the four pairs, fp16
                   const float2 f0 = __half22float2(*reinterpret_cast<const __half2*>(&cs4.x));
@@ -442,15 +440,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
                 const uint4 rr = *reinterpret_cast<const uint4*>(cell);
                 const uint32_t ru[4] = {rr.x, rr.y, rr.z, rr.w};
                 float gte[8];
-                if (ep.gate) {
-                  const float4 g0 = __ldg(reinterpret_cast<const float4*>(ep.gate + n));
-                  const float4 g1 = __ldg(reinterpret_cast<const float4*>(ep.gate + n + 4));
-                  gte[0] = g0.x, gte[1] = g0.y, gte[2] = g0.z, gte[3] = g0.w;
-                  gte[4] = g1.x, gte[5] = g1.y, gte[6] = g1.z, gte[7] = g1.w;
-                } else {
-#pragma unroll
-                  for (int j = 0; j < 8; ++j) gte[j] = 1.0f;
-                }
+                pick8(p_gate, c8, gte);
 #pragma unroll
                 for (int j = 0; j < 4; ++j) {
                   const float2 f = unpack_bf16x2(ru[j]);
