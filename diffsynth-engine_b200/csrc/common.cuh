@@ -327,6 +327,35 @@ __device__ __forceinline__ void mma_ss_cg2(uint32_t d_tmem, uint64_t adesc, uint
         : "memory");
   }
 }
+// The same two forms for an issue loop that the whole warp runs with one elected lane issuing (`leader` from
+// elect_one()), without the disable-output-lane operand.
+#define DSB_MMA_ELECT(CG, KINDSTR)                                                                              \
+  asm volatile("{\n .reg .pred p, q;\n setp.ne.b32 p, %4, 0;\n setp.ne.b32 q, %5, 0;\n"                         \
+               " @q tcgen05.mma.cta_group::" CG ".kind::" KINDSTR " [%0], %1, %2, %3, p;\n}\n" ::"r"(d_tmem),    \
+               "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(leader)                                 \
+               : "memory")
+template <int KIND, int CTAS>
+__device__ __forceinline__ void mma_ss_elect(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                             uint32_t accumulate, uint32_t leader) {
+  if constexpr (CTAS == 2) {
+    if constexpr (KIND == KIND_F16) DSB_MMA_ELECT("2", "f16");
+    else if constexpr (KIND == KIND_F8) DSB_MMA_ELECT("2", "f8f6f4");
+    else DSB_MMA_ELECT("2", "i8");
+  } else {
+    if constexpr (KIND == KIND_F16) DSB_MMA_ELECT("1", "f16");
+    else if constexpr (KIND == KIND_F8) DSB_MMA_ELECT("1", "f8f6f4");
+    else DSB_MMA_ELECT("1", "i8");
+  }
+}
+#undef DSB_MMA_ELECT
+__device__ __forceinline__ void tc_commit_cg2_elect(uint32_t cluster_addr, uint32_t leader) {
+  asm volatile(
+      "{\n .reg .pred q;\n setp.ne.b32 q, %1, 0;\n"
+      " @q tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];\n}\n" ::"r"(cluster_addr),
+      "r"(leader)
+      : "memory");
+}
+
 // D[tmem] (+)= A[tmem] * B[smem] (16-bit A, two elements per 32-bit TMEM column).
 __device__ __forceinline__ void mma_ts_f16(uint32_t d_tmem, uint32_t a_tmem, uint64_t bdesc, uint32_t idesc,
                                            uint32_t accumulate) {

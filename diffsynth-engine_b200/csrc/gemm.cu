@@ -193,7 +193,9 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
   producer_done:;
   } else if (warp == 1) {
     // -------------------------------------------------------------- MMA issuer
-    if (lane == 0 && leader) {
+    if (leader) {
+      // the whole warp runs the loop (descriptors stay warp-uniform); one elected lane issues
+      const uint32_t el = elect_one();
       int stage = 0;
       uint32_t phase = 0;
       int it = 0;
@@ -205,7 +207,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
         const uint32_t d_tmem = tmem_base + acc * BLOCK_N;
         const int num_kb = g.p[t >= tiles_first ? 1 : 0].num_kb;
         for (int kb = 0; kb < num_kb; ++kb) {
-          if (!mbar_wait(&full_bar[stage], phase, abort_flag)) goto mma_done;
+          if (!mbar_wait_spin(&full_bar[stage], phase, abort_flag)) goto mma_done;
           tc_fence_after();
           const uint32_t sa = smem_u32(smem + stage * SM::kStage);
           const uint64_t adesc = make_desc_k_sw128(sa);
@@ -213,16 +215,13 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
 #pragma unroll
           for (int k = 0; k < 4; ++k) {
             // advancing 32 bytes along K inside the swizzle row = +2 in the (addr >> 4) field
-            if constexpr (CTAS == 2)
-              mma_ss_cg2<KIND>(d_tmem, adesc + 2 * k, bdesc + 2 * k, kIdesc, (kb | k) != 0 ? 1u : 0u);
-            else
-              mma_ss<KIND>(d_tmem, adesc + 2 * k, bdesc + 2 * k, kIdesc, (kb | k) != 0 ? 1u : 0u);
+            mma_ss_elect<KIND, CTAS>(d_tmem, adesc + 2 * k, bdesc + 2 * k, kIdesc, (kb | k) != 0 ? 1u : 0u, el);
           }
           if constexpr (CTAS == 2) {  // the stage is free in both CTAs once these MMAs have read it
-            tc_commit_cg2(smem_u32(&empty_bar[stage]));
-            tc_commit_cg2(mapa_u32(smem_u32(&empty_bar[stage]), 1));
+            tc_commit_cg2_elect(smem_u32(&empty_bar[stage]), el);
+            tc_commit_cg2_elect(mapa_u32(smem_u32(&empty_bar[stage]), 1), el);
           } else {
-            tc_commit(&empty_bar[stage]);
+            tc_commit_elect(&empty_bar[stage], el);
           }
           if (++stage == kStages) {
             stage = 0;
@@ -230,10 +229,10 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
           }
         }
         if constexpr (CTAS == 2) {
-          tc_commit_cg2(smem_u32(&tmem_full[acc]));
-          tc_commit_cg2(mapa_u32(smem_u32(&tmem_full[acc]), 1));
+          tc_commit_cg2_elect(smem_u32(&tmem_full[acc]), el);
+          tc_commit_cg2_elect(mapa_u32(smem_u32(&tmem_full[acc]), 1), el);
         } else {
-          tc_commit(&tmem_full[acc]);
+          tc_commit_elect(&tmem_full[acc], el);
         }
       }
     }
