@@ -307,10 +307,11 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
 #pragma unroll
         for (int j = 0; j < 8; ++j) out[j] = __shfl_sync(0xffffffffu, mine[j % kPer], c8 / kPer + j / kPer);
       };
+      // the row's activation scale is fetched before the wait as well
+      const float rs = (ep.row_scale && m < M) ? __ldg(ep.row_scale + m) : 1.0f;
+      const float rs_t = (ep.col_scale && !ep.col_scale_stride) ? rs * __ldg(ep.col_scale) : rs;  // per-tensor scale folded in
       if (!mbar_wait(&tmem_full[acc], acc_phase, abort_flag)) break;
       tc_fence_after();
-      const float rs = (ep.row_scale && m < M) ? ep.row_scale[m] : 1.0f;
-      const float rs_t = (ep.col_scale && !ep.col_scale_stride) ? rs * __ldg(ep.col_scale) : rs;  // per-tensor scale folded in
       const bool second = n0 >= ep.split_col;
       const CUtensorMap* tmap_out = second ? &P.o1 : &P.o0;
       const bool out8 = (BLOCK_N == 256) && (second ? ep.out1_e4m3 : ep.out0_e4m3);
