@@ -439,12 +439,13 @@ __device__ __forceinline__ float fast_exp2(float x) {
 
 // ------------------------------------------------------------------- math
 __device__ __forceinline__ float gelu_tanh(float x) {
-  // 0.5 x (1 + tanh(sqrt(2/pi) (x + 0.044715 x^3)))
-  const float k0 = 0.7978845608028654f, k1 = 0.044715f;
-  float u = k0 * (x + k1 * x * x * x);
+  // 0.5 x (1 + tanh(sqrt(2/pi) (x + 0.044715 x^3))), arranged as six FP operations around the tanh
+  const float k0 = 0.7978845608028654f, k0k1 = 0.7978845608028654f * 0.044715f;
+  const float u = x * fmaf(k0k1, x * x, k0);
   float t;
   asm("tanh.approx.f32 %0, %1;" : "=f"(t) : "f"(u));  // relative error about 2^-11, below bf16 resolution
-  return 0.5f * x * (1.0f + t);
+  const float hx = 0.5f * x;
+  return fmaf(hx, t, hx);
 }
 __device__ __forceinline__ float silu(float x) { return x / (1.0f + __expf(-x)); }
 __device__ __forceinline__ float gelu_erf(float x) { return 0.5f * x * (1.0f + erff(x * 0.7071067811865476f)); }
