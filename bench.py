@@ -470,18 +470,20 @@ def main():
         eng._graph = eng._graph_saved
     gemm_flops = sum(r[0] for r in recs)
     gemm_ms = sum(r[1].elapsed_time(r[2]) for r in recs)
-    fp8 = args.fmt != "bf16"
+    fp8 = args.fmt != "bf16"          # any 8-bit weight format: the tensor pipe runs at twice the bf16 rate
+    int8 = args.fmt.startswith("int8")
+    kind = "int8" if int8 else "fp8"
     peak_tf = peaks["bf16"] * (2.0 if fp8 else 1.0)
     ach_tf = gemm_flops / (gemm_ms * 1e-3) / 1e12
     lin_f, attn_f = flux_step_flops(cfg)
-    roofline = {"kernel": "gemm_kernel<fp8> (256x256 CTA-pair tiles; 128x128 for the text stream)" if fp8
+    roofline = {"kernel": f"gemm_kernel<{kind}> (256x256 CTA-pair tiles; 128x128 for the text stream)" if fp8
                 else "gemm_kernel<bf16>", "bound": "tensor",
                 "achieved": ach_tf, "peak": peak_tf, "unit": "TFLOP/s", "frac": ach_tf / peak_tf,
                 # DRAM read+write bytes per GEMM launch: ncu capture of the 1+1-block case scaled by the block counts to the
                 # step's 30.8 GB of GEMM traffic, over this step's GEMM launches
                 # (the ncu summary of per-kernel DRAM traffic under profiles/); only meaningful for the full 19+38-block FP8 model
-                "traffic": (30.8e9 / max(1, len(recs)) if (fp8 and not args.blocks and args.workload != "qwen" and not sp) else None),
-                "peak_source": (f"2 x bf16_tflops of MEASURED_PEAKS.json ({peaks['source']}); no FP8 peak was measured"
+                "traffic": (30.8e9 / max(1, len(recs)) if (fp8 and not int8 and not args.blocks and args.workload != "qwen" and not sp) else None),
+                "peak_source": (f"2 x bf16_tflops of MEASURED_PEAKS.json ({peaks['source']}); no 8-bit peak was measured"
                                 if fp8 else f"bf16_tflops of MEASURED_PEAKS.json ({peaks['source']})"),
                 "launches_per_step": len(recs), "gemm_ms_per_step": gemm_ms,
                 "method": "CUDA events around each GEMM launch of one eager (un-graphed) step; 2MNK per launch",
@@ -491,7 +493,9 @@ def main():
     line = {"metric": "DiT denoise steps/s", "value": value, "unit": "steps/s", "n_gpus": world, "steps": args.steps,
             "warmup": max(3, args.warmup), "ms_per_step": ms_per_step, "higher_is_better": True,
             "scaling": "strong" if sp else "weak",
-            "vs_baseline": None, "dtype": "fp8_e4m3 x fp8_e4m3 -> fp32 (linear), bf16 (attention)" if fp8 else "bf16",
+            "vs_baseline": None,
+            "dtype": ("int8 x int8 -> int32 (linear), bf16 (attention)" if int8
+                      else "fp8_e4m3 x fp8_e4m3 -> fp32 (linear), bf16 (attention)" if fp8 else "bf16"),
             "data": "synthetic", "config": config, "clocks": clocks,
             "e2e": {"value": (1 if sp else world) * 1e3 / e2e_ms, "unit": "steps/s", "h2d_bytes_per_step": h2d,
                     "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms, "wall_ms_per_step": e2e_wall_ms},
