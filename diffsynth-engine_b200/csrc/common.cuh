@@ -125,6 +125,38 @@ __device__ __forceinline__ bool mbar_wait_spin(uint64_t* bar, uint32_t parity, v
   return true;
 }
 
+// Polling wait for a warp that shares its SM sub-partition with working warps: try_wait with a short suspend-time
+// hint (nanoseconds) parks the warp between polls, so it notices the phase flip within a few tens of cycles without
+// taking issue slots from its neighbours the way a test_wait spin does.
+__device__ __forceinline__ uint32_t mbar_try_wait_hint(uint64_t* bar, uint32_t parity, uint32_t ns) {
+  uint32_t ok;
+  asm volatile(
+      "{\n"
+      " .reg .pred p;\n"
+      " mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n"
+      " selp.u32 %0, 1, 0, p;\n"
+      "}\n"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity), "r"(ns)
+      : "memory");
+  return ok;
+}
+__device__ __forceinline__ bool mbar_wait_hint(uint64_t* bar, uint32_t parity, volatile int* abort_flag, uint32_t ns) {
+  if (mbar_test_wait(bar, parity)) return true;
+  const long long t0 = clock64();
+  uint32_t spins = 0;
+  while (!mbar_try_wait_hint(bar, parity, ns)) {
+    if (((++spins) & 0xffu) == 0) {
+      if (*abort_flag) return false;
+      if (clock64() - t0 > kWaitLimitCycles) {
+        *abort_flag = 1;
+        return false;
+      }
+    }
+  }
+  return true;
+}
+
 // --------------------------------------------------------------------- TMA
 // Plain (non-multicast) tiled loads only: each CTA fetches its own tiles.
 __device__ __forceinline__ void tma_prefetch_desc(const CUtensorMap* m) {
@@ -411,6 +443,16 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
       : "r"(taddr)
       : "memory");
 }
+// 16 consecutive fp32 columns of this thread's TMEM lane.
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr)
+      : "memory");
+}
 __device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32]) {
   asm volatile(
       "tcgen05.st.sync.aligned.32x32b.x32.b32 [%32], "
@@ -439,13 +481,15 @@ __device__ __forceinline__ float fast_exp2(float x) {
 
 // ------------------------------------------------------------------- math
 __device__ __forceinline__ float gelu_tanh(float x) {
-  // 0.5 x (1 + tanh(sqrt(2/pi) (x + 0.044715 x^3))), arranged as six FP operations around the tanh
+  // 0.5 x (1 + tanh(u)) = x * sigmoid(2u), u = sqrt(2/pi) (x + 0.044715 x^3): one ex2 and one reciprocal, both good to
+  // 2^-22 - the hidden activations this feeds are re-quantised to e4m3, where an error of 2^-11 (tanh.approx) would
+  // already move one value in two hundred across a rounding boundary
   const float k0 = 0.7978845608028654f, k0k1 = 0.7978845608028654f * 0.044715f;
   const float u = x * fmaf(k0k1, x * x, k0);
-  float t;
-  asm("tanh.approx.f32 %0, %1;" : "=f"(t) : "f"(u));  // relative error about 2^-11, below bf16 resolution
-  const float hx = 0.5f * x;
-  return fmaf(hx, t, hx);
+  float e, r;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(u * -2.8853900817779268f));  // exp(-2u)
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(1.0f + e));
+  return x * r;
 }
 __device__ __forceinline__ float silu(float x) { return x / (1.0f + __expf(-x)); }
 __device__ __forceinline__ float gelu_erf(float x) { return 0.5f * x * (1.0f + erff(x * 0.7071067811865476f)); }

@@ -123,7 +123,8 @@ class WanDiTEngine:
             for i, blk in enumerate(self.blocks):
                 pre = f"blocks.{i}.cross_attn."
                 blk.update(ck_img=P_(pre + "k_img"), cv_img=P_(pre + "v_img"), cnk_img=V(pre + "norm_k_img.weight"))
-        self.mod = torch.stack(mods).contiguous()          # [L, 6, d]
+        self.mod = (torch.stack(mods).contiguous() if mods                  # [L, 6, d]
+                    else torch.zeros(0, 6, self.d, dtype=torch.float32, device=self.dev))
         self.head = P_("head.head")
         self.head_mod = V("head.modulation").reshape(2, self.d)
         self.out_dim = self.head.out_features // 4

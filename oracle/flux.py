@@ -3,7 +3,8 @@ Citations: ``diffsynth_engine/models/flux/flux_dit.py`` and ``models/basic/{tran
 of modelscope/DiffSynth-Engine v0.1.1.
 
 ``rt`` is the rounding applied wherever the CUDA path materialises a bf16 tensor (identity for the
-exact oracle); ``lin`` is a ``LinearEval``."""
+exact oracle); ``lin`` is a ``LinearEval``.  With a rounding ``rt`` the attention also rounds its probabilities to
+bf16 (``ops.attention_bf16_probs``) and the RoPE factors are the fp16 values the projection's epilogue reads."""
 import torch
 import torch.nn.functional as F
 
@@ -32,7 +33,10 @@ def joint_attention(qkv_b, qkv_a, w, pre, H, table, rt=_ident):
     qkv_*: [S_*, 3*H*D] with feature layout [q | k | v], head-major inside each (flux_dit.py:166-167)."""
     d = qkv_a.shape[1] // 3
     def split(qkv, nq, nk):
-        q, k, v = qkv[:, :d], qkv[:, d:2 * d], qkv[:, 2 * d:]
+        # qkv is the UNROUNDED projection: the projection's epilogue normalises and rotates q and k from its fp32
+        # accumulator and rounds once, after the rotation (the reference rounds the projection first,
+        # flux_dit.py:164-171: one rounding more); v is rounded as it is stored
+        q, k, v = qkv[:, :d], qkv[:, d:2 * d], rt(qkv[:, 2 * d:])
         return O.rmsnorm(_heads(q, H), w[pre + nq]), O.rmsnorm(_heads(k, H), w[pre + nk]), _heads(v, H)
     q_a, k_a, v_a = split(qkv_a, "norm_q_a.weight", "norm_k_a.weight")
     if qkv_b is not None:
@@ -41,7 +45,8 @@ def joint_attention(qkv_b, qkv_a, w, pre, H, table, rt=_ident):
     else:
         q, k, v = q_a, k_a, v_a
     q, k = rt(O.apply_rope_pairs(q, table)), rt(O.apply_rope_pairs(k, table))
-    o = O.attention(q[None], k[None], v[None])[0]       # [H, S, D]
+    attn = O.attention if rt is _ident else O.attention_bf16_probs
+    o = attn(q[None], k[None], v[None])[0]              # [H, S, D]
     return rt(o.transpose(0, 1).reshape(o.shape[1], -1))  # flux_dit.py:183
 
 
@@ -55,15 +60,15 @@ def double_block(xa, xb, temb, table, w, pre, H, lin: LinearEval, rt=_ident):
         return O.ln_modulate(x, sh_msa, sc_msa), g_msa, sh_mlp, sc_mlp, g_mlp
     na, g_msa_a, sh_mlp_a, sc_mlp_a, g_mlp_a = ada(xa, "norm1_a")
     nb, g_msa_b, sh_mlp_b, sc_mlp_b, g_mlp_b = ada(xb, "norm1_b")
-    qkv_a = rt(lin(na, w[pre + "attn.a_to_qkv.weight"], w[pre + "attn.a_to_qkv.bias"]))
-    qkv_b = rt(lin(nb, w[pre + "attn.b_to_qkv.weight"], w[pre + "attn.b_to_qkv.bias"]))
+    qkv_a = lin(na, w[pre + "attn.a_to_qkv.weight"], w[pre + "attn.a_to_qkv.bias"], from_fp32=True)
+    qkv_b = lin(nb, w[pre + "attn.b_to_qkv.weight"], w[pre + "attn.b_to_qkv.bias"], from_fp32=True)
     att = joint_attention(qkv_b, qkv_a, w, pre + "attn.", H, table, rt)
     Sb = xb.shape[0]
     att_b, att_a = att[:Sb], att[Sb:]
     def tail(x, att_x, g_msa, sh_mlp, sc_mlp, g_mlp, s):
         x = rt(x.float() + g_msa * lin(att_x, w[pre + f"attn.{s}_to_out.weight"], w[pre + f"attn.{s}_to_out.bias"]))
         n = O.ln_modulate(x, sh_mlp, sc_mlp)
-        hid = O.gelu_tanh(lin(n, w[pre + f"ff_{s}.0.weight"], w[pre + f"ff_{s}.0.bias"]))
+        hid = O.gelu_tanh(lin(n, w[pre + f"ff_{s}.0.weight"], w[pre + f"ff_{s}.0.bias"], from_fp32=True))
         if not getattr(lin, "unit_scale_acts", False) or not UNIT_SCALE:
             hid = rt(hid)    # otherwise the projection's epilogue emits e4m3 straight from its fp32 values
         return rt(x + g_mlp * lin(hid, w[pre + f"ff_{s}.2.weight"], w[pre + f"ff_{s}.2.bias"],
@@ -80,8 +85,8 @@ def single_block(x, temb, table, w, pre, H, lin: LinearEval, rt=_ident):
               act_quant=False)[0]
     shift, scale, gate = emb.chunk(3)  # transformer_helper.py:32-36
     n = O.ln_modulate(x, shift, scale)
-    h = lin(n, w[pre + "to_qkv_mlp.weight"], w[pre + "to_qkv_mlp.bias"])
-    qkv, mlp = rt(h[:, :3 * d]), O.gelu_tanh(h[:, 3 * d:])
+    h = lin(n, w[pre + "to_qkv_mlp.weight"], w[pre + "to_qkv_mlp.bias"], from_fp32=True)
+    qkv, mlp = h[:, :3 * d], O.gelu_tanh(h[:, 3 * d:])
     if not getattr(lin, "unit_scale_acts", False) or not UNIT_SCALE:
         mlp = rt(mlp)
     att = joint_attention(None, qkv, w, pre, H, table, rt)
@@ -135,6 +140,8 @@ def flux_dit_forward(w, latents, timestep, prompt_emb, pooled, guidance, text_id
     cond = (cond + timestep_mlp(pooled[0:1].float(), w, "pooled_text_embedder.", lin))[0]
     xb = rt(lin(prompt_emb[0], w["context_embedder.weight"], w["context_embedder.bias"]))
     table = O.flux_rope_table(ids)
+    if rt is not _ident:
+        table = table.half().float()   # the rotation factors reach the projection's epilogue as fp16 (exact to 2^-12)
     xa = rt(lin(patchify(latents)[0], w["x_embedder.weight"], w["x_embedder.bias"]))
     for i in range(n_double):
         xa, xb = double_block(xa, xb, cond, table, w, f"blocks.{i}.", H, lin, rt)
@@ -147,6 +154,6 @@ def flux_dit_forward(w, latents, timestep, prompt_emb, pooled, guidance, text_id
               act_quant=False)[0]
     scale, shift = emb.chunk(2)  # flux_dit.py:333: scale first
     x = O.ln_modulate(x, shift, scale)
-    x = rt(lin(x, w["final_proj_out.weight"], w["final_proj_out.bias"]))
+    x = rt(lin(x, w["final_proj_out.weight"], w["final_proj_out.bias"], from_fp32=True))
     out = unpatchify(x[None], height, width)
     return (out, hidden) if return_hidden else out

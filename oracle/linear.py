@@ -34,13 +34,16 @@ class LinearEval:
         emit e4m3 directly; a per-row scale would need the finished row."""
         return self.mode in ("fp8_tensor", "fp8_channel")
 
-    def __call__(self, x, W, b=None, act_quant=True):
-        """``act_quant``: True = per-row dynamic scale, False = fp32 activations, "unit" = e4m3 cast with scale 1."""
+    def __call__(self, x, W, b=None, act_quant=True, from_fp32=False):
+        """``act_quant``: True = per-row dynamic scale, False = fp32 activations, "unit" = e4m3 cast with scale 1.
+        ``from_fp32``: the activation is quantised straight from its fp32 values - the case of a Linear fed by a
+        LayerNorm, whose kernel emits the 8-bit rows itself - instead of from a bf16 tensor (one rounding less)."""
         x = x.float()
         if self.mode == "fp32":
             y = x @ W.float().t()
         elif self.mode == "bf16":
-            y = x.bfloat16().float() @ W.bfloat16().float().t()
+            # the M = 1 Linears (modulation, embedders) run as GEMVs on fp32 activations
+            y = (x if act_quant is False else x.bfloat16().float()) @ W.bfloat16().float().t()
         else:
             q, s = self._wq(W)
             sd = s if s.numel() == 1 else s[:, None]
@@ -48,7 +51,8 @@ class LinearEval:
                 xq = x.clamp(-448, 448).to(torch.float8_e4m3fn)
                 y = O.linear_quant(xq, torch.ones(x.shape[0]), q, s)
             elif act_quant:
-                xq, xs = (O.quant_rows_int8 if self.mode == "int8_channel" else O.quant_rows_e4m3)(x.bfloat16())
+                xq, xs = (O.quant_rows_int8 if self.mode == "int8_channel" else O.quant_rows_e4m3)(
+                    x if from_fp32 else x.bfloat16())
                 y = O.linear_quant(xq, xs, q, s)
             else:
                 y = x @ (q.float() * sd).t()

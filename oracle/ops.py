@@ -91,6 +91,26 @@ def attention(q, k, v, sm_scale=None):
     return F.scaled_dot_product_attention(q.float(), k.float(), v.float(), scale=sm_scale)
 
 
+def attention_bf16_probs(q, k, v, sm_scale=None):
+    """The same attention as GPU flash kernels evaluate it (the SDPA kernel the reference reaches on CUDA, and this
+    library's): fp32 scores from bf16 operands, probabilities ROUNDED TO BF16 for the P.V product, fp32 row sum of the
+    unrounded probabilities.  The probabilities are taken relative to an integer power of two,
+    ``p = exp2(s*c - M)`` with ``M = ceil(rowmax * c)`` and ``c = scale * log2(e)``: scaling by 2^integer is exact, so
+    the rounded values - and with them the result - do not depend on which integer ``M`` an implementation uses or on
+    how it tiles the keys.  q, k, v: [B, H, S, D]; the same-rounding counterpart of :func:`attention`."""
+    B, H, Sq, D = q.shape
+    scale = (1.0 / math.sqrt(D)) if sm_scale is None else sm_scale
+    c = torch.tensor(scale, dtype=torch.float32) * torch.tensor(1.4426950408889634, dtype=torch.float32)
+    out = torch.empty(B, H, Sq, v.shape[-1])
+    for b in range(B):
+        for h in range(H):
+            s = q[b, h].float() @ k[b, h].float().t()
+            m = torch.ceil(s.amax(dim=1) * c)
+            p = torch.exp2(s * c - m[:, None])
+            out[b, h] = (p.bfloat16().float() @ v[b, h].float()) / p.sum(dim=1, keepdim=True)
+    return out
+
+
 # ---------------------------------------------------------------------------- quantisation
 def quant_rows_e4m3(x):
     """Dynamic per-row FP8 quantisation: s = amax/448 (1 for an all-zero row), q = e4m3(clamp(x * (1/s))).

@@ -18,9 +18,11 @@ def _mh(x, H):
     return x.reshape(x.shape[0], H, -1).transpose(0, 1)  # [H, S, D]
 
 
-def _attend(q, k, v, H):
-    """wan_dit.py:18-22."""
-    o = O.attention(_mh(q, H)[None], _mh(k, H)[None], _mh(v, H)[None])[0]
+def _attend(q, k, v, H, rt=_ident):
+    """wan_dit.py:18-22.  With a rounding ``rt`` (the same-rounding oracle) the probabilities are rounded to bf16 as a
+    GPU flash kernel does."""
+    attn = O.attention if rt is _ident else O.attention_bf16_probs
+    o = attn(_mh(q, H)[None], _mh(k, H)[None], _mh(v, H)[None])[0]
     return o.transpose(0, 1).reshape(q.shape[0], -1)
 
 
@@ -37,29 +39,30 @@ def wan_block(x, context, t_mod, table, w, pre, H, lin: LinearEval, rt=_ident, e
         return lin(inp, w[pre + name + ".weight"], w[pre + name + ".bias"], **kw)
     # self-attention, wan_dit.py:101-107
     n = O.ln_modulate(x, sh_msa, sc_msa, eps)
-    q = rt(O.rmsnorm(rt(L(n, "self_attn.q")), w[pre + "self_attn.norm_q.weight"], eps))
-    k = rt(O.rmsnorm(rt(L(n, "self_attn.k")), w[pre + "self_attn.norm_k.weight"], eps))
-    v = rt(L(n, "self_attn.v"))
+    # the projection is rounded (it is stored), norm and rotation then run in one pass with one rounding at its end
+    q = O.rmsnorm(rt(L(n, "self_attn.q", from_fp32=True)), w[pre + "self_attn.norm_q.weight"], eps)
+    k = O.rmsnorm(rt(L(n, "self_attn.k", from_fp32=True)), w[pre + "self_attn.norm_k.weight"], eps)
+    v = rt(L(n, "self_attn.v", from_fp32=True))
     q, k = rt(_rope(q, table, H)), rt(_rope(k, table, H))
-    x = rt(x.float() + g_msa * L(rt(_attend(q, k, v, H)), "self_attn.o"))
+    x = rt(x.float() + g_msa * L(rt(_attend(q, k, v, H, rt)), "self_attn.o"))
     # cross-attention, wan_dit.py:136-152; norm3 is an affine LayerNorm (:178,190).  Image-to-video models carry
     # k_img/v_img: the first 257 context rows are CLIP tokens with their own key/value projection, attended
     # separately, and the two attention outputs are summed before the output projection (:137-152).
     has_img = (pre + "cross_attn.k_img.weight") in w
     img, ctx = (context[:IMG_TOKENS], context[IMG_TOKENS:]) if has_img else (None, context)
     n3 = O.layer_norm(x, eps) * w[pre + "norm3.weight"].float() + w[pre + "norm3.bias"].float()
-    q = rt(O.rmsnorm(rt(L(n3, "cross_attn.q")), w[pre + "cross_attn.norm_q.weight"], eps))
+    q = rt(O.rmsnorm(rt(L(n3, "cross_attn.q", from_fp32=True)), w[pre + "cross_attn.norm_q.weight"], eps))
     k = rt(O.rmsnorm(rt(L(ctx, "cross_attn.k")), w[pre + "cross_attn.norm_k.weight"], eps))
     v = rt(L(ctx, "cross_attn.v"))
-    att = rt(_attend(q, k, v, H))
+    att = rt(_attend(q, k, v, H, rt))
     if has_img:
         k_i = rt(O.rmsnorm(rt(L(img, "cross_attn.k_img")), w[pre + "cross_attn.norm_k_img.weight"], eps))
         v_i = rt(L(img, "cross_attn.v_img"))
-        att = rt(att + rt(_attend(q, k_i, v_i, H)))
+        att = rt(att + rt(_attend(q, k_i, v_i, H, rt)))
     x = rt(x + L(att, "cross_attn.o"))
     # FFN, wan_dit.py:179-182,191-192
     n2 = O.ln_modulate(x, sh_mlp, sc_mlp, eps)
-    hid = O.gelu_tanh(L(n2, "ffn.0"))
+    hid = O.gelu_tanh(L(n2, "ffn.0", from_fp32=True))
     if getattr(lin, "unit_scale_acts", False):   # FP8 weights: the first FFN GEMM emits e4m3 (unit scale) directly
         return rt(x + g_mlp * L(hid, "ffn.2", act_quant="unit"))
     return rt(x + g_mlp * L(rt(hid), "ffn.2"))
@@ -85,12 +88,12 @@ def img_emb(clip_feature, w, lin, rt=_ident):
     GELU -> Linear -> LayerNorm."""
     def ln(t, i):
         return O.layer_norm(t, 1e-5) * w[f"img_emb.proj.{i}.weight"].float() + w[f"img_emb.proj.{i}.bias"].float()
-    h = rt(F.gelu(lin(ln(clip_feature, 0), w["img_emb.proj.1.weight"], w["img_emb.proj.1.bias"])))
+    h = rt(F.gelu(lin(ln(clip_feature, 0), w["img_emb.proj.1.weight"], w["img_emb.proj.1.bias"], from_fp32=True)))
     return rt(ln(rt(lin(h, w["img_emb.proj.3.weight"], w["img_emb.proj.3.bias"])), 4))
 
 
 def wan_dit_forward(w, x, context, timestep, num_layers, H, freq_dim=256, eps=1e-6, lin: LinearEval = None,
-                    rt=_ident, clip_feature=None, y=None):
+                    rt=_ident, clip_feature=None, y=None, return_hidden=False):
     """WanDiT.forward, wan_dit.py:319-351, batch 1.  With ``clip_feature`` [1,257,1280] and ``y`` (conditioning
     latents, concatenated to x on the channel axis) the image-to-video branch (:330-333)."""
     lin = lin or LinearEval("fp32")
@@ -107,9 +110,11 @@ def wan_dit_forward(w, x, context, timestep, num_layers, H, freq_dim=256, eps=1e
     h, grid = patchify(x, w, lin)
     h = rt(h)
     table = O.wan_rope_table(*grid, head_dim=d // H)
+    h_in = h
     for i in range(num_layers):
         h = wan_block(h, ctx, t_mod, table, w, f"blocks.{i}.", H, lin, rt, eps)
     mod = w["head.modulation"].float().reshape(2, d) + t[0]
     shift, scale = mod
-    out = rt(L(O.ln_modulate(h, shift, scale, eps), "head.head"))
-    return unpatchify(out, grid, out.shape[1] // 4)
+    out = rt(L(O.ln_modulate(h, shift, scale, eps), "head.head", from_fp32=True))
+    out = unpatchify(out, grid, out.shape[1] // 4)
+    return (out, h_in, h) if return_hidden else out      # hidden state before the first and after the last block

@@ -329,6 +329,22 @@ def test_flash_attn_peaked_rows(dsb, cuda_dev):
     assert O.rel_l2(out.float().cpu(), ref) < 4e-3
 
 
+def test_flash_attn_one_key_far_above_the_reference_maximum(dsb, cuda_dev):
+    """One key deep in the sequence scores more than 2^100 above everything before it for about half of the rows (and
+    as far below for the rest): the chunk that meets it is redone with clamped exponents, the next tile refreshes
+    the reference maximum, and the rows it dominates return that key's value."""
+    g = _gen(19)
+    H, S = 2, 2048
+    q = _bf(torch.randn(1, S, H, 128, generator=g))
+    k = _bf(torch.randn(1, S, H, 128, generator=g))
+    v = _bf(torch.randn(1, S, H, 128, generator=g))
+    k[:, 1500] *= 300.0
+    ref = O.attention(q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2)).transpose(1, 2)
+    out = dsb.ops.flash_attn(q.to(cuda_dev), k.to(cuda_dev), v.to(cuda_dev)).float().cpu()
+    assert torch.isfinite(out).all()
+    assert O.rel_l2(out, ref) < 4e-3
+
+
 def test_flash_attn_strided_views(dsb, cuda_dev):
     """q/k/v as column blocks of one fused projection buffer [S, 3*H*128] (text rows first), and
     [B,H,S,D]-strided tensors as the reference's _attn_func receives them (models/flux/flux_dit.py:166-182)."""
