@@ -1,16 +1,18 @@
 #!/usr/bin/env python
-"""Benchmark of the DiT denoising step (Flux.1-dev architecture, 1024x1024, FP8 e4m3 per-tensor weights, bf16
-activations, batch 1, random-init weights, synthetic inputs) on B200.
+"""Benchmark of the DiT denoising step on B200 (random-init weights of the architecture, synthetic inputs).
 
     python bench.py --gpus N --steps K --warmup W            # this library
     python bench.py --impl reference --steps K --warmup W     # the reference arithmetic on the host CPU cores
 
-Prints ONE JSON line.  `value` = whole-job denoise steps/s with inputs resident in HBM (CUDA-graph replay of the
-step, CUDA events, max over ranks); `e2e` = the same through `FluxDiTEngine.forward`-style host buffers (pinned
-host -> device copies of every input and a device -> host read of the model output inside the timed region).
-With N > 1 every rank denoises its own latent (independent replicas, weak scaling, no data-path collective).
-By default the line also carries, under "wan", the Wan2.1-14B-architecture 480p step run sequence-parallel
-(Ulysses) over the same N GPUs on ONE video (strong scaling); `--workload flux|wan` runs one of the two.
+Prints ONE JSON line.  The headline (`value`) is the Wan2.1-14B-architecture 480p step (81 frames x 480 x 832 ->
+32760 tokens, 40 blocks, FP8 e4m3 per-channel weights, bf16 activations, batch 1) run sequence-parallel (Ulysses)
+over the N GPUs on ONE video: strong scaling, `value` = whole-job denoise steps/s with inputs resident in HBM (CUDA
+events, max over ranks), `e2e` = the same through host buffers (pinned host -> device copies of every input and a
+device -> host read of the model output inside the timed region).  At N = 1 the line also carries, under "flux", the
+Flux.1-dev-architecture step at 1024 x 1024 (19 + 38 blocks, FP8 per-tensor weights) with its own roofline entry.
+`parity` holds correctness checks made outside the timed region: finiteness of the timed output, a reduced-depth
+model at full width against the CPU oracle, and (N > 1) the sequence-parallel output against a one-GPU run.
+`--workload flux|wan|qwen|sweeps` runs one of the single workloads.
 """
 import argparse
 import importlib
@@ -33,6 +35,8 @@ FLUX = dict(d=3072, H=24, n_double=19, n_single=38, S_txt=512, height=128, width
 QWEN = dict(d=3072, H=24, n_double=60, n_single=0, S_txt=256, height=166, width=166, txt_dim=3584, pooled_dim=768)
 # Wan2.1-14B text-to-video at 81 frames x 480 x 832: latent 21 x 60 x 104, patch (1,2,2) -> 21*30*52 = 32760 tokens
 WAN = dict(d=5120, ffn=13824, num_layers=40, H=40, frames=21, height=60, width=104, ctx=512, text_dim=4096)
+# the CPU arm's sample of the Wan step: one block on the first 1023 tokens as queries against all 32760 keys
+WAN_CPU_ROWS = 1023   # about 1/32 of the sequence: the sample is 1023 / 32760 of one of the 40 blocks
 
 
 def load_package():
@@ -51,8 +55,8 @@ def measured_peaks():
     if os.path.exists(path):
         with open(path) as f:
             p = json.load(f)
-        return dict(hbm_gbs=p["hbm_gbs"], bf16=p["bf16_tflops"], bf16_sustained=p.get("bf16_tflops_sustained"),
-                    source="measured")
+        return dict(hbm_gbs=p["hbm_gbs"], bf16=p["bf16_tflops"],
+                    bf16_sustained=p.get("bf16_tflops_sustained") or p["bf16_tflops"], source="measured")
     return dict(hbm_gbs=6650.0, bf16=1590.0, bf16_sustained=1400.0, source="fallback")
 
 
@@ -65,6 +69,15 @@ def flux_step_flops(c=FLUX):
     lin = c["n_double"] * lin_double + c["n_single"] * lin_single
     lin += 2 * St * c["txt_dim"] * d + 2 * Si * 64 * d * 2
     attn = (c["n_double"] + c["n_single"]) * 4 * S * S * d
+    return lin, attn
+
+
+def wan_step_flops(c=WAN):
+    """Per block: six d x d Linears (self q, k, v, o; cross q, o) and the two FFN Linears on all S tokens, the
+    cross-attention k and v Linears on the context tokens; self-attention 4*S^2*d, cross-attention 4*S*ctx*d."""
+    S, d, L = c["frames"] * (c["height"] // 2) * (c["width"] // 2), c["d"], c["num_layers"]
+    lin = L * (2 * S * d * (6 * d + 2 * c["ffn"]) + 2 * c["ctx"] * d * 2 * d)
+    attn = L * (4 * S * S * d + 4 * S * c["ctx"] * d)
     return lin, attn
 
 
@@ -118,9 +131,50 @@ class ClockSampler:
 
 
 # ------------------------------------------------------------------------- CPU arm (oracle port)
-def cpu_reference_arm(steps=1, warmup=0, budget_s=150.0):
-    """The reference's arithmetic on the host cores: the fp32 PyTorch restatement of one double-stream and one
-    single-stream block (oracle/flux.py) at the full sequence length, extrapolated by the block counts."""
+def cpu_wan_arm(steps=1, warmup=0, budget_s=900.0):
+    """The reference's arithmetic on the host cores, as the fp32 PyTorch restatement of one Wan DiTBlock
+    (oracle/wan.py) evaluated the way one member of a sequence-parallel group evaluates it: WAN_CPU_ROWS tokens as
+    queries (all token-wise work on them) against the keys and values of all 32760 tokens.  One such evaluation is
+    one "step" of this arm; it is rows / 32760 of one of the 40 blocks, and the denoise-step rate is extrapolated
+    from it (the full step is 1678 TFLOP, about an hour of CPU time)."""
+    import torch
+    from oracle import ops as O
+    from oracle import wan as OW
+    from oracle.linear import LinearEval
+    load_package()
+    synth = importlib.import_module("diffsynth_engine_b200.synth")
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    c = WAN
+    d, H, rows = c["d"], c["H"], WAN_CPU_ROWS
+    S = c["frames"] * (c["height"] // 2) * (c["width"] // 2)
+    w = synth.make_state_dict(synth.wan_block_shapes("", d, c["ffn"]), seed=0)
+    x, ctx, tmod = synth.randn((rows, d), 1), synth.randn((c["ctx"], d), 2), synth.randn((6, d), 3) * 0.1
+    other = (synth.randn((S - rows, d), 4), synth.randn((S - rows, d), 5))
+    table = O.wan_rope_table(c["frames"], c["height"] // 2, c["width"] // 2)[:rows]
+    lin = LinearEval("fp32")
+    times, t_start = [], time.time()
+    with torch.no_grad():
+        for i in range(warmup + steps):
+            if times and time.time() - t_start > budget_s:
+                break
+            t0 = time.time()
+            OW.wan_block(x, ctx, tmod, table, w, "", H, lin, other_kv=other)
+            if i >= warmup or (warmup + steps) == 1:
+                times.append(time.time() - t0)
+    t_sample = statistics.mean(times)
+    fraction = rows / S / c["num_layers"]
+    step_s = t_sample / fraction
+    return dict(value=1.0 / step_s, unit="steps/s", cores=cores, kind="port",
+                sample=(f"one Wan DiTBlock (oracle port, fp32, {cores} threads) on {rows} tokens as queries against all "
+                        f"{S} keys = {fraction:.3e} of a step; {t_sample:.2f} s each (mean of {len(times)}), "
+                        f"extrapolated to the 40-block, {S}-token step; embedders and head (<0.1% of the work) left out"),
+                sample_ms=t_sample * 1e3, sample_fraction=fraction, samples=len(times))
+
+
+def cpu_flux_arm(steps=1, warmup=0, budget_s=900.0):
+    """Flux: the fp32 restatement of one double-stream and one single-stream block (oracle/flux.py) at the full
+    sequence length, extrapolated by the block counts."""
     import torch
     from oracle import flux as OF
     from oracle import ops as O
@@ -156,22 +210,162 @@ def cpu_reference_arm(steps=1, warmup=0, budget_s=150.0):
                 sample=(f"1 double-stream + 1 single-stream block at S=512+4096, fp32, {cores} threads "
                         f"({td:.2f}s + {tsg:.2f}s, mean of {len(times)}), extrapolated x19 / x38; embedders and "
                         f"final layer (<0.1% of the work) left out"),
-                ms_per_step=step_s * 1e3, samples=len(times))
+                sample_ms=(td + tsg) * 1e3, sample_fraction=(td + tsg) / step_s, samples=len(times))
 
 
-def wan_step_flops(c=WAN):
-    S, d, L = c["frames"] * (c["height"] // 2) * (c["width"] // 2), c["d"], c["num_layers"]
-    lin = L * (2 * S * d * (8 * d + 2 * c["ffn"]) + 2 * c["ctx"] * d * 2 * d)
-    attn = L * (4 * S * S * d + 4 * S * c["ctx"] * d)
-    return lin, attn
+# --------------------------------------------------------------------------------------- helpers
+class Ctx:
+    """What every workload needs: torch, the package, the device, the process group and the timing helpers."""
+
+    def __init__(self, torch, pkg, dev, dist, rank, world, local_rank):
+        self.torch, self.pkg, self.dev, self.dist = torch, pkg, dev, dist
+        self.rank, self.world, self.local_rank = rank, world, local_rank
+        self.synth = importlib.import_module("diffsynth_engine_b200.synth")
+
+    def barrier(self):
+        self.torch.cuda.synchronize()
+        if self.dist is not None:
+            self.dist.barrier()
+        self.torch.cuda.synchronize()
+
+    def max_over_ranks(self, *vals):
+        if self.dist is None:
+            return vals if len(vals) > 1 else vals[0]
+        t = self.torch.tensor(list(vals), device=self.dev, dtype=self.torch.float64)
+        self.dist.all_reduce(t, op=self.dist.ReduceOp.MAX)
+        out = [float(v) for v in t]
+        return out if len(out) > 1 else out[0]
+
+    def timed_steps(self, fn, steps):
+        """`steps` calls of fn between two CUDA events on the current stream, barrier + synchronize on both sides;
+        returns the mean milliseconds per call, max over ranks."""
+        torch = self.torch
+        self.barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            fn()
+        e1.record()
+        self.barrier()
+        return self.max_over_ranks(e0.elapsed_time(e1)) / steps
 
 
-def run_wan(args, torch, pkg, synth, dev, dist, rank, world, steps, warmup):
+def timed_launches(ctx, module, names, run):
+    """Runs `run()` once with the named functions of `module` wrapped in CUDA events; returns [(name, args, ms)]."""
+    torch = ctx.torch
+    recs, saved = [], {n: getattr(module, n) for n in names}
+
+    def wrap(name, fn):
+        def inner(*a, **kw):
+            s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            s.record()
+            r = fn(*a, **kw)
+            e.record()
+            recs.append((name, a, kw, s, e))
+            return r
+        return inner
+
+    for n, fn in saved.items():
+        setattr(module, n, wrap(n, fn))
+    try:
+        run()
+        torch.cuda.synchronize()
+    finally:
+        for n, fn in saved.items():
+            setattr(module, n, fn)
+    return [(n, a, kw, s.elapsed_time(e)) for n, a, kw, s, e in recs]
+
+
+def library_fp8_gemm_tflops(torch, dev):
+    """cuBLASLt's FP8 GEMM (torch._scaled_mm, the kernel the reference's FP8 Linear calls, utils/fp8_linear.py:41)
+    on 8192^3, best of 5: printed next to the assumed 8-bit peak so the assumption can be read against a
+    measurement of this run.  None if the call is unavailable."""
+    try:
+        n = 8192
+        a = torch.randn(n, n, device=dev).to(torch.float8_e4m3fn)
+        b = torch.randn(n, n, device=dev).to(torch.float8_e4m3fn)
+        one = torch.tensor(1.0, device=dev)
+        best = None
+        for _ in range(6):
+            s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            s.record()
+            torch._scaled_mm(a, b.t(), scale_a=one, scale_b=one, out_dtype=torch.bfloat16)
+            e.record()
+            torch.cuda.synchronize()
+            ms = s.elapsed_time(e)
+            best = ms if best is None else min(best, ms)
+        return 2.0 * n ** 3 / best / 1e9
+    except Exception:
+        return None
+
+
+# ------------------------------------------------------------------------------------------- Wan
+def wan_parity(ctx, args):
+    """Correctness evidence for the Wan path, outside any timed region.
+    (1) rank 0, one GPU: a 1-block model at full width on a 21 x 15 x 13 token grid (4095 tokens, the share of one
+        of eight ranks) against the CPU oracle with the same quantisation: rel-L2 of the hidden state after the block
+        and of the block's update;
+    (2) N > 1: a 2-block model at full width on the FULL video, sequence-parallel over all ranks, against the same
+        model run on rank 0 alone."""
+    torch, synth, dev = ctx.torch, ctx.synth, ctx.dev
+    wan = importlib.import_module("diffsynth_engine_b200.wan")
+    c = WAN
+    out = {}
+    shapes = synth.wan_dit_shapes(d=c["d"], ffn=c["ffn"], num_layers=2, text_dim=c["text_dim"])
+    sd = synth.make_state_dict(shapes, seed=77, device=dev, dtype=torch.bfloat16)
+    x = synth.randn((1, 16, c["frames"], c["height"], c["width"]), 78).bfloat16()
+    ctxt = synth.randn((1, c["ctx"], c["text_dim"]), 79).bfloat16()
+    t = torch.tensor([417.0])
+    if ctx.world > 1:
+        eng = wan.WanDiTEngine(dict(sd), fmt=args.wan_fmt, device=dev, num_layers=2, num_heads=c["H"],
+                               group=ctx.dist.group.WORLD)
+        y_sp = eng(x.to(dev), ctxt.to(dev), t.to(dev)).float()
+        del eng
+        if ctx.rank == 0:
+            one = wan.WanDiTEngine(dict(sd), fmt=args.wan_fmt, device=dev, num_layers=2, num_heads=c["H"])
+            y_1 = one(x.to(dev), ctxt.to(dev), t.to(dev)).float()
+            del one
+            out["sp_vs_one_gpu_rel_l2"] = float((y_sp - y_1).norm() / y_1.norm())
+            out["sp_vs_one_gpu_tolerance"] = 3e-3
+            out["sp_check"] = f"2-block model at full width, full 32760-token video, sp{ctx.world} vs rank 0 alone"
+        ctx.barrier()
+    if ctx.rank == 0 and not args.no_oracle_parity:
+        from oracle import flux as OF
+        from oracle import ops as O
+        from oracle import wan as OW
+        from oracle.linear import LinearEval
+        w1 = {k: v.float().cpu() for k, v in sd.items() if not k.startswith("blocks.1.")}
+        xs = synth.randn((1, 16, 21, 30, 26), 80).bfloat16().float()
+        cs = ctxt.float()
+        mode = args.wan_fmt
+        with torch.no_grad():
+            _, h0_ref, h1_ref = OW.wan_dit_forward(w1, xs, cs, t, num_layers=1, H=c["H"], lin=LinearEval(mode),
+                                                   rt=OF.round_bf16, return_hidden=True)
+        e1 = wan.WanDiTEngine(dict(w1), fmt=args.wan_fmt, device=dev, num_layers=1, num_heads=c["H"])
+        e1(xs.to(dev), cs.to(dev), t.to(dev))
+        h1 = e1.hidden().float().cpu()
+        e0 = wan.WanDiTEngine(dict(w1), fmt=args.wan_fmt, device=dev, num_layers=0, num_heads=c["H"])
+        e0(xs.to(dev), cs.to(dev), t.to(dev))
+        h0 = e0.hidden().float().cpu()
+        del e0, e1
+        out["block_4095_tokens_rel_l2_vs_oracle"] = O.rel_l2(h1, h1_ref)
+        out["block_update_rel_l2_vs_oracle"] = O.rel_l2(h1 - h0, h1_ref - h0_ref)
+        out["oracle_tolerance"] = 2e-3 if mode == "bf16" else 1e-2
+    del sd
+    torch.cuda.empty_cache()
+    if ctx.dist is not None:
+        ctx.barrier()
+    return out
+
+
+def run_wan(ctx, args, steps, warmup):
     """Wan2.1-14B-architecture step, sequence-parallel (Ulysses) over all ranks: ONE video, strong scaling."""
+    torch, pkg, synth, dev, dist = ctx.torch, ctx.pkg, ctx.synth, ctx.dev, ctx.dist
     wan = importlib.import_module("diffsynth_engine_b200.wan")
     c = dict(WAN)
     if args.wan_layers:
         c["num_layers"] = args.wan_layers
+    parity = wan_parity(ctx, args) if not args.no_parity else {}
     shapes = synth.wan_dit_shapes(d=c["d"], ffn=c["ffn"], num_layers=c["num_layers"], text_dim=c["text_dim"])
     sd = synth.make_state_dict(shapes, seed=1234, device=dev, dtype=torch.bfloat16)   # same weights on every rank
     eng = wan.WanDiTEngine(sd, fmt=args.wan_fmt, device=dev, num_layers=c["num_layers"], num_heads=c["H"],
@@ -183,52 +377,200 @@ def run_wan(args, torch, pkg, synth, dev, dist, rank, world, steps, warmup):
     h_ctx = synth.randn((1, c["ctx"], c["text_dim"]), 8).bfloat16().pin_memory()
     h_t = torch.tensor([500.0]).pin_memory()
     h_out = torch.empty((1, 16, c["frames"], c["height"], c["width"]), dtype=torch.bfloat16).pin_memory()
-
-    def sync():
-        torch.cuda.synchronize()
-        if dist is not None:
-            dist.barrier()
-        torch.cuda.synchronize()
-
     eng.set_inputs(h_x, h_ctx, h_t)
     n0 = pkg._lib.launches
-    for _ in range(max(1, warmup)):
+    eng.step()
+    launches = pkg._lib.launches - n0
+    for _ in range(max(0, warmup - 1)):
         eng.step()
-    launches = (pkg._lib.launches - n0) // max(1, warmup)
-    sync()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for _ in range(steps):
-        eng.step()
-    e1.record()
-    sync()
-    ms = e0.elapsed_time(e1) / steps
-    e0.record()
-    for _ in range(steps):
+    # ---- device-resident throughput, clocks sampled during exactly this loop
+    sampler = ClockSampler(ctx.local_rank).start() if ctx.rank == 0 else None
+    torch.cuda.profiler.start()   # lets a profiler started with --profile-from-start off see exactly the timed region
+    ms = ctx.timed_steps(eng.step, steps)
+    torch.cuda.profiler.stop()
+    clocks = sampler.stop() if sampler else None
+    out_dev = eng.step()
+    finite = bool(torch.isfinite(out_dev).all())
+    checksum = float(out_dev.float().abs().mean())
+
+    # ---- end to end: host buffers in, host buffer out, every step
+    def e2e_step():
         eng.set_inputs(h_x, h_ctx, h_t)
         out = eng.step()
-        if rank == 0:
+        if ctx.rank == 0:
             h_out.copy_(out, non_blocking=True)
         torch.cuda.current_stream().synchronize()
-    e1.record()
-    sync()
-    ms_e2e = e0.elapsed_time(e1) / steps
-    if dist is not None:
-        t = torch.tensor([ms, ms_e2e], device=dev)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms, ms_e2e = float(t[0]), float(t[1])
+
+    e2e_step()
+    ms_e2e = ctx.timed_steps(e2e_step, steps)
     pkg.ops.check_status(dev.index)
-    lin_f, attn_f = wan_step_flops(c)
+    # ---- roofline of the dominant kernel (self-attention): CUDA events around every launch of one eager step
+    recs = timed_launches(ctx, pkg.ops, ["flash_attn"], eng.step)
+    S = c["frames"] * (c["height"] // 2) * (c["width"] // 2)
+    self_attn = [r for r in recs if r[1][1].shape[1] > c["ctx"] + 257]        # keys = tokens, not the context
+    attn_ms = sum(r[3] for r in self_attn)
+    attn_flops = sum(4.0 * r[1][0].shape[1] * r[1][1].shape[1] * r[1][0].shape[2] * 128 for r in self_attn)
     peaks = measured_peaks()
+    lin_f, attn_f = wan_step_flops(c)
     fp8 = args.wan_fmt != "bf16"
+    ach = attn_flops / (attn_ms * 1e-3) / 1e12 if attn_ms > 0 else 0.0
     roof_ms = (lin_f / (peaks["bf16"] * (2 if fp8 else 1) * 1e12) + attn_f / (peaks["bf16"] * 1e12)) * 1e3
+    roofline = {
+        "kernel": "flash_attn_kernel (bf16, head_dim 128; self-attention launches of one step)", "bound": "tensor",
+        "achieved": ach, "peak": peaks["bf16_sustained"], "unit": "TFLOP/s", "frac": ach / peaks["bf16_sustained"],
+        "peak_source": f"bf16_tflops_sustained of MEASURED_PEAKS.json ({peaks['source']}): the kernel is timed inside "
+                       f"a seconds-long step under the power cap",
+        "peak_burst": peaks["bf16"], "frac_of_burst_peak": ach / peaks["bf16"],
+        "traffic": None, "traffic_source": "not measured in this run (needs an ncu capture)",
+        "launches_per_step": len(self_attn), "kernel_ms_per_step": attn_ms,
+        "share_of_step": attn_ms / ms if ms > 0 else None,
+        "method": "CUDA events around each self-attention launch of one eager step; 4*Sq*Sk*H*128 flop per launch",
+        "step_tflop": (lin_f + attn_f) / 1e12,
+        "step_roofline_ms": roof_ms,
+        "step_frac_of_roofline_all_gpus": roof_ms / (ms * ctx.world),
+        "step_roofline_note": "linear flops at 2 x bf16 burst peak (no 8-bit peak in MEASURED_PEAKS.json) + attention "
+                              "flops at the bf16 burst peak"}
+    parity.update({"finite": finite, "mean_abs_output": checksum})
     return {"workload": f"wan2.1-14B-arch t2v DiT step, 81x480x832 (32760 tokens, 512 context tokens), batch 1, "
-                        f"{c['num_layers']} blocks, weights {args.wan_fmt}, Ulysses sequence parallel x{world}",
+                        f"{c['num_layers']} blocks, weights {args.wan_fmt}, bf16 activations",
             "steps_per_s": 1e3 / ms, "ms_per_step": ms, "e2e_steps_per_s": 1e3 / ms_e2e, "e2e_ms_per_step": ms_e2e,
-            "n_gpus": world, "scaling": "strong", "step_tflop": (lin_f + attn_f) / 1e12,
-            "frac_of_roofline_all_gpus": roof_ms / (ms * world), "gpu_launches_per_step": launches,
+            "n_gpus": ctx.world, "gpu_launches_per_step": launches, "clocks": clocks, "roofline": roofline,
+            "parity": parity,
             "h2d_bytes_per_step": sum(t.numel() * t.element_size() for t in (h_x, h_ctx, h_t)),
             "d2h_bytes_per_step": h_out.numel() * h_out.element_size()}
+
+
+# ------------------------------------------------------------------------------------------ Flux
+def flux_parity(ctx, args, cfg):
+    """A 1 + 1 block model at full width and the full 4096 + 512 token sequence against the CPU oracle with the same
+    quantisation (rank 0 only; a few seconds of CPU)."""
+    torch, synth, dev = ctx.torch, ctx.synth, ctx.dev
+    if ctx.rank != 0 or args.no_parity or args.no_oracle_parity:
+        return {}
+    from oracle import flux as OF
+    from oracle import ops as O
+    from oracle.linear import LinearEval
+    flux = importlib.import_module("diffsynth_engine_b200.flux")
+    shapes = synth.flux_dit_shapes(d=cfg["d"], H=cfg["H"], n_double=1, n_single=1, txt_dim=cfg["txt_dim"],
+                                   pooled_dim=cfg["pooled_dim"])
+    w = {k: v.bfloat16().float().cpu() for k, v in synth.make_state_dict(shapes, seed=55, device=dev).items()}
+    lat = synth.randn((1, 16, cfg["height"], cfg["width"]), 56).bfloat16().float()
+    pe = synth.randn((1, cfg["S_txt"], cfg["txt_dim"]), 57).bfloat16().float()
+    pooled = synth.randn((1, cfg["pooled_dim"]), 58)
+    t, g = torch.tensor([500.0]), torch.tensor([3.5])
+    with torch.no_grad():
+        ref, hid_ref = OF.flux_dit_forward(w, lat, t, pe, pooled, g, n_double=1, n_single=1, H=cfg["H"],
+                                           lin=LinearEval(args.fmt), rt=OF.round_bf16, return_hidden=True)
+    eng = flux.FluxDiTEngine(dict(w), fmt=args.fmt, device=dev, n_double=1, n_single=1, num_heads=cfg["H"])
+    out = eng(lat.to(dev), t.to(dev), pe.to(dev), pooled.to(dev), g.to(dev)).float().cpu()
+    hid = eng._bufs["x"].float().cpu()
+    del eng
+    torch.cuda.empty_cache()
+    return {"model_1p1_blocks_hidden_rel_l2_vs_oracle": O.rel_l2(hid, hid_ref),
+            "model_1p1_blocks_output_rel_l2_vs_oracle": O.rel_l2(out, ref),
+            "oracle_tolerance": 2e-3 if args.fmt == "bf16" else 1e-2}
+
+
+def run_flux(ctx, args, cfg, workload, steps, warmup):
+    """Flux.1-dev-architecture (or the Qwen-arch stand-in) step on every rank: replicas, or with --sp ONE image whose
+    token sequence is split over all ranks."""
+    torch, pkg, synth, dev, dist = ctx.torch, ctx.pkg, ctx.synth, ctx.dev, ctx.dist
+    ops = pkg.ops
+    flux = importlib.import_module("diffsynth_engine_b200.flux")
+    sp = args.sp and ctx.world > 1
+    parity = flux_parity(ctx, args, cfg) if workload != "qwen" and not args.blocks else {}
+    # random-init weights of the architecture, drawn on the device, packed to FP8 layer by layer
+    shapes = synth.flux_dit_shapes(d=cfg["d"], H=cfg["H"], n_double=cfg["n_double"], n_single=cfg["n_single"],
+                                   txt_dim=cfg["txt_dim"], pooled_dim=cfg["pooled_dim"])
+    seed = 0 if sp else ctx.rank        # sequence parallel: every rank holds the same model and the same inputs
+    sd = synth.make_state_dict(shapes, seed=seed, device=dev, dtype=torch.bfloat16)
+    eng = flux.FluxDiTEngine(sd, fmt=args.fmt, device=dev, n_double=cfg["n_double"], n_single=cfg["n_single"],
+                             num_heads=cfg["H"], release_source=True, group=dist.group.WORLD if sp else None)
+    del sd
+    torch.cuda.empty_cache()
+    eng.prepare(cfg["S_txt"], cfg["height"], cfg["width"], cfg["txt_dim"], cfg["pooled_dim"])
+    # inputs on the host (pinned), as a pipeline would hold them between steps
+    h_lat = synth.randn((1, 16, cfg["height"], cfg["width"]), 100 + seed).bfloat16().pin_memory()
+    h_pe = synth.randn((1, cfg["S_txt"], cfg["txt_dim"]), 200 + seed).bfloat16().pin_memory()
+    h_pool = synth.randn((1, cfg["pooled_dim"]), 300 + seed).pin_memory()
+    h_t, h_g = torch.tensor([500.0]).pin_memory(), torch.tensor([3.5]).pin_memory()
+    h_out = torch.empty((1, 16, cfg["height"], cfg["width"]), dtype=torch.bfloat16).pin_memory()
+    h2d = sum(t.numel() * t.element_size() for t in (h_lat, h_pe, h_pool, h_t, h_g))
+    d2h = h_out.numel() * h_out.element_size()
+    eng.set_inputs(h_lat, h_t, h_pe, h_pool, h_g)
+    n0 = pkg._lib.launches
+    eng.step()
+    launches_per_step = pkg._lib.launches - n0
+    torch.cuda.synchronize()
+    ops.check_status(ctx.local_rank)
+    eng.capture()
+    for _ in range(max(3, warmup)):
+        eng.step()
+    sampler = ClockSampler(ctx.local_rank).start() if ctx.rank == 0 else None
+    torch.cuda.profiler.start()
+    ms_per_step = ctx.timed_steps(eng.step, steps)
+    torch.cuda.profiler.stop()
+    clocks = sampler.stop() if sampler else None
+    out_dev = eng.step()
+    parity.update({"finite": bool(torch.isfinite(out_dev).all()), "mean_abs_output": float(out_dev.float().abs().mean())})
+    value = (1 if sp else ctx.world) * 1e3 / ms_per_step
+
+    def e2e_step():
+        eng.set_inputs(h_lat, h_t, h_pe, h_pool, h_g)
+        out = eng.step()
+        h_out.copy_(out, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+
+    for _ in range(3):
+        e2e_step()
+    e2e_ms = ctx.timed_steps(e2e_step, steps)
+    ops.check_status(ctx.local_rank)
+    # ---- roofline of the dominant kernel (the FP8 GEMM): CUDA events around every launch of one eager step
+    peaks = measured_peaks()
+    eng._graph_saved, eng._graph = eng._graph, None
+    try:
+        recs = timed_launches(ctx, ops, ["gemm", "gemm_qkv", "gemm_group"], eng.step)
+    finally:
+        eng._graph = eng._graph_saved
+
+    def flops_of(name, a):
+        probs = a[0] if name == "gemm_group" else [dict(a=a[0], w=a[1])]
+        return sum(2.0 * p["a"].shape[0] * p["a"].shape[1] * p["w"].shape[0] for p in probs)
+
+    gemm_flops = sum(flops_of(n, a) for n, a, _, _ in recs)
+    gemm_ms = sum(r[3] for r in recs)
+    fp8 = args.fmt != "bf16"          # any 8-bit weight format: the tensor pipe runs at twice the bf16 rate
+    int8 = args.fmt.startswith("int8")
+    kind = "int8" if int8 else "fp8"
+    mult = 2.0 if fp8 else 1.0
+    ach_tf = gemm_flops / (gemm_ms * 1e-3) / 1e12
+    lin_f, attn_f = flux_step_flops(cfg)
+    lib_tf = library_fp8_gemm_tflops(torch, dev) if (fp8 and not int8 and ctx.rank == 0) else None
+    roofline = {"kernel": f"gemm_kernel<{kind}> (256x256 CTA-pair tiles; 128x128 for the text stream)" if fp8
+                else "gemm_kernel<bf16>", "bound": "tensor",
+                "achieved": ach_tf, "peak": mult * peaks["bf16_sustained"], "unit": "TFLOP/s",
+                "frac": ach_tf / (mult * peaks["bf16_sustained"]),
+                "peak_source": (f"{'2 x ' if fp8 else ''}bf16_tflops_sustained of MEASURED_PEAKS.json ({peaks['source']}): "
+                                f"the launches are timed inside a step under the power cap"
+                                + ("; no 8-bit peak was measured by the driver, 2 x the bf16 figure is assumed" if fp8 else "")),
+                "peak_burst": mult * peaks["bf16"], "frac_of_burst_peak": ach_tf / (mult * peaks["bf16"]),
+                "library_fp8_gemm_tflops_8192": lib_tf,
+                "traffic": None, "traffic_source": "not measured in this run (needs an ncu capture)",
+                "launches_per_step": len(recs), "kernel_ms_per_step": gemm_ms,
+                "method": "CUDA events around each GEMM launch of one eager (un-graphed) step; 2MNK per launch",
+                "step_tflop": (lin_f + attn_f) / 1e12,
+                "step_frac_of_roofline": ((lin_f / (mult * peaks["bf16"] * 1e12) + attn_f / (peaks["bf16"] * 1e12)) * 1e3)
+                / (ms_per_step * (ctx.world if sp else 1)),
+                "step_roofline_note": "linear flops at 2 x bf16 burst peak + attention flops at the bf16 burst peak"}
+    del eng
+    torch.cuda.empty_cache()
+    return {"value": value, "ms_per_step": ms_per_step, "clocks": clocks, "parity": parity,
+            "scaling": "strong" if sp else "weak",
+            "dtype": ("int8 x int8 -> int32 (linear), bf16 (attention)" if int8
+                      else "fp8_e4m3 x fp8_e4m3 -> fp32 (linear), bf16 (attention)" if fp8 else "bf16"),
+            "e2e": {"value": (1 if sp else ctx.world) * 1e3 / e2e_ms, "unit": "steps/s", "h2d_bytes_per_step": h2d,
+                    "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms},
+            "gpu_launches_per_step": launches_per_step, "roofline": roofline}
 
 
 def run_sweeps(torch, pkg, dev):
@@ -286,15 +628,16 @@ def main():
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
-    ap.add_argument("--fmt", default="fp8_tensor")
+    ap.add_argument("--fmt", default="fp8_tensor", help="weight format of the flux / qwen workloads")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-parity", action="store_true", help="skip the correctness checks made before timing")
+    ap.add_argument("--no-oracle-parity", action="store_true", help="skip only the CPU-oracle part of them")
     ap.add_argument("--blocks", default=None, help="n_double,n_single override (reduced-depth debugging; not a bench)")
     ap.add_argument("--workload", default="both", choices=["flux", "wan", "both", "qwen", "sweeps"],
-                    help="flux: the headline line; wan: Wan-14B sequence-parallel step only; both: flux line with the "
-                         "wan result attached under 'wan'")
+                    help="both (default): the Wan sequence-parallel step as the line's value, the Flux step attached "
+                         "under 'flux' at one GPU; wan / flux / qwen: that workload alone as the line's value")
     ap.add_argument("--wan-fmt", default="fp8_channel")
     ap.add_argument("--wan-layers", type=int, default=0, help="reduced depth (debugging; not a bench)")
-    ap.add_argument("--wan-steps", type=int, default=2)
     ap.add_argument("--sp", action="store_true",
                     help="flux/qwen workloads under torchrun: ONE image, its token sequence split over all ranks (Ulysses, "
                          "strong scaling) instead of one replica per GPU")
@@ -302,38 +645,35 @@ def main():
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
-    cfg = dict(QWEN if args.workload == "qwen" else FLUX)
-    if args.blocks:
-        cfg["n_double"], cfg["n_single"] = (int(v) for v in args.blocks.split(","))
-    if args.workload == "qwen":
-        wl = ("qwen-image-arch stand-in (Flux-style double-stream blocks), 1328x1328 (6889 image + 256 text tokens of "
-              f"width 3584), batch 1, {cfg['n_double']} double blocks, weights {args.fmt}, bf16 activations")
-    else:
-        wl = ("flux1-dev-arch DiT step, 1024x1024 (4096 image + 512 text tokens), batch 1, "
-              f"{cfg['n_double']} double + {cfg['n_single']} single blocks, weights {args.fmt}, bf16 activations")
-    sp = args.sp and world > 1
-    config = {"workload": wl,
-              "parallelism": (f"sp{world} (Ulysses, one image)" if sp else f"replicas x{world}") if world > 1
-              else "single GPU",
-              "l2": "per-step working set (11.9 GB of weights) exceeds the 126 MB L2; no flush between steps"}
+    warmup = max(3, args.warmup)
+    steps = max(1, args.steps)
+    wan_headline = args.workload in ("both", "wan")
+    S_wan = WAN["frames"] * (WAN["height"] // 2) * (WAN["width"] // 2)
+    wan_cfg = {"workload": (f"wan2.1-14B-arch t2v DiT step, 81x480x832 ({S_wan} tokens, 512 context tokens), batch 1, "
+                            f"{args.wan_layers or WAN['num_layers']} blocks, weights {args.wan_fmt}, bf16 activations"),
+               "parallelism": f"sp{world} (Ulysses sequence parallel, one video)" if world > 1 else "single GPU",
+               "l2": "per-step working set (14 GB of weights, 335 MB activations per tensor) exceeds the 126 MB L2; no "
+                     "flush between steps"}
 
     if args.impl == "reference":
         if rank != 0:
             return
-        r = cpu_reference_arm(steps=max(1, args.steps), warmup=args.warmup)
+        r = (cpu_wan_arm if wan_headline else cpu_flux_arm)(steps=steps, warmup=args.warmup)
+        cfg = wan_cfg if wan_headline else {"workload": "flux1-dev-arch DiT step, 1024x1024 (4096 image + 512 text tokens), "
+                                            "batch 1, 19 double + 38 single blocks", "parallelism": "single GPU"}
         line = {"impl": "reference", "metric": "DiT denoise steps/s", "value": r["value"], "unit": "steps/s",
-                "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": r["ms_per_step"],
-                "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "fp32", "data": "synthetic",
-                "config": config, "cpu_baseline": {k: r[k] for k in ("value", "unit", "cores", "kind", "sample")},
+                "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+                # one timed "step" of this arm is the bounded sample below; `value` extrapolates it to a whole step
+                "ms_per_step": r["sample_ms"], "sample_fraction_of_a_step": r["sample_fraction"], "extrapolated": True,
+                "higher_is_better": True, "scaling": "strong" if wan_headline else "weak", "vs_baseline": None,
+                "dtype": "fp32", "data": "synthetic", "config": cfg,
+                "cpu_baseline": {k: r[k] for k in ("value", "unit", "cores", "kind", "sample")},
                 "e2e": {"value": r["value"], "unit": "steps/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
         print(json.dumps(line), flush=True)
         return
 
     import torch
     pkg = load_package()
-    ops = pkg.ops
-    synth = importlib.import_module("diffsynth_engine_b200.synth")
-    flux = importlib.import_module("diffsynth_engine_b200.flux")
     if not torch.cuda.is_available():
         raise SystemExit("bench.py needs a CUDA device: the library has no CPU path")
     torch.cuda.set_device(local_rank)
@@ -344,170 +684,56 @@ def main():
             os.environ["NCCL_DEBUG"] = "WARN"   # keep NCCL's version banner off stdout: one JSON line only
         import torch.distributed as dist
         dist.init_process_group("nccl", device_id=dev)
+    ctx = Ctx(torch, pkg, dev, dist, rank, world, local_rank)
 
     if args.workload == "sweeps":
         if rank == 0:
             print(json.dumps(run_sweeps(torch, pkg, dev)), flush=True)
         return
-    if args.workload == "wan":
-        r = run_wan(args, torch, pkg, synth, dev, dist, rank, world, max(1, args.steps), max(1, min(args.warmup, 3)))
-        if rank == 0:
-            line = {"metric": "DiT denoise steps/s", "value": r["steps_per_s"], "unit": "steps/s", "n_gpus": world,
-                    "steps": args.steps, "warmup": max(1, min(args.warmup, 3)), "ms_per_step": r["ms_per_step"],
-                    "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
-                    "dtype": "fp8_e4m3 linear, bf16 attention" if args.wan_fmt != "bf16" else "bf16",
-                    "data": "synthetic", "config": {"workload": r["workload"], "parallelism": f"sp{world}"},
-                    "e2e": {"value": r["e2e_steps_per_s"], "unit": "steps/s",
-                            "h2d_bytes_per_step": r["h2d_bytes_per_step"], "d2h_bytes_per_step": r["d2h_bytes_per_step"]},
-                    "gpu_launches": r["gpu_launches_per_step"] * args.steps, "wan": r}
-            print(json.dumps(line), flush=True)
-        if dist is not None:
-            dist.barrier()
-            dist.destroy_process_group()
-        return
 
-    # random-init weights of the architecture, drawn on the device, packed to FP8 layer by layer
-    shapes = synth.flux_dit_shapes(d=cfg["d"], H=cfg["H"], n_double=cfg["n_double"], n_single=cfg["n_single"],
-                                   txt_dim=cfg["txt_dim"], pooled_dim=cfg["pooled_dim"])
-    seed = 0 if sp else rank            # sequence parallel: every rank holds the same model and the same inputs
-    sd = synth.make_state_dict(shapes, seed=seed, device=dev, dtype=torch.bfloat16)
-    eng = flux.FluxDiTEngine(sd, fmt=args.fmt, device=dev, n_double=cfg["n_double"], n_single=cfg["n_single"],
-                             num_heads=cfg["H"], release_source=True, group=dist.group.WORLD if sp else None)
-    del sd
-    torch.cuda.empty_cache()
-    eng.prepare(cfg["S_txt"], cfg["height"], cfg["width"], cfg["txt_dim"], cfg["pooled_dim"])
-    # inputs on the host (pinned), as a pipeline would hold them between steps
-    h_lat = synth.randn((1, 16, cfg["height"], cfg["width"]), 100 + seed).bfloat16().pin_memory()
-    h_pe = synth.randn((1, cfg["S_txt"], cfg["txt_dim"]), 200 + seed).bfloat16().pin_memory()
-    h_pool = synth.randn((1, cfg["pooled_dim"]), 300 + seed).pin_memory()
-    h_t, h_g = torch.tensor([500.0]).pin_memory(), torch.tensor([3.5]).pin_memory()
-    h_out = torch.empty((1, 16, cfg["height"], cfg["width"]), dtype=torch.bfloat16).pin_memory()
-    h2d = sum(t.numel() * t.element_size() for t in (h_lat, h_pe, h_pool, h_t, h_g))
-    d2h = h_out.numel() * h_out.element_size()
-    eng.set_inputs(h_lat, h_t, h_pe, h_pool, h_g)
-    n0 = pkg._lib.launches
-    eng.step()
-    launches_per_step = pkg._lib.launches - n0
-    torch.cuda.synchronize()
-    ops.check_status(local_rank)
-    eng.capture()
-
-    def barrier():
-        torch.cuda.synchronize()
-        if dist is not None:
-            dist.barrier()
-        torch.cuda.synchronize()
-
-    def max_over_ranks(ms):
-        if dist is None:
-            return ms
-        t = torch.tensor([ms], device=dev)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        return float(t.item())
-
-    # ---- device-resident throughput
-    for _ in range(max(3, args.warmup)):
-        eng.step()
-    sampler = ClockSampler(local_rank).start() if rank == 0 else None
-    barrier()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    torch.cuda.profiler.start()  # lets `ncu --profile-from-start off` see exactly the timed region
-    e0.record()
-    for _ in range(args.steps):
-        eng.step()
-    e1.record()
-    barrier()
-    torch.cuda.profiler.stop()
-    ms_total = max_over_ranks(e0.elapsed_time(e1))
-    clocks = sampler.stop() if sampler else None
-    ms_per_step = ms_total / args.steps
-    value = (1 if sp else world) * 1e3 / ms_per_step
-
-    # ---- end to end: host buffers in, host buffer out, every step
-    def e2e_step():
-        eng.set_inputs(h_lat, h_t, h_pe, h_pool, h_g)
-        out = eng.step()
-        h_out.copy_(out, non_blocking=True)
-        torch.cuda.current_stream().synchronize()
-
-    for _ in range(3):
-        e2e_step()
-    barrier()
-    t0 = time.perf_counter()
-    e0.record()
-    for _ in range(args.steps):
-        e2e_step()
-    e1.record()
-    barrier()
-    e2e_ms = max_over_ranks(max(e0.elapsed_time(e1), 0.0)) / args.steps
-    e2e_wall_ms = (time.perf_counter() - t0) * 1e3 / args.steps
-    ops.check_status(local_rank)
-
-    # ---- roofline of the dominant kernel (the FP8 GEMM): CUDA events around every launch of one eager step
-    peaks = measured_peaks()
-    recs = []
-    real_gemm, real_gemm_qkv, real_group = ops.gemm, ops.gemm_qkv, ops.gemm_group
-
-    def timed(fn, grouped=False):
-        def wrapper(a, *rest, **kw):
-            s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            s.record()
-            r = fn(a, *rest, **kw)
-            e.record()
-            probs = a if grouped else [dict(a=a, w=rest[0])]
-            recs.append((sum(2.0 * p["a"].shape[0] * p["a"].shape[1] * p["w"].shape[0] for p in probs), s, e))
-            return r
-        return wrapper
-
-    eng._graph_saved, eng._graph = eng._graph, None
-    # all three entry points launch gemm_kernel (a grouped launch runs two problems in one persistent grid)
-    ops.gemm, ops.gemm_qkv, ops.gemm_group = timed(real_gemm), timed(real_gemm_qkv), timed(real_group, True)
-    try:
-        eng.step()
-        torch.cuda.synchronize()
-    finally:
-        ops.gemm, ops.gemm_qkv, ops.gemm_group = real_gemm, real_gemm_qkv, real_group
-        eng._graph = eng._graph_saved
-    gemm_flops = sum(r[0] for r in recs)
-    gemm_ms = sum(r[1].elapsed_time(r[2]) for r in recs)
-    fp8 = args.fmt != "bf16"          # any 8-bit weight format: the tensor pipe runs at twice the bf16 rate
-    int8 = args.fmt.startswith("int8")
-    kind = "int8" if int8 else "fp8"
-    peak_tf = peaks["bf16"] * (2.0 if fp8 else 1.0)
-    ach_tf = gemm_flops / (gemm_ms * 1e-3) / 1e12
-    lin_f, attn_f = flux_step_flops(cfg)
-    roofline = {"kernel": f"gemm_kernel<{kind}> (256x256 CTA-pair tiles; 128x128 for the text stream)" if fp8
-                else "gemm_kernel<bf16>", "bound": "tensor",
-                "achieved": ach_tf, "peak": peak_tf, "unit": "TFLOP/s", "frac": ach_tf / peak_tf,
-                # DRAM read+write bytes per GEMM launch: ncu capture of the 1+1-block case scaled by the block counts to the
-                # step's 30.8 GB of GEMM traffic, over this step's GEMM launches
-                # (the ncu summary of per-kernel DRAM traffic under profiles/); only meaningful for the full 19+38-block FP8 model
-                "traffic": (30.8e9 / max(1, len(recs)) if (fp8 and not int8 and not args.blocks and args.workload != "qwen" and not sp) else None),
-                "peak_source": (f"2 x bf16_tflops of MEASURED_PEAKS.json ({peaks['source']}); no 8-bit peak was measured"
-                                if fp8 else f"bf16_tflops of MEASURED_PEAKS.json ({peaks['source']})"),
-                "launches_per_step": len(recs), "gemm_ms_per_step": gemm_ms,
-                "method": "CUDA events around each GEMM launch of one eager (un-graphed) step; 2MNK per launch",
-                "step_tflop": (lin_f + attn_f) / 1e12,
-                "step_frac_of_roofline": ((lin_f / (peak_tf * 1e12) + attn_f / (peaks["bf16"] * 1e12)) * 1e3) / (ms_per_step * (world if sp else 1))}
-
-    line = {"metric": "DiT denoise steps/s", "value": value, "unit": "steps/s", "n_gpus": world, "steps": args.steps,
-            "warmup": max(3, args.warmup), "ms_per_step": ms_per_step, "higher_is_better": True,
-            "scaling": "strong" if sp else "weak",
-            "vs_baseline": None,
-            "dtype": ("int8 x int8 -> int32 (linear), bf16 (attention)" if int8
-                      else "fp8_e4m3 x fp8_e4m3 -> fp32 (linear), bf16 (attention)" if fp8 else "bf16"),
-            "data": "synthetic", "config": config, "clocks": clocks,
-            "e2e": {"value": (1 if sp else world) * 1e3 / e2e_ms, "unit": "steps/s", "h2d_bytes_per_step": h2d,
-                    "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms, "wall_ms_per_step": e2e_wall_ms},
-            "gpu_launches": launches_per_step * args.steps, "gpu_launches_per_step": launches_per_step,
-            "roofline": roofline}
-    if args.workload == "both":
-        del eng
-        torch.cuda.empty_cache()
-        line["wan"] = run_wan(args, torch, pkg, synth, dev, dist, rank, world, args.wan_steps, 1)
+    line = {"metric": "DiT denoise steps/s", "unit": "steps/s", "n_gpus": world, "steps": steps, "warmup": warmup,
+            "higher_is_better": True, "vs_baseline": None, "data": "synthetic"}
+    if wan_headline:
+        r = run_wan(ctx, args, steps, warmup)
+        line.update({"value": r["steps_per_s"], "ms_per_step": r["ms_per_step"], "scaling": "strong",
+                     "dtype": "fp8_e4m3 x fp8_e4m3 -> fp32 (linear), bf16 (attention)" if args.wan_fmt != "bf16" else "bf16",
+                     "config": wan_cfg, "clocks": r["clocks"],
+                     "e2e": {"value": r["e2e_steps_per_s"], "unit": "steps/s", "ms_per_step": r["e2e_ms_per_step"],
+                             "h2d_bytes_per_step": r["h2d_bytes_per_step"], "d2h_bytes_per_step": r["d2h_bytes_per_step"]},
+                     "gpu_launches": r["gpu_launches_per_step"] * steps,
+                     "gpu_launches_per_step": r["gpu_launches_per_step"],
+                     "roofline": r["roofline"], "parity": r["parity"]})
+        if args.workload == "both" and world == 1:
+            f = run_flux(ctx, args, dict(FLUX), "flux", steps, warmup)
+            f["config"] = {"workload": "flux1-dev-arch DiT step, 1024x1024 (4096 image + 512 text tokens), batch 1, "
+                                       f"19 double + 38 single blocks, weights {args.fmt}, bf16 activations",
+                           "parallelism": "single GPU", "launch": "CUDA-graph replay of the step"}
+            f["metric"], f["unit"] = "DiT denoise steps/s", "steps/s"
+            line["flux"] = f
+    else:
+        cfg = dict(QWEN if args.workload == "qwen" else FLUX)
+        if args.blocks:
+            cfg["n_double"], cfg["n_single"] = (int(v) for v in args.blocks.split(","))
+        sp = args.sp and world > 1
+        if args.workload == "qwen":
+            wl = ("qwen-image-arch stand-in (Flux-style double-stream blocks), 1328x1328 (6889 image + 256 text tokens of "
+                  f"width 3584), batch 1, {cfg['n_double']} double blocks, weights {args.fmt}, bf16 activations")
+        else:
+            wl = ("flux1-dev-arch DiT step, 1024x1024 (4096 image + 512 text tokens), batch 1, "
+                  f"{cfg['n_double']} double + {cfg['n_single']} single blocks, weights {args.fmt}, bf16 activations")
+        f = run_flux(ctx, args, cfg, args.workload, steps, warmup)
+        line.update({"value": f["value"], "ms_per_step": f["ms_per_step"], "scaling": f["scaling"], "dtype": f["dtype"],
+                     "config": {"workload": wl,
+                                "parallelism": (f"sp{world} (Ulysses, one image)" if sp else f"replicas x{world}")
+                                if world > 1 else "single GPU",
+                                "l2": "per-step working set (11.9 GB of weights) exceeds the 126 MB L2; no flush "
+                                      "between steps"},
+                     "clocks": f["clocks"], "e2e": f["e2e"], "gpu_launches": f["gpu_launches_per_step"] * steps,
+                     "gpu_launches_per_step": f["gpu_launches_per_step"], "roofline": f["roofline"],
+                     "parity": f["parity"]})
     if rank == 0:
         if not args.no_cpu_baseline and world == 1:
-            r = cpu_reference_arm(steps=1, warmup=0)
+            r = (cpu_wan_arm if wan_headline else cpu_flux_arm)(steps=2, warmup=0, budget_s=40.0)
             line["cpu_baseline"] = {k: r[k] for k in ("value", "unit", "cores", "kind", "sample")}
         print(json.dumps(line), flush=True)
     if dist is not None:

@@ -26,6 +26,7 @@ c_i, c_i64, c_f, c_p = ctypes.c_int, ctypes.c_int64, ctypes.c_float, ctypes.c_vo
 # argument lists, in the order of include/dsb.h
 _SIGS = {
     "dsb_version": [],
+    "dsb_selftest_wait_timeout": [ctypes.c_longlong, c_p, c_p, c_p],
     "dsb_ln_modulate": [c_p, c_i64, c_p, c_p, c_p, c_i64, c_p, c_i, c_i, c_f, c_i, c_p],
     "dsb_ln_modulate2": [c_p, c_i64, c_p, c_p, c_i, c_p, c_p, c_p, c_i64, c_p, c_i, c_i, c_f, c_i, c_p],
     "dsb_gate_residual": [c_p, c_i64, c_p, c_i64, c_p, c_p, c_i64, c_i, c_i, c_p],

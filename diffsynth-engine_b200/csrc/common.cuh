@@ -77,20 +77,24 @@ __device__ __forceinline__ uint32_t mbar_try_wait(uint64_t* bar, uint32_t parity
 }
 // Bounded wait.  Returns false when the budget ran out or another role of the
 // CTA already gave up; the caller must then leave its loop.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
+__device__ __forceinline__ bool mbar_wait_limit(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
+                                                long long limit_cycles) {
   if (mbar_try_wait(bar, parity)) return true;
   const long long t0 = clock64();
   uint32_t spins = 0;
   while (!mbar_try_wait(bar, parity)) {
     if (((++spins) & 0xffu) == 0) {
       if (*abort_flag) return false;
-      if (clock64() - t0 > kWaitLimitCycles) {
+      if (clock64() - t0 > limit_cycles) {
         *abort_flag = 1;
         return false;
       }
     }
   }
   return true;
+}
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
+  return mbar_wait_limit(bar, parity, abort_flag, kWaitLimitCycles);
 }
 
 // Latency-critical variant: polls with the non-suspending test_wait, so the waiter notices the phase flip within a

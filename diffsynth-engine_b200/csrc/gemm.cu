@@ -16,7 +16,6 @@
 // HBM layout: A and W are row-major with K contiguous, so both operands are
 // "K-major" for the tensor core and no transpose or repack is ever needed; the
 // FP8/INT8 payload is the plain [N,K] byte matrix produced by the prepack.
-#include <cstdlib>
 #include <mutex>
 
 #include "common.cuh"
@@ -544,17 +543,6 @@ static int launch_group(GemmGroup& grp, cudaStream_t st) {
   return cudaGetLastError() == cudaSuccess ? DSB_OK : DSB_ERR_CUDA;
 }
 
-// CTA pairs (256 x 256 tiles) are used when the problem has enough rows to fill them; DSB_GEMM_PAIR=0 in the
-// environment turns them off (single-CTA tiles only).
-static bool pair_mode_enabled() {
-  static int v = -1;
-  if (v < 0) {
-    const char* e = getenv("DSB_GEMM_PAIR");
-    v = (e && e[0] == '0') ? 0 : 1;
-  }
-  return v == 1;
-}
-
 // Tile width: 256 columns unless that leaves SMs idle that 128-wide tiles would fill.
 static int pick_block_n(int M, int N) {
   const int tm = (M + kBlockM - 1) / kBlockM;
@@ -683,7 +671,8 @@ extern "C" int dsb_gemm_group(const dsb_gemm_args* args, int count, int fmt, int
     any_norm = any_norm || live[i]->nq_w != nullptr || live[i]->out0_fmt == DSB_FMT_E4M3 ||
                (live[i]->out1 && live[i]->out1_fmt == DSB_FMT_E4M3);  // both need a warp's full 128 columns
   const int bn = any_norm ? 256 : pick_block_n(live[0]->M, live[0]->N);
-  const bool pair = pair_mode_enabled() && bn == 256 && live[0]->M > 256 && live[0]->N >= 256;
+  // CTA pairs (256 x 256 tiles) when the first problem has enough rows to fill them
+  const bool pair = bn == 256 && live[0]->M > 256 && live[0]->N >= 256;
   for (int i = 0; i < grp.count; ++i) {
     const int rc = shape_problem(*live[i], fmt, bn, pair ? 2 : 1, &grp.p[i]);
     if (rc != DSB_OK) return rc;

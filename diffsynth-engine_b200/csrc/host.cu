@@ -111,11 +111,44 @@ __global__ void __launch_bounds__(256) pack_rows_kernel(const void* __restrict__
   }
 }
 
+// The give-up path of the bounded waits, exercised on purpose: one warp waits on a barrier that nothing ever
+// arrives at, with a short cycle budget; a second warp stands for the other roles of a real kernel, polls the abort
+// flag and leaves when it is raised.  Both meet at the common exit, where the status word is written - the same
+// sequence the GEMM and attention kernels run when a wait of theirs runs out.
+__global__ void __launch_bounds__(64) wait_timeout_selftest_kernel(long long limit_cycles, int* status, int* left) {
+  __shared__ uint64_t bar;
+  __shared__ int abort_word;
+  volatile int* abort_flag = &abort_word;
+  if (threadIdx.x == 0) {
+    mbar_init(&bar, 1);
+    *abort_flag = 0;
+    fence_mbar_init();
+  }
+  __syncthreads();
+  const int warp = threadIdx.x >> 5;
+  if (warp == 0) {
+    if (threadIdx.x == 0) mbar_wait_limit(&bar, 0, abort_flag, limit_cycles);   // nobody arrives: must give up
+  } else if (threadIdx.x == 32) {
+    // a neighbour role: its own (long) wait on the same barrier ends as soon as the first role has given up
+    const bool done = mbar_wait(&bar, 0, abort_flag);
+    if (left) *left = done ? 0 : 1;
+  }
+  __syncthreads();
+  if (threadIdx.x == 0 && *abort_flag && status) atomicCAS(status, 0, DSB_ERR_TIMEOUT);
+}
+
 }  // namespace dsb
 
 using namespace dsb;
 
 extern "C" int dsb_version(void) { return 100; }
+
+extern "C" int dsb_selftest_wait_timeout(long long limit_cycles, int* status, int* neighbour_left, void* stream) {
+  if (!status || limit_cycles <= 0 || limit_cycles > kWaitLimitCycles) return DSB_ERR_ARG;
+  wait_timeout_selftest_kernel<<<1, 64, 0, reinterpret_cast<cudaStream_t>(stream)>>>(limit_cycles, status,
+                                                                                      neighbour_left);
+  return cudaGetLastError() == cudaSuccess ? DSB_OK : DSB_ERR_CUDA;
+}
 
 extern "C" int dsb_pack_quant_weight(const void* W, int64_t ld_w, int src_is_bf16, void* Wq, int64_t ld_q,
                                      float* scales, int N, int K, int fmt, int per_channel, float* work,

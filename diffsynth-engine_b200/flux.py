@@ -37,6 +37,14 @@ def flux_rope_table(ids: torch.Tensor, axes_dim=(16, 56, 56), theta=10000) -> to
     return torch.cat(cols, dim=1).float().contiguous()
 
 
+def _ids_key(ids: Optional[torch.Tensor]):
+    """Identity of a position-id tensor for the engine's geometry cache: None (default ids), else its shape and
+    content (a few KB; the synchronising copy happens once per forward, next to the input copies)."""
+    if ids is None:
+        return None
+    return (tuple(ids.shape), ids.detach().float().cpu().numpy().tobytes())
+
+
 def sequence_slice(S_txt: int, S_img: int, world: int, rank: int) -> Dict[str, int]:
     """This rank's contiguous slice of the joint [text | image] token sequence under sequence parallelism: the
     sequence is padded to ``S_pad`` (a multiple of ``world``), rank r owns rows ``[g0, g0 + Sl)``; of its local rows
@@ -60,6 +68,8 @@ class FluxDiTEngine:
         self.xchg = HeadExchange(group)
         # without a group the engine is a one-GPU replica even inside an initialised process group
         self.P, self.rank = (self.xchg.world, self.xchg.rank) if group is not None else (1, 0)
+        if group is None:
+            self.xchg.world, self.xchg.rank = 1, 0
         if num_heads % self.P:
             raise ValueError(f"{num_heads} heads do not split over {self.P} ranks")
         self.dev = torch.device(device)
@@ -365,11 +375,18 @@ class FluxDiTEngine:
     def forward(self, hidden_states, timestep, prompt_emb, pooled_prompt_emb, guidance, text_ids=None,
                 image_ids=None, **kwargs):
         """Signature of ``FluxDiT.forward`` (flux_dit.py:392-403), batch 1."""
+        if hidden_states.shape[0] != 1 or prompt_emb.shape[0] != 1:
+            raise ValueError("FluxDiTEngine runs one sample per call (batch 1)")
         S_txt = prompt_emb.shape[1]
         height, width = hidden_states.shape[-2:]
         b = self._bufs
-        if b is None or (b["S_txt"], b["height"], b["width"]) != (S_txt, height, width):
+        # buffers and the RoPE table belong to one geometry, one pair of embedding widths and one set of position ids
+        # (the reference recomputes the table from the ids on every call, flux_dit.py:417)
+        key = (S_txt, height, width, prompt_emb.shape[-1], pooled_prompt_emb.shape[-1], _ids_key(text_ids),
+               _ids_key(image_ids))
+        if b is None or b.get("key") != key:
             self.prepare(S_txt, height, width, prompt_emb.shape[-1], pooled_prompt_emb.shape[-1], text_ids, image_ids)
+            self._bufs["key"] = key
         self.set_inputs(hidden_states, timestep, prompt_emb, pooled_prompt_emb, guidance)
         return self.step().clone()
 

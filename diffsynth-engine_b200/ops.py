@@ -21,9 +21,24 @@ def _stream():
 
 
 def _require_cuda(*ts):
+    """Every tensor of a call must live on the CURRENT CUDA device: kernels launch on its current stream, and the
+    status word and the static scratch of ``dsb_linear_static`` belong to it."""
+    cur = None
     for t in ts:
-        if t is not None and not t.is_cuda:
+        if t is None:
+            continue
+        if not t.is_cuda:
             raise _lib.DsbError("dsb ops take CUDA tensors only (no CPU fallback exists)")
+        if cur is None:
+            cur = torch.cuda.current_device()
+        if t.device.index != cur:
+            raise _lib.DsbError(f"tensor on cuda:{t.device.index} but the current device is cuda:{cur}: wrap the call "
+                                "in torch.cuda.device(tensor.device)")
+
+
+def _require_bf16(t, what):
+    if t.dtype != torch.bfloat16:
+        raise _lib.DsbError(f"{what} takes bf16 rows, got {t.dtype}")
 
 
 def status_word(device) -> torch.Tensor:
@@ -41,6 +56,19 @@ def check_status(device=None):
     if code != 0:
         status_word(dev).zero_()
         _lib.check(code, "device kernel")
+
+
+def selftest_wait_timeout(limit_cycles: int = 2_000_000, device=None):
+    """Runs ``dsb_selftest_wait_timeout`` on its own status word; returns ``(status, neighbour_left)`` as Python
+    ints (synchronises).  A healthy library returns ``(ERR_TIMEOUT, 1)`` after about ``limit_cycles`` SM cycles."""
+    dev = torch.device("cuda", torch.cuda.current_device() if device is None else device)
+    with torch.cuda.device(dev):
+        words = torch.zeros(2, dtype=torch.int32, device=dev)
+        rc = _lib.lib().dsb_selftest_wait_timeout(int(limit_cycles), ctypes.c_void_p(words.data_ptr()),
+                                                  ctypes.c_void_p(words.data_ptr() + 4), _stream())
+        check(rc, "dsb_selftest_wait_timeout")
+        status, left = words.tolist()
+    return status, left
 
 
 def _fmt_of(t: torch.Tensor) -> int:
@@ -126,7 +154,8 @@ def rmsnorm_full(buf, w, rope=None, rope_row0=0, eps=1e-6, out=None, chunks=1):
 
 
 def quant_rows(x, out_fmt=FMT_E4M3, out=None, row_scale=None):
-    _require_cuda(x)
+    _require_cuda(x, out, row_scale)
+    _require_bf16(x, "quant_rows")
     M, K, ld_x = _rows(x)
     if out is None:
         out = torch.empty((M, K), dtype=_OUT_DTYPE[out_fmt], device=x.device)
@@ -375,6 +404,7 @@ def linear_static(x, w_payload, w_scale, bias=None, act=ACT_NONE, out=None):
     include/dsb.h for who needs that, the size limit and the sharing rules).  Only the output is allocated here,
     and not at all when ``out`` is given."""
     _require_cuda(x, w_payload, w_scale, bias, out)
+    _require_bf16(x, "linear_static")
     M, K, ld_x = _rows(x)
     N, Kw, ld_w = _rows(w_payload)
     if K != Kw:

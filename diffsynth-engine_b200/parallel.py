@@ -31,27 +31,28 @@ class ParallelWorkerError(RuntimeError):
     pass
 
 
-def to_device(data, device):
-    if isinstance(data, dict):
-        return {k: to_device(v, device) for k, v in data.items()}
-    if isinstance(data, (tuple, list)):
-        return [to_device(t, device) for t in data]
-    if isinstance(data, torch.Tensor):
-        return data.to(device)
-    return data
+def map_tensors(tree, fn):
+    """A copy of a nest of dicts / lists / tuples with ``fn`` applied to every tensor leaf (sequences come back as
+    lists, other leaves unchanged)."""
+    if torch.is_tensor(tree):
+        return fn(tree)
+    if isinstance(tree, dict):
+        return {key: map_tensors(value, fn) for key, value in tree.items()}
+    if isinstance(tree, (list, tuple)):
+        return [map_tensors(value, fn) for value in tree]
+    return tree
 
 
-def split_and_get(data, num, index):
-    """Batch split of every tensor leaf (parallel.py:50-59 of the reference, same error)."""
-    if isinstance(data, dict):
-        return {k: split_and_get(v, num, index) for k, v in data.items()}
-    if isinstance(data, (tuple, list)):
-        return [split_and_get(t, num, index) for t in data]
-    if isinstance(data, torch.Tensor):
-        if data.shape[0] < num:
+def batch_slice(tree, parts: int, index: int):
+    """Part ``index`` of ``parts`` equal slices along dimension 0 of every tensor leaf: the batch split of the
+    reference's CFG / batch parallelism (utils/parallel.py:50-59 raises the same ValueError for a batch that is too
+    small)."""
+    def take(t):
+        if t.shape[0] < parts:
             raise ValueError("data.shape[0] < num, batch split failed")
-        return torch.split(data, data.shape[0] // num, dim=0)[index]
-    return data
+        step = t.shape[0] // parts
+        return t.narrow(0, index * step, step)
+    return map_tensors(tree, take) if parts > 1 else tree
 
 
 def wan_engine_factory(state_dict, rank, sp_group, device, **engine_kwargs):
@@ -118,6 +119,10 @@ def _worker_loop(rank: int, world_size: int, conn, payload, factory: Callable, s
         os.environ["MASTER_ADDR"] = "127.0.0.1"
         os.environ["MASTER_PORT"] = str(master_port)
         if device.startswith("cuda"):
+            # A worker that fails leaves between steps, but the parent may also end survivors (close()).  A rank that
+            # dies while its buffers are bound to an NVLink multicast object can fault the GPUs of the other ranks, so
+            # this wrapper's NCCL never uses NVLS; the head exchange is an all-to-all, which NVLS does not serve anyway.
+            os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
             torch.cuda.set_device(rank)
             dev = f"cuda:{rank}"
         else:
@@ -135,7 +140,7 @@ def _worker_loop(rank: int, world_size: int, conn, payload, factory: Callable, s
             kwargs = _share_step_inputs(conn.recv() if rank == 0 else None, rank, dev)
             if isinstance(kwargs, str) and kwargs == TERMINATE:
                 break
-            kwargs = split_and_get(kwargs, batch_parallelism, bp_row)
+            kwargs = batch_slice(kwargs, batch_parallelism, bp_row)
             with torch.no_grad():
                 result = model(**kwargs)
             if sp_rank == 0 and batch_parallelism > 1:

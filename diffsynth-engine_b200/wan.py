@@ -76,7 +76,10 @@ class WanDiTEngine:
         self.fmt, self.afmt = fmt, act_format(fmt)
         self.L, self.H, self.eps, self.freq_dim = num_layers, num_heads, eps, freq_dim
         self.xchg = HeadExchange(group)
-        self.P, self.rank = self.xchg.world, self.xchg.rank
+        # without a group the engine is a one-GPU replica even inside an initialised process group
+        self.P, self.rank = (self.xchg.world, self.xchg.rank) if group is not None else (1, 0)
+        if group is None:
+            self.xchg.world, self.xchg.rank = 1, 0
         if num_heads % self.P:
             raise ValueError(f"{num_heads} heads do not split over {self.P} ranks")
         sd = state_dict
@@ -386,6 +389,9 @@ class WanDiTEngine:
     def forward(self, x, context, timestep, clip_feature=None, y=None):
         """Signature of ``WanDiT.forward`` (wan_dit.py:319-326).  ``clip_feature`` [1,257,1280] and ``y`` (conditioning
         latents on the grid of ``x``) are required by image-to-video weights and rejected by text-to-video ones."""
+        if x.shape[0] != 1 or context.shape[0] != 1:
+            raise ValueError("WanDiTEngine runs one sample per call (batch 1); split a CFG batch into two calls or use "
+                             "UlyssesParallelModel(batch_parallelism=2)")
         b = self._bufs
         shape = (x.shape[2], x.shape[3], x.shape[4], context.shape[1], context.shape[2])
         if b is None or (b["latents"].shape[2], b["latents"].shape[3], b["latents"].shape[4], b["ctx_len"],

@@ -49,6 +49,14 @@ extern "C" {
 /* Library/ABI version (major*100 + minor). */
 int dsb_version(void);
 
+/* Self-test of the bounded device waits (no counterpart in the reference, which has no device-side waits): a
+ * one-CTA kernel in which one role waits, for at most `limit_cycles` SM cycles (<= 2e9), on a barrier nothing ever
+ * arrives at, while a second role waits on the same barrier with the library's ordinary one-second budget.  The
+ * first role gives up and raises the CTA's abort flag, the second sees the flag and leaves too (`*neighbour_left`
+ * = 1), and `*status` becomes DSB_ERR_TIMEOUT - the sequence every kernel of this library follows when a wait of
+ * its own runs out.  The context stays usable.  `status` must be 0 on entry to observe the result. */
+int dsb_selftest_wait_timeout(long long limit_cycles, int* status, int* neighbour_left, void* stream);
+
 /*
  * AdaLN: y = LayerNorm(x; eps, no affine) * (1 + scale[d]) + shift[d] over rows of width D.
  * out_fmt BF16 writes bf16; E4M3 / INT8 write the quantised operand of the next GEMM and

@@ -31,8 +31,11 @@ def _rope(x, table, H):
     return O.apply_rope_pairs(_mh(x, H), table).transpose(0, 1).reshape(x.shape[0], -1)
 
 
-def wan_block(x, context, t_mod, table, w, pre, H, lin: LinearEval, rt=_ident, eps=1e-6):
-    """DiTBlock.forward, wan_dit.py:185-193.  x [S,d], context [L,d], t_mod [6,d]."""
+def wan_block(x, context, t_mod, table, w, pre, H, lin: LinearEval, rt=_ident, eps=1e-6, other_kv=None):
+    """DiTBlock.forward, wan_dit.py:185-193.  x [S,d], context [L,d], t_mod [6,d].
+    ``other_kv = (k, v)``: keys and values (normalised and rotated, [S', d]) of tokens OUTSIDE ``x`` that the
+    self-attention also attends to - the block as one rank of a sequence-parallel group evaluates it (its own token
+    slice as queries, everybody's tokens as keys); used by the benchmark's CPU arm to time a 1/P share of a block."""
     mod = w[pre + "modulation"].float().reshape(6, -1) + t_mod.float()
     sh_msa, sc_msa, g_msa, sh_mlp, sc_mlp, g_mlp = mod
     def L(inp, name, **kw):
@@ -44,6 +47,8 @@ def wan_block(x, context, t_mod, table, w, pre, H, lin: LinearEval, rt=_ident, e
     k = O.rmsnorm(rt(L(n, "self_attn.k", from_fp32=True)), w[pre + "self_attn.norm_k.weight"], eps)
     v = rt(L(n, "self_attn.v", from_fp32=True))
     q, k = rt(_rope(q, table, H)), rt(_rope(k, table, H))
+    if other_kv is not None:
+        k, v = torch.cat([k, other_kv[0]], dim=0), torch.cat([v, other_kv[1]], dim=0)
     x = rt(x.float() + g_msa * L(rt(_attend(q, k, v, H, rt)), "self_attn.o"))
     # cross-attention, wan_dit.py:136-152; norm3 is an affine LayerNorm (:178,190).  Image-to-video models carry
     # k_img/v_img: the first 257 context rows are CLIP tokens with their own key/value projection, attended

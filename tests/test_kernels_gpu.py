@@ -433,3 +433,20 @@ def test_gemm_e4m3_output_is_the_cast_of_the_epilogue_value(dsb, cuda_dev, M, N,
         assert O.rel_l2(o0.float().cpu(), acc[:, :split]) < 4e-3
         assert torch.equal(o1.view(torch.uint8).cpu(), out8[:, split:].contiguous().view(torch.uint8).cpu())
     dsb.ops.check_status(0)
+
+
+# ------------------------------------------------------------------------- bounded waits
+def test_bounded_wait_runs_out_and_reports_timeout(dsb, cuda_dev):
+    """A device wait that nothing ever satisfies gives up after its cycle budget: the CTA's abort flag is raised, the
+    other role leaves its own wait because of it, the status word reads DSB_ERR_TIMEOUT, and the context is still
+    good for the next launch.  (No trap, no endless loop: the wait is bounded by construction.)"""
+    import time
+    t0 = time.time()
+    status, left = dsb.ops.selftest_wait_timeout(limit_cycles=2_000_000)       # about a millisecond of SM cycles
+    assert status == dsb._lib.ERR_TIMEOUT and left == 1
+    assert time.time() - t0 < 5.0
+    # the context is intact: an ordinary kernel runs and the library's own status word was never touched
+    x = torch.randn(4, 256).to(torch.bfloat16).to(cuda_dev)
+    y, _ = dsb.ops.ln_modulate(x, torch.zeros(256, device=cuda_dev), torch.zeros(256, device=cuda_dev))
+    assert torch.isfinite(y.float()).all()
+    dsb.ops.check_status(0)

@@ -61,7 +61,8 @@ def test_flux_double_block_small():
 
 
 def test_flux_double_block_c1_config():
-    """BASELINE config 1: one double-stream block, hidden 3072, 24 heads, 1024 image + 512 text tokens, fp32."""
+    """The CPU-runnable benchmark configuration: one double-stream block, hidden 3072, 24 heads, 1024 image + 512 text
+    tokens, fp32."""
     d, H, side, S_txt = 3072, 24, 32, 512
     w = synth.make_state_dict(synth.flux_block_shapes("", d, H, "double"), seed=0)
     xa, xb, temb = synth.randn((1, side * side, d), 1)[0], synth.randn((1, S_txt, d), 2)[0], synth.randn((1, d), 3)[0]

@@ -10,7 +10,7 @@ import torch
 from tests.parallel_helpers import oracle_wan_attention, slice_attention_factory
 
 import diffsynth_engine_b200  # noqa: F401  (registers the package alias used by the worker processes)
-from diffsynth_engine_b200.parallel import ParallelWorkerError, UlyssesParallelModel, split_and_get
+from diffsynth_engine_b200.parallel import ParallelWorkerError, UlyssesParallelModel, batch_slice, map_tensors
 
 _PORT = [29720]
 
@@ -101,12 +101,17 @@ def test_worker_exit_is_detected():
         model.close(grace_s=1.0)
 
 
-def test_split_and_get_matches_reference_contract():
+def test_batch_slice_matches_reference_contract():
+    """The batch split of utils/parallel.py:50-59 of the reference: every tensor leaf, other leaves untouched, the
+    same ValueError for a batch smaller than the number of parts."""
     d = {"a": torch.arange(8).reshape(4, 2), "b": [torch.zeros(2, 1), "keep"], "c": 3}
-    s = split_and_get(d, 2, 1)
+    s = batch_slice(d, 2, 1)
     assert s["a"].tolist() == [[4, 5], [6, 7]] and s["b"][0].shape == (1, 1) and s["b"][1] == "keep" and s["c"] == 3
+    assert batch_slice(d, 1, 0) is d
     with pytest.raises(ValueError, match="batch split failed"):
-        split_and_get(torch.zeros(1, 3), 2, 0)
+        batch_slice(torch.zeros(1, 3), 2, 0)
+    doubled = map_tensors(d, lambda t: t * 2)
+    assert doubled["a"].tolist()[0] == [0, 2] and doubled["c"] == 3 and doubled["b"][1] == "keep"
 
 
 def test_joint_sequence_slices_cover_every_token_once():

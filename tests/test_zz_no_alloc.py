@@ -23,6 +23,14 @@ def _pair(dsb, dev, M, N, K, fmt, per_channel, act, seed):
     xq, rs = ops.quant_rows(x, code)                                   # caller-allocated scratch
     want = ops.gemm(xq, Wq, row_scale=rs, col_scale=ws, bias=bias, act=act)
     got = ops.linear_static(x, Wq, ws, bias=bias, act=act)             # scratch inside the library
+    # and the CPU oracle of the same quantised Linear (same quantisation rules, fp32 accumulation)
+    mode = ("fp8_channel" if per_channel else "fp8_tensor") if fmt == "e4m3" else "int8_channel"
+    oq, os_ = O.quant_weight(W.cpu(), mode)
+    aq, as_ = (O.quant_rows_e4m3 if fmt == "e4m3" else O.quant_rows_int8)(x.cpu())
+    ref = O.linear_quant(aq, as_, oq, os_, bias.cpu())
+    if act == ops.ACT_GELU_TANH:
+        ref = O.gelu_tanh(ref)
+    assert O.rel_l2(got.float().cpu(), ref) < 4e-3                     # bf16 output rounding only
     return got, want
 
 
