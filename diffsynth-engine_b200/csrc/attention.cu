@@ -322,8 +322,8 @@ __global__ void __launch_bounds__(kAttnThreads, 1)
     const float cs = p.scale_log2;
     float m_ref = 0.f;          // reference maximum (integer, log2 units) the exponentials, the row sum and O use
     float run_max = -INFINITY;  // this thread's running maximum of s*c over its columns, all tiles so far
-    // four running maxima (raw scores) and four partial row sums live across the key tiles (folded only once per
-    // tile / at the end), so no reduction chain sits between the last exponential and the hand-over of P
+    // four partial maxima (raw scores of the current tile) and four partial row sums (all tiles) are only folded
+    // once per tile / at the end, so no reduction chain sits between the last exponential and the hand-over of P
     float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
     float2 ls2[2] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
     bool ok = true;
@@ -362,7 +362,6 @@ __global__ void __launch_bounds__(kAttnThreads, 1)
             if (c * 16 + i < valid) m0 = fmaxf(m0, __uint_as_float(sa[i]));
         }
         run_max = m0 * cs;
-        mx[0] = m0;
         xchg_publish(&slot_mine[0], 1u, m0);
         float mo;
         if (!xchg_read(&slot_other[0], 1u, &mo, abort_flag)) {
@@ -401,6 +400,7 @@ __global__ void __launch_bounds__(kAttnThreads, 1)
       if (lane == 0) DSB_TR(q * 4 + quad, j, half * 8 + 1);
       const float2 cs2 = make_float2(cs, cs), nm2 = make_float2(-m_ref, -m_ref);
       uint32_t pk[16];
+      mx[0] = mx[1] = mx[2] = mx[3] = -INFINITY;  // maxima of THIS tile's raw scores
       // 16 scores (columns [16 s, 16 s + 16) of my 64) -> 8 packed probabilities pk[8 (s & 1) ..]
       auto piece = [&](const uint32_t (&sc)[16], int s16) {
         const int o = (s16 & 1) * 8;
@@ -443,7 +443,9 @@ __global__ void __launch_bounds__(kAttnThreads, 1)
       tmem_st16(t_s + 16, pk);
       if (lane == 0) DSB_TR(q * 4 + quad, j, half * 8 + 3);
       // my running maximum, for the partner's (and my) refresh test at the next tile; the arrival below releases it
-      run_max = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])) * cs;
+      // A score more than 2^100 above the reference was exponentiated as 2^100 (the clamp), so the reference may
+      // only follow it that far: the row then stays finite and is dominated by that key, as it should be.
+      run_max = fmaxf(run_max, fminf(fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])) * cs, m_ref + 100.f));
       max_mine[(j & 1) * 128] = run_max;
       hand_over(1);
       if (lane == 0) DSB_TR(q * 4 + quad, j, half * 8 + 4);

