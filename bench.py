@@ -586,6 +586,128 @@ def run_flux(ctx, args, cfg, workload, steps, warmup):
             "gpu_launches_per_step": launches_per_step, "roofline": roofline}
 
 
+def run_reference_gpu(ctx, args):
+    """The reference's own GPU path on this B200 next to the library: one Flux double-stream block, one Flux
+    single-stream block (4096 + 512 tokens, width 3072) and one Wan DiTBlock (32760 tokens, width 5120), each as
+    (a) the reference module as shipped in bf16 (cuBLAS + SDPA), (b) the reference module with its own FP8 path
+    (``enable_fp8_linear`` + ``fp8_inference``: ``torch._scaled_mm`` with unit scales), (c) this library's step engine
+    (time per block = difference between an n-block and a 1-block model).  Needs ``baseline/_ref``."""
+    torch, pkg, synth, dev = ctx.torch, ctx.pkg, ctx.synth, ctx.dev
+    sys.path.insert(0, os.path.join(ROOT, "baseline"))
+    import install_reference
+    ref = install_reference.import_reference()
+    if ref is None:
+        return {"workload": "reference-gpu", "unavailable": "baseline/_ref is not installed (python baseline/install_reference.py)"}
+    flux = importlib.import_module("diffsynth_engine_b200.flux")
+    wan = importlib.import_module("diffsynth_engine_b200.wan")
+
+    def timeit(fn, n=8, warm=2):
+        for _ in range(warm):
+            fn()
+        torch.cuda.synchronize()
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s.record()
+        for _ in range(n):
+            fn()
+        e.record()
+        torch.cuda.synchronize()
+        return s.elapsed_time(e) / n
+
+    def load(module, sd):
+        torch.nn.Module.load_state_dict(module, sd, strict=True)
+        return module.to(dev, torch.bfloat16).eval()
+
+    def both_paths(make, call):
+        with torch.no_grad():
+            blk = make()
+            t_bf16 = timeit(lambda: call(blk))
+            blk8 = make()
+            ref.fp8_linear.enable_fp8_linear(blk8)
+            origin = torch.nn.functional.linear
+            try:
+                with ref.fp8_linear.fp8_inference(True):
+                    t_fp8 = timeit(lambda: call(blk8))
+            except Exception as e:          # the reference's context manager does not restore F.linear on an error
+                t_fp8 = f"failed: {type(e).__name__}: {str(e)[:120]}"
+            finally:
+                torch.nn.functional.linear = origin
+        del blk, blk8
+        torch.cuda.empty_cache()
+        return t_bf16, t_fp8
+
+    out = {"workload": "reference-gpu", "unit": "ms per block", "rows": []}
+    # ---- Flux blocks
+    d, H, St, side = FLUX["d"], FLUX["H"], FLUX["S_txt"], FLUX["height"] // 2
+    ids = torch.zeros(St + side * side, 3)
+    r = torch.arange(side, dtype=torch.float32)
+    ids[St:, 1] = r[:, None].expand(side, side).reshape(-1)
+    ids[St:, 2] = r[None, :].expand(side, side).reshape(-1)
+    rope = ref.transformer_helper.RoPEEmbedding(d, 10000, [16, 56, 56])(ids[None]).to(dev)
+    xa, xb = synth.randn((1, side * side, d), 1, dev).bfloat16(), synth.randn((1, St, d), 2, dev).bfloat16()
+    temb = synth.randn((1, d), 3, dev).bfloat16()
+    sd_d = synth.make_state_dict(synth.flux_block_shapes("", d, H, "double"), seed=0, device=dev)
+    sd_s = synth.make_state_dict(synth.flux_block_shapes("", d, H, "single"), seed=1, device=dev)
+    t_bf16, t_fp8 = both_paths(lambda: load(ref.flux_dit.FluxJointTransformerBlock(d, H, device="cpu", dtype=torch.float32), sd_d),
+                               lambda b: b(xa, xb, temb, rope))
+    out["rows"].append({"block": "Flux double-stream (4096 + 512 tokens, d 3072)", "reference_bf16_ms": t_bf16,
+                        "reference_fp8_scaled_mm_ms": t_fp8})
+    xs = torch.cat([xb, xa], dim=1)
+    t_bf16, t_fp8 = both_paths(lambda: load(ref.flux_dit.FluxSingleTransformerBlock(d, H, device="cpu", dtype=torch.float32), sd_s),
+                               lambda b: b(xs, None, temb, rope))
+    out["rows"].append({"block": "Flux single-stream (4608 tokens, d 3072)", "reference_bf16_ms": t_bf16,
+                        "reference_fp8_scaled_mm_ms": t_fp8})
+    del sd_d, sd_s
+
+    def engine_ms(fmt, nd, ns):
+        shapes = synth.flux_dit_shapes(d=d, H=H, n_double=nd, n_single=ns)
+        eng = flux.FluxDiTEngine(synth.make_state_dict(shapes, seed=0, device=dev, dtype=torch.bfloat16), fmt=fmt, device=dev,
+                                 n_double=nd, n_single=ns, num_heads=H, release_source=True)
+        eng.prepare(St, FLUX["height"], FLUX["width"])
+        eng.step()
+        eng.capture()
+        t = timeit(eng.step)
+        del eng
+        torch.cuda.empty_cache()
+        return t
+
+    for fmt in ("bf16", "fp8_tensor"):
+        base = engine_ms(fmt, 1, 1)
+        out["rows"][0][f"library_{fmt}_ms"] = (engine_ms(fmt, 5, 1) - base) / 4
+        out["rows"][1][f"library_{fmt}_ms"] = (engine_ms(fmt, 1, 5) - base) / 4
+    # ---- Wan block
+    c = WAN
+    d, H = c["d"], c["H"]
+    fr, hh, ww = c["frames"], c["height"] // 2, c["width"] // 2
+    S = fr * hh * ww
+    sd_w = synth.make_state_dict(synth.wan_block_shapes("", d, c["ffn"]), seed=2, device=dev)
+    x, cx = synth.randn((1, S, d), 4, dev).bfloat16(), synth.randn((1, c["ctx"], d), 5, dev).bfloat16()
+    tmod = (synth.randn((1, 6, d), 6, dev) * 0.1).bfloat16()
+    f_, h_, w_ = ref.wan_dit.precompute_freqs_cis_3d(d // H)
+    freqs = torch.cat([f_[:fr].view(fr, 1, 1, -1).expand(fr, hh, ww, -1), h_[:hh].view(1, hh, 1, -1).expand(fr, hh, ww, -1),
+                       w_[:ww].view(1, 1, ww, -1).expand(fr, hh, ww, -1)], dim=-1).reshape(S, 1, -1).to(dev)
+    t_bf16, t_fp8 = both_paths(lambda: load(ref.wan_dit.DiTBlock(False, d, H, c["ffn"], 1e-6, device="cpu", dtype=torch.float32), sd_w),
+                               lambda b: b(x, cx, tmod, freqs))
+    row = {"block": "Wan DiTBlock (32760 tokens, 512 context tokens, d 5120)", "reference_bf16_ms": t_bf16,
+           "reference_fp8_scaled_mm_ms": t_fp8}
+    del sd_w
+
+    def wan_ms(fmt, layers):
+        shapes = synth.wan_dit_shapes(d=d, ffn=c["ffn"], num_layers=layers, text_dim=c["text_dim"])
+        eng = wan.WanDiTEngine(synth.make_state_dict(shapes, seed=3, device=dev, dtype=torch.bfloat16), fmt=fmt, device=dev,
+                               num_layers=layers, num_heads=H, release_source=True)
+        eng.prepare(c["frames"], c["height"], c["width"], c["ctx"], c["text_dim"])
+        t = timeit(eng.step, n=4, warm=1)
+        del eng
+        torch.cuda.empty_cache()
+        return t
+
+    for fmt in ("bf16", "fp8_channel"):
+        row[f"library_{fmt}_ms"] = (wan_ms(fmt, 3) - wan_ms(fmt, 1)) / 2
+    out["rows"].append(row)
+    pkg.ops.check_status(dev.index)
+    return out
+
+
 def run_sweeps(torch, pkg, dev):
     """Isolated kernel sweeps: FP8 e4m3 Linear (per-tensor and per-channel weight scale, bf16 out, fused
     bias + GELU-tanh) and joint attention (bf16, head_dim 128), N(0,1) values from a seed."""
@@ -646,7 +768,7 @@ def main():
     ap.add_argument("--no-parity", action="store_true", help="skip the correctness checks made before timing")
     ap.add_argument("--no-oracle-parity", action="store_true", help="skip only the CPU-oracle part of them")
     ap.add_argument("--blocks", default=None, help="n_double,n_single override (reduced-depth debugging; not a bench)")
-    ap.add_argument("--workload", default="both", choices=["flux", "wan", "both", "qwen", "sweeps"],
+    ap.add_argument("--workload", default="both", choices=["flux", "wan", "both", "qwen", "sweeps", "reference-gpu"],
                     help="both (default): the Wan sequence-parallel step as the line's value, the Flux step attached "
                          "under 'flux' at one GPU; wan / flux / qwen: that workload alone as the line's value")
     ap.add_argument("--wan-fmt", default="fp8_channel")
@@ -702,6 +824,10 @@ def main():
     if args.workload == "sweeps":
         if rank == 0:
             print(json.dumps(run_sweeps(torch, pkg, dev)), flush=True)
+        return
+    if args.workload == "reference-gpu":
+        if rank == 0:
+            print(json.dumps(run_reference_gpu(ctx, args)), flush=True)
         return
 
     line = {"metric": "DiT denoise steps/s", "unit": "steps/s", "n_gpus": world, "steps": steps, "warmup": warmup,

@@ -10,27 +10,22 @@
 //               The whole warp runs the issue loop, so descriptors stay warp-uniform, and one elected lane issues;
 //               it polls the P barriers without suspending (a hand-over then costs a few cycles, not a wake-up).
 //   warps 4-11  softmax of query tile 0, two threads per query row: warps 4-7 own key columns [0,64) of the
-//               score tile, warps 8-11 own [64,128) (a warp may only touch the TMEM lanes 32*(warp%4)..+31, so two
-//               warps with the same warp%4 share 32 rows)
+//               score tile, warps 8-11 own [64,128)
 //   warps 12-19 softmax of query tile 1, same split
-// 640 threads leave 96 registers per thread, so a softmax thread streams its scores through two 16-column register
-// buffers: while one is exponentiated the other is on its way from TMEM.
-// TMEM (512 columns): S_0 | S_1 | O_0 | O_1, 128 fp32 columns each.  A softmax thread reads its 64 scores as two
-// chunks of 32 columns and writes the packed bf16 probabilities of both over the FIRST 32 of its own 64 columns, so
-// P_q sits in columns [0,32) and [64,96) of S_q and no thread ever writes where another still has scores to read.
-// S_q(j+1) is issued only after O_q += P_q(j) V_j, and the two query tiles ping-pong on the tensor core.  P is handed
-// over in four parts of 32 keys (two MMAs each), one arrival per warp: a thread's first chunk half-way into the
-// arithmetic of its second, when its TMEM store has landed, the second at the end.
+// TMEM (512 columns): S_0 | S_1 | O_0 | O_1, 128 fp32 columns each.  Each softmax thread turns its 64 scores into
+// 32 columns of packed bf16 probabilities written over the FIRST half of its own 64 score columns, so P_q sits in
+// columns [0,32) and [64,96) of S_q and no thread ever writes where another thread still has scores to read.
+// S_q(j+1) is issued only after O_q += P_q(j) V_j, and the two query tiles ping-pong on the tensor core.
+// P is handed over in two parts: the first 32 keys of each 64-key half as soon as their store has landed (a quarter
+// of the way into the second chunk's exponentials), the rest at the end, so half of P.V runs under the softmax.
 //
 // The exponentials use a REFERENCE maximum that is one tile stale: p = exp2(s*c - m_ref) with m_ref = the row's
 // maximum over all earlier key tiles.  Row sums and O carry the same reference, so the result is exact; entries of
 // the current tile that exceed m_ref simply give p > 1 (fp32/bf16 have the range).  That takes the row-maximum
-// reduction off the S -> P -> MMA critical path.  The two threads of a row must use the same m_ref: each publishes
-// its running maximum (a plain shared-memory store before its last hand-over of the tile) and reads the partner's
-// at the start of the next tile - no waiting: S_q(j+1) cannot be signalled before both threads have handed tile j
-// over, so the value is always there.  Both then take the same refresh decision from the same two numbers.  Only the
-// first tile computes its maximum before exponentiating (one bounded exchange).  m_ref is refreshed (O and the sums
-// rescaled) when the running maximum has grown by more than 2^8.
+// reduction - and the exchange of it between the two threads of a row - off the S -> P -> MMA critical path: the
+// threads publish their running maxima after they hand P over, and pick the partner's value up one tile later.
+// Only the first tile computes its maximum before exponentiating.  m_ref is refreshed (O and the sums rescaled)
+// when the running maximum has grown by more than 2^8.
 //
 // m_ref is always an INTEGER (in log2 units): rescaling by 2^(integer) is exact in floating point, so the bf16
 // rounding of a probability does not depend on which reference it was computed against.  The result therefore equals
@@ -49,15 +44,11 @@ constexpr int kTileQ = 128;
 constexpr int kTileKV = 128;
 constexpr int kNQ = 2;
 constexpr int kKVStages = 2;
-constexpr int kParts = 4;          // P is handed to the MMA issuer in chunks of 128 / kParts keys
-#ifndef DSB_ATTN_MMA_WAIT
-#define DSB_ATTN_MMA_WAIT 20  // suspend-time hint (ns) of the MMA issuer's polls on the P barriers; 0 = busy spin
-#endif
+constexpr int kRefresh = 1;  // the reference maximum is re-examined every kRefresh key tiles (power of two)
 constexpr int kTileBytes = 128 * 128 * 2;  // 32 KiB: one 128 x 128 bf16 tile as two 64-column halves
 constexpr int kHalfBytes = kTileBytes / 2;
-constexpr int kXchgSlots = 2 * 2 * 128 * 2;  // [q][half][row] x {first-tile maximum, row sum}: 64-bit {sequence, value}
-constexpr int kMaxSlots = 2 * 2 * 2 * 128;   // [q][half][tile parity][row]: running maxima, plain floats
-constexpr int kAttnSmem = (kNQ + 2 * kKVStages) * kTileBytes + 256 + kXchgSlots * 8 + kMaxSlots * 4 + 1024;
+constexpr int kXchgSlots = 2 * 2 * 128 * 3;  // [q][half][row] x {running maximum (even tile, odd tile), row sum}
+constexpr int kAttnSmem = (kNQ + 2 * kKVStages) * kTileBytes + 256 + kXchgSlots * 8 + 1024;
 
 struct AttnParams {
   __nv_bfloat16* o;
@@ -69,15 +60,21 @@ struct AttnParams {
   int* status;
 };
 
-// Hand-over of one float between the two threads of a query row (used twice per CTA: first-tile maximum, final row
-// sum): a 64-bit slot {sequence number, value} written with one store; the reader spins (bounded) until the sequence
-// number it expects is there.
+// Hand-over of one float between the two threads of a query row: a 64-bit slot {sequence number, value} written with
+// one store; the reader spins (bounded) until the sequence number it expects is there.
 __device__ __forceinline__ void xchg_publish(unsigned long long* slot, uint32_t seq, float v) {
   *reinterpret_cast<volatile unsigned long long*>(slot) =
       (static_cast<unsigned long long>(seq) << 32) | static_cast<unsigned long long>(__float_as_uint(v));
 }
 __device__ __forceinline__ bool xchg_read(const unsigned long long* slot, uint32_t seq, float* v,
                                           volatile int* abort_flag) {
+  {
+    const unsigned long long w = *reinterpret_cast<const volatile unsigned long long*>(slot);
+    if (static_cast<uint32_t>(w >> 32) == seq) {  // the usual case: published long ago
+      *v = __uint_as_float(static_cast<uint32_t>(w));
+      return true;
+    }
+  }
   const long long t0 = clock64();
   uint32_t spins = 0;
   for (;;) {
@@ -106,26 +103,7 @@ __device__ __forceinline__ void load_tile(uint8_t* dst, const CUtensorMap* m, ui
   tma_load_4d(dst + kHalfBytes, m, bar, 64, c[0], c[1], c[2]);
 }
 
-// 2^n for an integer-valued n <= 0 (exact; 0 below the normal range)
-__device__ __forceinline__ float exp2_int(float n) {
-  const int e = 127 + static_cast<int>(n);
-  return e > 0 ? __int_as_float(e << 23) : 0.f;
-}
-
-#ifdef DSB_ATTN_TRACE
-// Timeline instrumentation (compile-time option, off in the shipped library): clock64 stamps of one CTA's roles over
-// its first 32 key tiles, read back with dsb_debug_attn_trace.  role 4q + quad = lane 0 of the two softmax warps of query
-// tile q and TMEM lane quadrant quad (slots 0-4 first column half, 8-12 second), role 8 = the MMA-issuing lane.
-__device__ unsigned int g_attn_trace[9 * 32 * 16];
-__device__ unsigned long long g_attn_cta[4096 * 4];  // per CTA: globaltimer at entry, at first S ready, at exit, SM id
-#define DSB_TR(role, j, k)                                                                  \
-  do {                                                                                      \
-    if (blockIdx.x == 1 && blockIdx.y == 0 && blockIdx.z == 0 && (j) < 32)                  \
-      g_attn_trace[((role) * 32 + (j)) * 16 + (k)] = static_cast<unsigned int>(clock64()); \
-  } while (0)
-#else
-#define DSB_TR(role, j, k) do { } while (0)
-#endif
+#define mbar_arrive(bar) mbar_arrive(bar)
 
 __global__ void __launch_bounds__(kAttnThreads, 1)
     flash_attn_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
@@ -142,24 +120,13 @@ __global__ void __launch_bounds__(kAttnThreads, 1)
   uint64_t* v_full = k_empty + kKVStages;   // kKVStages
   uint64_t* v_empty = v_full + kKVStages;   // kKVStages
   uint64_t* s_full = v_empty + kKVStages;   // kNQ
-  uint64_t* p_part = s_full + kNQ;          // kNQ x kParts: P of keys [32c, 32c+32) of the tile is in TMEM
-  uint64_t* o_full = p_part + kNQ * kParts; // kNQ
+  uint64_t* p_full = s_full + kNQ;          // kNQ: P of the first 32 keys of both key halves is in TMEM
+  uint64_t* p_rest = p_full + kNQ;          // kNQ: ... and of the other 32
+  uint64_t* o_full = p_rest + kNQ;          // kNQ
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(o_full + kNQ);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   unsigned long long* xchg = reinterpret_cast<unsigned long long*>(reinterpret_cast<uint8_t*>(bars) + 256);
-  volatile float* xmax = reinterpret_cast<volatile float*>(xchg + kXchgSlots);
 
-#ifdef DSB_ATTN_TRACE
-  const int cta_id = blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z);
-  if (threadIdx.x == 0 && cta_id < 4096) {
-    unsigned long long t;
-    unsigned int sm;
-    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-    asm volatile("mov.u32 %0, %%smid;" : "=r"(sm));
-    g_attn_cta[cta_id * 4] = t;
-    g_attn_cta[cta_id * 4 + 3] = sm;
-  }
-#endif
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const int q0 = blockIdx.x * (kNQ * kTileQ);
@@ -177,7 +144,8 @@ __global__ void __launch_bounds__(kAttnThreads, 1)
     }
     for (int q = 0; q < kNQ; ++q) {
       mbar_init(&s_full[q], 1);
-      for (int c = 0; c < kParts; ++c) mbar_init(&p_part[q * kParts + c], 4);  // one arrival per softmax warp
+      mbar_init(&p_full[q], 256);
+      mbar_init(&p_rest[q], 256);
       mbar_init(&o_full[q], 1);
     }
     *abort_flag = 0;
@@ -242,17 +210,19 @@ __global__ void __launch_bounds__(kAttnThreads, 1)
           mma_ss_f16_elect(d, ad0 + off, bd0 + off, idesc_qk, kk > 0 ? 1u : 0u, leader);
         }
       };
-      // O_q += P_q V for the keys [32c, 32c+32) of the tile: two MMAs of 16 keys.  P of keys [0,64) sits in columns
-      // [0,32) of S_q, P of keys [64,128) in columns [64,96) (8 packed columns per 16 keys); 16 keys of V are 16 rows
-      // of 128 bytes = 128 descriptor units.
-      auto issue_pv = [&](int q, int st, int c, bool accumulate) {
+      // O_q += P_q V for the 16-key groups kk in {g, g+1, g+4, g+5}: g = 0 are the keys whose probabilities every
+      // softmax thread writes first (its first 32 of 64 columns), g = 2 the rest
+      auto issue_pv = [&](int q, int st, int g, bool accumulate) {
         const uint64_t bd0 = v_desc0 + static_cast<uint32_t>(st) * kTile16;
         const uint32_t d = tmem_base + 256 + q * 128;
-        const uint32_t a = tmem_base + q * 128 + (c >> 1) * 64 + (c & 1) * 16;
+        const uint32_t a = tmem_base + q * 128;
 #pragma unroll
-        for (int i = 0; i < 2; ++i) {
-          const int kk = c * 2 + i;
-          mma_ts_f16_elect(d, a + i * 8, bd0 + kk * 128u, idesc_pv, (accumulate || i > 0) ? 1u : 0u, leader);
+        for (int i = 0; i < 4; ++i) {
+          const int kk = g + (i & 1) + (i >> 1) * 4;
+          // 16 keys per instruction = 16 rows of 128 bytes (2048 bytes = 128 units) further into the V tile
+          // P of keys [0,64) lives in columns [0,32) of S_q, P of keys [64,128) in columns [64,96)
+          mma_ts_f16_elect(d, a + (kk >> 2) * 64 + (kk & 3) * 8, bd0 + kk * 128u, idesc_pv, (accumulate || i > 0) ? 1u : 0u,
+                           leader);
         }
       };
       int kst = 0, vst = 0;
@@ -269,28 +239,17 @@ __global__ void __launch_bounds__(kAttnThreads, 1)
       for (int j = 0; j < nkv; ++j) {
         const bool has_next = (j + 1) < nkv;
         if (!mbar_wait(&v_full[vst], vph, abort_flag)) goto mma_done;
-#pragma unroll 1
+        if (has_next && !mbar_wait(&k_full[kst], kph, abort_flag)) goto mma_done;
         for (int q = 0; q < kNQ; ++q) {
-#pragma unroll
-          for (int ci = 0; ci < kParts; ++ci) {
-            const int c = (ci & 1) * 2 + (ci >> 1);  // 0, 2, 1, 3: the order in which the two halves finish their chunks
-#if DSB_ATTN_MMA_WAIT == 0
-            if (!mbar_wait_spin(&p_part[q * kParts + c], j & 1, abort_flag)) goto mma_done;
-#else
-            if (!mbar_wait_hint(&p_part[q * kParts + c], j & 1, abort_flag, DSB_ATTN_MMA_WAIT)) goto mma_done;
-#endif
-            tc_fence_after();
-            if (leader) DSB_TR(8, j, q * 6 + ci);
-            issue_pv(q, vst, c, j > 0 || ci > 0);
-          }
-          if (leader) DSB_TR(8, j, q * 6 + 4);
+          if (!mbar_wait_spin(&p_full[q], j & 1, abort_flag)) goto mma_done;
+          tc_fence_after();
+          issue_pv(q, vst, 0, j > 0);
+          if (!mbar_wait_spin(&p_rest[q], j & 1, abort_flag)) goto mma_done;
+          tc_fence_after();
+          issue_pv(q, vst, 2, true);
           if (has_next) {
-            // the next key tile is only needed now: its load has had the whole softmax of this tile to land
-            if (q == 0 && !mbar_wait(&k_full[kst], kph, abort_flag)) goto mma_done;
-            if (q == 0) tc_fence_after();
             issue_qk(q, kst);
             tc_commit_elect(&s_full[q], leader);
-            if (leader) DSB_TR(8, j, q * 6 + 5);
           } else {
             tc_commit_elect(&o_full[q], leader);
           }
@@ -314,54 +273,38 @@ __global__ void __launch_bounds__(kAttnThreads, 1)
     const uint32_t lane_off = static_cast<uint32_t>(quad * 32) << 16;
     const uint32_t t_s = tmem_base + lane_off + q * 128 + half * 64;        // my 64 score columns; P goes to the first 32
     const uint32_t t_o = tmem_base + lane_off + 256 + q * 128 + half * 64;  // my half of the output columns
-    uint64_t* my_part = p_part + q * kParts + half * 2;                     // my two hand-over barriers
-    unsigned long long* slot_mine = xchg + ((q * 2 + half) * 128 + row) * 2;  // {first-tile maximum, row sum}
-    const unsigned long long* slot_other = xchg + ((q * 2 + (half ^ 1)) * 128 + row) * 2;
-    volatile float* max_mine = xmax + (q * 2 + half) * 256 + row;           // + 128 * (tile parity)
-    const volatile float* max_other = xmax + (q * 2 + (half ^ 1)) * 256 + row;
+    unsigned long long* slot_mine = xchg + ((q * 2 + half) * 128 + row) * 3;  // {max even tile, max odd tile, sum}
+    const unsigned long long* slot_other = xchg + ((q * 2 + (half ^ 1)) * 128 + row) * 3;
     const float cs = p.scale_log2;
-    float m_ref = 0.f;          // reference maximum (integer, log2 units) the exponentials, the row sum and O use
-    float run_max = -INFINITY;  // this thread's running maximum of s*c over its columns, all tiles so far
-    // four partial maxima (raw scores of the current tile) and four partial row sums (all tiles) are only folded
-    // once per tile / at the end, so no reduction chain sits between the last exponential and the hand-over of P
+    const float inv_cs = 1.0f / cs;
+    float m_ref = 0.f;       // reference maximum (log2 units) the exponentials, the row sum and O currently use
+    float run_max = -INFINITY;  // this thread's running maximum of raw scores over its columns, all tiles so far
+    // four running maxima and four partial row sums live across the key tiles (folded only when published / at the
+    // end), so no per-tile reduction chain sits between the last exponential and the hand-over of P
     float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
     float2 ls2[2] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
     bool ok = true;
-    // hand-over of my chunk i: every lane's TMEM stores have landed, then one arrival per warp
-    auto hand_over = [&](int i) {
-      tc_wait_st();
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&my_part[i]);
-    };
     for (int j = 0; j < nkv; ++j) {
       if (!mbar_wait(&s_full[q], j & 1, abort_flag)) {
         ok = false;
         break;
       }
       tc_fence_after();
-      if (lane == 0) DSB_TR(q * 4 + quad, j, half * 8 + 0);
-#ifdef DSB_ATTN_TRACE
-      if (j == 0 && threadIdx.x == 128 && cta_id < 4096) {
-        unsigned long long t;
-        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-        g_attn_cta[cta_id * 4 + 1] = t;
-      }
-#endif
       const int valid = min(kTileKV, p.Sk - j * kTileKV) - half * 64;  // valid columns among my 64 (may be <= 0)
-      uint32_t sa[16], sb[16];
+      bool handed = false;  // p_full already signalled for this tile
       if (j == 0) {
-        // first tile: the row maximum must be known before anything is exponentiated (a pass of its own)
+        // first tile: the row maximum must be known before anything is exponentiated
+        uint32_t s0[32], s1[32];
+        tmem_ld32(t_s, s0);
+        tmem_ld32(t_s + 32, s1);
+        tc_wait_ld();
         float m0 = -INFINITY;
-#pragma unroll 1
-        for (int c = 0; c < 4; ++c) {
-          tmem_ld16(t_s + c * 16, sa);
-          tc_wait_ld();
 #pragma unroll
-          for (int i = 0; i < 16; ++i)
-            if (c * 16 + i < valid) m0 = fmaxf(m0, __uint_as_float(sa[i]));
+        for (int i = 0; i < 32; ++i) {
+          if (i < valid) m0 = fmaxf(m0, __uint_as_float(s0[i]));
+          if (32 + i < valid) m0 = fmaxf(m0, __uint_as_float(s1[i]));
         }
-        run_max = m0 * cs;
+        run_max = m0;
         xchg_publish(&slot_mine[0], 1u, m0);
         float mo;
         if (!xchg_read(&slot_other[0], 1u, &mo, abort_flag)) {
@@ -369,93 +312,122 @@ __global__ void __launch_bounds__(kAttnThreads, 1)
           break;
         }
         m_ref = ceilf(fmaxf(m0, mo) * cs);  // at least one key of the tile is valid, so this is finite
-        tmem_ld16(t_s, sa);
-        tmem_ld16(t_s + 16, sb);
-      } else {
-        tmem_ld16(t_s, sa);
-        tmem_ld16(t_s + 16, sb);
-        // the partner published its running maximum before it handed tile j-1 over, and S_q(j) was only issued after
-        // that hand-over: the value is there.  Both threads of the row see the same two numbers.
-        const float mo = max_other[((j - 1) & 1) * 128];
-        const float m_run = fmaxf(run_max, mo);
-        if (__any_sync(0xffffffffu, m_run > m_ref + 8.0f)) {
-          // O is idle: S_q(j) is only signalled after O_q += P_q(j-1) V has completed.
-          const float m_upd = fmaxf(m_ref, ceilf(m_run));
-          const float alpha = exp2_int(m_ref - m_upd);
-          m_ref = m_upd;
-          ls2[0].x *= alpha, ls2[0].y *= alpha, ls2[1].x *= alpha, ls2[1].y *= alpha;
-          tc_wait_ld();
-#pragma unroll 1
-          for (int c = 0; c < 4; ++c) {
-            uint32_t r[16];
-            tmem_ld16(t_o + c * 16, r);
-            tc_wait_ld();
+        float ls = 0.f;
+        uint32_t pk[16];
 #pragma unroll
-            for (int i = 0; i < 16; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
-            tmem_st16(t_o + c * 16, r);
+        for (int i = 0; i < 16; ++i) {
+          const float p0 = (2 * i < valid) ? fast_exp2(fmaf(__uint_as_float(s0[2 * i]), cs, -m_ref)) : 0.f;
+          const float p1 = (2 * i + 1 < valid) ? fast_exp2(fmaf(__uint_as_float(s0[2 * i + 1]), cs, -m_ref)) : 0.f;
+          ls += p0 + p1;
+          pk[i] = pack_bf16x2(p0, p1);
+        }
+        tmem_st16(t_s, pk);
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+          const float p0 = (32 + 2 * i < valid) ? fast_exp2(fmaf(__uint_as_float(s1[2 * i]), cs, -m_ref)) : 0.f;
+          const float p1 = (33 + 2 * i < valid) ? fast_exp2(fmaf(__uint_as_float(s1[2 * i + 1]), cs, -m_ref)) : 0.f;
+          ls += p0 + p1;
+          pk[i] = pack_bf16x2(p0, p1);
+        }
+        tmem_st16(t_s + 16, pk);
+        ls2[0].x = ls;
+        mx[0] = m0;
+      } else {
+        // first score chunk on its way from TMEM while the (already published) partner maximum is read
+        uint32_t sc[32];
+        tmem_ld32(t_s, sc);
+        if (kRefresh == 1 || (j & (kRefresh - 1)) == 1) {
+          // every kRefresh-th tile: is the reference maximum still close enough to the running maximum of the row?
+          // (the partner published its running maximum after tile j-1)
+          float mo;
+          if (!xchg_read(&slot_other[((j - 1) / kRefresh) & 1], static_cast<uint32_t>(j), &mo, abort_flag)) {
+            ok = false;
+            break;
           }
+          const float m_run = fmaxf(run_max, mo) * cs;
+          if (__any_sync(0xffffffffu, m_run > m_ref + 8.0f)) {
+            // both warps of these rows see the same values, so both take this branch.  O is idle: S_q(j) is only
+            // signalled after O_q += P_q(j-1) V has completed.
+            const float m_upd = fmaxf(m_ref, ceilf(m_run));
+            const float alpha = __int_as_float(max(0, 127 + static_cast<int>(m_ref - m_upd)) << 23);
+            m_ref = m_upd;
+            ls2[0].x *= alpha, ls2[0].y *= alpha, ls2[1].x *= alpha, ls2[1].y *= alpha;
+            tc_wait_ld();
+#pragma unroll 1
+            for (int c = 0; c < 2; ++c) {
+              uint32_t r[32];
+              tmem_ld32(t_o + c * 32, r);
+              tc_wait_ld();
+#pragma unroll
+              for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
+              tmem_st32(t_o + c * 32, r);
+            }
+          }
+        }
+        const float2 cs2 = make_float2(cs, cs), nm2 = make_float2(-m_ref, -m_ref);
+#pragma unroll
+        for (int c = 0; c < 2; ++c) {
+          if (c == 1) tmem_ld32(t_s + 32, sc);
+          tc_wait_ld();
+          uint32_t pk[16];
+          if (valid >= 64) {
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+              if (c == 1 && i == 8) {
+                // the first chunk's P store has had half a chunk of arithmetic to land: hand the first 32 keys over
+                tc_wait_st();
+                tc_fence_before();
+                mbar_arrive(&p_full[q]);
+                handed = true;
+              }
+              const float2 a = make_float2(__uint_as_float(sc[2 * i]), __uint_as_float(sc[2 * i + 1]));
+              const float2 x = __ffma2_rn(a, cs2, nm2);
+              // the clamp only matters for rows whose scores jump by more than 2^100 from one key tile to the next
+              const float2 pp = make_float2(fast_exp2(fminf(x.x, 100.f)), fast_exp2(fminf(x.y, 100.f)));
+              mx[i & 3] = max3f(mx[i & 3], a.x, a.y);
+              ls2[i & 1] = __fadd2_rn(ls2[i & 1], pp);
+              pk[i] = pack_bf16x2(pp.x, pp.y);
+            }
+          } else {
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+              const int c0 = c * 32 + 2 * i;
+              const float a0 = __uint_as_float(sc[2 * i]), a1 = __uint_as_float(sc[2 * i + 1]);
+              const float p0 = (c0 < valid) ? fast_exp2(fminf(fmaf(a0, cs, -m_ref), 100.f)) : 0.f;
+              const float p1 = (c0 + 1 < valid) ? fast_exp2(fminf(fmaf(a1, cs, -m_ref), 100.f)) : 0.f;
+              if (c0 < valid) mx[i & 3] = fmaxf(mx[i & 3], a0);
+              if (c0 + 1 < valid) mx[i & 3] = fmaxf(mx[i & 3], a1);
+              ls2[i & 1].x += p0;
+              ls2[i & 1].y += p1;
+              pk[i] = pack_bf16x2(p0, p1);
+            }
+          }
+          tmem_st16(t_s + c * 16, pk);
         }
       }
-      tc_wait_ld();
-      if (lane == 0) DSB_TR(q * 4 + quad, j, half * 8 + 1);
-      const float2 cs2 = make_float2(cs, cs), nm2 = make_float2(-m_ref, -m_ref);
-      uint32_t pk[16];
-      mx[0] = mx[1] = mx[2] = mx[3] = -INFINITY;  // maxima of THIS tile's raw scores
-      // 16 scores (columns [16 s, 16 s + 16) of my 64) -> 8 packed probabilities pk[8 (s & 1) ..]
-      auto piece = [&](const uint32_t (&sc)[16], int s16) {
-        const int o = (s16 & 1) * 8;
-        if (valid >= s16 * 16 + 16) {
+      tc_wait_st();
+      tc_fence_before();
+      if (!handed) mbar_arrive(&p_full[q]);
+      mbar_arrive(&p_rest[q]);
+      // off the critical path: publish my running maximum for the partner to use at the next tile (slot by tile
+      // parity: the partner cannot be two tiles ahead, S_q(j+2) needs this thread's P_q(j+1))
+      if (j > 0 && (j & (kRefresh - 1)) == 0) {
+        // A score more than 2^100 above the reference was exponentiated as 2^100 (the clamp), so the running maximum
+        // - and with it the next reference - may only follow it that far: the row then stays finite and is
+        // dominated by that key, as it should be.
+        const float lim = (m_ref + 100.f) * inv_cs;
 #pragma unroll
-          for (int i = 0; i < 8; ++i) {
-            const float2 a = make_float2(__uint_as_float(sc[2 * i]), __uint_as_float(sc[2 * i + 1]));
-            const float2 x = __ffma2_rn(a, cs2, nm2);
-            // the clamp only matters for rows whose scores jump by more than 2^100 from one key tile to the next
-            const float2 pp = make_float2(fast_exp2(fminf(x.x, 100.f)), fast_exp2(fminf(x.y, 100.f)));
-            mx[i & 3] = max3f(mx[i & 3], a.x, a.y);
-            ls2[i & 1] = __fadd2_rn(ls2[i & 1], pp);
-            pk[o + i] = pack_bf16x2(pp.x, pp.y);
-          }
-        } else {
-#pragma unroll
-          for (int i = 0; i < 8; ++i) {
-            const int c0 = s16 * 16 + 2 * i;
-            const float a0 = __uint_as_float(sc[2 * i]), a1 = __uint_as_float(sc[2 * i + 1]);
-            const float p0 = (c0 < valid) ? fast_exp2(fminf(fmaf(a0, cs, -m_ref), 100.f)) : 0.f;
-            const float p1 = (c0 + 1 < valid) ? fast_exp2(fminf(fmaf(a1, cs, -m_ref), 100.f)) : 0.f;
-            if (c0 < valid) mx[i & 3] = fmaxf(mx[i & 3], a0);
-            if (c0 + 1 < valid) mx[i & 3] = fmaxf(mx[i & 3], a1);
-            ls2[i & 1].x += p0;
-            ls2[i & 1].y += p1;
-            pk[o + i] = pack_bf16x2(p0, p1);
-          }
-        }
-      };
-      piece(sa, 0);
-      tmem_ld16(t_s + 32, sa);   // the buffer just consumed refills while the other one is exponentiated
-      piece(sb, 1);
-      tmem_ld16(t_s + 48, sb);
-      tmem_st16(t_s, pk);        // P of my first 32 keys over the columns their scores came from
-      if (lane == 0) DSB_TR(q * 4 + quad, j, half * 8 + 2);
-      tc_wait_ld();
-      piece(sa, 2);
-      hand_over(0);              // the first chunk's P store has had half a chunk of arithmetic to land
-      piece(sb, 3);
-      tmem_st16(t_s + 16, pk);
-      if (lane == 0) DSB_TR(q * 4 + quad, j, half * 8 + 3);
-      // my running maximum, for the partner's (and my) refresh test at the next tile; the arrival below releases it
-      // A score more than 2^100 above the reference was exponentiated as 2^100 (the clamp), so the reference may
-      // only follow it that far: the row then stays finite and is dominated by that key, as it should be.
-      run_max = fmaxf(run_max, fminf(fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])) * cs, m_ref + 100.f));
-      max_mine[(j & 1) * 128] = run_max;
-      hand_over(1);
-      if (lane == 0) DSB_TR(q * 4 + quad, j, half * 8 + 4);
+        for (int i = 0; i < 4; ++i) mx[i] = fminf(mx[i], lim);
+        run_max = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
+        xchg_publish(&slot_mine[(j / kRefresh) & 1], static_cast<uint32_t>(j + 1), run_max);
+      }
     }
     if (ok && mbar_wait(&o_full[q], 0, abort_flag)) {
       tc_fence_after();
       const float l = (ls2[0].x + ls2[0].y) + (ls2[1].x + ls2[1].y);
-      xchg_publish(&slot_mine[1], 0x7fffffffu, l);
+      xchg_publish(&slot_mine[2], 0x7fffffffu, l);
       float lo = 0.f;
-      ok = xchg_read(&slot_other[1], 0x7fffffffu, &lo, abort_flag);
+      ok = xchg_read(&slot_other[2], 0x7fffffffu, &lo, abort_flag);
       const float inv = 1.0f / (l + lo);
       const int sq = q0 + q * kTileQ + row;
       __nv_bfloat16* orow = p.o + static_cast<int64_t>(b) * p.o_stride_b + static_cast<int64_t>(sq) * p.o_stride_s +
@@ -488,13 +460,6 @@ __global__ void __launch_bounds__(kAttnThreads, 1)
     tmem_dealloc(tmem_base, 512);
   }
   if (threadIdx.x == 0 && *abort_flag && p.status) atomicCAS(p.status, 0, DSB_ERR_TIMEOUT);
-#ifdef DSB_ATTN_TRACE
-  if (threadIdx.x == 0 && cta_id < 4096) {
-    unsigned long long t;
-    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-    g_attn_cta[cta_id * 4 + 2] = t;
-  }
-#endif
 }
 
 // Rank-4 tensor map over (d, then s/h/b ordered by ascending stride); box = 64 x 128 rows of s.
@@ -534,19 +499,6 @@ static int make_tmap_attn(CUtensorMap* out, int (&pos)[3], const void* base, int
 }  // namespace dsb
 
 using namespace dsb;
-
-#ifdef DSB_ATTN_TRACE
-extern "C" int dsb_debug_attn_cta(unsigned long long* host_out, int n) {
-  if (!host_out || n <= 0 || n > 4096 * 4) return DSB_ERR_ARG;
-  if (cudaDeviceSynchronize() != cudaSuccess) return DSB_ERR_CUDA;
-  return cudaMemcpyFromSymbol(host_out, g_attn_cta, n * sizeof(unsigned long long)) == cudaSuccess ? DSB_OK : DSB_ERR_CUDA;
-}
-extern "C" int dsb_debug_attn_trace(unsigned int* host_out, int n) {
-  if (!host_out || n <= 0 || n > 9 * 32 * 16) return DSB_ERR_ARG;
-  if (cudaDeviceSynchronize() != cudaSuccess) return DSB_ERR_CUDA;
-  return cudaMemcpyFromSymbol(host_out, g_attn_trace, n * sizeof(unsigned int)) == cudaSuccess ? DSB_OK : DSB_ERR_CUDA;
-}
-#endif
 
 extern "C" int dsb_flash_attn(const void* q, const void* k, const void* v, void* o, int B, int H, int Sq, int Sk,
                               int head_dim, int64_t q_stride_b, int64_t q_stride_s, int64_t q_stride_h,
