@@ -302,7 +302,7 @@ def library_fp8_gemm_tflops(torch, dev):
 # ------------------------------------------------------------------------------------------- Wan
 def wan_parity(ctx, args):
     """Correctness evidence for the Wan path, outside any timed region.
-    (1) rank 0, one GPU: a 1-block model at full width on a 21 x 15 x 13 token grid (4095 tokens, the share of one
+    (1) N = 1 only: a 1-block model at full width on a 21 x 15 x 13 token grid (4095 tokens, the share of one
         of eight ranks) against the CPU oracle with the same quantisation: rel-L2 of the hidden state after the block
         and of the block's update;
     (2) N > 1: a 2-block model at full width on the FULL video, sequence-parallel over all ranks, against the same
@@ -329,7 +329,7 @@ def wan_parity(ctx, args):
             out["sp_vs_one_gpu_tolerance"] = 3e-3
             out["sp_check"] = f"2-block model at full width, full 32760-token video, sp{ctx.world} vs rank 0 alone"
         ctx.barrier()
-    if ctx.rank == 0 and not args.no_oracle_parity:
+    if ctx.rank == 0 and ctx.world == 1 and not args.no_oracle_parity:   # (N > 1: the other ranks would idle meanwhile)
         from oracle import flux as OF
         from oracle import ops as O
         from oracle import wan as OW
@@ -811,6 +811,15 @@ def main():
         print(json.dumps(line), flush=True)
         return
 
+    # Libraries underneath may write to the process's stdout (NCCL prints a version banner at the first communicator
+    # under some NCCL_DEBUG settings): everything but the final JSON line goes to stderr.
+    sys.stdout.flush()
+    json_fd = os.dup(1)
+    os.dup2(2, 1)
+
+    def emit(obj):
+        os.write(json_fd, (json.dumps(obj) + "\n").encode())
+
     import torch
     pkg = load_package()
     if not torch.cuda.is_available():
@@ -827,11 +836,11 @@ def main():
 
     if args.workload == "sweeps":
         if rank == 0:
-            print(json.dumps(run_sweeps(torch, pkg, dev)), flush=True)
+            emit(run_sweeps(torch, pkg, dev))
         return
     if args.workload == "reference-gpu":
         if rank == 0:
-            print(json.dumps(run_reference_gpu(ctx, args)), flush=True)
+            emit(run_reference_gpu(ctx, args))
         return
 
     line = {"metric": "DiT denoise steps/s", "unit": "steps/s", "n_gpus": world, "steps": steps, "warmup": warmup,
@@ -879,7 +888,7 @@ def main():
         if not args.no_cpu_baseline and world == 1:
             r = (cpu_wan_arm if wan_headline else cpu_flux_arm)(steps=2, warmup=0, budget_s=40.0)
             line["cpu_baseline"] = {k: r[k] for k in ("value", "unit", "cores", "kind", "sample")}
-        print(json.dumps(line), flush=True)
+        emit(line)
     if dist is not None:
         dist.barrier()
         dist.destroy_process_group()

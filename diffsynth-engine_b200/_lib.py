@@ -36,6 +36,7 @@ _SIGS = {
     "dsb_quant_rows": [c_p, c_i64, c_p, c_i64, c_p, c_i, c_i, c_i, c_p],
     "dsb_dequant_q8_0": [c_p, c_i64, c_i, c_i, c_p, c_i64, c_p],
     "dsb_dequant_q4_k": [c_p, c_i64, c_i, c_i, c_p, c_i64, c_p],
+    "dsb_dequant_gguf": [c_i, c_p, c_i64, c_i, c_i, c_p, c_i64, c_p],
     "dsb_cast_quant": [c_p, c_i64, c_p, c_i64, c_i, c_i, c_i, c_i, c_p],
     "dsb_gemv": [c_p, c_i64, c_i, c_p, c_p, c_i, c_p, c_p, c_i, c_i, c_i, c_i, c_i, c_p],
     "dsb_timestep_embedding": [c_p, c_i, c_i, c_f, c_i, c_i, c_p, c_p],

@@ -518,6 +518,128 @@ __global__ void __launch_bounds__(256) dequant_q4_k_kernel(const uint8_t* __rest
   }
 }
 
+// ------------------------------------------------------ GGUF block formats (generic path)
+// One thread turns 16 consecutive weights of a row into bf16, for every block format the reference dequantises
+// (utils/gguf.py:171-368).  Arithmetic and rounding follow the reference with a bf16 compute dtype: the fp16 block
+// scales are rounded to bf16, and every product and every sum is rounded to bf16 again, in the reference's order.
+// Block sizes such as 18, 22, 110 or 210 bytes leave nothing aligned, so the bytes are fetched one by one (this
+// runs once per weight, when a checkpoint is attached).
+enum : int { GG_Q4_0 = 2, GG_Q4_1 = 3, GG_Q5_0 = 6, GG_Q5_1 = 7, GG_Q8_0 = 8, GG_Q2_K = 10, GG_Q3_K = 11, GG_Q4_K = 12,
+             GG_Q5_K = 13, GG_Q6_K = 14 };
+
+__device__ __forceinline__ float gg_f16(const uint8_t* p) {   // fp16 field -> bf16-rounded float
+  const __half_raw h = {static_cast<unsigned short>(__ldg(p) | (static_cast<unsigned>(__ldg(p + 1)) << 8))};
+  return rbf(__half2float(*reinterpret_cast<const __half*>(&h)));
+}
+__device__ __forceinline__ uint32_t gg_u32(const uint8_t* p) {
+  return __ldg(p) | (static_cast<uint32_t>(__ldg(p + 1)) << 8) | (static_cast<uint32_t>(__ldg(p + 2)) << 16) |
+         (static_cast<uint32_t>(__ldg(p + 3)) << 24);
+}
+// the eight 6-bit (scale, min) pairs of a K-quant super-block (get_scale_min, gguf.py:158-168)
+__device__ __forceinline__ void gg_k_scale(const uint8_t* s, int j, uint32_t* sc, uint32_t* mn) {
+  if (j < 4) {
+    *sc = __ldg(s + j) & 63u;
+    *mn = __ldg(s + j + 4) & 63u;
+  } else {
+    *sc = (__ldg(s + j + 4) & 15u) | ((__ldg(s + j - 4) >> 6) << 4);
+    *mn = (__ldg(s + j + 4) >> 4) | ((__ldg(s + j) >> 6) << 4);
+  }
+}
+
+template <int T>
+__device__ __forceinline__ void gg_deq16(const uint8_t* blk, int v0, float (&o)[16]) {
+  if constexpr (T == GG_Q4_0 || T == GG_Q4_1 || T == GG_Q5_0 || T == GG_Q5_1) {
+    constexpr bool kHasMin = (T == GG_Q4_1 || T == GG_Q5_1), kFive = (T == GG_Q5_0 || T == GG_Q5_1);
+    const float d = gg_f16(blk), m = kHasMin ? gg_f16(blk + 2) : 0.f;
+    const uint8_t* hp = blk + (kHasMin ? 4 : 2);
+    const uint8_t* qs = hp + (kFive ? 4 : 0);
+    const uint32_t qh = kFive ? gg_u32(hp) : 0u;
+    const int shift = v0 >= 16 ? 4 : 0;   // values 0..15 are the low nibbles of the 16 bytes, 16..31 the high ones
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      int q = (__ldg(qs + i) >> shift) & 15;
+      if (kFive) q |= static_cast<int>((qh >> (v0 + i)) & 1u) << 4;
+      if (T == GG_Q4_0) q -= 8;
+      if (T == GG_Q5_0) q -= 16;
+      const float dq = rbf(d * static_cast<float>(q));
+      o[i] = kHasMin ? rbf(dq + m) : dq;
+    }
+  } else if constexpr (T == GG_Q8_0) {
+    const float d = gg_f16(blk);
+#pragma unroll
+    for (int i = 0; i < 16; ++i) o[i] = rbf(d * static_cast<float>(static_cast<int8_t>(__ldg(blk + 2 + v0 + i))));
+  } else if constexpr (T == GG_Q2_K) {
+    const uint32_t s = __ldg(blk + (v0 >> 4));
+    const float dl = rbf(gg_f16(blk + 80) * static_cast<float>(s & 15u));
+    const float ml = rbf(gg_f16(blk + 82) * static_cast<float>(s >> 4));
+    const uint8_t* qs = blk + 16 + (v0 >> 7) * 32 + (v0 & 31);
+    const int sh = ((v0 & 127) >> 5) * 2;
+#pragma unroll
+    for (int i = 0; i < 16; ++i) o[i] = rbf(rbf(dl * static_cast<float>((__ldg(qs + i) >> sh) & 3)) - ml);
+  } else if constexpr (T == GG_Q3_K) {
+    const int k = v0 >> 4;
+    const uint8_t* s = blk + 96;
+    const int low = k < 8 ? (__ldg(s + k) & 15) : (__ldg(s + k - 8) >> 4);
+    const int high = (__ldg(s + 8 + (k & 3)) >> (2 * (k >> 2))) & 3;
+    const float dl = rbf(gg_f16(blk + 108) * static_cast<float>((low | (high << 4)) - 32));
+    const uint8_t* qs = blk + 32 + (v0 >> 7) * 32 + (v0 & 31);
+    const uint8_t* hm = blk + (v0 & 31);
+    const int sh = ((v0 & 127) >> 5) * 2, hb = v0 >> 5;
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      const int q = ((__ldg(qs + i) >> sh) & 3) - ((((__ldg(hm + i) >> hb) & 1) ^ 1) << 2);
+      o[i] = rbf(dl * static_cast<float>(q));
+    }
+  } else if constexpr (T == GG_Q4_K || T == GG_Q5_K) {
+    const int j = v0 >> 5;
+    uint32_t sc, mn;
+    gg_k_scale(blk + 4, j, &sc, &mn);
+    const float dsc = rbf(gg_f16(blk) * static_cast<float>(sc)), dm = rbf(gg_f16(blk + 2) * static_cast<float>(mn));
+    const uint8_t* qs = blk + (T == GG_Q5_K ? 48 : 16) + (j >> 1) * 32 + (v0 & 31);
+    const uint8_t* qh = blk + 16 + (v0 & 31);
+    const int sh = (j & 1) * 4;
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      int q = (__ldg(qs + i) >> sh) & 15;
+      if (T == GG_Q5_K) q |= ((__ldg(qh + i) >> j) & 1) << 4;
+      o[i] = rbf(rbf(dsc * static_cast<float>(q)) - dm);
+    }
+  } else {  // GG_Q6_K
+    const int h = v0 >> 7, r = v0 & 127;
+    const float dl = rbf(gg_f16(blk + 208) * static_cast<float>(static_cast<int8_t>(__ldg(blk + 192 + (v0 >> 4)))));
+    const uint8_t* ql = blk + h * 64 + (r & 63);
+    const uint8_t* qh = blk + 128 + h * 32 + (r & 31);
+    const int sl = (r >> 6) * 4, shh = (r >> 5) * 2;
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      const int q = (((__ldg(ql + i) >> sl) & 15) | (((__ldg(qh + i) >> shh) & 3) << 4)) - 32;
+      o[i] = rbf(dl * static_cast<float>(q));
+    }
+  }
+}
+
+template <int T>
+__global__ void __launch_bounds__(256) dequant_gguf_kernel(const uint8_t* __restrict__ raw, int64_t row_bytes,
+                                                           __nv_bfloat16* __restrict__ out, int64_t ld_out, int N, int K,
+                                                           int type_size, int block_size) {
+  const int groups = K >> 4;
+  const int64_t total = static_cast<int64_t>(N) * groups;
+  for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < total;
+       i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const int64_t n = i / groups;
+    const int col = static_cast<int>(i - n * groups) << 4;
+    const uint8_t* blk = raw + n * row_bytes + static_cast<int64_t>(col / block_size) * type_size;
+    float o[16];
+    gg_deq16<T>(blk, col % block_size, o);
+    uint32_t w[8];
+#pragma unroll
+    for (int k = 0; k < 8; ++k) w[k] = pack_bf16x2(o[2 * k], o[2 * k + 1]);
+    uint4* dst = reinterpret_cast<uint4*>(out + n * ld_out + col);
+    dst[0] = make_uint4(w[0], w[1], w[2], w[3]);
+    dst[1] = make_uint4(w[4], w[5], w[6], w[7]);
+  }
+}
+
 // ------------------------------------------------------------------- gemv
 // y[n] = (sum_k W[n,k] * f(x[k])) * w_scale[n or 0] + bias[n].  The activation vector is staged once per CTA
 // in shared memory; each warp walks groups of four consecutive rows so that every 64-byte read of the
@@ -862,6 +984,41 @@ int dsb_dequant_q4_k(const void* blocks, int64_t row_bytes, int N, int K, void* 
   if (nblk > cap) nblk = cap;
   dequant_q4_k_kernel<<<nblk, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
       reinterpret_cast<const uint8_t*>(blocks), row_bytes, reinterpret_cast<__nv_bfloat16*>(out), ld_out, N, spr);
+  return cudaGetLastError() == cudaSuccess ? DSB_OK : DSB_ERR_CUDA;
+}
+
+int dsb_dequant_gguf(int ggml_type, const void* blocks, int64_t row_bytes, int N, int K, void* out, int64_t ld_out,
+                     void* stream) {
+  int tsz, bsz;
+  switch (ggml_type) {
+    case GG_Q4_0: tsz = 18, bsz = 32; break;
+    case GG_Q4_1: tsz = 20, bsz = 32; break;
+    case GG_Q5_0: tsz = 22, bsz = 32; break;
+    case GG_Q5_1: tsz = 24, bsz = 32; break;
+    case GG_Q8_0: tsz = 34, bsz = 32; break;
+    case GG_Q2_K: tsz = 84, bsz = 256; break;
+    case GG_Q3_K: tsz = 110, bsz = 256; break;
+    case GG_Q4_K: tsz = 144, bsz = 256; break;
+    case GG_Q5_K: tsz = 176, bsz = 256; break;
+    case GG_Q6_K: tsz = 210, bsz = 256; break;
+    default: return DSB_ERR_UNSUPPORTED;
+  }
+  if (N < 0 || K <= 0 || (K % bsz) || (ld_out & 7) || row_bytes < static_cast<int64_t>(K / bsz) * tsz) return DSB_ERR_ARG;
+  if (N == 0) return DSB_OK;
+  if (!blocks || !out || !aligned16(out)) return DSB_ERR_ARG;
+  const int64_t total = static_cast<int64_t>(N) * (K >> 4);
+  int nblk = static_cast<int>((total + 255) / 256);
+  const int cap = sm_count() * 16;
+  if (nblk > cap) nblk = cap;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  const uint8_t* rp = reinterpret_cast<const uint8_t*>(blocks);
+  __nv_bfloat16* op = reinterpret_cast<__nv_bfloat16*>(out);
+#define DSB_GG(T) case T: dequant_gguf_kernel<T><<<nblk, 256, 0, st>>>(rp, row_bytes, op, ld_out, N, K, tsz, bsz); break;
+  switch (ggml_type) {
+    DSB_GG(GG_Q4_0) DSB_GG(GG_Q4_1) DSB_GG(GG_Q5_0) DSB_GG(GG_Q5_1) DSB_GG(GG_Q8_0) DSB_GG(GG_Q2_K) DSB_GG(GG_Q3_K)
+    DSB_GG(GG_Q4_K) DSB_GG(GG_Q5_K) DSB_GG(GG_Q6_K)
+  }
+#undef DSB_GG
   return cudaGetLastError() == cudaSuccess ? DSB_OK : DSB_ERR_CUDA;
 }
 

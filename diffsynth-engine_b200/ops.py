@@ -209,6 +209,28 @@ def dequant_q4_k(raw, out=None):
     return out
 
 
+# ggml type number, bytes per block, weights per block
+GGUF_TYPES = {"Q4_0": (2, 18, 32), "Q4_1": (3, 20, 32), "Q5_0": (6, 22, 32), "Q5_1": (7, 24, 32), "Q8_0": (8, 34, 32),
+              "Q2_K": (10, 84, 256), "Q3_K": (11, 110, 256), "Q4_K": (12, 144, 256), "Q5_K": (13, 176, 256),
+              "Q6_K": (14, 210, 256)}
+
+
+def dequant_gguf(raw, qtype: str, out=None):
+    """GGUF bytes ``[N, K / block * bytes]`` (uint8) of block format ``qtype`` -> bf16 ``[N, K]``."""
+    _require_cuda(raw, out)
+    if qtype not in GGUF_TYPES:
+        raise _lib.DsbError(f"unsupported GGUF block format {qtype}")
+    code, tsz, bsz = GGUF_TYPES[qtype]
+    if raw.dtype != torch.uint8 or raw.dim() != 2 or raw.stride(1) != 1 or raw.shape[1] % tsz:
+        raise _lib.DsbError(f"dequant_gguf({qtype}) takes uint8 rows of {tsz}-byte blocks")
+    N, K = raw.shape[0], raw.shape[1] // tsz * bsz
+    if out is None:
+        out = torch.empty((N, K), dtype=torch.bfloat16, device=raw.device)
+    rc = _lib.lib().dsb_dequant_gguf(code, _ptr(raw), raw.stride(0), N, K, _ptr(out), out.stride(0), _stream())
+    check(rc, "dsb_dequant_gguf")
+    return out
+
+
 def cast_quant(x, out, out_fmt=FMT_E4M3, split=False):
     """Saturating cast of bf16 ``x [M, D]`` into the 8-bit window ``out`` (may be a column slice): ``[M, D]``, or
     with ``split`` (e4m3) ``[M, 3D]`` = [head | remainder | head]."""

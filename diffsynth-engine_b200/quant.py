@@ -51,11 +51,12 @@ class QuantLinearWeight(nn.Parameter):
 
 
 def _gguf_type(weight):
-    """"Q8_0" / "Q4_K" for a ``GGUFParameter`` (utils/gguf.py:9-59: raw uint8 rows plus a ``quant_dtype`` tag) of a
-    type this library dequantises itself, else None."""
+    """The block format name ("Q8_0", "Q4_K", "Q6_K", ...) of a ``GGUFParameter`` (utils/gguf.py:9-59: raw uint8 rows
+    plus a ``quant_dtype`` tag) if it is one this library dequantises itself - every format the reference does -
+    else None."""
     qd = getattr(weight, "quant_dtype", None)
     name = None if qd is None else getattr(qd, "name", str(qd))
-    return name if name in ("Q8_0", "Q4_K") else None
+    return name if name in ops.GGUF_TYPES else None
 
 
 def _is_gguf_q8_0(weight) -> bool:
@@ -75,7 +76,9 @@ def _enable_b200_linear(module: nn.Module, fmt: str):
         if not raw.is_cuda:
             raise ops._lib.DsbError("enable_b200_linear: move the module to the GPU first (no CPU path exists)")
         raw = raw.reshape(raw.shape[0], -1).contiguous()
-        w = ops.dequant_q8_0(raw) if _gguf_type(module.weight) == "Q8_0" else ops.dequant_q4_k(raw)
+        qt = _gguf_type(module.weight)
+        w = (ops.dequant_q8_0(raw) if qt == "Q8_0" else ops.dequant_q4_k(raw) if qt == "Q4_K"
+             else ops.dequant_gguf(raw, qt))
         if fmt == "bf16":
             payload, scale = w, None
         else:

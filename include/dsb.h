@@ -137,6 +137,14 @@ int dsb_dequant_q8_0(const void* blocks, int64_t row_bytes, int N, int K, void* 
  */
 int dsb_dequant_q4_k(const void* blocks, int64_t row_bytes, int N, int K, void* out, int64_t ld_out, void* stream);
 
+/* Any GGUF block format the reference dequantises (utils/gguf.py:137-147 `dequantize_functions`, :171-368): Q4_0,
+ * Q4_1, Q5_0, Q5_1, Q8_0, Q2_K, Q3_K, Q4_K, Q5_K, Q6_K, named by ggml's type number (2, 3, 6, 7, 8, 10, 11, 12, 13,
+ * 14).  raw rows `[N, K / block * bytes]` -> bf16 `[N, K]`, bit-identical to the reference's `dequantize` with bf16
+ * as compute dtype (the same products and sums, each rounded to bf16).  K must be a multiple of the block size (32,
+ * or 256 for the K-quants); `row_bytes` is the pitch of a raw row.  DSB_ERR_UNSUPPORTED for any other type. */
+int dsb_dequant_gguf(int ggml_type, const void* blocks, int64_t row_bytes, int N, int K, void* out, int64_t ld_out,
+                     void* stream);
+
 /*
  * y = saturating cast of bf16 x [M, ld_x] (D columns, D % 8 == 0) to e4m3 (round-to-nearest-even, +-448) or int8
  * (round-half-even, +-127), no scale: the values are already in operand units.  y may be a column window of a wider

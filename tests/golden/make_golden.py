@@ -1,7 +1,8 @@
 """Generates the fixtures in this directory by EXECUTING THE REFERENCE (modelscope/DiffSynth-Engine
 v0.1.1, imported from its source tree) on seeded inputs.  Run where the reference is mounted:
 
-    python tests/golden/make_golden.py <path to the DiffSynth-Engine source tree>
+    python tests/golden/make_golden.py <path to the DiffSynth-Engine source tree>             # reference_outputs.safetensors
+    python tests/golden/make_golden.py <path to the DiffSynth-Engine source tree> --gguf      # gguf_blocks.safetensors
 
 Only outputs (and small inputs) are stored; weights and large inputs are regenerated from their seeds by
 ``diffsynth-engine_b200/synth.py``, which the reference run, the oracle and the CUDA path all share.
@@ -53,6 +54,26 @@ def flux_ids(S_txt, side):
     ids[S_txt:, 1] = r[:, None].expand(side, side).reshape(-1)
     ids[S_txt:, 2] = r[None, :].expand(side, side).reshape(-1)
     return ids
+
+
+@torch.no_grad()
+def gguf_fixtures(ref_root):
+    """``gguf_blocks.safetensors``: for every GGUF block format the reference dequantises (utils/gguf.py:137-147),
+    seeded well-formed random blocks and what the reference's ``dequantize`` makes of them with bf16 and fp32 as
+    compute dtype."""
+    import_reference(ref_root)
+    import gguf as gguf_pkg
+    from diffsynth_engine.utils import gguf as ref_gguf
+    from oracle import gguf as OG
+    out = {}
+    for i, qt in enumerate(sorted(OG.SIZES)):
+        raw = OG.random_blocks(qt, 3, 512, 700 + i)
+        qd = getattr(gguf_pkg.GGMLQuantizationType, qt)
+        out[f"{qt}.raw"] = raw
+        out[f"{qt}.bf16"] = ref_gguf.dequantize(raw, quant_dtype=qd, compute_dtype=torch.bfloat16).float()
+        out[f"{qt}.f32"] = ref_gguf.dequantize(raw, quant_dtype=qd, compute_dtype=torch.float32)
+    save_file({k: v.contiguous() for k, v in out.items()}, os.path.join(HERE, "gguf_blocks.safetensors"))
+    print("wrote gguf_blocks.safetensors:", sorted(out))
 
 
 @torch.no_grad()
@@ -203,4 +224,8 @@ def main(ref_root):
 
 
 if __name__ == "__main__":
-    main(sys.argv[1] if len(sys.argv) > 1 else os.path.join(os.path.expanduser("~"), "reference"))
+    root = sys.argv[1] if len(sys.argv) > 1 else os.path.join(os.path.expanduser("~"), "reference")
+    if "--gguf" in sys.argv:
+        gguf_fixtures(root)
+    else:
+        main(root)

@@ -116,9 +116,9 @@ def test_set_attn_implementation_names(dsb):
 class _Q8Param(torch.nn.Parameter):
     """Stand-in for the reference's GGUFParameter: raw bytes plus a ``quant_dtype`` tag with a ``name``."""
 
-    def __new__(cls, data):
+    def __new__(cls, data, qtype="Q8_0"):
         self = torch.Tensor._make_subclass(cls, data, False)
-        self.quant_dtype = type("QT", (), {"name": "Q8_0"})()
+        self.quant_dtype = type("QT", (), {"name": qtype})()
         return self
 
     __torch_function__ = torch._C._disabled_torch_function_impl
@@ -167,3 +167,40 @@ def test_gguf_q4_k_dequantisation_is_bit_exact(dsb, cuda_dev):
     with b200_inference():
         y = lin(x.to(cuda_dev)).float().cpu()
     assert O.rel_l2(y, x.float() @ ref_w.float().t()) < 3e-3
+
+
+@pytest.mark.parametrize("qtype", ["Q4_0", "Q4_1", "Q5_0", "Q5_1", "Q8_0", "Q2_K", "Q3_K", "Q4_K", "Q5_K", "Q6_K"])
+def test_gguf_every_block_format_is_bit_exact(dsb, cuda_dev, qtype):
+    """``dsb_dequant_gguf`` against the reference-generated fixture (3 x 512 weights per format) and, on a larger
+    seeded matrix, against the oracle restatement that the fixture pins: identical bf16 bits."""
+    import os
+    from safetensors.torch import load_file
+    from oracle import gguf as OG
+    GG = load_file(os.path.join(os.path.dirname(__file__), "golden", "gguf_blocks.safetensors"))
+    got = dsb.ops.dequant_gguf(GG[f"{qtype}.raw"].to(cuda_dev), qtype).float().cpu()
+    assert torch.equal(got, GG[f"{qtype}.bf16"])
+    raw = OG.random_blocks(qtype, 40, 1024, 900)
+    wide = torch.zeros(40, 1024 + 64, dtype=torch.bfloat16, device=cuda_dev)          # strided output rows
+    dsb.ops.dequant_gguf(raw.to(cuda_dev), qtype, out=wide[:, :1024])
+    assert torch.equal(wide[:, :1024].float().cpu(), OG.dequantize(raw, qtype, torch.bfloat16).float())
+    assert float(wide[:, 1024:].abs().max()) == 0.0
+    with pytest.raises(dsb.DsbError):
+        dsb.ops.dequant_gguf(raw.to(cuda_dev), "Q9_9")
+
+
+def test_gguf_q6_k_parameter_goes_through_enable_b200_linear(dsb, cuda_dev):
+    """A Linear whose weight is a GGUF Q6_K parameter (a real Q4_K_S checkpoint mixes Q4_K with Q5_K / Q6_K tensors):
+    dequantised once on the device, then the bf16 drop-in equals the reference's dequantise-then-linear."""
+    from oracle import gguf as OG
+    from diffsynth_engine_b200.quant import QuantLinearWeight, b200_inference, enable_b200_linear
+    N, K = 64, 512
+    raw = OG.random_blocks("Q6_K", N, K, 901)
+    lin = nn.Linear(K, N, bias=False).to(cuda_dev)
+    lin.weight = _Q8Param(raw.to(cuda_dev), "Q6_K")
+    enable_b200_linear(lin, "bf16")
+    assert isinstance(lin.weight, QuantLinearWeight)
+    x = synth.randn((7, K), 902).bfloat16()
+    with torch.no_grad(), b200_inference():
+        y = lin(x.to(cuda_dev)).float().cpu()
+    ref = x.float() @ OG.dequantize(raw, "Q6_K", torch.bfloat16).float().t()
+    assert O.rel_l2(y, ref) < 4e-3

@@ -176,3 +176,17 @@ def test_q4_k_dequantisation_matches_reference():
     assert torch.equal(raw, O.q4_k_random_blocks(6, 512, 68))
     assert torch.equal(O.q4_k_dequantize(raw, torch.bfloat16).float(), G["q4_k.dequant_bf16"])
     assert torch.equal(O.q4_k_dequantize(raw, torch.float32), G["q4_k.dequant_f32"])
+
+
+@pytest.mark.parametrize("qtype", ["Q4_0", "Q4_1", "Q5_0", "Q5_1", "Q8_0", "Q2_K", "Q3_K", "Q4_K", "Q5_K", "Q6_K"])
+def test_gguf_block_formats_match_reference(qtype):
+    """Every GGUF block format the reference dequantises (utils/gguf.py:171-368): the element-by-element restatement
+    in oracle/gguf.py against what the reference's ``dequantize`` made of the same seeded bytes, bit for bit, with bf16
+    and with fp32 as compute dtype."""
+    from oracle import gguf as OG
+    GG = load_file(os.path.join(os.path.dirname(__file__), "golden", "gguf_blocks.safetensors"))
+    raw = GG[f"{qtype}.raw"]
+    i = sorted(OG.SIZES).index(qtype)
+    assert torch.equal(raw, OG.random_blocks(qtype, 3, 512, 700 + i))
+    assert torch.equal(OG.dequantize(raw, qtype, torch.bfloat16).float(), GG[f"{qtype}.bf16"])
+    assert torch.equal(OG.dequantize(raw, qtype, torch.float32), GG[f"{qtype}.f32"])
