@@ -149,7 +149,9 @@ def test_reference_gguf_parameter_is_recognised(dsb):
                            compute_dtype=torch.bfloat16)
         assert not quant._is_gguf_q8_0(q4) and quant._gguf_type(q4) == "Q4_K"
         q6 = GGUFParameter(raw, quant_dtype=gguf.GGMLQuantizationType.Q6_K, compute_dtype=torch.bfloat16)
-        assert quant._gguf_type(q6) is None                                   # left to the reference's gguf_inference
+        assert quant._gguf_type(q6) == "Q6_K"                                 # every block format of the reference
+        f16 = GGUFParameter(raw, quant_dtype=gguf.GGMLQuantizationType.F16, compute_dtype=torch.bfloat16)
+        assert quant._gguf_type(f16) is None                                  # plain tensors stay with the reference
         assert not quant._is_gguf_q8_0(torch.nn.Parameter(torch.zeros(2, 2)))
     finally:
         if saved is None:
