@@ -81,9 +81,13 @@ struct GemmSmem {
   static constexpr int kStageA = kBlockM * kSlabBytes;
   static constexpr int kStageB = (BLOCK_N / CTAS) * kSlabBytes;
   static constexpr int kStage = kStageA + kStageB;
-  static constexpr int kStages = (kStage == 48 * 1024) ? 4 : 6;
+  // per epilogue warp: four per-column parameter vectors (scale, bias, gate, head-norm weight) of its BLOCK_N/2 columns
+  static constexpr int kParamFloats = 4 * (BLOCK_N / 2);
+  static constexpr int kParamBytes = kEpiWarps * kParamFloats * 4;
   static constexpr int kBarBytes = 256;
-  static constexpr int kTotal = kStages * kStage + kStageBytes + kBarBytes + 1024;  // + alignment slack
+  static constexpr int kFixed = kStageBytes + kParamBytes + kBarBytes + 1024;  // + alignment slack
+  static constexpr int kStages = (227 * 1024 - kFixed) / kStage;                // 5 of 32 KiB, 3 of 48 KiB
+  static constexpr int kTotal = kStages * kStage + kFixed;
 };
 
 template <int KIND, int BLOCK_N, int CTAS>
@@ -108,7 +112,8 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
   // 1024-byte alignment: the 128-byte swizzle pattern repeats every 8 rows = 1024 bytes.
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* stage_base = smem + kStages * SM::kStage;  // 1024-aligned: stages are multiples of 16 KiB
-  uint8_t* bar_base = stage_base + kStageBytes;
+  float* param_base = reinterpret_cast<float*>(stage_base + kStageBytes);
+  uint8_t* bar_base = stage_base + kStageBytes + SM::kParamBytes;
   uint64_t* full_bar = reinterpret_cast<uint64_t*>(bar_base);
   uint64_t* empty_bar = full_bar + kStages;
   uint64_t* tmem_full = empty_bar + kStages;
@@ -242,6 +247,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
     const int ew = warp - 2;
     const int half = ew >> 2;  // which half of the tile's 64-column blocks this warp drains
     uint8_t* sbuf = stage_base + ew * kStageSlotBytes;
+    float* ptab = param_base + ew * SM::kParamFloats;
     uint64_t* rbar = resid_bar + ew;
     uint32_t rphase = 0;
     constexpr int kBlocksPerWarp = BLOCK_N / 64 / 2;
@@ -280,31 +286,43 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
         }
         __syncwarp();
       }
-      // Per-column epilogue parameters (bias, per-channel scale, gate, head-norm weight) of this warp's column range:
-      // lane l keeps kPer consecutive columns' values in registers, fetched once per tile before the accumulator is
-      // ready, and the 8-column groups below pick theirs up by warp shuffles.  (Loading them group by group, right
-      // where they are used, cost a serial L2 round trip per group: 20.8k cycles of epilogue per 256x256 tile
-      // against 16k of mainloop at K = 3072.)
+      // Per-column epilogue parameters (per-channel scale, bias, gate, head-norm weight) of this warp's column range:
+      // lane l fetches kPer consecutive columns' values once per tile, before the accumulator is ready, into the
+      // warp's own table in shared memory; the 8-column groups below read theirs back as two 16-byte broadcasts per
+      // vector.  (Loading them group by group from global memory, right where they are used, cost a serial L2 round
+      // trip per group; keeping them in registers and handing them round by warp shuffles cost 8 shuffles per
+      // vector and group, and the shuffle unit issues one per cycle for the whole SM.)
       constexpr int kWarpCols = BLOCK_N / 2, kPer = kWarpCols / 32;
       const int wcol0 = n0 + half * kWarpCols;
-      float p_bias[kPer], p_cs[kPer], p_gate[kPer], p_hw[kPer];
       {
         const int c = wcol0 + lane * kPer;
         const bool in = c < N;
         const bool chan = ep.col_scale && ep.col_scale_stride;
         const float* hw = (wcol0 < ep.d_model) ? ep.nq_w : ep.nk_w;
+        float p_cs[kPer], p_bias[kPer], p_gate[kPer], p_hw[kPer];
 #pragma unroll
         for (int j = 0; j < kPer; ++j) {
-          p_bias[j] = (in && ep.bias) ? __ldg(ep.bias + c + j) : 0.f;
           p_cs[j] = (in && chan) ? __ldg(ep.col_scale + c + j) : 1.f;
+          p_bias[j] = (in && ep.bias) ? __ldg(ep.bias + c + j) : 0.f;
           p_gate[j] = (in && ep.gate) ? __ldg(ep.gate + c + j) : 1.f;
           p_hw[j] = (fuse_norm && hw) ? __ldg(hw + ((lane * kPer + j) & 127)) : 1.f;
         }
-      }
-      // the 8 values of the column group that starts at column c8 (a multiple of 8) of the warp's range
-      auto pick8 = [&](const float (&mine)[kPer], int c8, float (&out)[8]) {
+        __syncwarp();  // every lane has read the previous tile's values
 #pragma unroll
-        for (int j = 0; j < 8; ++j) out[j] = __shfl_sync(0xffffffffu, mine[j % kPer], c8 / kPer + j / kPer);
+        for (int j = 0; j < kPer; ++j) {
+          ptab[0 * kWarpCols + lane * kPer + j] = p_cs[j];
+          ptab[1 * kWarpCols + lane * kPer + j] = p_bias[j];
+          ptab[2 * kWarpCols + lane * kPer + j] = p_gate[j];
+          ptab[3 * kWarpCols + lane * kPer + j] = p_hw[j];
+        }
+        __syncwarp();
+      }
+      // the 8 values of vector `which` for the column group that starts at column c8 (a multiple of 8) of the range
+      auto pick8 = [&](int which, int c8, float (&out)[8]) {
+        const float4 lo = *reinterpret_cast<const float4*>(ptab + which * kWarpCols + c8);
+        const float4 hi = *reinterpret_cast<const float4*>(ptab + which * kWarpCols + c8 + 4);
+        out[0] = lo.x, out[1] = lo.y, out[2] = lo.z, out[3] = lo.w;
+        out[4] = hi.x, out[5] = hi.y, out[6] = hi.z, out[7] = hi.w;
       };
       // the row's activation scale is fetched before the wait as well
       const float rs = (ep.row_scale && m < M) ? __ldg(ep.row_scale + m) : 1.0f;
@@ -327,8 +345,8 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
 #pragma unroll
           for (int g = 0; g < 4; ++g) {
             float cs8[8], b8[8];
-            pick8(p_cs, c * 32 + g * 8, cs8);
-            pick8(p_bias, c * 32 + g * 8, b8);
+            pick8(0, c * 32 + g * 8, cs8);
+            pick8(1, c * 32 + g * 8, b8);
 #pragma unroll
             for (int j = 0; j < 8; ++j) cs8[j] *= rs_t;   // rs_t = row scale x per-tensor scale (1 if per-channel)
 #pragma unroll
@@ -397,14 +415,14 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
               const int c8 = cb_local * 64 + h * 32 + g * 8;   // first column of the group inside the warp's range
               {
                 float cs8[8], b8[8];
-                pick8(p_cs, c8, cs8);
-                pick8(p_bias, c8, b8);
+                pick8(0, c8, cs8);
+                pick8(1, c8, b8);
 #pragma unroll
                 for (int j = 0; j < 8; ++j) v[j] = fmaf(v[j], cs8[j] * rs_t, b8[j]);
               }
               if (fuse_norm) {
                 float w8[8];
-                pick8(p_hw, c8, w8);
+                pick8(3, c8, w8);
 #pragma unroll
                 for (int j = 0; j < 8; ++j) v[j] *= rnorm * w8[j];
                 if (do_rope) {
@@ -439,7 +457,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
                 const uint4 rr = *reinterpret_cast<const uint4*>(cell);
                 const uint32_t ru[4] = {rr.x, rr.y, rr.z, rr.w};
                 float gte[8];
-                pick8(p_gate, c8, gte);
+                pick8(2, c8, gte);
 #pragma unroll
                 for (int j = 0; j < 4; ++j) {
                   const float2 f = unpack_bf16x2(ru[j]);
