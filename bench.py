@@ -318,8 +318,9 @@ def wan_parity(ctx, args):
     t = torch.tensor([417.0])
     if ctx.world > 1:
         eng = wan.WanDiTEngine(dict(sd), fmt=args.wan_fmt, device=dev, num_layers=2, num_heads=c["H"],
-                               group=ctx.dist.group.WORLD)
+                               group=ctx.dist.group.WORLD, exchange=args.wan_exchange)
         y_sp = eng(x.to(dev), ctxt.to(dev), t.to(dev)).float()
+        exch = eng.exchange
         del eng
         if ctx.rank == 0:
             one = wan.WanDiTEngine(dict(sd), fmt=args.wan_fmt, device=dev, num_layers=2, num_heads=c["H"])
@@ -327,7 +328,8 @@ def wan_parity(ctx, args):
             del one
             out["sp_vs_one_gpu_rel_l2"] = float((y_sp - y_1).norm() / y_1.norm())
             out["sp_vs_one_gpu_tolerance"] = 3e-3
-            out["sp_check"] = f"2-block model at full width, full 32760-token video, sp{ctx.world} vs rank 0 alone"
+            out["sp_check"] = (f"2-block model at full width, full 32760-token video, sp{ctx.world} "
+                               f"(exchange: {exch}) vs rank 0 alone")
         ctx.barrier()
     if ctx.rank == 0 and ctx.world == 1 and not args.no_oracle_parity:   # (N > 1: the other ranks would idle meanwhile)
         from oracle import flux as OF
@@ -376,7 +378,8 @@ def run_wan(ctx, args, steps, warmup):
     shapes = synth.wan_dit_shapes(d=c["d"], ffn=c["ffn"], num_layers=c["num_layers"], text_dim=c["text_dim"])
     sd = synth.make_state_dict(shapes, seed=1234, device=dev, dtype=torch.bfloat16)   # same weights on every rank
     eng = wan.WanDiTEngine(sd, fmt=args.wan_fmt, device=dev, num_layers=c["num_layers"], num_heads=c["H"],
-                           group=(dist.group.WORLD if dist is not None else None), release_source=True)
+                           group=(dist.group.WORLD if dist is not None else None), release_source=True,
+                           exchange=args.wan_exchange)
     del sd
     torch.cuda.empty_cache()
     eng.prepare(c["frames"], c["height"], c["width"], c["ctx"], c["text_dim"])
@@ -413,11 +416,18 @@ def run_wan(ctx, args, steps, warmup):
     ms_e2e = ctx.timed_steps(e2e_step, steps)
     pkg.ops.check_status(dev.index)
     # ---- roofline of the dominant kernel (self-attention): CUDA events around every launch of one eager step
-    recs = timed_launches(ctx, pkg.ops, ["flash_attn"], eng.step)
+    recs = timed_launches(ctx, pkg.ops, ["flash_attn", "flash_attn_parts"], eng.step)
     S = c["frames"] * (c["height"] // 2) * (c["width"] // 2)
-    self_attn = [r for r in recs if r[1][1].shape[1] > c["ctx"] + 257]        # keys = tokens, not the context
+
+    def dims(r):   # (Sq, Sk, H) of a recorded attention launch
+        a = r[1]
+        if r[0] == "flash_attn_parts":   # (q_parts, q_rows, q_strides, k, v, o_parts, o_rows, o_strides, H, Sq)
+            return a[9], a[3].shape[1], a[8]
+        return a[0].shape[1], a[1].shape[1], a[0].shape[2]
+
+    self_attn = [r for r in recs if dims(r)[1] > c["ctx"] + 257]              # keys = tokens, not the context
     attn_ms = sum(r[3] for r in self_attn)
-    attn_flops = sum(4.0 * r[1][0].shape[1] * r[1][1].shape[1] * r[1][0].shape[2] * 128 for r in self_attn)
+    attn_flops = sum(4.0 * dims(r)[0] * dims(r)[1] * dims(r)[2] * 128 for r in self_attn)
     peaks = measured_peaks()
     lin_f, attn_f = wan_step_flops(c)
     fp8 = args.wan_fmt != "bf16"
@@ -444,6 +454,8 @@ def run_wan(ctx, args, steps, warmup):
             "steps_per_s": 1e3 / ms, "ms_per_step": ms, "e2e_steps_per_s": 1e3 / ms_e2e, "e2e_ms_per_step": ms_e2e,
             "n_gpus": ctx.world, "gpu_launches_per_step": launches, "clocks": clocks, "roofline": roofline,
             "parity": parity,
+            # how q and the attention output cross ranks ("peer": inside the attention kernel over mapped peer memory)
+            "exchange": eng.exchange if ctx.world > 1 else None,
             # the prompt embedding is the same tensor at every step (as in the reference pipeline): it is copied, and the
             # cross-attention keys / values of all blocks are computed from it, once - during warm-up
             "cross_attention_kv_cache": "warm (context unchanged since warm-up; it is not copied or projected again)",
@@ -777,6 +789,8 @@ def main():
                          "under 'flux' at one GPU; wan / flux / qwen: that workload alone as the line's value")
     ap.add_argument("--wan-fmt", default="fp8_channel")
     ap.add_argument("--wan-layers", type=int, default=0, help="reduced depth (debugging; not a bench)")
+    ap.add_argument("--wan-exchange", default="auto", choices=["auto", "peer", "nccl"],
+                    help="how q and the attention output cross ranks at N > 1 (see WanDiTEngine)")
     ap.add_argument("--sp", action="store_true",
                     help="flux/qwen workloads under torchrun: ONE image, its token sequence split over all ranks (Ulysses, "
                          "strong scaling) instead of one replica per GPU")
@@ -855,6 +869,7 @@ def main():
                      "gpu_launches": r["gpu_launches_per_step"] * steps,
                      "gpu_launches_per_step": r["gpu_launches_per_step"],
                      "cross_attention_kv_cache": r["cross_attention_kv_cache"],
+                     "sp_exchange": r["exchange"],
                      "roofline": r["roofline"], "parity": r["parity"]})
         if args.workload == "both" and world == 1:
             f = run_flux(ctx, args, dict(FLUX), "flux", steps, warmup)

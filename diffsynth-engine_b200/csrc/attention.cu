@@ -50,8 +50,18 @@ constexpr int kHalfBytes = kTileBytes / 2;
 constexpr int kXchgSlots = 2 * 2 * 128 * 3;  // [q][half][row] x {running maximum (even tile, odd tile), row sum}
 constexpr int kAttnSmem = (kNQ + 2 * kKVStages) * kTileBytes + 256 + kXchgSlots * 8 + 1024;
 
+constexpr int kMaxParts = 8;
+// The query rows (and, independently, the output rows) may be cut into up to kMaxParts equal row ranges that live in
+// different buffers - e.g. in the memory of different GPUs of a sequence-parallel group, where rank r holds the
+// queries of its own tokens and receives the output rows of its own tokens from every rank.
+struct AttnQMaps {
+  CUtensorMap m[kMaxParts];
+};
 struct AttnParams {
   __nv_bfloat16* o;
+  __nv_bfloat16* o_part[kMaxParts];
+  int q_rows_per_part;  // 0: one query buffer (map 0); else a multiple of kTileQ
+  int o_rows_per_part;  // 0: one output buffer (o); else row s goes to o_part[s / o_rows_per_part]
   int64_t o_stride_b, o_stride_s, o_stride_h;
   int Sq, Sk;
   float scale_log2;  // sm_scale * log2(e)
@@ -106,7 +116,7 @@ __device__ __forceinline__ void load_tile(uint8_t* dst, const CUtensorMap* m, ui
 #define mbar_arrive(bar) mbar_arrive(bar)
 
 __global__ void __launch_bounds__(kAttnThreads, 1)
-    flash_attn_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
+    flash_attn_kernel(const __grid_constant__ AttnQMaps qmaps, const __grid_constant__ CUtensorMap tmap_k,
                       const __grid_constant__ CUtensorMap tmap_v, AttnParams p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -153,7 +163,7 @@ __global__ void __launch_bounds__(kAttnThreads, 1)
   }
   for (int i = threadIdx.x; i < kXchgSlots; i += blockDim.x) xchg[i] = 0ull;  // sequence 0 = nothing published
   if (warp == 0 && lane == 0) {
-    tma_prefetch_desc(&tmap_q);
+    tma_prefetch_desc(&qmaps.m[0]);
     tma_prefetch_desc(&tmap_k);
     tma_prefetch_desc(&tmap_v);
   }
@@ -170,7 +180,14 @@ __global__ void __launch_bounds__(kAttnThreads, 1)
     // ------------------------------------------------------------ TMA producer
     if (lane == 0) {
       mbar_expect_tx(q_full, kNQ * kTileBytes);
-      for (int q = 0; q < kNQ; ++q) load_tile(sQ + q * kTileBytes, &tmap_q, q_full, p.q_pos, q0 + q * kTileQ, h, b);
+      for (int q = 0; q < kNQ; ++q) {
+        int s0 = q0 + q * kTileQ, part = 0;
+        if (p.q_rows_per_part > 0) {  // a 128-row tile never straddles two parts
+          part = min(s0 / p.q_rows_per_part, kMaxParts - 1);
+          s0 -= part * p.q_rows_per_part;
+        }
+        load_tile(sQ + q * kTileBytes, &qmaps.m[part], q_full, p.q_pos, s0, h, b);
+      }
       int st = 0;
       uint32_t ph = 0;
       for (int j = 0; j < nkv; ++j) {
@@ -430,8 +447,14 @@ __global__ void __launch_bounds__(kAttnThreads, 1)
       ok = xchg_read(&slot_other[2], 0x7fffffffu, &lo, abort_flag);
       const float inv = 1.0f / (l + lo);
       const int sq = q0 + q * kTileQ + row;
-      __nv_bfloat16* orow = p.o + static_cast<int64_t>(b) * p.o_stride_b + static_cast<int64_t>(sq) * p.o_stride_s +
-                            static_cast<int64_t>(h) * p.o_stride_h + half * 64;
+      __nv_bfloat16* obase = p.o + static_cast<int64_t>(b) * p.o_stride_b;
+      int so = sq;
+      if (p.o_rows_per_part > 0) {
+        const int part = min(sq / p.o_rows_per_part, kMaxParts - 1);
+        obase = p.o_part[part];
+        so = sq - part * p.o_rows_per_part;
+      }
+      __nv_bfloat16* orow = obase + static_cast<int64_t>(so) * p.o_stride_s + static_cast<int64_t>(h) * p.o_stride_h + half * 64;
 #pragma unroll 1
       for (int c = 0; c < 2; ++c) {
         uint32_t r[32];
@@ -500,28 +523,67 @@ static int make_tmap_attn(CUtensorMap* out, int (&pos)[3], const void* base, int
 
 using namespace dsb;
 
-extern "C" int dsb_flash_attn(const void* q, const void* k, const void* v, void* o, int B, int H, int Sq, int Sk,
-                              int head_dim, int64_t q_stride_b, int64_t q_stride_s, int64_t q_stride_h,
-                              int64_t k_stride_b, int64_t k_stride_s, int64_t k_stride_h, int64_t v_stride_b,
-                              int64_t v_stride_s, int64_t v_stride_h, int64_t o_stride_b, int64_t o_stride_s,
-                              int64_t o_stride_h, float sm_scale, int* status, void* stream) {
-  if (!q || !k || !v || !o || B <= 0 || H <= 0 || Sq < 0 || Sk <= 0) return DSB_ERR_ARG;
+// q_parts / o_parts: nullptr for one buffer (q / o), else n equal row ranges in separate buffers
+static int launch_attn(const void* q, const void* const* q_parts, int n_q_parts, int q_rows_per_part, const void* k,
+                       const void* v, void* o, void* const* o_parts, int n_o_parts, int o_rows_per_part, int B, int H,
+                       int Sq, int Sk, int head_dim, int64_t q_stride_b, int64_t q_stride_s, int64_t q_stride_h,
+                       int64_t k_stride_b, int64_t k_stride_s, int64_t k_stride_h, int64_t v_stride_b,
+                       int64_t v_stride_s, int64_t v_stride_h, int64_t o_stride_b, int64_t o_stride_s,
+                       int64_t o_stride_h, float sm_scale, int* status, void* stream) {
+  if (!k || !v || B <= 0 || H <= 0 || Sq < 0 || Sk <= 0) return DSB_ERR_ARG;
   if (head_dim != 128) return DSB_ERR_UNSUPPORTED;
   if (H > 65535 || B > 65535) return DSB_ERR_UNSUPPORTED;
   auto al16 = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; };
-  if (!al16(q) || !al16(k) || !al16(v) || !al16(o)) return DSB_ERR_ARG;
+  if (!al16(k) || !al16(v)) return DSB_ERR_ARG;
+  if (q_parts) {
+    if (B != 1 || n_q_parts < 1 || n_q_parts > kMaxParts || q_rows_per_part <= 0 || (q_rows_per_part % kTileQ) ||
+        static_cast<int64_t>(n_q_parts) * q_rows_per_part < Sq)
+      return DSB_ERR_ARG;
+    for (int i = 0; i < n_q_parts; ++i)
+      if (!q_parts[i] || !al16(q_parts[i])) return DSB_ERR_ARG;
+  } else if (!q || !al16(q)) {
+    return DSB_ERR_ARG;
+  }
+  if (o_parts) {
+    if (B != 1 || n_o_parts < 1 || n_o_parts > kMaxParts || o_rows_per_part <= 0 ||
+        static_cast<int64_t>(n_o_parts) * o_rows_per_part < Sq)
+      return DSB_ERR_ARG;
+    for (int i = 0; i < n_o_parts; ++i)
+      if (!o_parts[i] || !al16(o_parts[i])) return DSB_ERR_ARG;
+  } else if (!o || !al16(o)) {
+    return DSB_ERR_ARG;
+  }
   const int64_t strides[] = {q_stride_s, q_stride_h, k_stride_s, k_stride_h, v_stride_s, v_stride_h,
                              o_stride_s, o_stride_h, q_stride_b, k_stride_b, v_stride_b, o_stride_b};
   for (int64_t s : strides)
     if (s < 0 || (s & 7)) return DSB_ERR_ARG;
   if (Sq == 0) return DSB_OK;
-  AttnParams p;
-  CUtensorMap tq, tk, tv;
+  AttnParams p = {};
+  AttnQMaps qm;
+  CUtensorMap tk, tv;
   int rc;
-  if ((rc = make_tmap_attn(&tq, p.q_pos, q, Sq, H, B, q_stride_s, q_stride_h, q_stride_b)) != DSB_OK) return rc;
+  if (q_parts) {
+    for (int i = 0; i < kMaxParts; ++i) {
+      // rows of part i that exist (the last parts may be short or empty: their map still needs one row)
+      int rows = Sq - i * q_rows_per_part;
+      rows = rows > q_rows_per_part ? q_rows_per_part : (rows < 1 ? 1 : rows);
+      const void* base = q_parts[i < n_q_parts ? i : n_q_parts - 1];
+      if ((rc = make_tmap_attn(&qm.m[i], p.q_pos, base, rows, H, 1, q_stride_s, q_stride_h, q_stride_b)) != DSB_OK)
+        return rc;
+    }
+    p.q_rows_per_part = q_rows_per_part;
+  } else {
+    if ((rc = make_tmap_attn(&qm.m[0], p.q_pos, q, Sq, H, B, q_stride_s, q_stride_h, q_stride_b)) != DSB_OK) return rc;
+    for (int i = 1; i < kMaxParts; ++i) qm.m[i] = qm.m[0];
+  }
   if ((rc = make_tmap_attn(&tk, p.k_pos, k, Sk, H, B, k_stride_s, k_stride_h, k_stride_b)) != DSB_OK) return rc;
   if ((rc = make_tmap_attn(&tv, p.v_pos, v, Sk, H, B, v_stride_s, v_stride_h, v_stride_b)) != DSB_OK) return rc;
   p.o = reinterpret_cast<__nv_bfloat16*>(o);
+  if (o_parts) {
+    for (int i = 0; i < kMaxParts; ++i)
+      p.o_part[i] = reinterpret_cast<__nv_bfloat16*>(o_parts[i < n_o_parts ? i : n_o_parts - 1]);
+    p.o_rows_per_part = o_rows_per_part;
+  }
   p.o_stride_b = o_stride_b;
   p.o_stride_s = o_stride_s;
   p.o_stride_h = o_stride_h;
@@ -531,6 +593,27 @@ extern "C" int dsb_flash_attn(const void* q, const void* k, const void* v, void*
   p.status = status;
   DSB_ENSURE_SMEM(flash_attn_kernel, kAttnSmem);
   dim3 grid((Sq + kNQ * kTileQ - 1) / (kNQ * kTileQ), H, B);
-  flash_attn_kernel<<<grid, kAttnThreads, kAttnSmem, reinterpret_cast<cudaStream_t>(stream)>>>(tq, tk, tv, p);
+  flash_attn_kernel<<<grid, kAttnThreads, kAttnSmem, reinterpret_cast<cudaStream_t>(stream)>>>(qm, tk, tv, p);
   return cudaGetLastError() == cudaSuccess ? DSB_OK : DSB_ERR_CUDA;
+}
+
+extern "C" int dsb_flash_attn(const void* q, const void* k, const void* v, void* o, int B, int H, int Sq, int Sk,
+                              int head_dim, int64_t q_stride_b, int64_t q_stride_s, int64_t q_stride_h,
+                              int64_t k_stride_b, int64_t k_stride_s, int64_t k_stride_h, int64_t v_stride_b,
+                              int64_t v_stride_s, int64_t v_stride_h, int64_t o_stride_b, int64_t o_stride_s,
+                              int64_t o_stride_h, float sm_scale, int* status, void* stream) {
+  return launch_attn(q, nullptr, 0, 0, k, v, o, nullptr, 0, 0, B, H, Sq, Sk, head_dim, q_stride_b, q_stride_s, q_stride_h,
+                     k_stride_b, k_stride_s, k_stride_h, v_stride_b, v_stride_s, v_stride_h, o_stride_b, o_stride_s,
+                     o_stride_h, sm_scale, status, stream);
+}
+
+extern "C" int dsb_flash_attn_parts(const void* const* q_parts, int n_q_parts, int q_rows_per_part, const void* k,
+                                    const void* v, void* const* o_parts, int n_o_parts, int o_rows_per_part, int H,
+                                    int Sq, int Sk, int head_dim, int64_t q_stride_s, int64_t q_stride_h,
+                                    int64_t k_stride_s, int64_t k_stride_h, int64_t v_stride_s, int64_t v_stride_h,
+                                    int64_t o_stride_s, int64_t o_stride_h, float sm_scale, int* status, void* stream) {
+  if (!q_parts || !o_parts) return DSB_ERR_ARG;
+  return launch_attn(nullptr, q_parts, n_q_parts, q_rows_per_part, k, v, nullptr, o_parts, n_o_parts, o_rows_per_part, 1,
+                     H, Sq, Sk, head_dim, 0, q_stride_s, q_stride_h, 0, k_stride_s, k_stride_h, 0, v_stride_s,
+                     v_stride_h, 0, o_stride_s, o_stride_h, sm_scale, status, stream);
 }

@@ -137,11 +137,52 @@ __global__ void __launch_bounds__(64) wait_timeout_selftest_kernel(long long lim
   if (threadIdx.x == 0 && *abort_flag && status) atomicCAS(status, 0, DSB_ERR_TIMEOUT);
 }
 
+// A barrier among the ranks of a sequence-parallel group (one process and one GPU per rank).  flags.f[r] is rank r's
+// flag array (one int per rank) in memory that every rank has mapped.  Thread t tells rank t "rank `rank` has
+// reached `epoch`" (slot [rank] of rank t's array) and then waits until rank t has told this rank the same.  The
+// system-scope fence before the signal orders everything earlier launches of this stream wrote - to any rank's
+// memory - before it; the acquire on the waiting side makes those writes visible to later launches of the waiter.
+// Epochs only grow, so a rank that is already one barrier ahead never blocks a slower one.  The wait is bounded.
+struct RankFlags {
+  int* f[8];
+};
+__global__ void __launch_bounds__(32) rank_barrier_kernel(RankFlags flags, int n, int rank, int epoch,
+                                                          long long limit_cycles, int* status) {
+  const int t = threadIdx.x;
+  if (t >= n) return;
+  __threadfence_system();
+  asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(flags.f[t] + rank), "r"(epoch) : "memory");
+  const int* mine = flags.f[rank] + t;
+  // after one barrier of this process has timed out the run is lost anyway: later barriers do not wait again
+  if (status && *reinterpret_cast<volatile int*>(status) != 0) return;
+  const long long t0 = clock64();
+  for (;;) {
+    int v;
+    asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(mine) : "memory");
+    if (v - epoch >= 0) return;
+    if (clock64() - t0 > limit_cycles) break;
+    __nanosleep(100);
+  }
+  if (status) atomicCAS(status, 0, DSB_ERR_TIMEOUT);
+}
+
 }  // namespace dsb
 
 using namespace dsb;
 
 extern "C" int dsb_version(void) { return 100; }
+
+extern "C" int dsb_rank_barrier(int* const* flags, int n_ranks, int rank, int epoch, long long limit_cycles,
+                                int* status, void* stream) {
+  if (!flags || n_ranks < 1 || n_ranks > 8 || rank < 0 || rank >= n_ranks || limit_cycles <= 0) return DSB_ERR_ARG;
+  RankFlags f = {};
+  for (int i = 0; i < n_ranks; ++i) {
+    if (!flags[i] || (reinterpret_cast<uintptr_t>(flags[i]) & 3u)) return DSB_ERR_ARG;
+    f.f[i] = flags[i];
+  }
+  rank_barrier_kernel<<<1, 32, 0, reinterpret_cast<cudaStream_t>(stream)>>>(f, n_ranks, rank, epoch, limit_cycles, status);
+  return cudaGetLastError() == cudaSuccess ? DSB_OK : DSB_ERR_CUDA;
+}
 
 extern "C" int dsb_selftest_wait_timeout(long long limit_cycles, int* status, int* neighbour_left, void* stream) {
   if (!status || limit_cycles <= 0 || limit_cycles > kWaitLimitCycles) return DSB_ERR_ARG;

@@ -91,6 +91,31 @@ def _rows(t: torch.Tensor) -> Tuple[int, int, int]:
     return t.shape[0], t.shape[1], t.stride(0)
 
 
+def _check_gemm_io(M, N, out, out1, split_col, resid=None, row_scale=None, col_scale=None, bias=None, gate=None,
+                   e4m3_ok=False):
+    """The C entry points take raw pointers: every shape and dtype they rely on is checked here, so that a wrong
+    buffer raises instead of being written out of bounds."""
+    n0 = N if (out1 is None or split_col is None) else split_col
+    ok_out = (torch.bfloat16, torch.float8_e4m3fn) if e4m3_ok else (torch.bfloat16,)
+    for name, t, cols in (("out", out, n0), ("out1", out1, N - n0)):
+        if t is None:
+            continue
+        if t.dtype not in ok_out:
+            raise _lib.DsbError(f"gemm {name} must be bfloat16" + (" or float8_e4m3fn" if e4m3_ok else
+                                " (use gemm_group for an e4m3 output)"))
+        if t.dim() != 2 or t.stride(1) != 1 or t.shape[0] != M or t.shape[1] < cols:
+            raise _lib.DsbError(f"gemm {name} must be a [{M}, >={cols}] row view, got {tuple(t.shape)}")
+    if out1 is not None and not 0 < n0 < N:
+        raise _lib.DsbError("split_col must lie inside (0, N) when out1 is given")
+    if resid is not None and (resid.dtype != torch.bfloat16 or resid.dim() != 2 or resid.stride(1) != 1
+                              or resid.shape[0] != M or resid.shape[1] < N):
+        raise _lib.DsbError(f"gemm resid must be a bfloat16 [{M}, >={N}] row view")
+    for name, t, n in (("row_scale", row_scale, M), ("bias", bias, N), ("gate", gate, N),
+                       ("col_scale", col_scale, 1 if (col_scale is not None and col_scale.numel() == 1) else N)):
+        if t is not None and (t.dtype != torch.float32 or t.numel() < n or not t.is_contiguous()):
+            raise _lib.DsbError(f"gemm {name} must be contiguous float32 with at least {n} elements")
+
+
 def ln_modulate(x, shift, scale, eps=1e-6, out_fmt=FMT_BF16, out=None, row_scale=None, split_row=None,
                 shift_b=None, scale_b=None):
     """LayerNorm (no affine) then ``* (1 + scale) + shift``; optionally quantised per row.  With ``split_row``
@@ -301,6 +326,12 @@ def gemm(a, w, row_scale=None, col_scale=None, bias=None, act=ACT_NONE, act_col0
     if out is None:
         n0 = N if out1 is None else split_col
         out = torch.empty((M, n0), dtype=torch.bfloat16, device=a.device)
+    if torch.float8_e4m3fn in (out.dtype, None if out1 is None else out1.dtype):
+        # an e4m3 output selects the unit-scale 8-bit epilogue, which only the grouped entry point describes
+        gemm_group([dict(a=a, w=w, row_scale=row_scale, col_scale=col_scale, bias=bias, act=act, act_col0=act_col0,
+                         gate=gate, resid=resid, out=out, out1=out1, split_col=split_col)])
+        return out
+    _check_gemm_io(M, N, out, out1, split_col, resid, row_scale, col_scale, bias, gate)
     cs_stride = 0 if (col_scale is None or col_scale.numel() == 1) else 1
     rc = _lib.lib().dsb_gemm(
         _ptr(a), lda, _ptr(w), ldw, _fmt_of(a), M, N, K, _ptr(row_scale), _ptr(col_scale), cs_stride, _ptr(bias), act,
@@ -331,6 +362,12 @@ def gemm_qkv(a, w, nq_w, nk_w, d_model, rope=None, rope_row0=0, eps=1e-6, row_sc
         raise _lib.DsbError("gemm operands disagree in K or format")
     if out is None:
         out = torch.empty((M, N if out1 is None else split_col), dtype=torch.bfloat16, device=a.device)
+    if torch.float8_e4m3fn in (out.dtype, None if out1 is None else out1.dtype):
+        gemm_group([dict(a=a, w=w, row_scale=row_scale, col_scale=col_scale, bias=bias, act=act, act_col0=act_col0,
+                         out=out, out1=out1, split_col=split_col, nq_w=nq_w, nk_w=nk_w, d_model=d_model, rope=rope,
+                         rope_row0=rope_row0, eps=eps)])
+        return out
+    _check_gemm_io(M, N, out, out1, split_col, None, row_scale, col_scale, bias, None)
     cs_stride = 0 if (col_scale is None or col_scale.numel() == 1) else 1
     rc = _lib.lib().dsb_gemm_qkv(
         _ptr(a), lda, _ptr(w), ldw, _fmt_of(a), M, N, K, _ptr(row_scale), _ptr(col_scale), cs_stride, _ptr(bias), act,
@@ -362,6 +399,8 @@ def gemm_group(problems):
         if pr.get("nq_w") is not None:
             _check_rope_table(pr.get("rope"), pr.get("rope_row0", 0) + M)
         cs = pr.get("col_scale")
+        _check_gemm_io(M, N, out, out1, pr.get("split_col"), resid, pr.get("row_scale"), cs, pr.get("bias"),
+                       pr.get("gate"), e4m3_ok=True)
         g = arr[i]
         g.A, g.lda, g.W, g.ldw, g.M, g.N, g.K = a.data_ptr(), lda, w.data_ptr(), ldw, M, N, K
         for name, key in (("row_scale", "row_scale"), ("col_scale", "col_scale"), ("bias", "bias"), ("gate", "gate"),
@@ -403,6 +442,58 @@ def flash_attn(q, k, v, out=None, sm_scale=None):
         float(sm_scale), _ptr(status_word(q.device)), _stream())
     check(rc, "dsb_flash_attn")
     return out
+
+
+def _addr_array(items):
+    """Host array of device addresses for the C side; items are tensors or integer addresses (memory of another GPU
+    that this process has mapped has no tensor here)."""
+    arr = (ctypes.c_void_p * len(items))()
+    for i, it in enumerate(items):
+        arr[i] = it.data_ptr() if isinstance(it, torch.Tensor) else int(it)
+    return arr
+
+
+def flash_attn_parts(q_parts, q_rows_per_part, q_strides, k, v, o_parts, o_rows_per_part, o_strides, H, Sq,
+                     sm_scale=None):
+    """``dsb_flash_attn_parts``: one sample whose query rows come from ``q_parts[i]`` (``q_rows_per_part`` rows each,
+    a multiple of 128) and whose output row s goes to ``o_parts[s // o_rows_per_part]``.  Parts are tensors or raw
+    device addresses (peer memory); ``q_strides`` / ``o_strides`` are the (token, head) strides in elements inside a
+    part.  k, v: [1, Sk, H, 128] views on the current device."""
+    _require_cuda(k, v, *[t for t in list(q_parts) + list(o_parts) if isinstance(t, torch.Tensor)])
+    if k.dim() != 4 or k.shape[0] != 1 or k.shape[2] != H or k.shape[3] != 128 or v.shape != k.shape:
+        raise _lib.DsbError("flash_attn_parts takes k and v as [1, Sk, H, 128]")
+    for t in (k, v):
+        if t.stride(3) != 1 or t.dtype != torch.bfloat16:
+            raise _lib.DsbError("flash_attn needs bf16 tensors with a contiguous head dimension")
+    for parts, rows, (ss, sh) in ((q_parts, q_rows_per_part, q_strides), (o_parts, o_rows_per_part, o_strides)):
+        if not 1 <= len(parts) <= 8 or rows <= 0 or len(parts) * rows < Sq:
+            raise _lib.DsbError("flash_attn_parts: 1..8 parts that together cover Sq rows")
+        for i, t in enumerate(parts):
+            if isinstance(t, torch.Tensor):
+                n_rows = max(0, min(rows, Sq - i * rows))          # rows of this part that exist
+                need = 0 if n_rows == 0 else (n_rows - 1) * ss + (H - 1) * sh + 128
+                if t.dtype != torch.bfloat16 or t.untyped_storage().nbytes() // 2 - t.storage_offset() < need:
+                    raise _lib.DsbError("flash_attn_parts: a part is not bf16 or too small for its rows")
+    if q_rows_per_part % 128:
+        raise _lib.DsbError("flash_attn_parts: q_rows_per_part must be a multiple of 128")
+    if sm_scale is None:
+        sm_scale = 1.0 / math.sqrt(128)
+    qa, oa = _addr_array(q_parts), _addr_array(o_parts)
+    rc = _lib.lib().dsb_flash_attn_parts(
+        qa, len(q_parts), q_rows_per_part, _ptr(k), _ptr(v), oa, len(o_parts), o_rows_per_part, H, Sq, k.shape[1], 128,
+        q_strides[0], q_strides[1], k.stride(1), k.stride(2), v.stride(1), v.stride(2), o_strides[0], o_strides[1],
+        float(sm_scale), _ptr(status_word(k.device)), _stream())
+    check(rc, "dsb_flash_attn_parts")
+
+
+def rank_barrier(flag_arrays, rank, epoch, limit_cycles=20_000_000_000, status=None):
+    """``dsb_rank_barrier`` on the current stream: ``flag_arrays[r]`` is rank r's int32 flag array (tensor or raw
+    device address mapped in this process).  ``limit_cycles`` SM cycles (default: about ten seconds) bound the wait;
+    a timeout lands in the device status word (``check_status``)."""
+    n = len(flag_arrays)
+    st = status if status is not None else status_word(torch.device("cuda", torch.cuda.current_device()))
+    rc = _lib.lib().dsb_rank_barrier(_addr_array(flag_arrays), n, rank, int(epoch), int(limit_cycles), _ptr(st), _stream())
+    check(rc, "dsb_rank_barrier")
 
 
 def pack_quant_weight(W, fmt=FMT_E4M3, per_channel=False):

@@ -10,12 +10,20 @@ the ranks of a ``torch.distributed`` group (Ulysses):
     into the per-peer-contiguous send layout ``[P][S/P][H/P*128]``, and the quantiser that feeds the output
     projection reads the returned ``[P][S/P][H/P*128]`` directly, so neither direction needs a pack kernel;
   * the exchanges run on a second stream, each as soon as its send layout is written; weights (14 GB in FP8) are
-    replicated.
+    replicated;
+  * with ``exchange="peer"`` (the default when the ranks can map each other's memory) only k and v travel that way:
+    the attention kernel itself reads the queries of each token range from the rank that owns it and writes each
+    output row into the memory of the rank that owns the token (``dsb_flash_attn_parts`` over peer pointers), with
+    one ``dsb_rank_barrier`` before and after it - the exchanges of q and of the attention output cost no launch
+    and no exposed time.
 
-Per block, in launch order (P = 1 drops the exchanges):
-  ln_modulate+quantise -> ONE q|k|v GEMM (N = 3d) -> rmsnorm_full+rope of q -> [a2a q] | rmsnorm_full+rope of k
-  -> [a2a k] | v re-layout -> [a2a v] -> flash attention (H/P heads, all tokens) -> [a2a o] -> quantise
-  -> o GEMM with x += gate*(.) -> affine LN3+quantise -> q GEMM -> rmsnorm_full
+Per block, in launch order:
+  P = 1: ln_modulate+quantise -> ONE q|k|v GEMM (N = 3d) -> rmsnorm_full+rope of q, of k -> flash attention
+  P > 1: ln_modulate+quantise -> k GEMM -> rmsnorm_full+rope of k -> [a2a k] | v GEMM -> v re-layout -> [a2a v]
+         | q GEMM -> rmsnorm_full+rope of q -> (peer: rank barrier | nccl: [a2a q]) -> flash attention (H/P heads,
+         all tokens; peer: queries read from, output rows written to, the owning ranks) -> (peer: rank barrier |
+         nccl: [a2a o])
+  then: quantise -> o GEMM with x += gate*(.) -> affine LN3+quantise -> q GEMM -> rmsnorm_full
   -> flash attention (Sk = context; keys and values of the context are cached per prompt) -> quantise
   -> o GEMM with x += (.) -> ln_modulate+quantise -> FFN GEMM (+GELU) -> quantise -> FFN GEMM with x += gate*(.)
 """
@@ -80,10 +88,29 @@ class HeadExchange:
         return recv
 
 
+class PeerMemory:
+    """One device buffer per rank, mapped into the address space of every rank of the group (torch symmetric memory:
+    CUDA virtual-memory handles exchanged through the group's store).  ``ptrs[r]`` is rank r's buffer as this
+    process addresses it; ``local`` is this rank's own buffer as a uint8 tensor.  Binding the buffers to an NVLink
+    multicast object is switched off: only plain peer loads and stores are used here, and a rank that dies while
+    bound takes the other ranks' GPUs with it."""
+
+    def __init__(self, nbytes: int, device, group):
+        import os
+        os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
+        import torch.distributed._symmetric_memory as symm
+        self.local = symm.empty(nbytes, dtype=torch.uint8, device=device)
+        self.local.zero_()
+        self.handle = symm.rendezvous(self.local, group)
+        self.ptrs = [int(p) for p in self.handle.buffer_ptrs]
+        if len(self.ptrs) != self.handle.world_size or self.ptrs[self.handle.rank] != self.local.data_ptr():
+            raise RuntimeError("symmetric memory handle does not describe this group")
+
+
 class WanDiTEngine:
     def __init__(self, state_dict: Dict[str, torch.Tensor], fmt: str = "fp8_channel", device="cuda:0",
                  num_layers: int = 40, num_heads: int = 40, eps: float = 1e-6, freq_dim: int = 256, group=None,
-                 release_source: bool = False, overlap: bool = True):
+                 release_source: bool = False, overlap: bool = True, exchange: str = "auto"):
         self.dev = torch.device(device)
         self.fmt, self.afmt = fmt, act_format(fmt)
         self.L, self.H, self.eps, self.freq_dim = num_layers, num_heads, eps, freq_dim
@@ -99,6 +126,13 @@ class WanDiTEngine:
         if self.d // num_heads != 128:
             raise ValueError("head_dim must be 128")
         self.overlap = overlap and self.P > 1
+        # how q and the attention output cross ranks: "nccl" = all-to-all like k and v; "peer" = inside the attention
+        # kernel over mapped peer memory; "auto" = peer when the mapping can be set up (decided in prepare)
+        if exchange not in ("auto", "peer", "nccl"):
+            raise ValueError("exchange must be 'auto', 'peer' or 'nccl'")
+        self.exchange = "nccl" if self.P == 1 else exchange
+        self._group = group
+        self._epoch = 0
 
         def P_(name):
             p = pack_linear(sd[name + ".weight"], sd.get(name + ".bias"), fmt, self.dev)
@@ -138,8 +172,9 @@ class WanDiTEngine:
             for i, blk in enumerate(self.blocks):
                 pre = f"blocks.{i}.cross_attn."
                 blk.update(ck_img=P_(pre + "k_img"), cv_img=P_(pre + "v_img"), cnk_img=V(pre + "norm_k_img.weight"))
-        for blk in self.blocks:
-            blk["sqkv"] = _stack_linears([blk.pop("sq"), blk.pop("sk"), blk.pop("sv")])   # one N = 3d projection
+        if self.P == 1:
+            for blk in self.blocks:
+                blk["sqkv"] = _stack_linears([blk.pop("sq"), blk.pop("sk"), blk.pop("sv")])   # one N = 3d projection
         self.mod = (torch.stack(mods).contiguous() if mods                  # [L, 6, d]
                     else torch.zeros(0, 6, self.d, dtype=torch.float32, device=self.dev))
         self.head = P_("head.head")
@@ -154,8 +189,10 @@ class WanDiTEngine:
         d, dev, P = self.d, self.dev, self.P
         gh, gw = height // 2, width // 2
         S = frames * gh * gw
-        S_pad = (S + P - 1) // P * P     # a token count that does not split evenly is padded; the padded rows are
-        Sl = S_pad // P                  # ordinary rows whose results are dropped and that never act as keys
+        Sl = (S + P - 1) // P            # a token count that does not split evenly is padded; the padded rows are
+        if self.exchange != "nccl":      # ordinary rows whose results are dropped and that never act as keys
+            Sl = (Sl + 127) // 128 * 128                  # the attention kernel reads whole 128-row query tiles per rank
+        S_pad = Sl * P
         ffn = self.blocks[0]["f0"].out_features if self.blocks else 4 * d
         qdt = {ops.FMT_BF16: torch.bfloat16, ops.FMT_E4M3: torch.float8_e4m3fn, ops.FMT_INT8: torch.int8}[self.afmt]
         bf, f32 = torch.bfloat16, torch.float32
@@ -184,6 +221,36 @@ class WanDiTEngine:
         b["recv"] = torch.zeros(3, P, Sl, C, dtype=bf, device=dev) if P > 1 else None
         b["ao"] = torch.zeros(P, Sl, C, dtype=bf, device=dev)                # attention out: [S, H/P*128]
         b["ao_back"] = torch.zeros(P, Sl, C, dtype=bf, device=dev) if P > 1 else None
+        b["peer"] = None
+        if self.exchange != "nccl":
+            # this rank's normalised queries [Sl, d] and its returned attention rows [P][Sl][C] live in a buffer every
+            # rank maps; flags for the rank barrier behind them
+            part = Sl * d * 2
+            try:
+                pm = PeerMemory(2 * part + 1024, dev, self._group)
+            except Exception as e:       # no peer mapping on this system: every tensor goes through the all-to-all
+                if self.exchange == "peer":
+                    raise
+                import sys
+                print(f"[wan] peer memory unavailable ({type(e).__name__}: {str(e)[:200]}); using all-to-all", file=sys.stderr)
+                pm = None
+            # the ranks must agree (a rank that fell back while another did not would wait for ever)
+            ok = torch.tensor([1 if pm is not None else 0], dtype=torch.int32, device=dev)
+            self.xchg.dist.all_reduce(ok, op=self.xchg.dist.ReduceOp.MIN, group=self._group)
+            if int(ok.item()) == 0:
+                if self.exchange == "peer":
+                    raise RuntimeError("peer memory could not be mapped on every rank")
+                self.exchange = "nccl"
+                return self.prepare(frames, height, width, ctx_len, text_dim)
+            self.exchange = "peer"
+            b["peer"] = pm
+            b["qn"] = pm.local[:part].view(bf).view(Sl, d)
+            b["ao_back"] = pm.local[part:2 * part].view(bf).view(P, Sl, C)
+            b["flags"] = [ptr + 2 * part for ptr in pm.ptrs]
+            # peer r's queries of this rank's head group; this rank's chunk of peer r's returned attention rows
+            b["q_parts"] = [ptr + self.rank * C * 2 for ptr in pm.ptrs]
+            b["o_parts"] = [ptr + part + self.rank * Sl * C * 2 for ptr in pm.ptrs]
+            self.xchg.dist.barrier(group=self._group)           # every rank's flags are zero before the first signal
         # FFN hidden: bf16 (then row-quantised into xq) - or, with FP8 weights, e4m3 written by the first FFN GEMM itself
         # (its own buffer: that GEMM still reads its operand from xq)
         b["hid"] = torch.zeros(Sl, ffn, dtype=qdt if self.afmt == ops.FMT_E4M3 else bf, device=dev)
@@ -261,6 +328,11 @@ class WanDiTEngine:
             done.record(self._comm)
         return done
 
+    def _barrier(self):
+        """All ranks of the group, on the current stream (``dsb_rank_barrier`` over the mapped flag arrays)."""
+        self._epoch += 1
+        ops.rank_barrier(self._bufs["flags"], self.rank, self._epoch)
+
     def step(self):
         b, d, H, P = self._bufs, self.d, self.H, self.P
         Sl, S, Hl, C = b["Sl"], b["S"], self.H // self.P, self.d // self.P
@@ -328,8 +400,8 @@ class WanDiTEngine:
             m = b["modall"][li]
             # ---- self-attention (wan_dit.py:101-107) with the head exchange around it: q, k and v in ONE GEMM
             a, sc = self._ln(x, m[0], m[1], xq_d, rs[:Sl])
-            self._gemm(a, sc, blk["sqkv"], out=qkv)
             if P == 1:
+                self._gemm(a, sc, blk["sqkv"], out=qkv)
                 ops.rmsnorm_full(q_s, blk["snq"], rope, row0, self.eps)
                 ops.rmsnorm_full(k_s, blk["snk"], rope, row0, self.eps)
                 q4, k4, v4 = (t.unflatten(1, (H, 128)).unsqueeze(0) for t in (q_s, k_s, v_s))
@@ -337,24 +409,38 @@ class WanDiTEngine:
                 att3 = None
             else:
                 send, recv = b["send"], b["recv"]
-                # each tensor leaves for its head group's rank as soon as its send layout is written; the exchange of
-                # q runs under the normalisation of k, that of k under the re-layout of v
-                ops.rmsnorm_full(q_s, blk["snq"], rope, row0, self.eps, out=send[0], chunks=P)
-                e0 = self._exchange(send[0], recv[0])
+                S_pad = b["S_pad"]
+                peer = self.exchange == "peer"
+                # k, v, q are projected one after the other so that each tensor leaves for its head group's rank
+                # under the projection of the next one
+                self._gemm(a, sc, blk["sk"], out=k_s)
                 ops.rmsnorm_full(k_s, blk["snk"], rope, row0, self.eps, out=send[1], chunks=P)
                 e1 = self._exchange(send[1], recv[1])
+                self._gemm(a, sc, blk["sv"], out=v_s)
                 send[2].copy_(v_s.unflatten(1, (P, C)).permute(1, 0, 2))
                 e2 = self._exchange(send[2], recv[2])
+                self._gemm(a, sc, blk["sq"], out=q_s)
+                if peer:
+                    # the queries stay where they are: every rank's attention kernel fetches the rows it needs
+                    ops.rmsnorm_full(q_s, blk["snq"], rope, row0, self.eps, out=b["qn"])
+                    self._barrier()                                   # every rank's queries are written
+                    e0 = None
+                else:
+                    ops.rmsnorm_full(q_s, blk["snq"], rope, row0, self.eps, out=send[0], chunks=P)
+                    e0 = self._exchange(send[0], recv[0])
                 for e in (e0, e1, e2):
                     if e is not None:
                         cur.wait_event(e)
-                S_pad = b["S_pad"]
-                q4 = recv[0].view(1, S_pad, Hl, 128)
                 k4, v4 = (recv[i].view(S_pad, Hl, 128)[:S].unsqueeze(0) for i in (1, 2))   # real tokens only as keys
-                ops.flash_attn(q4, k4, v4, out=ao.view(1, S_pad, Hl, 128))
-                e3 = self._exchange(ao, b["ao_back"])
-                if e3 is not None:
-                    cur.wait_event(e3)
+                if peer:
+                    ops.flash_attn_parts(b["q_parts"], Sl, (d, 128), k4, v4, b["o_parts"], Sl, (C, 128), Hl, S_pad)
+                    self._barrier()                                   # every rank's output rows have arrived
+                else:
+                    q4 = recv[0].view(1, S_pad, Hl, 128)
+                    ops.flash_attn(q4, k4, v4, out=ao.view(1, S_pad, Hl, 128))
+                    e3 = self._exchange(ao, b["ao_back"])
+                    if e3 is not None:
+                        cur.wait_event(e3)
                 att3 = b["ao_back"]
             if self.afmt == ops.FMT_BF16:
                 att = ao.view(S, d) if P == 1 else att3.permute(1, 0, 2).reshape(Sl, d)

@@ -281,6 +281,36 @@ int dsb_flash_attn(const void* q, const void* k, const void* v, void* o, int B, 
                    int* status, void* stream);
 
 /*
+ * dsb_flash_attn for one sample (B = 1) whose query rows and output rows are each cut into equal row ranges that live
+ * in separate buffers: query rows [i*q_rows_per_part, (i+1)*q_rows_per_part) are read from q_parts[i] (addressed as
+ * base + s*q_stride_s + h*q_stride_h with s counted from the start of the part; q_rows_per_part a multiple of 128),
+ * output row s is written to o_parts[s / o_rows_per_part] at row s % o_rows_per_part.  The parts may be memory of
+ * other GPUs that this process has mapped (peer access): the kernel then reads its queries from, and writes its
+ * result to, the ranks that own those tokens - the all-to-all on both sides of the sequence-parallel attention of
+ * utils/parallel.py's ParallelModel users (pipelines/wan_video.py:434-455) happens inside the attention kernel
+ * (plain tiled TMA loads without multicast, plain stores).  q_parts / o_parts are host arrays of device pointers,
+ * n_*_parts <= 8 each, n * rows_per_part >= Sq.
+ */
+int dsb_flash_attn_parts(const void* const* q_parts, int n_q_parts, int q_rows_per_part, const void* k, const void* v,
+                         void* const* o_parts, int n_o_parts, int o_rows_per_part, int H, int Sq, int Sk, int head_dim,
+                         int64_t q_stride_s, int64_t q_stride_h, int64_t k_stride_s, int64_t k_stride_h,
+                         int64_t v_stride_s, int64_t v_stride_h, int64_t o_stride_s, int64_t o_stride_h,
+                         float sm_scale, int* status, void* stream);
+
+/*
+ * Barrier among the n_ranks (<= 8) GPUs of a sequence-parallel group, launched by every rank on its own stream:
+ * flags[r] points to rank r's array of n_ranks ints (zero before the first barrier) in memory all ranks have mapped;
+ * epoch must grow by one per barrier.  Everything this rank's earlier launches on the stream wrote, to any rank's
+ * memory, is visible to the launches that follow the barrier on every other rank.  A rank that does not arrive within
+ * limit_cycles SM cycles makes the waiters return with *status = DSB_ERR_TIMEOUT (no trap, the context stays usable);
+ * while *status is non-zero later barriers signal but do not wait.
+ * Stands where the reference's wrappers synchronise ranks through torch.distributed collectives
+ * (utils/parallel.py:112-135).
+ */
+int dsb_rank_barrier(int* const* flags, int n_ranks, int rank, int epoch, long long limit_cycles, int* status,
+                     void* stream);
+
+/*
  * Weight prepack: W[N,K] (fp32 or bf16 by src_is_bf16) -> quantised payload [N,K] row-major plus scales.
  *   fmt E4M3, per_channel 0: s = amax(|W|)/448 (one scale);   per_channel 1: s_n = amax(|W[n,:]|)/448
  *   fmt INT8 (per_channel 1 only): s_n = amax/127, q = round-half-even(W/s) clamped to +-127

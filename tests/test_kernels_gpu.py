@@ -450,3 +450,75 @@ def test_bounded_wait_runs_out_and_reports_timeout(dsb, cuda_dev):
     y, _ = dsb.ops.ln_modulate(x, torch.zeros(256, device=cuda_dev), torch.zeros(256, device=cuda_dev))
     assert torch.isfinite(y.float()).all()
     dsb.ops.check_status(0)
+
+
+# ------------------------------------------------------------ attention over row ranges in separate buffers
+def test_flash_attn_parts_equals_one_buffer(dsb, cuda_dev):
+    """Queries read from three separate buffers (256 rows each, the last one short) and output rows written to four
+    separate buffers of 200 rows (ranges that cut through the 128-row tiles) give bit for bit what the one-buffer
+    call gives: only addresses change.  On several GPUs the buffers are the other ranks' memory."""
+    H, Sq, Sk = 3, 640, 500
+    q = (torch.randn(1, Sq, H, 128) * 1.5).bfloat16().to(cuda_dev)
+    k = torch.randn(1, Sk, H, 128).bfloat16().to(cuda_dev)
+    v = torch.randn(1, Sk, H, 128).bfloat16().to(cuda_dev)
+    want = dsb.ops.flash_attn(q, k, v)
+    q_rows, o_rows = 256, 200
+    q_parts = [q[0, i * q_rows:(i + 1) * q_rows].clone() for i in range(3)]            # [rows, H, 128] each
+    o_parts = [torch.full((o_rows, H, 128), 7.0, dtype=torch.bfloat16, device=cuda_dev) for _ in range(4)]
+    dsb.ops.flash_attn_parts(q_parts, q_rows, (H * 128, 128), k, v, o_parts, o_rows, (H * 128, 128), H, Sq)
+    got = torch.cat(o_parts)[:Sq]
+    assert torch.equal(got, want[0])
+    assert (torch.cat(o_parts)[Sq:] == 7.0).all()                                       # rows past Sq stay untouched
+    dsb.ops.check_status(0)
+    with pytest.raises(dsb._lib.DsbError):                                              # a 128-row tile may not straddle parts
+        dsb.ops.flash_attn_parts(q_parts, 192, (H * 128, 128), k, v, o_parts, o_rows, (H * 128, 128), H, Sq)
+
+
+def test_rank_barrier_alone_passes_and_absent_rank_times_out(dsb, cuda_dev):
+    """One rank alone passes its barrier at once.  With a second rank that never arrives (its flag stays 0) the
+    waiter gives up after its cycle budget, reports DSB_ERR_TIMEOUT in the status word it was given, has still
+    delivered its own signal, and the context stays usable.  (The wait is bounded; nothing traps.)"""
+    import time
+    status = torch.zeros(1, dtype=torch.int32, device=cuda_dev)
+    mine = torch.zeros(8, dtype=torch.int32, device=cuda_dev)
+    for epoch in (1, 2, 3):
+        dsb.ops.rank_barrier([mine], 0, epoch, status=status)
+    assert status.item() == 0 and mine[0].item() == 3
+    other = torch.zeros(8, dtype=torch.int32, device=cuda_dev)
+    t0 = time.time()
+    dsb.ops.rank_barrier([mine, other], 0, 4, limit_cycles=2_000_000, status=status)
+    assert status.item() == dsb._lib.ERR_TIMEOUT
+    assert time.time() - t0 < 5.0
+    assert other[0].item() == 4 and mine[0].item() == 4 and mine[1].item() == 0
+    # a rank that is already ahead does not block: the flag only has to be at least the epoch
+    mine[1] = 9
+    status.zero_()
+    dsb.ops.rank_barrier([mine, other], 0, 5, limit_cycles=2_000_000, status=status)
+    assert status.item() == 0
+
+
+def test_gemm_front_end_rejects_buffers_the_kernel_would_overrun(dsb, cuda_dev):
+    """The C entry points take raw pointers, so the tensor front end checks shapes and dtypes: an output that is too
+    small or of the wrong type raises instead of being written past its end; an e4m3 output is routed to the
+    entry point that can describe it and equals the grouped call."""
+    M, N, K = 256, 512, 256
+    a = torch.randn(M, K).to(torch.float8_e4m3fn).to(cuda_dev)
+    w = torch.randn(N, K).to(torch.float8_e4m3fn).to(cuda_dev)
+    rs = (torch.rand(M) * 0.01 + 0.001).to(cuda_dev)
+    for bad in (torch.empty(M, N - 8, dtype=torch.bfloat16, device=cuda_dev),
+                torch.empty(M - 1, N, dtype=torch.bfloat16, device=cuda_dev),
+                torch.empty(M, N, dtype=torch.float16, device=cuda_dev)):
+        with pytest.raises(dsb._lib.DsbError):
+            dsb.ops.gemm(a, w, row_scale=rs, out=bad)
+    with pytest.raises(dsb._lib.DsbError):
+        dsb.ops.gemm(a, w, row_scale=rs[:M - 1])
+    with pytest.raises(dsb._lib.DsbError):
+        dsb.ops.gemm(a, w, bias=torch.zeros(N, dtype=torch.bfloat16, device=cuda_dev))
+    o8 = torch.empty(M, N, dtype=torch.float8_e4m3fn, device=cuda_dev)
+    o8g = torch.empty_like(o8)
+    dsb.ops.gemm(a, w, row_scale=rs, act=dsb.ops.ACT_GELU_TANH, out=o8)
+    dsb.ops.gemm_group([dict(a=a, w=w, row_scale=rs, act=dsb.ops.ACT_GELU_TANH, out=o8g)])
+    assert torch.equal(o8.view(torch.uint8), o8g.view(torch.uint8))
+    ref = torch.nn.functional.gelu((a.float() @ w.float().T) * rs[:, None], approximate="tanh")
+    assert O.rel_l2(o8.float(), ref.clamp(-448, 448)) < 4e-2          # e4m3 rounding of the output
+    dsb.ops.check_status(0)

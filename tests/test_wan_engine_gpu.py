@@ -99,17 +99,20 @@ def test_chunked_layout_kernels(dsb, cuda_dev):
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
-@pytest.mark.parametrize("fmt", ["fp8_channel", "bf16"])
-def test_sequence_parallel_two_gpus_matches_one(dsb, cuda_dev, fmt):
-    """UlyssesParallelModel (2 ranks, NCCL) against the single-GPU engine on the same weights and inputs."""
+@pytest.mark.parametrize("fmt,exchange", [("fp8_channel", "nccl"), ("bf16", "nccl"), ("fp8_channel", "peer"),
+                                          ("bf16", "peer")])
+def test_sequence_parallel_two_gpus_matches_one(dsb, cuda_dev, fmt, exchange):
+    """UlyssesParallelModel (2 ranks) against the single-GPU engine on the same weights and inputs, with q and the
+    attention output crossing ranks by all-to-all ("nccl") or inside the attention kernel over mapped peer memory
+    ("peer": 240 tokens, 128-row slices, 16 padded rows on the second rank)."""
     os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
     from diffsynth_engine_b200.parallel import UlyssesParallelModel
     from diffsynth_engine_b200.wan import WanDiTEngine
-    w, x, context, t = _case(seed=30, grid=(3, 8, 10))
+    w, x, context, t = _case(seed=30, grid=(3, 16, 20) if exchange == "peer" else (3, 8, 10))
     one = WanDiTEngine(dict(w), fmt=fmt, device=cuda_dev, num_layers=2, num_heads=H)
     ref = one(x.to(cuda_dev), context.to(cuda_dev), t.to(cuda_dev)).float().cpu()
     model = UlyssesParallelModel(dict(w), sp_degree=2, master_port=29641, device="cuda", timeout_s=120, fmt=fmt,
-                                 num_layers=2, num_heads=H)
+                                 num_layers=2, num_heads=H, exchange=exchange)
     try:
         out = model(x=x, context=context, timestep=t).float().cpu()
         out2 = model(x=x, context=context, timestep=t).float().cpu()
