@@ -563,12 +563,12 @@ static int launch_attn(const void* q, const void* const* q_parts, int n_q_parts,
   CUtensorMap tk, tv;
   int rc;
   if (q_parts) {
+    // every part is a buffer of q_rows_per_part rows (rows past Sq are read but never used), so all maps share one
+    // coordinate order; unused slots repeat the last part
     for (int i = 0; i < kMaxParts; ++i) {
-      // rows of part i that exist (the last parts may be short or empty: their map still needs one row)
-      int rows = Sq - i * q_rows_per_part;
-      rows = rows > q_rows_per_part ? q_rows_per_part : (rows < 1 ? 1 : rows);
       const void* base = q_parts[i < n_q_parts ? i : n_q_parts - 1];
-      if ((rc = make_tmap_attn(&qm.m[i], p.q_pos, base, rows, H, 1, q_stride_s, q_stride_h, q_stride_b)) != DSB_OK)
+      if ((rc = make_tmap_attn(&qm.m[i], p.q_pos, base, q_rows_per_part, H, 1, q_stride_s, q_stride_h, q_stride_b)) !=
+          DSB_OK)
         return rc;
     }
     p.q_rows_per_part = q_rows_per_part;

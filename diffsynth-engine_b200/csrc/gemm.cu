@@ -76,24 +76,24 @@ constexpr int kStageBytes = kEpiWarps * kStageSlotBytes;
 // CTAS = 1: one CTA computes 128 x BLOCK_N.  CTAS = 2: a CTA pair computes 256 x BLOCK_N with one tcgen05.mma
 // (cta_group::2); each CTA stages 128 rows of A and BLOCK_N/2 rows of W, which halves the shared-memory bytes
 // per flop (the single-CTA kernel is bound by that traffic) and the L2 reads of W.
-template <int BLOCK_N, int CTAS>
+template <int BLOCK_N, int CTAS, bool TABLE>
 struct GemmSmem {
   static constexpr int kStageA = kBlockM * kSlabBytes;
   static constexpr int kStageB = (BLOCK_N / CTAS) * kSlabBytes;
   static constexpr int kStage = kStageA + kStageB;
   // per epilogue warp: four per-column parameter vectors (scale, bias, gate, head-norm weight) of its BLOCK_N/2 columns
   static constexpr int kParamFloats = 4 * (BLOCK_N / 2);
-  static constexpr int kParamBytes = kEpiWarps * kParamFloats * 4;
+  static constexpr int kParamBytes = TABLE ? kEpiWarps * kParamFloats * 4 : 0;
   static constexpr int kBarBytes = 256;
   static constexpr int kFixed = kStageBytes + kParamBytes + kBarBytes + 1024;  // + alignment slack
-  static constexpr int kStages = (227 * 1024 - kFixed) / kStage;                // 5 of 32 KiB, 3 of 48 KiB
+  static constexpr int kStages = (227 * 1024 - kFixed) / kStage;   // 32-KiB stages: 6 (5 with the table); 48-KiB: 4 (3)
   static constexpr int kTotal = kStages * kStage + kFixed;
 };
 
-template <int KIND, int BLOCK_N, int CTAS>
+template <int KIND, int BLOCK_N, int CTAS, bool TABLE>
 __global__ void __launch_bounds__(kGemmThreads, 1)
     gemm_kernel(const __grid_constant__ GemmGroup g) {
-  using SM = GemmSmem<BLOCK_N, CTAS>;
+  using SM = GemmSmem<BLOCK_N, CTAS, TABLE>;
   constexpr int kStages = SM::kStages;
   constexpr int kElemBytes = (KIND == KIND_F16) ? 2 : 1;
   constexpr int kSlabElems = kSlabBytes / kElemBytes;
@@ -287,19 +287,21 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
         __syncwarp();
       }
       // Per-column epilogue parameters (per-channel scale, bias, gate, head-norm weight) of this warp's column range:
-      // lane l fetches kPer consecutive columns' values once per tile, before the accumulator is ready, into the
-      // warp's own table in shared memory; the 8-column groups below read theirs back as two 16-byte broadcasts per
-      // vector.  (Loading them group by group from global memory, right where they are used, cost a serial L2 round
-      // trip per group; keeping them in registers and handing them round by warp shuffles cost 8 shuffles per
-      // vector and group, and the shuffle unit issues one per cycle for the whole SM.)
+      // lane l fetches kPer consecutive columns' values once per tile, before the accumulator is ready.  (Loading
+      // them group by group from global memory, right where they are used, cost a serial L2 round trip per group.)
+      // TABLE: they go into the warp's own table in shared memory and the 8-column groups below read theirs back as
+      // two 16-byte broadcasts per vector.  Otherwise they stay in registers and are handed round by warp shuffles:
+      // 8 shuffles per vector and group, and the shuffle unit issues one per cycle for the whole SM - measured 5-8 %
+      // of the whole GEMM at K = 3072, where the epilogue is the longer half of the pipeline; at K >= 5120 the mainloop
+      // is, and the sixth operand stage the table's 16 KiB would displace is worth more (1-7 %).
       constexpr int kWarpCols = BLOCK_N / 2, kPer = kWarpCols / 32;
       const int wcol0 = n0 + half * kWarpCols;
+      float p_cs[kPer], p_bias[kPer], p_gate[kPer], p_hw[kPer];
       {
         const int c = wcol0 + lane * kPer;
         const bool in = c < N;
         const bool chan = ep.col_scale && ep.col_scale_stride;
         const float* hw = (wcol0 < ep.d_model) ? ep.nq_w : ep.nk_w;
-        float p_cs[kPer], p_bias[kPer], p_gate[kPer], p_hw[kPer];
 #pragma unroll
         for (int j = 0; j < kPer; ++j) {
           p_cs[j] = (in && chan) ? __ldg(ep.col_scale + c + j) : 1.f;
@@ -307,22 +309,31 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
           p_gate[j] = (in && ep.gate) ? __ldg(ep.gate + c + j) : 1.f;
           p_hw[j] = (fuse_norm && hw) ? __ldg(hw + ((lane * kPer + j) & 127)) : 1.f;
         }
-        __syncwarp();  // every lane has read the previous tile's values
+        if constexpr (TABLE) {
+          __syncwarp();  // every lane has read the previous tile's values
 #pragma unroll
-        for (int j = 0; j < kPer; ++j) {
-          ptab[0 * kWarpCols + lane * kPer + j] = p_cs[j];
-          ptab[1 * kWarpCols + lane * kPer + j] = p_bias[j];
-          ptab[2 * kWarpCols + lane * kPer + j] = p_gate[j];
-          ptab[3 * kWarpCols + lane * kPer + j] = p_hw[j];
+          for (int j = 0; j < kPer; ++j) {
+            ptab[0 * kWarpCols + lane * kPer + j] = p_cs[j];
+            ptab[1 * kWarpCols + lane * kPer + j] = p_bias[j];
+            ptab[2 * kWarpCols + lane * kPer + j] = p_gate[j];
+            ptab[3 * kWarpCols + lane * kPer + j] = p_hw[j];
+          }
+          __syncwarp();
         }
-        __syncwarp();
       }
-      // the 8 values of vector `which` for the column group that starts at column c8 (a multiple of 8) of the range
+      // the 8 values of vector `which` (0 scale, 1 bias, 2 gate, 3 norm weight) for the column group that starts at
+      // column c8 (a multiple of 8) of the warp's range
       auto pick8 = [&](int which, int c8, float (&out)[8]) {
-        const float4 lo = *reinterpret_cast<const float4*>(ptab + which * kWarpCols + c8);
-        const float4 hi = *reinterpret_cast<const float4*>(ptab + which * kWarpCols + c8 + 4);
-        out[0] = lo.x, out[1] = lo.y, out[2] = lo.z, out[3] = lo.w;
-        out[4] = hi.x, out[5] = hi.y, out[6] = hi.z, out[7] = hi.w;
+        if constexpr (TABLE) {
+          const float4 lo = *reinterpret_cast<const float4*>(ptab + which * kWarpCols + c8);
+          const float4 hi = *reinterpret_cast<const float4*>(ptab + which * kWarpCols + c8 + 4);
+          out[0] = lo.x, out[1] = lo.y, out[2] = lo.z, out[3] = lo.w;
+          out[4] = hi.x, out[5] = hi.y, out[6] = hi.z, out[7] = hi.w;
+        } else {
+          const float(&mine)[kPer] = which == 0 ? p_cs : which == 1 ? p_bias : which == 2 ? p_gate : p_hw;
+#pragma unroll
+          for (int j = 0; j < 8; ++j) out[j] = __shfl_sync(0xffffffffu, mine[j % kPer], c8 / kPer + j / kPer);
+        }
       };
       // the row's activation scale is fetched before the wait as well
       const float rs = (ep.row_scale && m < M) ? __ldg(ep.row_scale + m) : 1.0f;
@@ -522,10 +533,10 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
   if (threadIdx.x == 0 && *abort_flag && g.p[0].ep.status) atomicCAS(g.p[0].ep.status, 0, DSB_ERR_TIMEOUT);
 }
 
-template <int KIND, int BLOCK_N, int CTAS>
+template <int KIND, int BLOCK_N, int CTAS, bool TABLE>
 static int launch_group(GemmGroup& grp, cudaStream_t st) {
-  using SM = GemmSmem<BLOCK_N, CTAS>;
-  auto kern = gemm_kernel<KIND, BLOCK_N, CTAS>;
+  using SM = GemmSmem<BLOCK_N, CTAS, TABLE>;
+  auto kern = gemm_kernel<KIND, BLOCK_N, CTAS, TABLE>;
   DSB_ENSURE_SMEM(kern, SM::kTotal);
   int tiles = 0;
   for (int i = 0; i < grp.count; ++i) tiles += grp.p[i].num_tiles;
@@ -696,14 +707,19 @@ extern "C" int dsb_gemm_group(const dsb_gemm_args* args, int count, int fmt, int
     if (rc != DSB_OK) return rc;
   }
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
-#define DSB_GEMM_DISPATCH(KIND)                       \
-  (pair        ? launch_group<KIND, 256, 2>(grp, st)  \
-   : bn == 256 ? launch_group<KIND, 256, 1>(grp, st)  \
-               : launch_group<KIND, 128, 1>(grp, st))
+  // Short reductions (at most 32 K slabs: K <= 4096 in 8 bits, 2048 in bf16) leave the epilogue as the longer half of
+  // the pipeline: those launches take the kernel with the parameter table, the others the one with the deeper ring.
+  const bool table = grp.p[0].num_kb <= 32;
+#define DSB_GEMM_SHAPE(KIND, TABLE)                          \
+  (pair        ? launch_group<KIND, 256, 2, TABLE>(grp, st)  \
+   : bn == 256 ? launch_group<KIND, 256, 1, TABLE>(grp, st)  \
+               : launch_group<KIND, 128, 1, TABLE>(grp, st))
+#define DSB_GEMM_DISPATCH(KIND) (table ? DSB_GEMM_SHAPE(KIND, true) : DSB_GEMM_SHAPE(KIND, false))
   if (fmt == DSB_FMT_BF16) return DSB_GEMM_DISPATCH(KIND_F16);
   if (fmt == DSB_FMT_E4M3) return DSB_GEMM_DISPATCH(KIND_F8);
   return DSB_GEMM_DISPATCH(KIND_I8);
 #undef DSB_GEMM_DISPATCH
+#undef DSB_GEMM_SHAPE
 }
 
 extern "C" int dsb_gemm(const void* A, int64_t lda, const void* W, int64_t ldw, int fmt, int M, int N, int K,

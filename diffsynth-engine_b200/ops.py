@@ -470,7 +470,8 @@ def flash_attn_parts(q_parts, q_rows_per_part, q_strides, k, v, o_parts, o_rows_
             raise _lib.DsbError("flash_attn_parts: 1..8 parts that together cover Sq rows")
         for i, t in enumerate(parts):
             if isinstance(t, torch.Tensor):
-                n_rows = max(0, min(rows, Sq - i * rows))          # rows of this part that exist
+                # query parts are read in whole tiles: each holds all its rows; output rows past Sq are not written
+                n_rows = rows if parts is q_parts else max(0, min(rows, Sq - i * rows))
                 need = 0 if n_rows == 0 else (n_rows - 1) * ss + (H - 1) * sh + 128
                 if t.dtype != torch.bfloat16 or t.untyped_storage().nbytes() // 2 - t.storage_offset() < need:
                     raise _lib.DsbError("flash_attn_parts: a part is not bf16 or too small for its rows")

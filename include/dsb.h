@@ -283,7 +283,8 @@ int dsb_flash_attn(const void* q, const void* k, const void* v, void* o, int B, 
 /*
  * dsb_flash_attn for one sample (B = 1) whose query rows and output rows are each cut into equal row ranges that live
  * in separate buffers: query rows [i*q_rows_per_part, (i+1)*q_rows_per_part) are read from q_parts[i] (addressed as
- * base + s*q_stride_s + h*q_stride_h with s counted from the start of the part; q_rows_per_part a multiple of 128),
+ * base + s*q_stride_s + h*q_stride_h with s counted from the start of the part; q_rows_per_part a multiple of 128;
+ * every part holds q_rows_per_part rows, those past Sq are read and ignored),
  * output row s is written to o_parts[s / o_rows_per_part] at row s % o_rows_per_part.  The parts may be memory of
  * other GPUs that this process has mapped (peer access): the kernel then reads its queries from, and writes its
  * result to, the ranks that own those tokens - the all-to-all on both sides of the sequence-parallel attention of

@@ -454,7 +454,7 @@ def test_bounded_wait_runs_out_and_reports_timeout(dsb, cuda_dev):
 
 # ------------------------------------------------------------ attention over row ranges in separate buffers
 def test_flash_attn_parts_equals_one_buffer(dsb, cuda_dev):
-    """Queries read from three separate buffers (256 rows each, the last one short) and output rows written to four
+    """Queries read from three separate buffers (256 rows each, the last one half used) and output rows written to four
     separate buffers of 200 rows (ranges that cut through the 128-row tiles) give bit for bit what the one-buffer
     call gives: only addresses change.  On several GPUs the buffers are the other ranks' memory."""
     H, Sq, Sk = 3, 640, 500
@@ -463,7 +463,10 @@ def test_flash_attn_parts_equals_one_buffer(dsb, cuda_dev):
     v = torch.randn(1, Sk, H, 128).bfloat16().to(cuda_dev)
     want = dsb.ops.flash_attn(q, k, v)
     q_rows, o_rows = 256, 200
-    q_parts = [q[0, i * q_rows:(i + 1) * q_rows].clone() for i in range(3)]            # [rows, H, 128] each
+    q_parts = [torch.zeros(q_rows, H, 128, dtype=torch.bfloat16, device=cuda_dev) for _ in range(3)]
+    for i, part in enumerate(q_parts):                                                 # the last one is half filled
+        rows = q[0, i * q_rows:(i + 1) * q_rows]
+        part[:rows.shape[0]] = rows
     o_parts = [torch.full((o_rows, H, 128), 7.0, dtype=torch.bfloat16, device=cuda_dev) for _ in range(4)]
     dsb.ops.flash_attn_parts(q_parts, q_rows, (H * 128, 128), k, v, o_parts, o_rows, (H * 128, 128), H, Sq)
     got = torch.cat(o_parts)[:Sq]
