@@ -27,6 +27,8 @@ c_i, c_i64, c_f, c_p = ctypes.c_int, ctypes.c_int64, ctypes.c_float, ctypes.c_vo
 _SIGS = {
     "dsb_version": [],
     "dsb_selftest_wait_timeout": [ctypes.c_longlong, c_p, c_p, c_p],
+    "dsb_patchify": [c_p, c_i, c_i, c_i, c_i, c_i, c_i, c_i, c_p, c_i64, c_p, c_p],
+    "dsb_unpatchify": [c_p, c_i64, c_i, c_i, c_i, c_i, c_i, c_p, c_p],
     "dsb_rank_barrier": [c_p, c_i, c_i, c_i, ctypes.c_longlong, c_p, c_p],
     "dsb_flash_attn_parts": [c_p, c_i, c_i, c_p, c_p, c_p, c_i, c_i, c_i, c_i, c_i, c_i] + [c_i64] * 8 + [c_f, c_p, c_p],
     "dsb_ln_modulate": [c_p, c_i64, c_p, c_p, c_p, c_i64, c_p, c_i, c_i, c_f, c_i, c_p],

@@ -386,6 +386,88 @@ __global__ void __launch_bounds__(256) quant_rows_kernel(const __nv_bfloat16* __
   }
 }
 
+// ------------------------------------------------------------- patchify / unpatchify
+// Latents [C, F, 2*gh, 2*gw] (bf16, contiguous) <-> token rows: token t = (f*gh + y)*gw + z holds the 2 x 2 patch
+// (rows 2y, 2y+1; columns 2z, 2z+1) of every channel of frame f.
+// patchify: feature c*4 + py*2 + pz (what a Conv3d / Conv2d with kernel = stride = (1,2,2) sees as one Linear input
+// row); rows [row0, row0 + n_rows) are written, rows past the last token as zeros; OUT 0 writes bf16, 1 / 2 write the
+// row quantised to e4m3 / int8 with its dynamic scale (the rule of quant_rows_kernel).  One warp per token, a lane
+// per (channel, patch row) pair = two adjacent latents = one 4-byte load.
+template <int OUT>
+__global__ void __launch_bounds__(256) patchify_kernel(const __nv_bfloat16* __restrict__ lat, int C, int F, int gh, int gw,
+                                                       int row0, int n_rows, void* __restrict__ out, int64_t ld_out,
+                                                       float* __restrict__ row_scale) {
+  constexpr int kMaxPairs = 8;  // pairs per lane: C*2 <= 256
+  const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  if (warp >= n_rows) return;
+  const int64_t t = static_cast<int64_t>(row0) + warp;
+  const int64_t tokens = static_cast<int64_t>(F) * gh * gw;
+  const int npairs = C * 2;
+  float2 v[kMaxPairs];
+  float amax = 0.f;
+  const int z = static_cast<int>(t % gw), y = static_cast<int>((t / gw) % gh), f = static_cast<int>(t / (static_cast<int64_t>(gw) * gh));
+#pragma unroll
+  for (int i = 0; i < kMaxPairs; ++i) {
+    const int pr = lane + i * 32;  // pair index = c*2 + py
+    v[i] = make_float2(0.f, 0.f);
+    if (pr < npairs && t < tokens) {
+      const int c = pr >> 1, py = pr & 1;
+      const int64_t src = ((static_cast<int64_t>(c) * F + f) * (2 * gh) + 2 * y + py) * (2 * gw) + 2 * z;
+      v[i] = unpack_bf16x2(*reinterpret_cast<const uint32_t*>(lat + src));
+      amax = fmaxf(amax, fmaxf(fabsf(v[i].x), fabsf(v[i].y)));
+    }
+  }
+  if constexpr (OUT == 0) {
+    __nv_bfloat16* orow = reinterpret_cast<__nv_bfloat16*>(out) + static_cast<int64_t>(warp) * ld_out;
+#pragma unroll
+    for (int i = 0; i < kMaxPairs; ++i) {
+      const int pr = lane + i * 32;
+      if (pr < npairs) *reinterpret_cast<uint32_t*>(orow + pr * 2) = pack_bf16x2(v[i].x, v[i].y);
+    }
+  } else {
+    amax = warp_max(amax);
+    const float sc = row_scale_from_amax(amax, OUT == 1 ? 448.0f : 127.0f);
+    const float inv = 1.0f / sc;
+    if (lane == 0) row_scale[warp] = sc;
+    uint8_t* orow = reinterpret_cast<uint8_t*>(out) + static_cast<int64_t>(warp) * ld_out;
+#pragma unroll
+    for (int i = 0; i < kMaxPairs; ++i) {
+      const int pr = lane + i * 32;
+      if (pr < npairs) {
+        const uint32_t q = (OUT == 1) ? pack_e4m3x4(v[i].x * inv, v[i].y * inv, 0.f, 0.f)
+                                      : pack_s8x4(v[i].x * inv, v[i].y * inv, 0.f, 0.f);
+        *reinterpret_cast<uint16_t*>(orow + pr * 2) = static_cast<uint16_t>(q & 0xffffu);
+      }
+    }
+  }
+}
+
+// unpatchify: token rows [tokens, >= C*4] -> latents [C, F, 2*gh, 2*gw].  c_fastest = 1: feature (py*2 + pz)*C + c
+// (Wan head, "(x y z c)", models/wan/wan_dit.py:307-317); 0: feature c*4 + py*2 + pz (Flux, flux_dit.py:369-374).
+// One thread per horizontally adjacent output pair.
+__global__ void __launch_bounds__(256) unpatchify_kernel(const __nv_bfloat16* __restrict__ tok, int64_t ld_tok, int C, int F,
+                                                         int gh, int gw, int c_fastest, __nv_bfloat16* __restrict__ out) {
+  const int64_t total = static_cast<int64_t>(C) * F * (2 * gh) * gw;  // pairs
+  for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < total;
+       i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const int z = static_cast<int>(i % gw);
+    int64_t r = i / gw;
+    const int yy = static_cast<int>(r % (2 * gh));
+    r /= 2 * gh;
+    const int f = static_cast<int>(r % F);
+    const int c = static_cast<int>(r / F);
+    const int y = yy >> 1, py = yy & 1;
+    const __nv_bfloat16* row = tok + ((static_cast<int64_t>(f) * gh + y) * gw + z) * ld_tok;
+    const int f0 = c_fastest ? (py * 2) * C + c : c * 4 + py * 2;
+    const int f1 = c_fastest ? (py * 2 + 1) * C + c : c * 4 + py * 2 + 1;
+    __nv_bfloat162 o;
+    o.x = row[f0];
+    o.y = row[f1];
+    *reinterpret_cast<__nv_bfloat162*>(out + i * 2) = o;
+  }
+}
+
 // ------------------------------------------------------------- cast_quant
 // bf16 [M, D] -> e4m3 (saturating, round-to-nearest-even) or int8 (round-half-even, clamp +-127) with no scale:
 // the values are already in the operand's units.  Fills the K-extension columns of a quantised activation
@@ -1102,6 +1184,44 @@ int dsb_cfg_euler_step(const void* latents, const void* pos, const void* neg, fl
     cfg_euler_step_kernel<<<blocks, 256, 0, st>>>(
         reinterpret_cast<const __nv_bfloat16*>(latents), reinterpret_cast<const __nv_bfloat16*>(pos),
         reinterpret_cast<const __nv_bfloat16*>(neg), cfg_scale, dt, reinterpret_cast<__nv_bfloat16*>(out), n);
+  return cudaGetLastError() == cudaSuccess ? DSB_OK : DSB_ERR_CUDA;
+}
+
+int dsb_patchify(const void* latents, int C, int F, int gh, int gw, int row0, int n_rows, int out_fmt, void* out,
+                 int64_t ld_out, float* row_scale, void* stream) {
+  if (C <= 0 || C > 128 || F <= 0 || gh <= 0 || gw <= 0 || row0 < 0 || n_rows < 0) return DSB_ERR_ARG;
+  if (n_rows == 0) return DSB_OK;
+  if (!latents || !out || (reinterpret_cast<uintptr_t>(latents) & 3u) || ld_out < C * 4) return DSB_ERR_ARG;
+  const int blocks = (n_rows + 7) / 8;  // 8 warps = 8 tokens per CTA
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  const __nv_bfloat16* lat = reinterpret_cast<const __nv_bfloat16*>(latents);
+  if (out_fmt == DSB_FMT_BF16) {
+    if ((reinterpret_cast<uintptr_t>(out) & 3u) || (ld_out & 1)) return DSB_ERR_ARG;
+    patchify_kernel<0><<<blocks, 256, 0, st>>>(lat, C, F, gh, gw, row0, n_rows, out, ld_out, nullptr);
+  } else if (out_fmt == DSB_FMT_E4M3 || out_fmt == DSB_FMT_INT8) {
+    if (!row_scale || (reinterpret_cast<uintptr_t>(out) & 1u) || (ld_out & 1)) return DSB_ERR_ARG;
+    if (out_fmt == DSB_FMT_E4M3)
+      patchify_kernel<1><<<blocks, 256, 0, st>>>(lat, C, F, gh, gw, row0, n_rows, out, ld_out, row_scale);
+    else
+      patchify_kernel<2><<<blocks, 256, 0, st>>>(lat, C, F, gh, gw, row0, n_rows, out, ld_out, row_scale);
+  } else {
+    return DSB_ERR_ARG;
+  }
+  return cudaGetLastError() == cudaSuccess ? DSB_OK : DSB_ERR_CUDA;
+}
+
+int dsb_unpatchify(const void* tokens, int64_t ld_tok, int C, int F, int gh, int gw, int c_fastest, void* out,
+                   void* stream) {
+  if (C <= 0 || F <= 0 || gh <= 0 || gw <= 0 || ld_tok < C * 4) return DSB_ERR_ARG;
+  if (!tokens || !out || (reinterpret_cast<uintptr_t>(out) & 3u) || (reinterpret_cast<uintptr_t>(tokens) & 1u))
+    return DSB_ERR_ARG;
+  const int64_t total = static_cast<int64_t>(C) * F * (2 * gh) * gw;
+  int blocks = static_cast<int>((total + 255) / 256);
+  const int cap = sm_count() * 8;
+  if (blocks > cap) blocks = cap;
+  unpatchify_kernel<<<blocks, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      reinterpret_cast<const __nv_bfloat16*>(tokens), ld_tok, C, F, gh, gw, c_fastest ? 1 : 0,
+      reinterpret_cast<__nv_bfloat16*>(out));
   return cudaGetLastError() == cudaSuccess ? DSB_OK : DSB_ERR_CUDA;
 }
 

@@ -154,6 +154,7 @@ class FluxDiTEngine:
         b["catq"] = torch.zeros(Sl if self.afmt != ops.FMT_BF16 else 1, 5 * d, dtype=qdt, device=dev)
         b["patches"] = torch.zeros(S_img, self.in_ch, dtype=bf, device=dev)
         b["out_tok"] = torch.zeros(Sl, self.in_ch, dtype=bf, device=dev)
+        b["out_lat"] = torch.zeros(1, self.in_ch // 4, height, width, dtype=bf, device=dev)
         if P > 1:   # head exchange: [P][Sl][q|k|v][d/P] out and back, attention output [S_pad, d/P] and its return
             b["send"] = torch.zeros(P, Sl, 3, C, dtype=bf, device=dev)
             b["recv"] = torch.zeros(P, Sl, 3, C, dtype=bf, device=dev)
@@ -226,13 +227,16 @@ class FluxDiTEngine:
         if t_loc > 0:
             a, s = self._quant(b["prompt"][g0:g0 + t_loc], xq[txt, :txt_dim], rs[txt])
             self._gemm(a, s, self.ctx_emb, out=x[txt])
-        b["patches"].copy_(b["latents"].reshape(self.in_ch // 4, b["height"] // 2, 2, b["width"] // 2, 2)
-                           .permute(1, 3, 0, 2, 4).reshape(b["S_img"], self.in_ch))
         n_img = n_loc - t_loc                    # image rows of this rank that exist (the rest is padding)
         if n_img > 0:
             p0 = g0 + t_loc - S_txt              # first image token of this rank
             rows = slice(t_loc, n_loc)
-            a, s = self._quant(b["patches"][p0:p0 + n_img], xq[rows, :self.in_ch], rs[rows])
+            # dsb_patchify: the 2 x 2 patches of this rank's tokens, gathered from the latents and quantised in one pass
+            lat = b["latents"].view(self.in_ch // 4, 1, b["height"], b["width"])
+            if self.afmt == ops.FMT_BF16:
+                a, s = ops.patchify(lat, p0, n_img, ops.FMT_BF16, out=b["patches"][p0:p0 + n_img])
+            else:
+                a, s = ops.patchify(lat, p0, n_img, self.afmt, out=xq[rows, :self.in_ch], row_scale=rs[rows])
             self._gemm(a, s, self.x_emb, out=x[rows])
 
         rope = b["rope_h"]
@@ -369,8 +373,8 @@ class FluxDiTEngine:
         else:
             tok = self._run()
         C = self.in_ch // 4
-        return (tok.reshape(b["height"] // 2, b["width"] // 2, C, 2, 2).permute(2, 0, 3, 1, 4)
-                .reshape(1, C, b["height"], b["width"]))
+        return ops.unpatchify(tok, C, 1, b["height"] // 2, b["width"] // 2, False, out=b["out_lat"]).view(
+            1, C, b["height"], b["width"])
 
     def forward(self, hidden_states, timestep, prompt_emb, pooled_prompt_emb, guidance, text_ids=None,
                 image_ids=None, **kwargs):

@@ -497,6 +497,47 @@ def rank_barrier(flag_arrays, rank, epoch, limit_cycles=20_000_000_000, status=N
     check(rc, "dsb_rank_barrier")
 
 
+def patchify(latents, row0=0, n_rows=None, out_fmt=FMT_BF16, out=None, row_scale=None):
+    """``dsb_patchify``: latents ``[C, F, 2gh, 2gw]`` (bf16, contiguous; a leading batch of 1 is accepted) -> token
+    rows ``[n_rows, C*4]`` from token ``row0`` on; 8-bit formats also return the per-row scale."""
+    _require_cuda(latents, out, row_scale)
+    _require_bf16(latents, "patchify")
+    lat = latents[0] if latents.dim() == 5 else latents
+    if lat.dim() != 4 or not lat.is_contiguous() or lat.shape[2] % 2 or lat.shape[3] % 2:
+        raise _lib.DsbError("patchify takes contiguous [C, F, H, W] latents with even H and W")
+    C, F, gh, gw = lat.shape[0], lat.shape[1], lat.shape[2] // 2, lat.shape[3] // 2
+    if n_rows is None:
+        n_rows = F * gh * gw - row0
+    if out is None:
+        out = torch.empty((n_rows, C * 4), dtype=_OUT_DTYPE[out_fmt], device=lat.device)
+    if out.dtype != _OUT_DTYPE[out_fmt] or out.dim() != 2 or out.stride(1) != 1 or out.shape[0] < n_rows or out.shape[1] < C * 4:
+        raise _lib.DsbError("patchify output must be [>= n_rows, >= C*4] rows of the requested format")
+    if out_fmt != FMT_BF16:
+        if row_scale is None:
+            row_scale = torch.empty(n_rows, dtype=torch.float32, device=lat.device)
+        if row_scale.dtype != torch.float32 or row_scale.numel() < n_rows or not row_scale.is_contiguous():
+            raise _lib.DsbError("patchify row_scale must be contiguous float32 [n_rows]")
+    rc = _lib.lib().dsb_patchify(_ptr(lat), C, F, gh, gw, row0, n_rows, out_fmt, _ptr(out), out.stride(0),
+                                 _ptr(row_scale) if out_fmt != FMT_BF16 else None, _stream())
+    check(rc, "dsb_patchify")
+    return out, (row_scale if out_fmt != FMT_BF16 else None)
+
+
+def unpatchify(tokens, C, F, gh, gw, c_fastest, out=None):
+    """``dsb_unpatchify``: token rows ``[F*gh*gw, >= C*4]`` (bf16) -> latents ``[1, C, F, 2gh, 2gw]``."""
+    _require_cuda(tokens, out)
+    _require_bf16(tokens, "unpatchify")
+    if tokens.dim() != 2 or tokens.stride(1) != 1 or tokens.shape[0] < F * gh * gw or tokens.shape[1] < C * 4:
+        raise _lib.DsbError("unpatchify takes [>= F*gh*gw, >= C*4] token rows")
+    if out is None:
+        out = torch.empty((1, C, F, 2 * gh, 2 * gw), dtype=torch.bfloat16, device=tokens.device)
+    if out.dtype != torch.bfloat16 or not out.is_contiguous() or out.numel() != C * F * 4 * gh * gw:
+        raise _lib.DsbError("unpatchify output must be a contiguous bf16 [C, F, 2gh, 2gw] tensor")
+    rc = _lib.lib().dsb_unpatchify(_ptr(tokens), tokens.stride(0), C, F, gh, gw, 1 if c_fastest else 0, _ptr(out), _stream())
+    check(rc, "dsb_unpatchify")
+    return out
+
+
 def pack_quant_weight(W, fmt=FMT_E4M3, per_channel=False):
     """Quantise a [N,K] fp32/bf16 weight on the device; returns (payload, scales)."""
     _require_cuda(W)

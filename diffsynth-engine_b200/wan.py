@@ -270,6 +270,7 @@ class WanDiTEngine:
             b["clip_in"] = torch.zeros(n_img, 1280, dtype=bf, device=dev)
         b["out_tok"] = torch.zeros(Sl, self.head.out_features, dtype=bf, device=dev)
         b["out_all"] = torch.zeros(S_pad, self.head.out_features, dtype=bf, device=dev) if P > 1 else None
+        b["out_lat"] = torch.zeros(1, self.out_dim, frames, height, width, dtype=bf, device=dev)
         self._bufs = b
         return self
 
@@ -386,10 +387,12 @@ class WanDiTEngine:
         # patch embedding: Conv3d with kernel = stride = (1,2,2) is a Linear over (c, y, z) patches (wan_dit.py:271-273)
         fr, gh, gw = b["grid"]
         Cin = b["in_ch"]
-        pat = (b["latents"][0].reshape(Cin, fr, gh, 2, gw, 2).permute(1, 2, 4, 0, 3, 5).reshape(S, Cin * 4))
-        n_own = max(0, min(Sl, S - row0))            # rows of this rank that exist (the rest of the buffer stays zero)
-        b["patches"][:n_own].copy_(pat[row0:row0 + n_own])
-        a, s = self._quant(b["patches"], xq[:, :Cin * 4], rs[:Sl])
+        # dsb_patchify gathers this rank's token rows straight from the latents and quantises them in the same pass
+        # (rows past the last token of a padded sequence come out as zeros)
+        if self.afmt == ops.FMT_BF16:
+            a, s = ops.patchify(b["latents"], row0, Sl, ops.FMT_BF16, out=b["patches"])
+        else:
+            a, s = ops.patchify(b["latents"], row0, Sl, self.afmt, out=xq[:, :Cin * 4], row_scale=rs[:Sl])
         self._gemm(a, s, self.patch, out=x)
 
         rope = b["rope"]
@@ -488,8 +491,7 @@ class WanDiTEngine:
             tok = b["out_all"][:S]
         else:
             tok = b["out_tok"]
-        od = self.out_dim
-        return tok.reshape(fr, gh, gw, 1, 2, 2, od).permute(6, 0, 3, 1, 4, 2, 5).reshape(1, od, fr, gh * 2, gw * 2)
+        return ops.unpatchify(tok, self.out_dim, fr, gh, gw, True, out=b["out_lat"])
 
     def forward(self, x, context, timestep, clip_feature=None, y=None):
         """Signature of ``WanDiT.forward`` (wan_dit.py:319-326).  ``clip_feature`` [1,257,1280] and ``y`` (conditioning

@@ -312,6 +312,25 @@ int dsb_rank_barrier(int* const* flags, int n_ranks, int rank, int epoch, long l
                      void* stream);
 
 /*
+ * Patch embedding input: latents [C, F, 2*gh, 2*gw] (bf16, contiguous) -> rows [n_rows, ld_out] for tokens
+ * row0 .. row0+n_rows-1 in (f, y, z) raster order, feature c*4 + py*2 + pz (C <= 128); rows past the last token are
+ * zeros.  out_fmt BF16 writes bf16; E4M3 / INT8 write the row quantised with its dynamic per-row scale (the rule of
+ * dsb_quant_rows) into row_scale[n_rows], so the row quantiser in front of the patch-embedding GEMM disappears.
+ * Replaces: the strided gather of WanDiT.patchify's Conv3d (models/wan/wan_dit.py:271-273,301-305) and
+ * FluxDiT.patchify (models/flux/flux_dit.py:364-367).
+ */
+int dsb_patchify(const void* latents, int C, int F, int gh, int gw, int row0, int n_rows, int out_fmt, void* out,
+                 int64_t ld_out, float* row_scale, void* stream);
+
+/*
+ * Token rows [F*gh*gw, ld_tok] (bf16, >= C*4 features) -> latents [C, F, 2*gh, 2*gw].  c_fastest 1: feature
+ * (py*2 + pz)*C + c (WanDiT.unpatchify, models/wan/wan_dit.py:307-317); 0: feature c*4 + py*2 + pz
+ * (FluxDiT.unpatchify, models/flux/flux_dit.py:369-374).
+ */
+int dsb_unpatchify(const void* tokens, int64_t ld_tok, int C, int F, int gh, int gw, int c_fastest, void* out,
+                   void* stream);
+
+/*
  * Weight prepack: W[N,K] (fp32 or bf16 by src_is_bf16) -> quantised payload [N,K] row-major plus scales.
  *   fmt E4M3, per_channel 0: s = amax(|W|)/448 (one scale);   per_channel 1: s_n = amax(|W[n,:]|)/448
  *   fmt INT8 (per_channel 1 only): s_n = amax/127, q = round-half-even(W/s) clamped to +-127

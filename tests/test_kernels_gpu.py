@@ -525,3 +525,43 @@ def test_gemm_front_end_rejects_buffers_the_kernel_would_overrun(dsb, cuda_dev):
     ref = torch.nn.functional.gelu((a.float() @ w.float().T) * rs[:, None], approximate="tanh")
     assert O.rel_l2(o8.float(), ref.clamp(-448, 448)) < 4e-2          # e4m3 rounding of the output
     dsb.ops.check_status(0)
+
+
+# ------------------------------------------------------------------ patch embedding input / output of the head
+@pytest.mark.parametrize("C,F,gh,gw", [(16, 3, 5, 7), (36, 2, 4, 6), (16, 1, 12, 10)])
+def test_patchify_matches_the_reference_rearrangement(dsb, cuda_dev, C, F, gh, gw):
+    """``dsb_patchify`` against the rearrangement the reference's Conv3d / patchify perform
+    (models/wan/wan_dit.py:271-273, flux_dit.py:364-367: feature order (c, py, pz), tokens in (f, y, z) raster order):
+    bit-exact in bf16; the quantised forms equal ``dsb_quant_rows`` of those rows; a row range that runs past the last
+    token is zero-filled."""
+    lat = torch.randn(C, F, 2 * gh, 2 * gw).bfloat16()
+    want = lat.reshape(C, F, gh, 2, gw, 2).permute(1, 2, 4, 0, 3, 5).reshape(F * gh * gw, C * 4)
+    S = F * gh * gw
+    got, _ = dsb.ops.patchify(lat.to(cuda_dev))
+    assert torch.equal(got.cpu(), want)
+    row0, n = 5, S                                              # 5 rows past the end
+    got, _ = dsb.ops.patchify(lat.to(cuda_dev), row0, n)
+    assert torch.equal(got.cpu()[:S - row0], want[row0:]) and (got.cpu()[S - row0:] == 0).all()
+    for fmt, qfn in ((dsb.ops.FMT_E4M3, O.quant_rows_e4m3), (dsb.ops.FMT_INT8, O.quant_rows_int8)):
+        wide = torch.zeros(n, C * 4 + 64, dtype=dsb.ops._OUT_DTYPE[fmt], device=cuda_dev)   # a column slice as output
+        q, s = dsb.ops.patchify(lat.to(cuda_dev), row0, n, fmt, out=wide[:, :C * 4])
+        rows = torch.cat([want[row0:], torch.zeros(row0, C * 4, dtype=torch.bfloat16)])
+        q_ref, s_ref = qfn(rows.float())
+        assert torch.equal(s.cpu(), s_ref)
+        assert torch.equal(q.cpu().view(torch.uint8), q_ref.view(torch.uint8))
+        assert (wide[:, C * 4:].view(torch.uint8) == 0).all()
+
+
+@pytest.mark.parametrize("c_fastest", [True, False])
+def test_unpatchify_matches_the_reference_rearrangement(dsb, cuda_dev, c_fastest):
+    """``dsb_unpatchify`` against WanDiT.unpatchify ("(x y z c)", wan_dit.py:307-317) and FluxDiT.unpatchify
+    ("(c ph pw)", flux_dit.py:369-374) on rows wider than the features they hold."""
+    C, F, gh, gw = 16, (3 if c_fastest else 1), 6, 5
+    tok = torch.randn(F * gh * gw, C * 4 + 8).bfloat16()
+    t = tok[:, :C * 4]
+    if c_fastest:
+        want = t.reshape(F, gh, gw, 1, 2, 2, C).permute(6, 0, 3, 1, 4, 2, 5).reshape(1, C, F, gh * 2, gw * 2)
+    else:
+        want = t.reshape(gh, gw, C, 2, 2).permute(2, 0, 3, 1, 4).reshape(1, C, 1, gh * 2, gw * 2)
+    got = dsb.ops.unpatchify(tok.to(cuda_dev), C, F, gh, gw, c_fastest)
+    assert torch.equal(got.cpu(), want)
