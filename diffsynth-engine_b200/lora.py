@@ -14,7 +14,8 @@ tensor-core GEMM as extra K columns:
              y         = gemm([x_q | t_ext], W_ext) * s_m * s_n + bias        (any fused epilogue of the main GEMM)
 
 because ``s_m s_n * t_q U_q = s_m s_n * (x.D_j / (s_m tau_j)) * (U_nj tau_j / s_n) = (x.D_j) U_nj``.  ``tau_j``
-balances the ranges of the two 8-bit factors of rank column j.  FP8: both factors are split into an e4m3 head and
+splits the 8-bit range between the two factors of rank column j (``_balance``: as much headroom as the range has
+goes to t, whose bound is only statistical).  FP8: both factors are split into an e4m3 head and
 an e4m3 remainder (E = 3R: t_ext = [t_hi | t_lo | t_hi] against U_ext = [U_hi | U_hi | U_lo]), so the LoRA term is
 as accurate as the main product; INT8: E = R, errors in units of the main GEMM's quantisation step, like R more
 weight columns.  A LoRA whose columns exceed the 8-bit range after balancing is rejected (keep it unfused).  With
@@ -43,6 +44,20 @@ class LoraExtension:
     up: Optional[torch.Tensor]      # bf16 [N, R] = coef * up (bf16 weights only)
 
 
+def _balance(a: torch.Tensor, bmax: torch.Tensor, qmax: float) -> torch.Tensor:
+    """tau_j for rank column j: the activation-side factor t_j = x_q.D_j / tau_j is expected to stay below
+    ``a_j / tau_j``, the weight-side factor is bounded by ``bmax_j * tau_j``; both must fit ``qmax``.  The weight-side
+    bound is exact, the activation-side one is a statistical estimate that an activation row aligned with D_j exceeds
+    (by up to sqrt(K)), and a value past ``qmax`` would saturate in ``dsb_cast_quant``.  So the expected t is aimed at
+    ``qmax / 8`` or the balanced point sqrt(a*bmax), whichever is smaller - but never below a*bmax/qmax, where the
+    weight-side factor reaches ``qmax``: every bit of slack the 8-bit range has goes to the side whose bound is not
+    exact."""
+    prod = a * bmax
+    target = torch.maximum(prod / qmax, torch.minimum(torch.sqrt(prod), torch.full_like(prod, qmax / 8.0)))
+    tau = a / target.clamp_min(1e-30)
+    return torch.where((a > 0) & (bmax > 0), tau, torch.ones_like(tau))
+
+
 def build_lora_extension(payload: torch.Tensor, scale: Optional[torch.Tensor], fmt: str,
                          loras: Sequence[Tuple[float, torch.Tensor, torch.Tensor]]) -> LoraExtension:
     """``loras``: (coef, up [N, r], down [r, K]) with coef = scale * alpha / rank.  ``payload``/``scale``: the
@@ -65,13 +80,13 @@ def build_lora_extension(payload: torch.Tensor, scale: Optional[torch.Tensor], f
     qmax = 127.0 if afmt == ops.FMT_INT8 else 448.0
     D_q, s_D = ops.pack_quant_weight(D, afmt, per_channel=True)
     s_n = scale.float().reshape(-1, 1) if scale.numel() > 1 else scale.float().reshape(1, 1)
-    a = qmax * D.norm(dim=1)
-    bmax = (U / s_n).abs().amax(dim=0)
-    tau = torch.sqrt(a / bmax.clamp_min(1e-30)).clamp_min(1e-30)
-    tau = torch.where((a > 0) & (bmax > 0), tau, torch.ones_like(tau))
+    a = qmax * D.norm(dim=1)                 # 4-sigma estimate of |x_q . D_j| for activations uncorrelated with D_j
+    bmax = (U / s_n).abs().amax(dim=0)       # exact bound of the other factor
+    tau = _balance(a, bmax, qmax)
     Up = U * tau[None, :] / s_n
-    if float(Up.abs().amax()) > qmax:
+    if float(Up.abs().amax()) > qmax * (1.0 + 1e-4):
         raise ValueError("a LoRA column is larger than the quantised weight's range allows; keep it unfused")
+    Up = Up.clamp(-qmax, qmax)
     if afmt == ops.FMT_INT8:
         U_q = torch.clamp(torch.round(Up), -127, 127).to(torch.int8)
     else:

@@ -101,7 +101,7 @@ def lora_extension(W_q, W_s, mode, loras, pad=64):
     ``U = cat(coef_i * up_i)`` [N, R] (R padded with zeros to a multiple of ``pad``), quantises D per row, and
     returns (W_ext_q [N, K+E], D_q, D_colscale [R]) such that
     ``(x_q W_q^T + t_ext U_ext^T) * s_m * s_n`` with ``t = bf16(x_q D_q^T * D_colscale)`` reproduces the LoRA sum;
-    tau balances the ranges of the two 8-bit factors per rank column.  FP8: both factors are split into an e4m3
+    tau splits the 8-bit range between the two factors per rank column (headroom goes to t, whose bound is statistical).  FP8: both factors are split into an e4m3
     head and an e4m3 remainder, t_ext = [t_hi | t_lo | t_hi] against U_ext = [U_hi | U_hi | U_lo] (E = 3R), which
     leaves only the remainder-times-remainder term out.  INT8: single columns (E = R)."""
     qmax = 127.0 if mode == "int8_channel" else 448.0
@@ -114,12 +114,16 @@ def lora_extension(W_q, W_s, mode, loras, pad=64):
     U = torch.cat([U, torch.zeros(N, Rp - R)], dim=1)
     D_q, D_s = O.quant_weight(D, "int8_channel" if mode == "int8_channel" else "fp8_channel")
     s_n = W_s.float().reshape(-1, 1) if W_s.numel() > 1 else W_s.float().reshape(1, 1)
-    a = qmax * D.norm(dim=1)                                  # 4-sigma bound of |x_q . D_j| for rows with amax qmax
+    a = qmax * D.norm(dim=1)                                  # 4-sigma estimate of |x_q . D_j| for rows with amax qmax
     bmax = (U / s_n).abs().amax(dim=0)
-    tau = torch.sqrt(a / bmax.clamp_min(1e-30)).clamp_min(1e-30)
+    # expected t aimed at min(balanced point, qmax/8), but not below the point where the weight-side factor reaches qmax
+    prod = a * bmax
+    target = torch.maximum(prod / qmax, torch.minimum(torch.sqrt(prod), torch.full_like(prod, qmax / 8.0)))
+    tau = a / target.clamp_min(1e-30)
     tau = torch.where((a > 0) & (bmax > 0), tau, torch.ones_like(tau))
     Up = U * tau[None, :] / s_n
-    assert float(Up.abs().amax()) <= qmax, "LoRA column beyond the quantised weight's range: the library keeps it unfused"
+    assert float(Up.abs().amax()) <= qmax * (1.0 + 1e-4), "LoRA column beyond the quantised weight's range: the library keeps it unfused"
+    Up = Up.clamp(-qmax, qmax)
     if mode == "int8_channel":
         U_ext = torch.clamp(torch.round(Up), -127, 127).to(torch.int8)
     else:

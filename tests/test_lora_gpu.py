@@ -138,3 +138,30 @@ def test_fuse_lora_on_a_module(dsb, cuda_dev):
         lin._lora_dict.clear()
         plain = lin(xb).float().cpu()
     assert O.rel_l2(plain, LinearEval("fp8_tensor")(x, W, b)) < 1e-2
+
+
+@pytest.mark.parametrize("fmt", ["fp8_tensor", "int8_channel"])
+def test_activation_rows_aligned_with_a_down_row_do_not_saturate(dsb, cuda_dev, fmt):
+    """A trained LoRA's down-projection correlates with the activations it was trained on.  Rows that point along a
+    down row make x_q.D_j several times larger than the uncorrelated estimate the range split starts from
+    (here sqrt(K)/4 = 5.6 times); the headroom that split leaves on the activation side absorbs it, so the LoRA term
+    of those rows is still resolved instead of being clipped at the 8-bit maximum."""
+    from diffsynth_engine_b200.lora import build_lora_extension, linear_lora
+    from diffsynth_engine_b200.packed import pack_linear
+    x, W, b, loras = _case(M=128, K=512, N=256, seed=130)
+    loras = [(c, u * 0.1, d) for c, u, d in loras]                 # a small adapter: the 8-bit range has slack to give
+    d0 = loras[0][2][0]
+    x[:64] = (d0 * 20.0).bfloat16().float()[None, :] * torch.linspace(0.5, 2.0, 64)[:, None]   # fully aligned rows
+    x = x.bfloat16().float()
+    exact = lora_reference(x, W, b, loras)
+    main = LinearEval("fp32")(x, W, b)
+    p = pack_linear(W, b, fmt, cuda_dev)
+    ext = build_lora_extension(p.w, p.scale, fmt, loras)
+    y = linear_lora(x.bfloat16().to(cuda_dev), p.w, p.scale, p.bias, ext).float().cpu()
+    dsb.ops.check_status(0)
+    ref = lora_linear_quant(x, W, b, loras, fmt)
+    assert O.rel_l2(y, ref) < 1e-2
+    base = LinearEval(fmt)(x, W, b)
+    part = O.rel_l2((y - base)[:64], (exact - main)[:64])
+    print(f"aligned rows {fmt}: LoRA part alone vs exact {part:.3e}")
+    assert part < (0.1 if fmt == "fp8_tensor" else 0.35)
