@@ -165,11 +165,45 @@ def cpu_wan_arm(steps=1, warmup=0, budget_s=900.0):
     t_sample = statistics.mean(times)
     fraction = rows / S / c["num_layers"]
     step_s = t_sample / fraction
-    return dict(value=1.0 / step_s, unit="steps/s", cores=cores, kind="port",
+    check = _reference_module_check(torch, synth, OW, O, lin, w, c, rows)
+    return dict(value=1.0 / step_s, unit="steps/s", cores=cores, kind="port", reference_module_check=check,
                 sample=(f"one Wan DiTBlock (oracle port, fp32, {cores} threads) on {rows} tokens as queries against all "
                         f"{S} keys = {fraction:.3e} of a step; {t_sample:.2f} s each (mean of {len(times)}), "
                         f"extrapolated to the 40-block, {S}-token step; embedders and head (<0.1% of the work) left out"),
                 sample_ms=t_sample * 1e3, sample_fraction=fraction, samples=len(times))
+
+
+def _reference_module_check(torch, synth, OW, O, lin, w, c, rows):
+    """That the port is a fair stand-in for the reference on these cores: the reference's own ``DiTBlock``
+    (models/wan/wan_dit.py:155-193, unmodified, from baseline/_ref, fp32) and the port on the same ``rows``-token
+    problem - time of each and the rel-L2 between their outputs.  None when baseline/_ref is not installed."""
+    try:
+        sys.path.insert(0, os.path.join(ROOT, "baseline"))
+        import install_reference
+        ref = install_reference.import_reference()
+        if ref is None:
+            return None
+        d, H = c["d"], c["H"]
+        fr, hh, ww = 3, 11, rows // 33
+        n = fr * hh * ww
+        blk = ref.wan_dit.DiTBlock(False, d, H, c["ffn"], 1e-6, device="cpu", dtype=torch.float32)
+        torch.nn.Module.load_state_dict(blk, w, strict=True)
+        blk.eval()
+        f_, h_, w_ = ref.wan_dit.precompute_freqs_cis_3d(d // H)
+        freqs = torch.cat([f_[:fr].view(fr, 1, 1, -1).expand(fr, hh, ww, -1), h_[:hh].view(1, hh, 1, -1).expand(fr, hh, ww, -1),
+                           w_[:ww].view(1, 1, ww, -1).expand(fr, hh, ww, -1)], dim=-1).reshape(n, 1, -1)
+        x, ctx, tmod = synth.randn((1, n, d), 11), synth.randn((1, c["ctx"], d), 12), synth.randn((1, 6, d), 13) * 0.1
+        with torch.no_grad():
+            t0 = time.time()
+            y_ref = blk(x, ctx, tmod, freqs)
+            t_ref = time.time() - t0
+            t0 = time.time()
+            y_port = OW.wan_block(x[0], ctx[0], tmod[0], O.wan_rope_table(fr, hh, ww), w, "", H, lin)
+            t_port = time.time() - t0
+        return {"tokens": n, "reference_DiTBlock_s": t_ref, "port_s": t_port,
+                "rel_l2_port_vs_reference": float((y_port - y_ref[0]).norm() / y_ref[0].norm())}
+    except Exception as e:   # a baseline, not a gate: report instead of failing the arm
+        return {"error": f"{type(e).__name__}: {str(e)[:160]}"}
 
 
 def cpu_flux_arm(steps=1, warmup=0, budget_s=900.0):
@@ -820,7 +854,7 @@ def main():
                 "ms_per_step": r["sample_ms"], "sample_fraction_of_a_step": r["sample_fraction"], "extrapolated": True,
                 "higher_is_better": True, "scaling": "strong" if wan_headline else "weak", "vs_baseline": None,
                 "dtype": "fp32", "data": "synthetic", "config": cfg,
-                "cpu_baseline": {k: r[k] for k in ("value", "unit", "cores", "kind", "sample")},
+                "cpu_baseline": {k: r[k] for k in ("value", "unit", "cores", "kind", "sample", "reference_module_check") if k in r},
                 "e2e": {"value": r["value"], "unit": "steps/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
         print(json.dumps(line), flush=True)
         return
@@ -902,7 +936,8 @@ def main():
     if rank == 0:
         if not args.no_cpu_baseline and world == 1:
             r = (cpu_wan_arm if wan_headline else cpu_flux_arm)(steps=2, warmup=0, budget_s=40.0)
-            line["cpu_baseline"] = {k: r[k] for k in ("value", "unit", "cores", "kind", "sample")}
+            line["cpu_baseline"] = {k: r[k] for k in ("value", "unit", "cores", "kind", "sample", "reference_module_check")
+                                    if k in r}
         emit(line)
     if dist is not None:
         dist.barrier()
