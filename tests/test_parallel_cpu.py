@@ -132,3 +132,34 @@ def test_joint_sequence_slices_cover_every_token_once():
             assert text_rows == list(range(S_txt))
             assert image_rows == list(range(S_txt, S_txt + S_img))
             assert pad == sl["S_pad"] - sl["S"]
+
+
+def test_peer_exchange_addressing_equals_full_attention():
+    """The addressing of the sequence-parallel attention over mapped peer memory (``wan.py`` with
+    ``exchange="peer"``), restated on the CPU for P = 4 emulated ranks: rank r keeps its normalised queries as
+    ``qn_r [Sl, d]`` and owns a return buffer ``ao_back_r [P][Sl][C]``.  Rank g (head group g) reads query part p from
+    ``qn_p`` at column offset g*C with strides (d, 128), attends over all real tokens, and writes output row s to
+    chunk g of ``ao_back_{s // Sl}`` at row s % Sl with strides (C, 128).  Afterwards
+    ``ao_back_r.permute(1, 0, 2).reshape(Sl, d)`` is rank r's slice of the full attention output; padded rows never act
+    as keys."""
+    from oracle import ops as O
+    P, H, S = 4, 8, 437                       # S does not split evenly: slices are padded to a multiple of 128
+    d, C, Hl = H * 128, H * 128 // P, H // P
+    Sl = ((S + P - 1) // P + 127) // 128 * 128
+    S_pad = Sl * P
+    g = torch.Generator().manual_seed(5)
+    q, k, v = (torch.randn(S_pad, d, generator=g) for _ in range(3))
+    q[S:], k[S:], v[S:] = 7.0, 9.0, -3.0      # padded rows hold junk that must not leak into real rows
+    full = O.attention(*(t[:S].reshape(1, S, H, 128).transpose(1, 2) for t in (q, k, v)))[0].transpose(0, 1).reshape(S, d)
+    qn = [q[r * Sl:(r + 1) * Sl].clone() for r in range(P)]
+    ao_back = [torch.zeros(P, Sl, C) for _ in range(P)]
+    for grp in range(P):                      # what rank grp's attention kernel does
+        cols = slice(grp * C, (grp + 1) * C)
+        q_all = torch.cat([qn[p][:, cols] for p in range(P)])                    # query part p comes from rank p
+        k_g, v_g = k[:S, cols], v[:S, cols]                                      # arrived by all-to-all; real tokens only
+        o = O.attention(*(t.reshape(1, -1, Hl, 128).transpose(1, 2) for t in (q_all, k_g, v_g)))[0]
+        o = o.transpose(0, 1).reshape(S_pad, C)
+        for s in range(S_pad):
+            ao_back[s // Sl][grp, s % Sl] = o[s]
+    got = torch.cat([ao_back[r].permute(1, 0, 2).reshape(Sl, d) for r in range(P)])
+    assert O.rel_l2(got[:S], full) < 1e-6
