@@ -53,6 +53,53 @@ __device__ __forceinline__ float row_scale_from_amax(float amax, float qmax) {
   return amax > 0.f ? amax / qmax : 1.0f;
 }
 
+// ------------------------------------------------------------ row prefetch ring
+// The row quantiser walks rows with persistent CTAs and keeps the next kRing-1 rows of each CTA in flight while one
+// is processed: thread t copies its own 16-byte vectors (t, t+T, t+2T, ...) of a row into a slot of a shared-memory
+// ring with cp.async and later reads exactly those vectors back itself, so the ring needs no barrier - only
+// cp.async.wait_group.  Measured at 32760 x 5120: 146 -> 107 us (3.4 -> 4.7 TB/s).  The LayerNorm and RMSNorm kernels
+// keep one row per CTA: they are bound by instruction issue (fp32 math on bf16 data plus per-column parameters), not
+// by bytes in flight - with the ring they were no faster (RMSNorm) or slower (LayerNorm: fewer resident warps).
+constexpr int kRing = 4;
+__device__ __forceinline__ void cp_async16(void* smem_dst, const void* gsrc) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(smem_dst)), "l"(gsrc) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() {
+  asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+// SRC(vi) -> global address of 16-byte vector vi of the row; THREADS = blockDim.x
+template <int NV, int THREADS, typename SRC>
+__device__ __forceinline__ void ring_issue(uint4* ring, int slot, int nvec, bool row_exists, SRC src) {
+  if (row_exists) {
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+      const int vi = threadIdx.x + i * THREADS;
+      if (vi < nvec) cp_async16(ring + (slot * NV + i) * THREADS + threadIdx.x, src(vi));
+    }
+  }
+  cp_async_commit();  // an empty group keeps the group count in step with the iteration count
+}
+template <int NV, int THREADS>
+__device__ __forceinline__ uint4 ring_read(const uint4* ring, int slot, int i) {
+  return ring[(slot * NV + i) * THREADS + threadIdx.x];
+}
+// grid of a persistent row kernel: the CTAs the device holds at once, at most one per row
+template <auto KERNEL>
+static int persistent_grid(int threads, size_t smem, int rows) {
+  static int per_sm[64] = {0};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return -1;
+  if (per_sm[dev] == 0) {
+    int n = 0;
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, KERNEL, threads, smem) != cudaSuccess || n <= 0) n = 1;
+    per_sm[dev] = n;
+  }
+  const int64_t cap = static_cast<int64_t>(per_sm[dev]) * sm_count();
+  return static_cast<int>(rows < cap ? rows : cap);
+}
+
 // ------------------------------------------------------------ ln_modulate
 // y = LayerNorm(x; eps, no affine) * (1 + scale[d]) + shift[d]
 // NV = 128-bit vectors per thread (row width D <= 128 * 8 * NV).
@@ -327,7 +374,80 @@ __global__ void __launch_bounds__(kRowThreads) rmsnorm_full_rope_kernel(const __
 
 // ------------------------------------------------------------- quant_rows
 // bf16 [M, K] -> e4m3 or int8 [M, K] plus row_scale[M] (dynamic, amax based).
-// The row is read twice; the second read is served by L1/L2.
+// Rows of up to 256 * NV 16-byte vectors (K <= 8192 with NV = 4): persistent CTAs with the prefetch ring, the row is
+// read once and held in registers between the amax pass and the quantising pass.
+template <int OUT, int NV>
+__global__ void __launch_bounds__(256) quant_rows_ring_kernel(const __nv_bfloat16* __restrict__ x, int64_t ld_x,
+                                                              int chunk_cols, int64_t chunk_stride,
+                                                              uint8_t* __restrict__ y, int64_t ld_y,
+                                                              float* __restrict__ row_scale, int M, int K) {
+  __shared__ float red[8];
+  extern __shared__ uint4 ring[];
+  const int nvec = K >> 3;
+  const int stride = gridDim.x;
+  // chunked input: column c of row m lives at x[(c / chunk_cols) * chunk_stride + m * ld_x + c % chunk_cols]
+  // (what a sequence/head all-to-all delivers: [P][rows][K/P]); chunk_cols == K is the plain row-major case
+  auto issue = [&](int slot, int r) {
+    const __nv_bfloat16* xrow = x + static_cast<int64_t>(r) * ld_x;
+    ring_issue<NV, 256>(ring, slot, nvec, r < M, [&](int vi) {
+      const int col = vi * 8;
+      const int ck = col / chunk_cols;
+      return xrow + ck * chunk_stride + (col - ck * chunk_cols);
+    });
+  };
+#pragma unroll
+  for (int k = 0; k < kRing - 1; ++k) issue(k, blockIdx.x + k * stride);
+  int it = 0;
+  for (int row = blockIdx.x; row < M; row += stride, ++it) {
+    issue((it + kRing - 1) % kRing, row + (kRing - 1) * stride);
+    cp_async_wait<kRing - 1>();
+    const int slot = it % kRing;
+    float f[NV][8];
+    float amax = 0.f;
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+      if (threadIdx.x + i * 256 < nvec) {
+        const uint4 pu = ring_read<NV, 256>(ring, slot, i);
+        const uint32_t u[4] = {pu.x, pu.y, pu.z, pu.w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float2 t = unpack_bf16x2(u[j]);
+          f[i][2 * j] = t.x, f[i][2 * j + 1] = t.y;
+          amax = fmaxf(amax, fmaxf(fabsf(t.x), fabsf(t.y)));
+        }
+      }
+    }
+    amax = warp_max(amax);
+    __syncthreads();  // the previous row's readers of red[] are done
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = amax;
+    __syncthreads();
+    amax = red[0];
+#pragma unroll
+    for (int i = 1; i < 8; ++i) amax = fmaxf(amax, red[i]);
+    const float qmax = (OUT == 1) ? 448.0f : 127.0f;
+    const float sc = row_scale_from_amax(amax, qmax);
+    const float inv = 1.0f / sc;
+    if (threadIdx.x == 0) row_scale[row] = sc;
+    uint8_t* yr = y + static_cast<int64_t>(row) * ld_y;
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+      const int vi = threadIdx.x + i * 256;
+      if (vi < nvec) {
+        uint2 o;
+        if constexpr (OUT == 1) {
+          o.x = pack_e4m3x4(f[i][0] * inv, f[i][1] * inv, f[i][2] * inv, f[i][3] * inv);
+          o.y = pack_e4m3x4(f[i][4] * inv, f[i][5] * inv, f[i][6] * inv, f[i][7] * inv);
+        } else {
+          o.x = pack_s8x4(f[i][0] * inv, f[i][1] * inv, f[i][2] * inv, f[i][3] * inv);
+          o.y = pack_s8x4(f[i][4] * inv, f[i][5] * inv, f[i][6] * inv, f[i][7] * inv);
+        }
+        *reinterpret_cast<uint2*>(yr + vi * 8) = o;
+      }
+    }
+  }
+}
+
+// Wider rows: one CTA per row, the row is read twice (the second read is served by L1/L2).
 template <int OUT>
 __global__ void __launch_bounds__(256) quant_rows_kernel(const __nv_bfloat16* __restrict__ x, int64_t ld_x,
                                                          int chunk_cols, int64_t chunk_stride,
@@ -1028,12 +1148,33 @@ static int quant_rows_impl(const void* x, int64_t ld_x, int chunk_cols, int64_t 
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   const __nv_bfloat16* xp = reinterpret_cast<const __nv_bfloat16*>(x);
   uint8_t* yp = reinterpret_cast<uint8_t*>(y);
-  if (out_fmt == DSB_FMT_E4M3)
-    quant_rows_kernel<1><<<M, 256, 0, st>>>(xp, ld_x, chunk_cols, chunk_stride, yp, ld_y, row_scale, M, K);
-  else if (out_fmt == DSB_FMT_INT8)
-    quant_rows_kernel<2><<<M, 256, 0, st>>>(xp, ld_x, chunk_cols, chunk_stride, yp, ld_y, row_scale, M, K);
-  else
-    return DSB_ERR_ARG;
+  if (out_fmt != DSB_FMT_E4M3 && out_fmt != DSB_FMT_INT8) return DSB_ERR_ARG;
+  const int nv = (K / 8 + 255) / 256;
+#define DSB_QR_RING(OUT, NV)                                                                                  \
+  {                                                                                                           \
+    constexpr size_t smem = static_cast<size_t>(kRing) * NV * 256 * 16;                                       \
+    DSB_ENSURE_SMEM((quant_rows_ring_kernel<OUT, NV>), static_cast<int>(smem));                               \
+    const int grid = persistent_grid<quant_rows_ring_kernel<OUT, NV>>(256, smem, M);                          \
+    if (grid <= 0) return DSB_ERR_CUDA;                                                                       \
+    quant_rows_ring_kernel<OUT, NV><<<grid, 256, smem, st>>>(xp, ld_x, chunk_cols, chunk_stride, yp, ld_y,    \
+                                                             row_scale, M, K);                                \
+  }
+#define DSB_QR_FMT(OUT)                                                                                       \
+  switch (nv) {                                                                                               \
+    case 1: DSB_QR_RING(OUT, 1) break;                                                                        \
+    case 2: DSB_QR_RING(OUT, 2) break;                                                                        \
+    case 3: DSB_QR_RING(OUT, 3) break;                                                                        \
+    case 4: DSB_QR_RING(OUT, 4) break;                                                                        \
+    default:                                                                                                  \
+      quant_rows_kernel<OUT><<<M, 256, 0, st>>>(xp, ld_x, chunk_cols, chunk_stride, yp, ld_y, row_scale, M, K); \
+  }
+  if (out_fmt == DSB_FMT_E4M3) {
+    DSB_QR_FMT(1)
+  } else {
+    DSB_QR_FMT(2)
+  }
+#undef DSB_QR_FMT
+#undef DSB_QR_RING
   return cudaGetLastError() == cudaSuccess ? DSB_OK : DSB_ERR_CUDA;
 }
 

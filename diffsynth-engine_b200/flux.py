@@ -403,5 +403,6 @@ class FluxDiTEngine:
         nq = {ops.FMT_BF16: 0, ops.FMT_E4M3: 1, ops.FMT_INT8: 2}[self.afmt]
         dbl = 2 + 4 + 1 + nq
         sgl = 3 + (1 if self.afmt != ops.FMT_BF16 else 0) + 1
-        pre = 1 + (6 if self.use_guidance else 4) + 1 + 2 + (2 if self.afmt != ops.FMT_BF16 else 0)
-        return pre + self.n_double * dbl + self.n_single * sgl + 2
+        # embedders: sinusoids, GEMVs, modulation GEMV, the two token-embedder GEMMs, the text quantiser, patchify
+        pre = 1 + (6 if self.use_guidance else 4) + 1 + 2 + (1 if self.afmt != ops.FMT_BF16 else 0) + 1
+        return pre + self.n_double * dbl + self.n_single * sgl + 3      # final LN, projection, unpatchify
