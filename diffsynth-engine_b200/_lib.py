@@ -51,6 +51,7 @@ _SIGS = {
     "dsb_gemm_qkv": [c_p, c_i64, c_p, c_i64, c_i, c_i, c_i, c_i, c_p, c_p, c_i, c_p, c_i, c_i, c_p, c_i64, c_p, c_i64, c_i,
                      c_p, c_p, c_i, c_p, c_i, c_f, c_p, c_p],
     "dsb_flash_attn": [c_p, c_p, c_p, c_p, c_i, c_i, c_i, c_i, c_i] + [c_i64] * 12 + [c_f, c_p, c_p],
+    "dsb_flash_attn_out8": [c_p, c_p, c_p, c_p, c_i, c_i, c_i, c_i, c_i] + [c_i64] * 12 + [c_f, c_p, c_p],
     "dsb_pack_quant_weight": [c_p, c_i64, c_i, c_p, c_i64, c_p, c_i, c_i, c_i, c_i, c_p, c_p],
     "dsb_linear_static": [c_p, c_i64, c_p, c_i64, c_i, c_i, c_i, c_i, c_p, c_i, c_p, c_i, c_p, c_i64, c_p, c_p],
 }

@@ -60,6 +60,7 @@ struct AttnQMaps {
 struct AttnParams {
   __nv_bfloat16* o;
   __nv_bfloat16* o_part[kMaxParts];
+  int out_e4m3;         // 1: the output is written as e4m3 (1 byte per element; strides count elements = bytes)
   int q_rows_per_part;  // 0: one query buffer (map 0); else a multiple of kTileQ
   int o_rows_per_part;  // 0: one output buffer (o); else row s goes to o_part[s / o_rows_per_part]
   int64_t o_stride_b, o_stride_s, o_stride_h;
@@ -454,21 +455,43 @@ __global__ void __launch_bounds__(kAttnThreads, 1)
         obase = p.o_part[part];
         so = sq - part * p.o_rows_per_part;
       }
-      __nv_bfloat16* orow = obase + static_cast<int64_t>(so) * p.o_stride_s + static_cast<int64_t>(h) * p.o_stride_h + half * 64;
+      const int64_t ooff = static_cast<int64_t>(so) * p.o_stride_s + static_cast<int64_t>(h) * p.o_stride_h + half * 64;
+      __nv_bfloat16* orow = obase + ooff;
+      // e4m3 output (the operand of a following FP8 Linear with unit activation scale): the value is rounded to bf16
+      // first and then cast with saturation, i.e. exactly what a bf16 output followed by dsb_cast_quant gives
+      uint8_t* orow8 = reinterpret_cast<uint8_t*>(p.o) + static_cast<int64_t>(b) * p.o_stride_b + ooff;
 #pragma unroll 1
       for (int c = 0; c < 2; ++c) {
         uint32_t r[32];
         tmem_ld32(t_o + c * 32, r);
         tc_wait_ld();
         if (ok && sq < p.Sq) {
+          if (p.out_e4m3) {
 #pragma unroll
-          for (int g = 0; g < 4; ++g) {
-            uint4 o;
-            o.x = pack_bf16x2(__uint_as_float(r[g * 8 + 0]) * inv, __uint_as_float(r[g * 8 + 1]) * inv);
-            o.y = pack_bf16x2(__uint_as_float(r[g * 8 + 2]) * inv, __uint_as_float(r[g * 8 + 3]) * inv);
-            o.z = pack_bf16x2(__uint_as_float(r[g * 8 + 4]) * inv, __uint_as_float(r[g * 8 + 5]) * inv);
-            o.w = pack_bf16x2(__uint_as_float(r[g * 8 + 6]) * inv, __uint_as_float(r[g * 8 + 7]) * inv);
-            *reinterpret_cast<uint4*>(orow + c * 32 + g * 8) = o;
+            for (int g = 0; g < 2; ++g) {
+              uint32_t w[4];
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                const float2 lo = unpack_bf16x2(pack_bf16x2(__uint_as_float(r[g * 16 + j * 4 + 0]) * inv,
+                                                            __uint_as_float(r[g * 16 + j * 4 + 1]) * inv));
+                const float2 hi = unpack_bf16x2(pack_bf16x2(__uint_as_float(r[g * 16 + j * 4 + 2]) * inv,
+                                                            __uint_as_float(r[g * 16 + j * 4 + 3]) * inv));
+                const __nv_fp8x2_storage_t a8 = __nv_cvt_float2_to_fp8x2(lo, __NV_SATFINITE, __NV_E4M3);
+                const __nv_fp8x2_storage_t b8 = __nv_cvt_float2_to_fp8x2(hi, __NV_SATFINITE, __NV_E4M3);
+                w[j] = static_cast<uint32_t>(a8) | (static_cast<uint32_t>(b8) << 16);
+              }
+              *reinterpret_cast<uint4*>(orow8 + c * 32 + g * 16) = make_uint4(w[0], w[1], w[2], w[3]);
+            }
+          } else {
+#pragma unroll
+            for (int g = 0; g < 4; ++g) {
+              uint4 o;
+              o.x = pack_bf16x2(__uint_as_float(r[g * 8 + 0]) * inv, __uint_as_float(r[g * 8 + 1]) * inv);
+              o.y = pack_bf16x2(__uint_as_float(r[g * 8 + 2]) * inv, __uint_as_float(r[g * 8 + 3]) * inv);
+              o.z = pack_bf16x2(__uint_as_float(r[g * 8 + 4]) * inv, __uint_as_float(r[g * 8 + 5]) * inv);
+              o.w = pack_bf16x2(__uint_as_float(r[g * 8 + 6]) * inv, __uint_as_float(r[g * 8 + 7]) * inv);
+              *reinterpret_cast<uint4*>(orow + c * 32 + g * 8) = o;
+            }
           }
         }
       }
@@ -529,8 +552,9 @@ static int launch_attn(const void* q, const void* const* q_parts, int n_q_parts,
                        int Sq, int Sk, int head_dim, int64_t q_stride_b, int64_t q_stride_s, int64_t q_stride_h,
                        int64_t k_stride_b, int64_t k_stride_s, int64_t k_stride_h, int64_t v_stride_b,
                        int64_t v_stride_s, int64_t v_stride_h, int64_t o_stride_b, int64_t o_stride_s,
-                       int64_t o_stride_h, float sm_scale, int* status, void* stream) {
+                       int64_t o_stride_h, float sm_scale, int out_e4m3, int* status, void* stream) {
   if (!k || !v || B <= 0 || H <= 0 || Sq < 0 || Sk <= 0) return DSB_ERR_ARG;
+  if (out_e4m3 && (o_parts || ((o_stride_s | o_stride_h | o_stride_b) & 15))) return DSB_ERR_ARG;
   if (head_dim != 128) return DSB_ERR_UNSUPPORTED;
   if (H > 65535 || B > 65535) return DSB_ERR_UNSUPPORTED;
   auto al16 = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; };
@@ -584,6 +608,7 @@ static int launch_attn(const void* q, const void* const* q_parts, int n_q_parts,
       p.o_part[i] = reinterpret_cast<__nv_bfloat16*>(o_parts[i < n_o_parts ? i : n_o_parts - 1]);
     p.o_rows_per_part = o_rows_per_part;
   }
+  p.out_e4m3 = out_e4m3 ? 1 : 0;
   p.o_stride_b = o_stride_b;
   p.o_stride_s = o_stride_s;
   p.o_stride_h = o_stride_h;
@@ -604,7 +629,17 @@ extern "C" int dsb_flash_attn(const void* q, const void* k, const void* v, void*
                               int64_t o_stride_h, float sm_scale, int* status, void* stream) {
   return launch_attn(q, nullptr, 0, 0, k, v, o, nullptr, 0, 0, B, H, Sq, Sk, head_dim, q_stride_b, q_stride_s, q_stride_h,
                      k_stride_b, k_stride_s, k_stride_h, v_stride_b, v_stride_s, v_stride_h, o_stride_b, o_stride_s,
-                     o_stride_h, sm_scale, status, stream);
+                     o_stride_h, sm_scale, 0, status, stream);
+}
+
+extern "C" int dsb_flash_attn_out8(const void* q, const void* k, const void* v, void* o, int B, int H, int Sq, int Sk,
+                                   int head_dim, int64_t q_stride_b, int64_t q_stride_s, int64_t q_stride_h,
+                                   int64_t k_stride_b, int64_t k_stride_s, int64_t k_stride_h, int64_t v_stride_b,
+                                   int64_t v_stride_s, int64_t v_stride_h, int64_t o_stride_b, int64_t o_stride_s,
+                                   int64_t o_stride_h, float sm_scale, int* status, void* stream) {
+  return launch_attn(q, nullptr, 0, 0, k, v, o, nullptr, 0, 0, B, H, Sq, Sk, head_dim, q_stride_b, q_stride_s, q_stride_h,
+                     k_stride_b, k_stride_s, k_stride_h, v_stride_b, v_stride_s, v_stride_h, o_stride_b, o_stride_s,
+                     o_stride_h, sm_scale, 1, status, stream);
 }
 
 extern "C" int dsb_flash_attn_parts(const void* const* q_parts, int n_q_parts, int q_rows_per_part, const void* k,
@@ -615,5 +650,5 @@ extern "C" int dsb_flash_attn_parts(const void* const* q_parts, int n_q_parts, i
   if (!q_parts || !o_parts) return DSB_ERR_ARG;
   return launch_attn(nullptr, q_parts, n_q_parts, q_rows_per_part, k, v, nullptr, o_parts, n_o_parts, o_rows_per_part, 1,
                      H, Sq, Sk, head_dim, 0, q_stride_s, q_stride_h, 0, k_stride_s, k_stride_h, 0, v_stride_s,
-                     v_stride_h, 0, o_stride_s, o_stride_h, sm_scale, status, stream);
+                     v_stride_h, 0, o_stride_s, o_stride_h, sm_scale, 0, status, stream);
 }

@@ -248,6 +248,7 @@ class FluxDiTEngine:
         k4 = qkv[:, d:2 * d].unflatten(1, (H, 128)).unsqueeze(0)
         v4 = qkv[:, 2 * d:].unflatten(1, (H, 128)).unsqueeze(0)
         o4 = attn_o.unflatten(1, (H, 128)).unsqueeze(0)
+        o8 = catq[:, :d].unflatten(1, (H, 128)).unsqueeze(0) if unit8 else None
         off = 0
         hid_all, hidq_all = cat[:, d:5 * d], catq[:, d:5 * d]
 
@@ -299,14 +300,20 @@ class FluxDiTEngine:
             ops.gemm_group([dict(a=a, w=p.w, row_scale=sc, col_scale=p.scale, bias=p.bias, nq_w=blk["nq"], nk_w=blk["nk"],
                                  d_model=d, rope=rope, rope_row0=g0, act=ops.ACT_GELU_TANH, act_col0=3 * d, out=qkv,
                                  out1=(catq if unit8 else cat)[:, d:], split_col=3 * d)])
-            self._attention(q4, k4, v4, o4)
-            if P > 1:   # bring the returned [P][Sl][d/P] layout back to rows next to gelu(mlp)
-                attn_o.copy_(b["ao_back"].permute(1, 0, 2).reshape(Sl, d))
-            if unit8:   # gelu(mlp) is already e4m3 (unit scale) in catq; the attention output joins it by a plain cast
-                ops.cast_quant(attn_o, catq[:, :d], ops.FMT_E4M3)
+            if unit8 and P == 1:
+                # gelu(mlp) is already e4m3 (unit scale) in catq; the attention kernel writes its output next to it in
+                # the same format (the bf16 result cast with saturation, as dsb_cast_quant would)
+                ops.flash_attn(q4, k4, v4, out=o8)
                 a, sc = catq, None
             else:
-                a, sc = self._quant(cat, catq, rs)
+                self._attention(q4, k4, v4, o4)
+                if P > 1:   # bring the returned [P][Sl][d/P] layout back to rows next to gelu(mlp)
+                    attn_o.copy_(b["ao_back"].permute(1, 0, 2).reshape(Sl, d))
+                if unit8:   # sequence parallel: the output came back as bf16 and joins catq by a plain cast
+                    ops.cast_quant(attn_o, catq[:, :d], ops.FMT_E4M3)
+                    a, sc = catq, None
+                else:
+                    a, sc = self._quant(cat, catq, rs)
             self._gemm(a, sc, blk["proj"], gate=m[2 * d:3 * d], resid=x, out=x)
         # final AdaLN (scale first, flux_dit.py:333) + projection; all local rows, the image rows are picked below
         m = mv[off:off + 2 * d]
@@ -402,7 +409,8 @@ class FluxDiTEngine:
         # GEMM as e4m3); single: LN, 2 GEMMs, attention, one quantiser or cast
         nq = {ops.FMT_BF16: 0, ops.FMT_E4M3: 1, ops.FMT_INT8: 2}[self.afmt]
         dbl = 2 + 4 + 1 + nq
-        sgl = 3 + (1 if self.afmt != ops.FMT_BF16 else 0) + 1
+        # (with FP8 weights the attention kernel writes e4m3 itself: no cast; INT8 keeps its row quantiser)
+        sgl = 3 + (1 if self.afmt == ops.FMT_INT8 else 0) + 1
         # embedders: sinusoids, GEMVs, modulation GEMV, the two token-embedder GEMMs, the text quantiser, patchify
         pre = 1 + (6 if self.use_guidance else 4) + 1 + 2 + (1 if self.afmt != ops.FMT_BF16 else 0) + 1
         return pre + self.n_double * dbl + self.n_single * sgl + 3      # final LN, projection, unpatchify

@@ -424,18 +424,24 @@ def gemm_group(problems):
 
 def flash_attn(q, k, v, out=None, sm_scale=None):
     """q: [B, Sq, H, 128], k/v: [B, Sk, H, 128] views (any strides that are multiples of 8, unit inner
-    stride); returns o as [B, Sq, H, 128] contiguous unless ``out`` is given."""
+    stride); returns o as [B, Sq, H, 128] contiguous unless ``out`` is given.  An ``out`` of dtype float8_e4m3fn
+    receives the saturating e4m3 cast of the bf16 result (``dsb_flash_attn_out8``)."""
     _require_cuda(q, k, v, out)
     B, Sq, H, D = q.shape
     Sk = k.shape[1]
     for t in (q, k, v):
         if t.stride(3) != 1 or t.dtype != torch.bfloat16:
             raise _lib.DsbError("flash_attn needs bf16 tensors with a contiguous head dimension")
+    if k.shape != (B, Sk, H, D) or v.shape != k.shape:
+        raise _lib.DsbError("flash_attn: k and v must be [B, Sk, H, 128] with the batch and heads of q")
     if out is None:
         out = torch.empty((B, Sq, H, D), dtype=torch.bfloat16, device=q.device)
+    if out.dtype not in (torch.bfloat16, torch.float8_e4m3fn) or tuple(out.shape) != (B, Sq, H, D) or out.stride(3) != 1:
+        raise _lib.DsbError("flash_attn out must be a bf16 or e4m3 [B, Sq, H, 128] view with a contiguous head dimension")
     if sm_scale is None:
         sm_scale = 1.0 / math.sqrt(D)
-    rc = _lib.lib().dsb_flash_attn(
+    fn = _lib.lib().dsb_flash_attn_out8 if out.dtype == torch.float8_e4m3fn else _lib.lib().dsb_flash_attn
+    rc = fn(
         _ptr(q), _ptr(k), _ptr(v), _ptr(out), B, H, Sq, Sk, D,
         q.stride(0), q.stride(1), q.stride(2), k.stride(0), k.stride(1), k.stride(2),
         v.stride(0), v.stride(1), v.stride(2), out.stride(0), out.stride(1), out.stride(2),

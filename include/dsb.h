@@ -281,6 +281,19 @@ int dsb_flash_attn(const void* q, const void* k, const void* v, void* o, int B, 
                    int* status, void* stream);
 
 /*
+ * dsb_flash_attn with the output written as e4m3 (1 byte per element, o strides in elements = bytes, multiples of 16):
+ * the value is rounded to bf16 and then cast with saturation, bit for bit what dsb_flash_attn followed by
+ * dsb_cast_quant (unit scale) produces - the activation rule of the reference's FP8 Linear (utils/fp8_linear.py:35)
+ * applied by the producing kernel, for callers whose next op is an FP8 Linear (Flux single blocks,
+ * models/flux/flux_dit.py:303-320).
+ */
+int dsb_flash_attn_out8(const void* q, const void* k, const void* v, void* o, int B, int H, int Sq, int Sk, int head_dim,
+                        int64_t q_stride_b, int64_t q_stride_s, int64_t q_stride_h, int64_t k_stride_b,
+                        int64_t k_stride_s, int64_t k_stride_h, int64_t v_stride_b, int64_t v_stride_s,
+                        int64_t v_stride_h, int64_t o_stride_b, int64_t o_stride_s, int64_t o_stride_h, float sm_scale,
+                        int* status, void* stream);
+
+/*
  * dsb_flash_attn for one sample (B = 1) whose query rows and output rows are each cut into equal row ranges that live
  * in separate buffers: query rows [i*q_rows_per_part, (i+1)*q_rows_per_part) are read from q_parts[i] (addressed as
  * base + s*q_stride_s + h*q_stride_h with s counted from the start of the part; q_rows_per_part a multiple of 128;

@@ -565,3 +565,23 @@ def test_unpatchify_matches_the_reference_rearrangement(dsb, cuda_dev, c_fastest
         want = t.reshape(gh, gw, C, 2, 2).permute(2, 0, 3, 1, 4).reshape(1, C, 1, gh * 2, gw * 2)
     got = dsb.ops.unpatchify(tok.to(cuda_dev), C, F, gh, gw, c_fastest)
     assert torch.equal(got.cpu(), want)
+
+
+def test_flash_attn_e4m3_output_equals_bf16_output_then_cast(dsb, cuda_dev):
+    """``dsb_flash_attn_out8`` writes bit for bit what ``dsb_flash_attn`` followed by ``dsb_cast_quant`` (unit scale,
+    saturating) writes - into a column slice of a wider e4m3 buffer, as the Flux single block uses it - including
+    values beyond the e4m3 range."""
+    H, Sq, Sk = 2, 300, 333
+    q = torch.randn(1, Sq, H, 128).bfloat16().to(cuda_dev)
+    k = torch.randn(1, Sk, H, 128).bfloat16().to(cuda_dev)
+    v = (torch.randn(1, Sk, H, 128) * 300).bfloat16().to(cuda_dev)          # outputs up to several hundred: some saturate
+    o = dsb.ops.flash_attn(q, k, v)
+    want = torch.empty(Sq, H * 128, dtype=torch.float8_e4m3fn, device=cuda_dev)
+    dsb.ops.cast_quant(o[0].reshape(Sq, H * 128), want, dsb.ops.FMT_E4M3)
+    wide = torch.zeros(Sq, 5 * H * 128, dtype=torch.float8_e4m3fn, device=cuda_dev)
+    got = wide[:, :H * 128].unflatten(1, (H, 128)).unsqueeze(0)
+    dsb.ops.flash_attn(q, k, v, out=got)
+    assert torch.equal(wide[:, :H * 128].view(torch.uint8), want.view(torch.uint8))
+    assert (wide[:, H * 128:].view(torch.uint8) == 0).all()
+    assert (want.float().abs() == 448).any()                                 # the case did exercise saturation
+    dsb.ops.check_status(0)
