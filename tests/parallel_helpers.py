@@ -66,3 +66,29 @@ class EchoModel:
 
 def echo_factory(payload, rank, group, device):
     return EchoModel(payload, rank, group, device)
+
+
+def wan_engine_factory_without_peer_memory(state_dict, rank, sp_group, device, **engine_kwargs):
+    """The Wan engine on a system where the ranks cannot map each other's memory: the mapping raises on every rank,
+    and an engine created with ``exchange="auto"`` has to fall back to the all-to-all for every tensor."""
+    from diffsynth_engine_b200 import wan
+
+    def unavailable(*a, **k):
+        raise RuntimeError("peer memory is switched off in this test")
+
+    wan.PeerMemory = unavailable
+    eng = wan.WanDiTEngine(state_dict, device=device, group=sp_group, **engine_kwargs)
+    return _ExchangeReporting(eng)
+
+
+class _ExchangeReporting:
+    """Forwards the call and appends nothing; after the first call the engine must have settled on the all-to-all."""
+
+    def __init__(self, eng):
+        self.eng = eng
+
+    def __call__(self, **kw):
+        out = self.eng(**kw)
+        if self.eng.exchange != "nccl":
+            raise RuntimeError(f"expected the all-to-all fallback, engine uses {self.eng.exchange}")
+        return out

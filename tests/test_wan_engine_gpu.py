@@ -160,3 +160,24 @@ def test_sequence_parallel_pads_a_token_count_that_does_not_split(dsb, cuda_dev)
         model.close()
     assert out.shape == ref.shape
     assert O.rel_l2(out, ref) < 3e-3
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_sequence_parallel_falls_back_to_all_to_all_without_peer_memory(dsb, cuda_dev):
+    """``exchange="auto"`` on a system whose ranks cannot map each other's memory (the mapping raises on every rank):
+    the engine says so on stderr, uses the all-to-all for all four tensors and still matches one GPU."""
+    os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+    from diffsynth_engine_b200.parallel import UlyssesParallelModel
+    from diffsynth_engine_b200.wan import WanDiTEngine
+    from tests.parallel_helpers import wan_engine_factory_without_peer_memory
+    w, x, context, t = _case(seed=70, grid=(3, 8, 10))
+    one = WanDiTEngine(dict(w), fmt="fp8_channel", device=cuda_dev, num_layers=2, num_heads=H)
+    ref = one(x.to(cuda_dev), context.to(cuda_dev), t.to(cuda_dev)).float().cpu()
+    model = UlyssesParallelModel(dict(w), sp_degree=2, master_port=29647, device="cuda", timeout_s=120,
+                                 factory=wan_engine_factory_without_peer_memory, fmt="fp8_channel", num_layers=2,
+                                 num_heads=H, exchange="auto")
+    try:
+        out = model(x=x, context=context, timestep=t).float().cpu()
+    finally:
+        model.close()
+    assert O.rel_l2(out, ref) < 3e-3
