@@ -105,7 +105,7 @@ static int persistent_grid(int threads, size_t smem, int rows) {
 // NV = 128-bit vectors per thread (row width D <= 128 * 8 * NV).
 // OUT: 0 bf16, 1 e4m3 + row scale, 2 int8 + row scale.
 template <int NV, int OUT>
-__global__ void __launch_bounds__(kRowThreads) ln_modulate_kernel(const __nv_bfloat16* __restrict__ x, int64_t ld_x,
+__global__ void __launch_bounds__(kRowThreads, (NV <= 6 ? 7 : 4)) ln_modulate_kernel(const __nv_bfloat16* __restrict__ x, int64_t ld_x,
                                                                   const float* __restrict__ shift_a,
                                                                   const float* __restrict__ scale_a, int split_row,
                                                                   const float* __restrict__ shift_b,
@@ -121,8 +121,12 @@ __global__ void __launch_bounds__(kRowThreads) ln_modulate_kernel(const __nv_bfl
   const float* scale = row < split_row ? scale_a : scale_b;
   const int nvec = D >> 3;
   const __nv_bfloat16* xr = x + static_cast<int64_t>(row) * ld_x;
-  float v[NV][8];
-  float s = 0.f;
+  // The row stays in registers as 4 x float2 per 128-bit vector and every pass uses the packed fp32 instructions
+  // (two lanes per issue slot): the kernel is bound by instruction issue, not by bytes in flight - at 5120-wide rows
+  // the scalar form spent ~600 issue slots per thread and row.  Same operations in the same order as the scalar form:
+  // ((x - mean) * rstd) * (1 + scale) + shift with the last two fused.
+  float2 v[NV][4];
+  float2 s2 = make_float2(0.f, 0.f);
 #pragma unroll
   for (int i = 0; i < NV; ++i) {
     const int vi = threadIdx.x + i * kRowThreads;
@@ -130,31 +134,31 @@ __global__ void __launch_bounds__(kRowThreads) ln_modulate_kernel(const __nv_bfl
       bf16x8 p = *reinterpret_cast<const bf16x8*>(xr + vi * 8);
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
-        float2 f = unpack_bf16x2(p.u[j]);
-        v[i][2 * j] = f.x;
-        v[i][2 * j + 1] = f.y;
-        s += f.x + f.y;
+        v[i][j] = unpack_bf16x2(p.u[j]);
+        s2 = __fadd2_rn(s2, v[i][j]);
       }
     } else {
 #pragma unroll
-      for (int j = 0; j < 8; ++j) v[i][j] = 0.f;
+      for (int j = 0; j < 4; ++j) v[i][j] = make_float2(0.f, 0.f);
     }
   }
-  const float mean = block_sum_128(s, red) / static_cast<float>(D);
-  float q = 0.f;
+  const float mean = block_sum_128(s2.x + s2.y, red) / static_cast<float>(D);
+  const float2 nmean = make_float2(-mean, -mean);
+  float2 q2 = make_float2(0.f, 0.f);
 #pragma unroll
   for (int i = 0; i < NV; ++i) {
     const int vi = threadIdx.x + i * kRowThreads;
     if (vi < nvec) {
 #pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        float d = v[i][j] - mean;
-        q += d * d;
+      for (int j = 0; j < 4; ++j) {
+        v[i][j] = __fadd2_rn(v[i][j], nmean);   // the centred value is kept for the last pass
+        q2 = __ffma2_rn(v[i][j], v[i][j], q2);
       }
     }
   }
-  const float var = block_sum_128(q, red) / static_cast<float>(D);
+  const float var = block_sum_128(q2.x + q2.y, red) / static_cast<float>(D);
   const float rstd = rsqrtf(var + eps);
+  const float2 rstd2 = make_float2(rstd, rstd), one2 = make_float2(1.f, 1.f);
   float amax = 0.f;
 #pragma unroll
   for (int i = 0; i < NV; ++i) {
@@ -164,13 +168,15 @@ __global__ void __launch_bounds__(kRowThreads) ln_modulate_kernel(const __nv_bfl
       const float4 sc1 = *reinterpret_cast<const float4*>(scale + vi * 8 + 4);
       const float4 sh0 = *reinterpret_cast<const float4*>(shift + vi * 8);
       const float4 sh1 = *reinterpret_cast<const float4*>(shift + vi * 8 + 4);
-      const float sc[8] = {sc0.x, sc0.y, sc0.z, sc0.w, sc1.x, sc1.y, sc1.z, sc1.w};
-      const float sh[8] = {sh0.x, sh0.y, sh0.z, sh0.w, sh1.x, sh1.y, sh1.z, sh1.w};
+      const float2 sc[4] = {make_float2(sc0.x, sc0.y), make_float2(sc0.z, sc0.w), make_float2(sc1.x, sc1.y),
+                            make_float2(sc1.z, sc1.w)};
+      const float2 sh[4] = {make_float2(sh0.x, sh0.y), make_float2(sh0.z, sh0.w), make_float2(sh1.x, sh1.y),
+                            make_float2(sh1.z, sh1.w)};
 #pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        float o = (v[i][j] - mean) * rstd * (1.0f + sc[j]) + sh[j];
+      for (int j = 0; j < 4; ++j) {
+        const float2 o = __ffma2_rn(__fmul2_rn(v[i][j], rstd2), __fadd2_rn(one2, sc[j]), sh[j]);
         v[i][j] = o;
-        amax = fmaxf(amax, fabsf(o));
+        amax = fmaxf(amax, fmaxf(fabsf(o.x), fabsf(o.y)));
       }
     }
   }
@@ -182,7 +188,7 @@ __global__ void __launch_bounds__(kRowThreads) ln_modulate_kernel(const __nv_bfl
       if (vi < nvec) {
         bf16x8 p;
 #pragma unroll
-        for (int j = 0; j < 4; ++j) p.u[j] = pack_bf16x2(v[i][2 * j], v[i][2 * j + 1]);
+        for (int j = 0; j < 4; ++j) p.u[j] = pack_bf16x2(v[i][j].x, v[i][j].y);
         *reinterpret_cast<bf16x8*>(yr + vi * 8) = p;
       }
     }
@@ -191,19 +197,23 @@ __global__ void __launch_bounds__(kRowThreads) ln_modulate_kernel(const __nv_bfl
     const float qmax = (OUT == 1) ? 448.0f : 127.0f;
     const float sc = row_scale_from_amax(amax, qmax);
     const float inv = 1.0f / sc;
+    const float2 inv2 = make_float2(inv, inv);
     if (threadIdx.x == 0) row_scale[row] = sc;
     uint8_t* yr = reinterpret_cast<uint8_t*>(y) + static_cast<int64_t>(row) * ld_y;
 #pragma unroll
     for (int i = 0; i < NV; ++i) {
       const int vi = threadIdx.x + i * kRowThreads;
       if (vi < nvec) {
+        float2 t[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) t[j] = __fmul2_rn(v[i][j], inv2);
         uint2 p;
         if constexpr (OUT == 1) {
-          p.x = pack_e4m3x4(v[i][0] * inv, v[i][1] * inv, v[i][2] * inv, v[i][3] * inv);
-          p.y = pack_e4m3x4(v[i][4] * inv, v[i][5] * inv, v[i][6] * inv, v[i][7] * inv);
+          p.x = pack_e4m3x4(t[0].x, t[0].y, t[1].x, t[1].y);
+          p.y = pack_e4m3x4(t[2].x, t[2].y, t[3].x, t[3].y);
         } else {
-          p.x = pack_s8x4(v[i][0] * inv, v[i][1] * inv, v[i][2] * inv, v[i][3] * inv);
-          p.y = pack_s8x4(v[i][4] * inv, v[i][5] * inv, v[i][6] * inv, v[i][7] * inv);
+          p.x = pack_s8x4(t[0].x, t[0].y, t[1].x, t[1].y);
+          p.y = pack_s8x4(t[2].x, t[2].y, t[3].x, t[3].y);
         }
         *reinterpret_cast<uint2*>(yr + vi * 8) = p;
       }
@@ -323,8 +333,12 @@ __global__ void __launch_bounds__(kRowThreads) rmsnorm_full_rope_kernel(const __
   if (row >= M) return;
   const int nvec = D >> 3;
   const __nv_bfloat16* xr = buf + static_cast<int64_t>(row) * ld;
-  float v[NV][8];
-  float ss = 0.f;
+  // this row's RoPE factors (512 bytes, used only after the reduction) start their trip from L2 now
+  if (rope && threadIdx.x < 4)
+    asm volatile("prefetch.global.L1 [%0];" ::"l"(rope + (static_cast<int64_t>(rope_row0) + row) * 64 + threadIdx.x * 16));
+  // packed fp32 arithmetic (two lanes per issue slot), operations in the order of the scalar form: (x * r) * w
+  float2 v[NV][4];
+  float2 ss2 = make_float2(0.f, 0.f);
 #pragma unroll
   for (int i = 0; i < NV; ++i) {
     const int vi = threadIdx.x + i * kRowThreads;
@@ -332,38 +346,38 @@ __global__ void __launch_bounds__(kRowThreads) rmsnorm_full_rope_kernel(const __
       bf16x8 p = *reinterpret_cast<const bf16x8*>(xr + vi * 8);
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
-        float2 f = unpack_bf16x2(p.u[j]);
-        v[i][2 * j] = f.x;
-        v[i][2 * j + 1] = f.y;
-        ss += f.x * f.x + f.y * f.y;
+        v[i][j] = unpack_bf16x2(p.u[j]);
+        ss2 = __ffma2_rn(v[i][j], v[i][j], ss2);
       }
     }
   }
-  const float r = rsqrtf(block_sum_128(ss, red) / static_cast<float>(D) + eps);
+  const float r = rsqrtf(block_sum_128(ss2.x + ss2.y, red) / static_cast<float>(D) + eps);
+  const float2 r2 = make_float2(r, r);
 #pragma unroll
   for (int i = 0; i < NV; ++i) {
     const int vi = threadIdx.x + i * kRowThreads;
     if (vi < nvec) {
       const float4 w0 = *reinterpret_cast<const float4*>(w + vi * 8);
       const float4 w1 = *reinterpret_cast<const float4*>(w + vi * 8 + 4);
-      const float ww[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
-      float o[8];
+      const float2 ww[4] = {make_float2(w0.x, w0.y), make_float2(w0.z, w0.w), make_float2(w1.x, w1.y),
+                            make_float2(w1.z, w1.w)};
+      float2 o[4];
 #pragma unroll
-      for (int j = 0; j < 8; ++j) o[j] = v[i][j] * r * ww[j];
+      for (int j = 0; j < 4; ++j) o[j] = __fmul2_rn(__fmul2_rn(v[i][j], r2), ww[j]);
       if (rope) {
         const int pair0 = ((vi * 8) & 127) >> 1;  // pair index inside the head
         const float2* rr = rope + (static_cast<int64_t>(rope_row0) + row) * 64 + pair0;
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
           const float2 c = rr[j];
-          const float a = o[2 * j], b = o[2 * j + 1];
-          o[2 * j] = c.x * a - c.y * b;
-          o[2 * j + 1] = c.y * a + c.x * b;
+          const float a = o[j].x, b = o[j].y;
+          o[j].x = c.x * a - c.y * b;
+          o[j].y = c.y * a + c.x * b;
         }
       }
       bf16x8 p;
 #pragma unroll
-      for (int j = 0; j < 4; ++j) p.u[j] = pack_bf16x2(o[2 * j], o[2 * j + 1]);
+      for (int j = 0; j < 4; ++j) p.u[j] = pack_bf16x2(o[j].x, o[j].y);
       const int col = vi * 8;
       const int ck = col / chunk_cols;
       *reinterpret_cast<bf16x8*>(out + ck * chunk_stride + static_cast<int64_t>(row) * ld_out + (col - ck * chunk_cols)) =
