@@ -30,7 +30,8 @@ _SIGS = {
     "dsb_patchify": [c_p, c_i, c_i, c_i, c_i, c_i, c_i, c_i, c_p, c_i64, c_p, c_p],
     "dsb_unpatchify": [c_p, c_i64, c_i, c_i, c_i, c_i, c_i, c_p, c_p],
     "dsb_rank_barrier": [c_p, c_i, c_i, c_i, ctypes.c_longlong, c_p, c_p],
-    "dsb_flash_attn_parts": [c_p, c_i, c_i, c_p, c_p, c_p, c_i, c_i, c_i, c_i, c_i, c_i] + [c_i64] * 8 + [c_f, c_p, c_p],
+    "dsb_flash_attn_parts": [c_p, c_i, c_i, c_p, c_p, c_p, c_i, c_i, c_i, c_i, c_i, c_i] + [c_i64] * 8 + [c_f, c_p, c_i64, c_p, c_p],
+    "dsb_flash_attn_workspace_bytes": [],
     "dsb_ln_modulate": [c_p, c_i64, c_p, c_p, c_p, c_i64, c_p, c_i, c_i, c_f, c_i, c_p],
     "dsb_ln_modulate2": [c_p, c_i64, c_p, c_p, c_i, c_p, c_p, c_p, c_i64, c_p, c_i, c_i, c_f, c_i, c_p],
     "dsb_gate_residual": [c_p, c_i64, c_p, c_i64, c_p, c_p, c_i64, c_i, c_i, c_p],
@@ -95,7 +96,7 @@ def lib():
         for name, args in _SIGS.items():
             fn = getattr(handle, name)
             fn.argtypes = args
-            fn.restype = c_i
+            fn.restype = c_i64 if name == "dsb_flash_attn_workspace_bytes" else c_i
         _lib = handle
     return _lib
 

@@ -51,6 +51,7 @@ constexpr int kXchgSlots = 2 * 2 * 128 * 3;  // [q][half][row] x {running maximu
 constexpr int kAttnSmem = (kNQ + 2 * kKVStages) * kTileBytes + 256 + kXchgSlots * 8 + 1024;
 
 constexpr int kMaxParts = 8;
+constexpr int kWsRow = 132;  // floats per row of a partial result (528 bytes: rows stay 16-byte aligned)
 // The query rows (and, independently, the output rows) may be cut into up to kMaxParts equal row ranges that live in
 // different buffers - e.g. in the memory of different GPUs of a sequence-parallel group, where rank r holds the
 // queries of its own tokens and receives the output rows of its own tokens from every rank.
@@ -61,6 +62,11 @@ struct AttnParams {
   __nv_bfloat16* o;
   __nv_bfloat16* o_part[kMaxParts];
   int out_e4m3;         // 1: the output is written as e4m3 (1 byte per element; strides count elements = bytes)
+  // Work items (query-tile pair, head) are numbered head-major along grid.x.  Items from n_full on - the ones that
+  // would form a partly filled last wave - are each cut into `split` CTAs over contiguous key ranges; those CTAs
+  // leave unnormalised partial results in `ws` and attn_combine_kernel finishes the rows.
+  int n_pairs, n_full, split;
+  float* ws;            // [tail item][part][256 rows][kWsRow floats]: 128 output columns, reference exponent, row sum
   int q_rows_per_part;  // 0: one query buffer (map 0); else a multiple of kTileQ
   int o_rows_per_part;  // 0: one output buffer (o); else row s goes to o_part[s / o_rows_per_part]
   int64_t o_stride_b, o_stride_s, o_stride_h;
@@ -140,10 +146,19 @@ __global__ void __launch_bounds__(kAttnThreads, 1)
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  const int q0 = blockIdx.x * (kNQ * kTileQ);
-  const int h = blockIdx.y;
+  int item = blockIdx.x, part = 0, nparts = 1;
+  if (p.split > 1 && item >= p.n_full) {
+    const int t = item - p.n_full;
+    part = t % p.split;
+    item = p.n_full + t / p.split;
+    nparts = p.split;
+  }
+  const int q0 = (item % p.n_pairs) * (kNQ * kTileQ);
+  const int h = item / p.n_pairs;
   const int b = blockIdx.z;
-  const int nkv = (p.Sk + kTileKV - 1) / kTileKV;
+  const int nkv_all = (p.Sk + kTileKV - 1) / kTileKV;
+  const int jb = static_cast<int>(static_cast<int64_t>(part) * nkv_all / nparts);  // first key tile of this CTA
+  const int nkv = static_cast<int>(static_cast<int64_t>(part + 1) * nkv_all / nparts) - jb;
 
   if (threadIdx.x == 0) {
     mbar_init(q_full, 1);
@@ -194,10 +209,10 @@ __global__ void __launch_bounds__(kAttnThreads, 1)
       for (int j = 0; j < nkv; ++j) {
         if (!mbar_wait(&k_empty[st], ph ^ 1, abort_flag)) break;
         mbar_expect_tx(&k_full[st], kTileBytes);
-        load_tile(sK + st * kTileBytes, &tmap_k, &k_full[st], p.k_pos, j * kTileKV, h, b);
+        load_tile(sK + st * kTileBytes, &tmap_k, &k_full[st], p.k_pos, (jb + j) * kTileKV, h, b);
         if (!mbar_wait(&v_empty[st], ph ^ 1, abort_flag)) break;
         mbar_expect_tx(&v_full[st], kTileBytes);
-        load_tile(sV + st * kTileBytes, &tmap_v, &v_full[st], p.v_pos, j * kTileKV, h, b);
+        load_tile(sV + st * kTileBytes, &tmap_v, &v_full[st], p.v_pos, (jb + j) * kTileKV, h, b);
         if (++st == kKVStages) {
           st = 0;
           ph ^= 1;
@@ -308,7 +323,7 @@ __global__ void __launch_bounds__(kAttnThreads, 1)
         break;
       }
       tc_fence_after();
-      const int valid = min(kTileKV, p.Sk - j * kTileKV) - half * 64;  // valid columns among my 64 (may be <= 0)
+      const int valid = min(kTileKV, p.Sk - (jb + j) * kTileKV) - half * 64;  // valid columns among my 64 (may be <= 0)
       bool handed = false;  // p_full already signalled for this tile
       if (j == 0) {
         // first tile: the row maximum must be known before anything is exponentiated
@@ -446,8 +461,28 @@ __global__ void __launch_bounds__(kAttnThreads, 1)
       xchg_publish(&slot_mine[2], 0x7fffffffu, l);
       float lo = 0.f;
       ok = xchg_read(&slot_other[2], 0x7fffffffu, &lo, abort_flag);
-      const float inv = 1.0f / (l + lo);
       const int sq = q0 + q * kTileQ + row;
+      if (nparts > 1) {
+        // one key range of a split item: O (relative to 2^m_ref), m_ref and the row sum go to the workspace
+        float* wrow = p.ws + ((static_cast<int64_t>(item - p.n_full) * nparts + part) * (kNQ * kTileQ) + q * kTileQ + row) * kWsRow;
+        if (half == 0) {
+          wrow[128] = m_ref;
+          wrow[129] = l + lo;
+        }
+#pragma unroll 1
+        for (int c = 0; c < 2; ++c) {
+          uint32_t r[32];
+          tmem_ld32(t_o + c * 32, r);
+          tc_wait_ld();
+          if (ok) {
+#pragma unroll
+            for (int g = 0; g < 8; ++g)
+              *reinterpret_cast<uint4*>(wrow + half * 64 + c * 32 + g * 4) =
+                  make_uint4(r[g * 4], r[g * 4 + 1], r[g * 4 + 2], r[g * 4 + 3]);
+          }
+        }
+      } else {
+      const float inv = 1.0f / (l + lo);
       __nv_bfloat16* obase = p.o + static_cast<int64_t>(b) * p.o_stride_b;
       int so = sq;
       if (p.o_rows_per_part > 0) {
@@ -495,6 +530,7 @@ __global__ void __launch_bounds__(kAttnThreads, 1)
           }
         }
       }
+      }  // whole-row result
     }
   }
 
@@ -506,6 +542,46 @@ __global__ void __launch_bounds__(kAttnThreads, 1)
     tmem_dealloc(tmem_base, 512);
   }
   if (threadIdx.x == 0 && *abort_flag && p.status) atomicCAS(p.status, 0, DSB_ERR_TIMEOUT);
+}
+
+// Finishes the rows of the split items: with M = max over parts of m_p, O = sum_p 2^(m_p - M) O_p and
+// l = sum_p 2^(m_p - M) l_p (the m_p are integers, so the factors are exact), out = O / l.  One warp per row,
+// four columns per lane.
+__global__ void __launch_bounds__(256) attn_combine_kernel(AttnParams p, int tail_items) {
+  const int gw = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  const int rows = kNQ * kTileQ;
+  if (gw >= tail_items * rows) return;
+  const int ti = gw / rows, r = gw % rows;
+  const int item = p.n_full + ti;
+  const int sq = (item % p.n_pairs) * rows + r;
+  const int h = item / p.n_pairs;
+  if (sq >= p.Sq) return;
+  const float* base = p.ws + (static_cast<int64_t>(ti) * p.split * rows + r) * kWsRow;
+  float M = -INFINITY;
+  for (int s = 0; s < p.split; ++s) M = fmaxf(M, base[static_cast<int64_t>(s) * rows * kWsRow + 128]);
+  float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+  float l = 0.f;
+  for (int s = 0; s < p.split; ++s) {
+    const float* pr = base + static_cast<int64_t>(s) * rows * kWsRow;
+    const float w = exp2f(pr[128] - M);
+    const float4 o = *reinterpret_cast<const float4*>(pr + lane * 4);
+    acc.x = fmaf(w, o.x, acc.x), acc.y = fmaf(w, o.y, acc.y), acc.z = fmaf(w, o.z, acc.z), acc.w = fmaf(w, o.w, acc.w);
+    l = fmaf(w, pr[129], l);
+  }
+  const float inv = 1.0f / l;
+  __nv_bfloat16* obase = p.o;
+  int so = sq;
+  if (p.o_rows_per_part > 0) {
+    const int part = min(sq / p.o_rows_per_part, kMaxParts - 1);
+    obase = p.o_part[part];
+    so = sq - part * p.o_rows_per_part;
+  }
+  __nv_bfloat16* orow = obase + static_cast<int64_t>(so) * p.o_stride_s + static_cast<int64_t>(h) * p.o_stride_h + lane * 4;
+  uint2 o2;
+  o2.x = pack_bf16x2(acc.x * inv, acc.y * inv);
+  o2.y = pack_bf16x2(acc.z * inv, acc.w * inv);
+  *reinterpret_cast<uint2*>(orow) = o2;
 }
 
 // Rank-4 tensor map over (d, then s/h/b ordered by ascending stride); box = 64 x 128 rows of s.
@@ -552,11 +628,13 @@ static int launch_attn(const void* q, const void* const* q_parts, int n_q_parts,
                        int Sq, int Sk, int head_dim, int64_t q_stride_b, int64_t q_stride_s, int64_t q_stride_h,
                        int64_t k_stride_b, int64_t k_stride_s, int64_t k_stride_h, int64_t v_stride_b,
                        int64_t v_stride_s, int64_t v_stride_h, int64_t o_stride_b, int64_t o_stride_s,
-                       int64_t o_stride_h, float sm_scale, int out_e4m3, int* status, void* stream) {
+                       int64_t o_stride_h, float sm_scale, int out_e4m3, void* ws, int64_t ws_bytes, int* status,
+                       void* stream) {
   if (!k || !v || B <= 0 || H <= 0 || Sq < 0 || Sk <= 0) return DSB_ERR_ARG;
+  if (ws && ((reinterpret_cast<uintptr_t>(ws) & 15u) || ws_bytes < 0)) return DSB_ERR_ARG;
   if (out_e4m3 && (o_parts || ((o_stride_s | o_stride_h | o_stride_b) & 15))) return DSB_ERR_ARG;
   if (head_dim != 128) return DSB_ERR_UNSUPPORTED;
-  if (H > 65535 || B > 65535) return DSB_ERR_UNSUPPORTED;
+  if (B > 65535) return DSB_ERR_UNSUPPORTED;
   auto al16 = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; };
   if (!al16(k) || !al16(v)) return DSB_ERR_ARG;
   if (q_parts) {
@@ -617,8 +695,40 @@ static int launch_attn(const void* q, const void* const* q_parts, int n_q_parts,
   p.scale_log2 = sm_scale * 1.4426950408889634f;
   p.status = status;
   DSB_ENSURE_SMEM(flash_attn_kernel, kAttnSmem);
-  dim3 grid((Sq + kNQ * kTileQ - 1) / (kNQ * kTileQ), H, B);
-  flash_attn_kernel<<<grid, kAttnThreads, kAttnSmem, reinterpret_cast<cudaStream_t>(stream)>>>(qm, tk, tv, p);
+  const int n_pairs = (Sq + kNQ * kTileQ - 1) / (kNQ * kTileQ);
+  const int64_t items = static_cast<int64_t>(n_pairs) * H;
+  if (items > 0x3fffffff) return DSB_ERR_UNSUPPORTED;
+  p.n_pairs = n_pairs;
+  p.n_full = static_cast<int>(items);
+  p.split = 1;
+  p.ws = nullptr;
+  // One CTA per SM: the items run in waves of sm_count().  A partly filled last wave costs a whole item's duration
+  // (measured: 590 items on 148 SMs 1.94 ms, 595 items 2.34 ms at 32760 keys), so when the caller provides a
+  // workspace its items are cut along the keys into as many CTAs as fill that wave, plus a combine pass.
+  int tail = 0;
+  if (ws && B == 1 && !out_e4m3) {
+    const int sms = sm_count();
+    const int nkv = (Sk + kTileKV - 1) / kTileKV;
+    tail = static_cast<int>(items % sms);
+    int split = tail > 0 && items > sms ? sms / tail : 1;
+    if (split > 4) split = 4;
+    if (split > nkv / 8) split = nkv / 8;  // every key range keeps at least 8 tiles
+    const int64_t need = static_cast<int64_t>(tail) * split * (kNQ * kTileQ) * kWsRow * 4;
+    if (split >= 2 && need <= ws_bytes) {
+      p.split = split;
+      p.n_full = static_cast<int>(items) - tail;
+      p.ws = reinterpret_cast<float*>(ws);
+    }
+  }
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  const int ctas = p.n_full + (p.split > 1 ? tail * p.split : 0);
+  dim3 grid(ctas, 1, B);
+  flash_attn_kernel<<<grid, kAttnThreads, kAttnSmem, st>>>(qm, tk, tv, p);
+  if (cudaGetLastError() != cudaSuccess) return DSB_ERR_CUDA;
+  if (p.split > 1) {
+    const int warps = tail * kNQ * kTileQ;
+    attn_combine_kernel<<<(warps + 7) / 8, 256, 0, st>>>(p, tail);
+  }
   return cudaGetLastError() == cudaSuccess ? DSB_OK : DSB_ERR_CUDA;
 }
 
@@ -629,7 +739,7 @@ extern "C" int dsb_flash_attn(const void* q, const void* k, const void* v, void*
                               int64_t o_stride_h, float sm_scale, int* status, void* stream) {
   return launch_attn(q, nullptr, 0, 0, k, v, o, nullptr, 0, 0, B, H, Sq, Sk, head_dim, q_stride_b, q_stride_s, q_stride_h,
                      k_stride_b, k_stride_s, k_stride_h, v_stride_b, v_stride_s, v_stride_h, o_stride_b, o_stride_s,
-                     o_stride_h, sm_scale, 0, status, stream);
+                     o_stride_h, sm_scale, 0, nullptr, 0, status, stream);
 }
 
 extern "C" int dsb_flash_attn_out8(const void* q, const void* k, const void* v, void* o, int B, int H, int Sq, int Sk,
@@ -639,16 +749,22 @@ extern "C" int dsb_flash_attn_out8(const void* q, const void* k, const void* v, 
                                    int64_t o_stride_h, float sm_scale, int* status, void* stream) {
   return launch_attn(q, nullptr, 0, 0, k, v, o, nullptr, 0, 0, B, H, Sq, Sk, head_dim, q_stride_b, q_stride_s, q_stride_h,
                      k_stride_b, k_stride_s, k_stride_h, v_stride_b, v_stride_s, v_stride_h, o_stride_b, o_stride_s,
-                     o_stride_h, sm_scale, 1, status, stream);
+                     o_stride_h, sm_scale, 1, nullptr, 0, status, stream);
 }
 
 extern "C" int dsb_flash_attn_parts(const void* const* q_parts, int n_q_parts, int q_rows_per_part, const void* k,
                                     const void* v, void* const* o_parts, int n_o_parts, int o_rows_per_part, int H,
                                     int Sq, int Sk, int head_dim, int64_t q_stride_s, int64_t q_stride_h,
                                     int64_t k_stride_s, int64_t k_stride_h, int64_t v_stride_s, int64_t v_stride_h,
-                                    int64_t o_stride_s, int64_t o_stride_h, float sm_scale, int* status, void* stream) {
+                                    int64_t o_stride_s, int64_t o_stride_h, float sm_scale, void* workspace,
+                                    int64_t workspace_bytes, int* status, void* stream) {
   if (!q_parts || !o_parts) return DSB_ERR_ARG;
   return launch_attn(nullptr, q_parts, n_q_parts, q_rows_per_part, k, v, nullptr, o_parts, n_o_parts, o_rows_per_part, 1,
                      H, Sq, Sk, head_dim, 0, q_stride_s, q_stride_h, 0, k_stride_s, k_stride_h, 0, v_stride_s,
-                     v_stride_h, 0, o_stride_s, o_stride_h, sm_scale, 0, status, stream);
+                     v_stride_h, 0, o_stride_s, o_stride_h, sm_scale, 0, workspace, workspace_bytes, status, stream);
+}
+
+extern "C" int64_t dsb_flash_attn_workspace_bytes(void) {
+  // tail * split <= sm_count() by construction
+  return static_cast<int64_t>(sm_count()) * (kNQ * kTileQ) * kWsRow * 4;
 }

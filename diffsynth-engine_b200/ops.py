@@ -459,12 +459,21 @@ def _addr_array(items):
     return arr
 
 
+def flash_attn_workspace(device) -> torch.Tensor:
+    """A workspace large enough for any ``flash_attn_parts`` call on ``device`` (``dsb_flash_attn_workspace_bytes``;
+    about 20 MB on a 148-SM part): lets the kernel cut the items of a partly filled last wave along the keys."""
+    with torch.cuda.device(device):
+        n = int(_lib.lib().dsb_flash_attn_workspace_bytes())
+    return torch.empty(n, dtype=torch.uint8, device=device)
+
+
 def flash_attn_parts(q_parts, q_rows_per_part, q_strides, k, v, o_parts, o_rows_per_part, o_strides, H, Sq,
-                     sm_scale=None):
+                     sm_scale=None, workspace=None):
     """``dsb_flash_attn_parts``: one sample whose query rows come from ``q_parts[i]`` (``q_rows_per_part`` rows each,
     a multiple of 128) and whose output row s goes to ``o_parts[s // o_rows_per_part]``.  Parts are tensors or raw
     device addresses (peer memory); ``q_strides`` / ``o_strides`` are the (token, head) strides in elements inside a
-    part.  k, v: [1, Sk, H, 128] views on the current device."""
+    part.  k, v: [1, Sk, H, 128] views on the current device.  ``workspace`` (``flash_attn_workspace``): optional,
+    lets a partly filled last wave be cut along the keys."""
     _require_cuda(k, v, *[t for t in list(q_parts) + list(o_parts) if isinstance(t, torch.Tensor)])
     if k.dim() != 4 or k.shape[0] != 1 or k.shape[2] != H or k.shape[3] != 128 or v.shape != k.shape:
         raise _lib.DsbError("flash_attn_parts takes k and v as [1, Sk, H, 128]")
@@ -486,10 +495,15 @@ def flash_attn_parts(q_parts, q_rows_per_part, q_strides, k, v, o_parts, o_rows_
     if sm_scale is None:
         sm_scale = 1.0 / math.sqrt(128)
     qa, oa = _addr_array(q_parts), _addr_array(o_parts)
+    if workspace is not None:
+        _require_cuda(workspace)
+        if workspace.dtype != torch.uint8 or not workspace.is_contiguous():
+            raise _lib.DsbError("flash_attn_parts workspace must be a contiguous uint8 tensor")
     rc = _lib.lib().dsb_flash_attn_parts(
         qa, len(q_parts), q_rows_per_part, _ptr(k), _ptr(v), oa, len(o_parts), o_rows_per_part, H, Sq, k.shape[1], 128,
         q_strides[0], q_strides[1], k.stride(1), k.stride(2), v.stride(1), v.stride(2), o_strides[0], o_strides[1],
-        float(sm_scale), _ptr(status_word(k.device)), _stream())
+        float(sm_scale), _ptr(workspace), 0 if workspace is None else workspace.numel(),
+        _ptr(status_word(k.device)), _stream())
     check(rc, "dsb_flash_attn_parts")
 
 

@@ -248,6 +248,7 @@ class WanDiTEngine:
             b["ao_back"] = pm.local[part:2 * part].view(bf).view(P, Sl, C)
             b["flags"] = [ptr + 2 * part for ptr in pm.ptrs]
             # peer r's queries of this rank's head group; this rank's chunk of peer r's returned attention rows
+            b["attn_ws"] = ops.flash_attn_workspace(dev)
             b["q_parts"] = [ptr + self.rank * C * 2 for ptr in pm.ptrs]
             b["o_parts"] = [ptr + part + self.rank * Sl * C * 2 for ptr in pm.ptrs]
             self.xchg.dist.barrier(group=self._group)           # every rank's flags are zero before the first signal
@@ -436,7 +437,8 @@ class WanDiTEngine:
                         cur.wait_event(e)
                 k4, v4 = (recv[i].view(S_pad, Hl, 128)[:S].unsqueeze(0) for i in (1, 2))   # real tokens only as keys
                 if peer:
-                    ops.flash_attn_parts(b["q_parts"], Sl, (d, 128), k4, v4, b["o_parts"], Sl, (C, 128), Hl, S_pad)
+                    ops.flash_attn_parts(b["q_parts"], Sl, (d, 128), k4, v4, b["o_parts"], Sl, (C, 128), Hl, S_pad,
+                                         workspace=b["attn_ws"])
                     self._barrier()                                   # every rank's output rows have arrived
                 else:
                     q4 = recv[0].view(1, S_pad, Hl, 128)

@@ -304,12 +304,20 @@ int dsb_flash_attn_out8(const void* q, const void* k, const void* v, void* o, in
  * utils/parallel.py's ParallelModel users (pipelines/wan_video.py:434-455) happens inside the attention kernel
  * (plain tiled TMA loads without multicast, plain stores).  q_parts / o_parts are host arrays of device pointers,
  * n_*_parts <= 8 each, n * rows_per_part >= Sq.
+ * workspace (optional, device memory on the launching GPU, 16-byte aligned): when the (query-tile pair, head) items do
+ * not fill the last wave of one CTA per SM, the items of that wave are cut along the keys into 2..4 CTAs each and a
+ * small second kernel combines their partial results; needs tail_items * split * 256 * 528 bytes
+ * (dsb_flash_attn_workspace_bytes gives the bound); without it, or if it is too small, nothing is cut.
  */
 int dsb_flash_attn_parts(const void* const* q_parts, int n_q_parts, int q_rows_per_part, const void* k, const void* v,
                          void* const* o_parts, int n_o_parts, int o_rows_per_part, int H, int Sq, int Sk, int head_dim,
                          int64_t q_stride_s, int64_t q_stride_h, int64_t k_stride_s, int64_t k_stride_h,
                          int64_t v_stride_s, int64_t v_stride_h, int64_t o_stride_s, int64_t o_stride_h,
-                         float sm_scale, int* status, void* stream);
+                         float sm_scale, void* workspace, int64_t workspace_bytes, int* status, void* stream);
+
+/* Upper bound of the workspace dsb_flash_attn_parts can use on the current device (a last wave of sm_count - 1 items
+ * cut in four). */
+int64_t dsb_flash_attn_workspace_bytes(void);
 
 /*
  * Barrier among the n_ranks (<= 8) GPUs of a sequence-parallel group, launched by every rank on its own stream:
