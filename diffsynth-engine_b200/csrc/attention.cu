@@ -710,9 +710,17 @@ static int launch_attn(const void* q, const void* const* q_parts, int n_q_parts,
     const int sms = sm_count();
     const int nkv = (Sk + kTileKV - 1) / kTileKV;
     tail = static_cast<int>(items % sms);
-    int split = tail > 0 && items > sms ? sms / tail : 1;
-    if (split > 4) split = 4;
-    if (split > nkv / 8) split = nkv / 8;  // every key range keeps at least 8 tiles
+    // cut in `split`: the last wave's items take ceil(tail * split / sms) rounds of 1/split of an item's duration
+    // (plus a few per cent per CTA for prologue, partial-result stores and the combine pass)
+    int split = 1;
+    if (tail > 0 && items > sms) {
+      double best = 1.0;
+      for (int sp = 2; sp <= 4; ++sp) {
+        if (nkv / sp < 8) break;  // every key range keeps at least 8 tiles
+        const double cost = static_cast<double>((static_cast<int64_t>(tail) * sp + sms - 1) / sms) / sp + 0.05;
+        if (cost < best - 1e-9) best = cost, split = sp;
+      }
+    }
     const int64_t need = static_cast<int64_t>(tail) * split * (kNQ * kTileQ) * kWsRow * 4;
     if (split >= 2 && need <= ws_bytes) {
       p.split = split;
@@ -765,6 +773,6 @@ extern "C" int dsb_flash_attn_parts(const void* const* q_parts, int n_q_parts, i
 }
 
 extern "C" int64_t dsb_flash_attn_workspace_bytes(void) {
-  // tail * split <= sm_count() by construction
-  return static_cast<int64_t>(sm_count()) * (kNQ * kTileQ) * kWsRow * 4;
+  // a last wave of at most sm_count() - 1 items, cut in at most four
+  return static_cast<int64_t>(sm_count()) * 4 * (kNQ * kTileQ) * kWsRow * 4;
 }

@@ -461,7 +461,7 @@ def _addr_array(items):
 
 def flash_attn_workspace(device) -> torch.Tensor:
     """A workspace large enough for any ``flash_attn_parts`` call on ``device`` (``dsb_flash_attn_workspace_bytes``;
-    about 20 MB on a 148-SM part): lets the kernel cut the items of a partly filled last wave along the keys."""
+    80 MB on a 148-SM part): lets the kernel cut the items of a partly filled last wave along the keys."""
     with torch.cuda.device(device):
         n = int(_lib.lib().dsb_flash_attn_workspace_bytes())
     return torch.empty(n, dtype=torch.uint8, device=device)

@@ -316,7 +316,7 @@ int dsb_flash_attn_parts(const void* const* q_parts, int n_q_parts, int q_rows_p
                          float sm_scale, void* workspace, int64_t workspace_bytes, int* status, void* stream);
 
 /* Upper bound of the workspace dsb_flash_attn_parts can use on the current device (a last wave of sm_count - 1 items
- * cut in four). */
+ * cut in four: 80 MB on a 148-SM part). */
 int64_t dsb_flash_attn_workspace_bytes(void);
 
 /*
