@@ -352,7 +352,8 @@ def wan_parity(ctx, args):
     t = torch.tensor([417.0])
     if ctx.world > 1:
         eng = wan.WanDiTEngine(dict(sd), fmt=args.wan_fmt, device=dev, num_layers=2, num_heads=c["H"],
-                               group=ctx.dist.group.WORLD, exchange=args.wan_exchange)
+                               group=ctx.dist.group.WORLD, exchange=args.wan_exchange,
+                               tail_split=args.wan_tail_split == "on")
         y_sp = eng(x.to(dev), ctxt.to(dev), t.to(dev)).float()
         exch = eng.exchange
         del eng
@@ -413,7 +414,7 @@ def run_wan(ctx, args, steps, warmup):
     sd = synth.make_state_dict(shapes, seed=1234, device=dev, dtype=torch.bfloat16)   # same weights on every rank
     eng = wan.WanDiTEngine(sd, fmt=args.wan_fmt, device=dev, num_layers=c["num_layers"], num_heads=c["H"],
                            group=(dist.group.WORLD if dist is not None else None), release_source=True,
-                           exchange=args.wan_exchange)
+                           exchange=args.wan_exchange, tail_split=args.wan_tail_split == "on")
     del sd
     torch.cuda.empty_cache()
     eng.prepare(c["frames"], c["height"], c["width"], c["ctx"], c["text_dim"])
@@ -823,6 +824,8 @@ def main():
                          "under 'flux' at one GPU; wan / flux / qwen: that workload alone as the line's value")
     ap.add_argument("--wan-fmt", default="fp8_channel")
     ap.add_argument("--wan-layers", type=int, default=0, help="reduced depth (debugging; not a bench)")
+    ap.add_argument("--wan-tail-split", default="on", choices=["on", "off"],
+                    help="peer exchange only: cut the attention items of a partly filled last wave along the keys")
     ap.add_argument("--wan-exchange", default="auto", choices=["auto", "peer", "nccl"],
                     help="how q and the attention output cross ranks at N > 1 (see WanDiTEngine)")
     ap.add_argument("--sp", action="store_true",

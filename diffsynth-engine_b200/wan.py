@@ -110,7 +110,7 @@ class PeerMemory:
 class WanDiTEngine:
     def __init__(self, state_dict: Dict[str, torch.Tensor], fmt: str = "fp8_channel", device="cuda:0",
                  num_layers: int = 40, num_heads: int = 40, eps: float = 1e-6, freq_dim: int = 256, group=None,
-                 release_source: bool = False, overlap: bool = True, exchange: str = "auto"):
+                 release_source: bool = False, overlap: bool = True, exchange: str = "auto", tail_split: bool = True):
         self.dev = torch.device(device)
         self.fmt, self.afmt = fmt, act_format(fmt)
         self.L, self.H, self.eps, self.freq_dim = num_layers, num_heads, eps, freq_dim
@@ -133,6 +133,9 @@ class WanDiTEngine:
         self.exchange = "nccl" if self.P == 1 else exchange
         self._group = group
         self._epoch = 0
+        # peer mode: let the attention kernel cut the items of a partly filled last wave along the keys (the cut rows
+        # then differ from an uncut evaluation in fp32 summation order)
+        self.tail_split = tail_split
 
         def P_(name):
             p = pack_linear(sd[name + ".weight"], sd.get(name + ".bias"), fmt, self.dev)
@@ -248,7 +251,7 @@ class WanDiTEngine:
             b["ao_back"] = pm.local[part:2 * part].view(bf).view(P, Sl, C)
             b["flags"] = [ptr + 2 * part for ptr in pm.ptrs]
             # peer r's queries of this rank's head group; this rank's chunk of peer r's returned attention rows
-            b["attn_ws"] = ops.flash_attn_workspace(dev)
+            b["attn_ws"] = ops.flash_attn_workspace(dev) if self.tail_split else None
             b["q_parts"] = [ptr + self.rank * C * 2 for ptr in pm.ptrs]
             b["o_parts"] = [ptr + part + self.rank * Sl * C * 2 for ptr in pm.ptrs]
             self.xchg.dist.barrier(group=self._group)           # every rank's flags are zero before the first signal
