@@ -122,6 +122,8 @@ __device__ __forceinline__ void load_tile(uint8_t* dst, const CUtensorMap* m, ui
 
 #define mbar_arrive(bar) mbar_arrive(bar)
 
+// SPLIT: the launch has items cut along the keys (see AttnParams); the plain instantiation carries none of that code.
+template <bool SPLIT>
 __global__ void __launch_bounds__(kAttnThreads, 1)
     flash_attn_kernel(const __grid_constant__ AttnQMaps qmaps, const __grid_constant__ CUtensorMap tmap_k,
                       const __grid_constant__ CUtensorMap tmap_v, AttnParams p) {
@@ -147,18 +149,20 @@ __global__ void __launch_bounds__(kAttnThreads, 1)
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   int item = blockIdx.x, part = 0, nparts = 1;
-  if (p.split > 1 && item >= p.n_full) {
-    const int t = item - p.n_full;
-    part = t % p.split;
-    item = p.n_full + t / p.split;
-    nparts = p.split;
+  if constexpr (SPLIT) {
+    if (item >= p.n_full) {
+      const int t = item - p.n_full;
+      part = t % p.split;
+      item = p.n_full + t / p.split;
+      nparts = p.split;
+    }
   }
   const int q0 = (item % p.n_pairs) * (kNQ * kTileQ);
   const int h = item / p.n_pairs;
   const int b = blockIdx.z;
   const int nkv_all = (p.Sk + kTileKV - 1) / kTileKV;
-  const int jb = static_cast<int>(static_cast<int64_t>(part) * nkv_all / nparts);  // first key tile of this CTA
-  const int nkv = static_cast<int>(static_cast<int64_t>(part + 1) * nkv_all / nparts) - jb;
+  const int jb = SPLIT ? static_cast<int>(static_cast<int64_t>(part) * nkv_all / nparts) : 0;  // first key tile of this CTA
+  const int nkv = SPLIT ? static_cast<int>(static_cast<int64_t>(part + 1) * nkv_all / nparts) - jb : nkv_all;
 
   if (threadIdx.x == 0) {
     mbar_init(q_full, 1);
@@ -462,7 +466,7 @@ __global__ void __launch_bounds__(kAttnThreads, 1)
       float lo = 0.f;
       ok = xchg_read(&slot_other[2], 0x7fffffffu, &lo, abort_flag);
       const int sq = q0 + q * kTileQ + row;
-      if (nparts > 1) {
+      if (SPLIT && nparts > 1) {
         // one key range of a split item: O (relative to 2^m_ref), m_ref and the row sum go to the workspace
         float* wrow = p.ws + ((static_cast<int64_t>(item - p.n_full) * nparts + part) * (kNQ * kTileQ) + q * kTileQ + row) * kWsRow;
         if (half == 0) {
@@ -694,7 +698,8 @@ static int launch_attn(const void* q, const void* const* q_parts, int n_q_parts,
   p.Sk = Sk;
   p.scale_log2 = sm_scale * 1.4426950408889634f;
   p.status = status;
-  DSB_ENSURE_SMEM(flash_attn_kernel, kAttnSmem);
+  DSB_ENSURE_SMEM(flash_attn_kernel<false>, kAttnSmem);
+  DSB_ENSURE_SMEM(flash_attn_kernel<true>, kAttnSmem);
   const int n_pairs = (Sq + kNQ * kTileQ - 1) / (kNQ * kTileQ);
   const int64_t items = static_cast<int64_t>(n_pairs) * H;
   if (items > 0x3fffffff) return DSB_ERR_UNSUPPORTED;
@@ -731,7 +736,10 @@ static int launch_attn(const void* q, const void* const* q_parts, int n_q_parts,
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   const int ctas = p.n_full + (p.split > 1 ? tail * p.split : 0);
   dim3 grid(ctas, 1, B);
-  flash_attn_kernel<<<grid, kAttnThreads, kAttnSmem, st>>>(qm, tk, tv, p);
+  if (p.split > 1)
+    flash_attn_kernel<true><<<grid, kAttnThreads, kAttnSmem, st>>>(qm, tk, tv, p);
+  else
+    flash_attn_kernel<false><<<grid, kAttnThreads, kAttnSmem, st>>>(qm, tk, tv, p);
   if (cudaGetLastError() != cudaSuccess) return DSB_ERR_CUDA;
   if (p.split > 1) {
     const int warps = tail * kNQ * kTileQ;
