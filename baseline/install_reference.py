@@ -14,9 +14,11 @@ import types
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 TARGET = os.path.join(HERE, "_ref")
+# default place of the reference's source tree: a directory ``reference`` beside this repository
+DEFAULT_SOURCE = os.path.join(os.path.dirname(os.path.dirname(HERE)), "reference")
 
 
-def install(source: str = "/root/reference", force: bool = False) -> bool:
+def install(source: str = DEFAULT_SOURCE, force: bool = False) -> bool:
     """True when ``baseline/_ref`` holds the package afterwards."""
     if os.path.isdir(os.path.join(TARGET, "diffsynth_engine")) and not force:
         return True
@@ -51,5 +53,5 @@ def import_reference():
 
 
 if __name__ == "__main__":
-    ok = install(*(sys.argv[1:2] or ["/root/reference"]), force="--force" in sys.argv)
+    ok = install(*([a for a in sys.argv[1:] if not a.startswith("--")][:1] or [DEFAULT_SOURCE]), force="--force" in sys.argv)
     print("installed" if ok else "not installed")
