@@ -90,7 +90,22 @@ struct GemmSmem {
   static constexpr int kTotal = kStages * kStage + kFixed;
 };
 
-template <int KIND, int BLOCK_N, int CTAS, bool TABLE>
+// EPI: which epilogue the launch needs, decided on the host from the problem description.  The generic epilogue tests
+// its options at run time inside the per-group code (residual? activation from which column? e4m3 output? a
+// normalised head?); those warp-uniform branches and the code they guard cost the drain of a tile about 15 % at
+// K = 3072 (4096 x 3072 -> 12288 with GELU and e4m3 output: 134 -> 114 us with the options fixed at compile time),
+// so the common cases are instantiated with their options as constants.
+enum : int {
+  EPI_GENERIC = 0,  // everything decided at run time (split outputs, activation on a column range, other activations)
+  EPI_PLAIN = 1,    // scales + bias, bf16 out
+  EPI_RESID = 2,    // ... + gate * (.) + residual, bf16 out
+  EPI_GELU = 3,     // ... + GELU-tanh on every column, bf16 out
+  EPI_GELU8 = 4,    // ... + GELU-tanh on every column, e4m3 out (unit scale)
+  EPI_NORM = 5,     // per-head RMSNorm (+ RoPE) on the q and k columns, bf16 out, nothing else
+  EPI_NORM_GELU8 = 6,  // ... and GELU-tanh from act_col0 on, those columns (second output) as e4m3: q|k|v|mlp projection
+};
+
+template <int KIND, int BLOCK_N, int CTAS, bool TABLE, int EPI>
 __global__ void __launch_bounds__(kGemmThreads, 1)
     gemm_kernel(const __grid_constant__ GemmGroup g) {
   using SM = GemmSmem<BLOCK_N, CTAS, TABLE>;
@@ -268,13 +283,15 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
       // Fused QK-RMSNorm (+RoPE): with 256-wide tiles this warp's 128 columns are exactly one head, one row per
       // thread, so the row's sum of squares needs no cross-thread traffic - just a first pass over TMEM.
       const int head_col0 = n0 + half * 128;
-      const bool fuse_norm = (BLOCK_N == 256) && ep.nq_w != nullptr && head_col0 < 2 * ep.d_model && head_col0 < N;
+      constexpr bool kAnyNorm = (EPI == EPI_GENERIC || EPI == EPI_NORM || EPI == EPI_NORM_GELU8) && BLOCK_N == 256;
+      const bool fuse_norm = kAnyNorm && ep.nq_w != nullptr && head_col0 < 2 * ep.d_model && head_col0 < N;
       const bool rope_tile = fuse_norm && ep.has_rope;
+      const bool has_resid = (EPI == EPI_GENERIC) ? (ep.has_resid != 0) : (EPI == EPI_RESID);
       // The tile-shaped epilogue input of this warp's FIRST 64-column block (residual rows, or RoPE factors) does not
       // depend on the accumulator: request it before waiting for the MMAs, so its L2 round trip runs under them.
       // The staging slot must first have been read out by the previous tile's store.
       const int pre_nb = n0 + half * kBlocksPerWarp * 64;
-      const bool pre_issued = (ep.has_resid || rope_tile) && pre_nb < N;
+      const bool pre_issued = (has_resid || rope_tile) && pre_nb < N;
       if (pre_issued) {
         if (lane == 0) {
           bulk_wait_read<0>();
@@ -295,6 +312,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
       // of the whole GEMM at K = 3072, where the epilogue is the longer half of the pipeline; at K >= 5120 the mainloop
       // is, and the sixth operand stage the table's 16 KiB would displace is worth more (1-7 %).
       constexpr int kWarpCols = BLOCK_N / 2, kPer = kWarpCols / 32;
+      constexpr bool kNeedGate = EPI == EPI_GENERIC || EPI == EPI_RESID;
       const int wcol0 = n0 + half * kWarpCols;
       float p_cs[kPer], p_bias[kPer], p_gate[kPer], p_hw[kPer];
       {
@@ -306,7 +324,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
         for (int j = 0; j < kPer; ++j) {
           p_cs[j] = (in && chan) ? __ldg(ep.col_scale + c + j) : 1.f;
           p_bias[j] = (in && ep.bias) ? __ldg(ep.bias + c + j) : 0.f;
-          p_gate[j] = (in && ep.gate) ? __ldg(ep.gate + c + j) : 1.f;
+          p_gate[j] = (kNeedGate && in && ep.gate) ? __ldg(ep.gate + c + j) : 1.f;
           p_hw[j] = (fuse_norm && hw) ? __ldg(hw + ((lane * kPer + j) & 127)) : 1.f;
         }
         if constexpr (TABLE) {
@@ -315,8 +333,8 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
           for (int j = 0; j < kPer; ++j) {
             ptab[0 * kWarpCols + lane * kPer + j] = p_cs[j];
             ptab[1 * kWarpCols + lane * kPer + j] = p_bias[j];
-            ptab[2 * kWarpCols + lane * kPer + j] = p_gate[j];
-            ptab[3 * kWarpCols + lane * kPer + j] = p_hw[j];
+            if constexpr (kNeedGate) ptab[2 * kWarpCols + lane * kPer + j] = p_gate[j];
+            if constexpr (kAnyNorm) ptab[3 * kWarpCols + lane * kPer + j] = p_hw[j];
           }
           __syncwarp();
         }
@@ -342,7 +360,9 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
       tc_fence_after();
       const bool second = n0 >= ep.split_col;
       const CUtensorMap* tmap_out = second ? &P.o1 : &P.o0;
-      const bool out8 = (BLOCK_N == 256) && (second ? ep.out1_e4m3 : ep.out0_e4m3);
+      const bool out8 = (BLOCK_N == 256) && (EPI == EPI_GENERIC      ? ((second ? ep.out1_e4m3 : ep.out0_e4m3) != 0)
+                                             : EPI == EPI_NORM_GELU8 ? second
+                                                                     : (EPI == EPI_GELU8));
       const int col_shift = second ? ep.split_col : 0;
       const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + acc * BLOCK_N;
       float rnorm = 1.0f;
@@ -390,7 +410,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
         // output block is then written over cell by cell): the residual block, or for a normalised head the RoPE
         // factors of these rows - 32 pairs of fp16 (cos, sin) are the same 128 bytes per row as 64 bf16 outputs.
         const bool do_rope = rope_tile;
-        if (ep.has_resid || do_rope) {
+        if (has_resid || do_rope) {
           if (lane == 0 && !(pre_issued && nb == pre_nb)) {  // the first block's input is already on its way
             mbar_expect_tx(rbar, kStageSlotBytes);
             if (do_rope)
@@ -452,19 +472,29 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
                   v[6] = t0, v[7] = t1;
                 }
               }
-              if (ep.act != DSB_ACT_NONE && n >= ep.act_col0) {
-                if (ep.act == DSB_ACT_GELU_TANH) {
+              if constexpr (EPI == EPI_GELU || EPI == EPI_GELU8) {
+#pragma unroll
+                for (int j = 0; j < 8; ++j) v[j] = gelu_tanh(v[j]);
+              } else if constexpr (EPI == EPI_NORM_GELU8) {
+                if (n >= ep.act_col0) {
 #pragma unroll
                   for (int j = 0; j < 8; ++j) v[j] = gelu_tanh(v[j]);
-                } else if (ep.act == DSB_ACT_SILU) {
+                }
+              } else if constexpr (EPI == EPI_GENERIC) {
+                if (ep.act != DSB_ACT_NONE && n >= ep.act_col0) {
+                  if (ep.act == DSB_ACT_GELU_TANH) {
 #pragma unroll
-                  for (int j = 0; j < 8; ++j) v[j] = silu(v[j]);
-                } else {
+                    for (int j = 0; j < 8; ++j) v[j] = gelu_tanh(v[j]);
+                  } else if (ep.act == DSB_ACT_SILU) {
 #pragma unroll
-                  for (int j = 0; j < 8; ++j) v[j] = gelu_erf(v[j]);
+                    for (int j = 0; j < 8; ++j) v[j] = silu(v[j]);
+                  } else {
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) v[j] = gelu_erf(v[j]);
+                  }
                 }
               }
-              if (ep.has_resid) {
+              if (has_resid) {
                 const uint4 rr = *reinterpret_cast<const uint4*>(cell);
                 const uint32_t ru[4] = {rr.x, rr.y, rr.z, rr.w};
                 float gte[8];
@@ -533,10 +563,10 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
   if (threadIdx.x == 0 && *abort_flag && g.p[0].ep.status) atomicCAS(g.p[0].ep.status, 0, DSB_ERR_TIMEOUT);
 }
 
-template <int KIND, int BLOCK_N, int CTAS, bool TABLE>
+template <int KIND, int BLOCK_N, int CTAS, bool TABLE, int EPI>
 static int launch_group(GemmGroup& grp, cudaStream_t st) {
   using SM = GemmSmem<BLOCK_N, CTAS, TABLE>;
-  auto kern = gemm_kernel<KIND, BLOCK_N, CTAS, TABLE>;
+  auto kern = gemm_kernel<KIND, BLOCK_N, CTAS, TABLE, EPI>;
   DSB_ENSURE_SMEM(kern, SM::kTotal);
   int tiles = 0;
   for (int i = 0; i < grp.count; ++i) tiles += grp.p[i].num_tiles;
@@ -710,16 +740,43 @@ extern "C" int dsb_gemm_group(const dsb_gemm_args* args, int count, int fmt, int
   // Short reductions (at most 32 K slabs: K <= 4096 in 8 bits, 2048 in bf16) leave the epilogue as the longer half of
   // the pipeline: those launches take the kernel with the parameter table, the others the one with the deeper ring.
   const bool table = grp.p[0].num_kb <= 32;
-#define DSB_GEMM_SHAPE(KIND, TABLE)                          \
-  (pair        ? launch_group<KIND, 256, 2, TABLE>(grp, st)  \
-   : bn == 256 ? launch_group<KIND, 256, 1, TABLE>(grp, st)  \
-               : launch_group<KIND, 128, 1, TABLE>(grp, st))
+  // the epilogue instantiation every problem of the launch fits (see the EPI enum); 128-wide tiles keep the generic one
+  auto classify = [](const dsb_gemm_args& a) {
+    const bool o8 = a.out0_fmt == DSB_FMT_E4M3;
+    const bool split = a.out1 != nullptr;
+    if (a.nq_w) {
+      if (!split && !o8 && a.act == DSB_ACT_NONE && !a.resid) return int(EPI_NORM);
+      if (split && !o8 && a.out1_fmt == DSB_FMT_E4M3 && a.act == DSB_ACT_GELU_TANH && a.act_col0 == a.split_col && !a.resid)
+        return int(EPI_NORM_GELU8);
+      return int(EPI_GENERIC);
+    }
+    if (split) return int(EPI_GENERIC);
+    if (a.resid) return (a.act == DSB_ACT_NONE && !o8) ? int(EPI_RESID) : int(EPI_GENERIC);
+    if (a.act == DSB_ACT_GELU_TANH && a.act_col0 <= 0) return o8 ? int(EPI_GELU8) : int(EPI_GELU);
+    if (a.act == DSB_ACT_NONE && !o8) return int(EPI_PLAIN);
+    return int(EPI_GENERIC);
+  };
+  int epi = bn == 256 ? classify(*live[0]) : int(EPI_GENERIC);
+  for (int i = 1; i < grp.count; ++i)
+    if (classify(*live[i]) != epi) epi = EPI_GENERIC;
+#define DSB_GEMM_EPI(KIND, TABLE, EPI)                                          \
+  (pair ? launch_group<KIND, 256, 2, TABLE, EPI>(grp, st) : launch_group<KIND, 256, 1, TABLE, EPI>(grp, st))
+#define DSB_GEMM_SHAPE(KIND, TABLE)                                             \
+  (bn != 256             ? launch_group<KIND, 128, 1, TABLE, EPI_GENERIC>(grp, st) \
+   : epi == EPI_PLAIN    ? DSB_GEMM_EPI(KIND, TABLE, EPI_PLAIN)                 \
+   : epi == EPI_RESID    ? DSB_GEMM_EPI(KIND, TABLE, EPI_RESID)                 \
+   : epi == EPI_GELU     ? DSB_GEMM_EPI(KIND, TABLE, EPI_GELU)                  \
+   : epi == EPI_GELU8    ? DSB_GEMM_EPI(KIND, TABLE, EPI_GELU8)                 \
+   : epi == EPI_NORM     ? DSB_GEMM_EPI(KIND, TABLE, EPI_NORM)                  \
+   : epi == EPI_NORM_GELU8 ? DSB_GEMM_EPI(KIND, TABLE, EPI_NORM_GELU8)          \
+                         : DSB_GEMM_EPI(KIND, TABLE, EPI_GENERIC))
 #define DSB_GEMM_DISPATCH(KIND) (table ? DSB_GEMM_SHAPE(KIND, true) : DSB_GEMM_SHAPE(KIND, false))
   if (fmt == DSB_FMT_BF16) return DSB_GEMM_DISPATCH(KIND_F16);
   if (fmt == DSB_FMT_E4M3) return DSB_GEMM_DISPATCH(KIND_F8);
   return DSB_GEMM_DISPATCH(KIND_I8);
 #undef DSB_GEMM_DISPATCH
 #undef DSB_GEMM_SHAPE
+#undef DSB_GEMM_EPI
 }
 
 extern "C" int dsb_gemm(const void* A, int64_t lda, const void* W, int64_t ldw, int fmt, int M, int N, int K,
