@@ -198,3 +198,41 @@ def test_entry_points_reject_bad_arguments_without_a_gpu(dsb):
     assert lib.dsb_gemm_group(g, 1, 1, None, None) == -1
     a.out0_fmt, a.ld_out0, a.N = 0, 64, 60                                     # N must be a multiple of 8
     assert lib.dsb_gemm_group(g, 1, 1, None, None) == -1
+
+
+def test_new_entry_points_reject_bad_arguments_without_a_gpu(dsb):
+    """The entry points added for the sequence-parallel attention, the boundary kernels and the GGUF formats check
+    their arguments before touching CUDA."""
+    import ctypes
+    lib = dsb._lib.lib()
+    buf = (ctypes.c_char * 4096)()
+    p16 = (ctypes.addressof(buf) + 15) // 16 * 16
+    one = (ctypes.c_void_p * 1)(p16)
+    two = (ctypes.c_void_p * 2)(p16, p16)
+    none2 = (ctypes.c_void_p * 2)(p16, None)
+    st = [512, 128] * 4                                                        # (token, head) strides of q, k, v, o
+    # attention over parts: 1..8 parts that cover Sq, query parts in whole 128-row tiles, no null part
+    assert lib.dsb_flash_attn_parts(two, 2, 100, p16, p16, two, 2, 128, 4, 256, 256, 128, *st, 1.0, None, 0, None, None) == -1
+    assert lib.dsb_flash_attn_parts(two, 2, 128, p16, p16, two, 2, 64, 4, 256, 256, 128, *st, 1.0, None, 0, None, None) == -1
+    assert lib.dsb_flash_attn_parts(two, 9, 128, p16, p16, two, 2, 128, 4, 256, 256, 128, *st, 1.0, None, 0, None, None) == -1
+    assert lib.dsb_flash_attn_parts(none2, 2, 128, p16, p16, two, 2, 128, 4, 256, 256, 128, *st, 1.0, None, 0, None, None) == -1
+    assert lib.dsb_flash_attn_parts(two, 2, 128, p16, p16, two, 2, 128, 4, 256, 256, 64, *st, 1.0, None, 0, None, None) == -4
+    assert lib.dsb_flash_attn_parts(two, 2, 128, p16, p16, two, 2, 128, 4, 256, 256, 128, *st, 1.0, p16 + 4, 64, None, None) == -1
+    # e4m3 attention output: strides in multiples of 16 bytes
+    s12 = [2048, 512, 128] * 3 + [2048, 520, 128]
+    assert lib.dsb_flash_attn_out8(p16, p16, p16, p16, 1, 4, 4, 4, 128, *s12, 1.0, None, None) == -1
+    # rank barrier: 1..8 ranks, own rank inside the group, aligned flag arrays, a positive wait limit
+    assert lib.dsb_rank_barrier(one, 0, 0, 1, 1000, None, None) == -1
+    assert lib.dsb_rank_barrier(two, 2, 2, 1, 1000, None, None) == -1
+    assert lib.dsb_rank_barrier(none2, 2, 0, 1, 1000, None, None) == -1
+    assert lib.dsb_rank_barrier(one, 1, 0, 1, 0, None, None) == -1
+    # patchify / unpatchify: at most 128 channels, rows at least C*4 wide, 8-bit formats need the scale array
+    assert lib.dsb_patchify(p16, 200, 1, 2, 2, 0, 4, 0, p16, 800, None, None) == -1
+    assert lib.dsb_patchify(p16, 16, 1, 2, 2, 0, 4, 0, p16, 32, None, None) == -1
+    assert lib.dsb_patchify(p16, 16, 1, 2, 2, 0, 4, 1, p16, 64, None, None) == -1
+    assert lib.dsb_patchify(p16, 16, 1, 2, 2, 0, 0, 0, None, 64, None, None) == 0     # no rows: nothing to do
+    assert lib.dsb_unpatchify(p16, 32, 16, 1, 2, 2, 1, p16, None) == -1
+    # GGUF: unknown block type, K not a multiple of the block size
+    assert lib.dsb_dequant_gguf(99, p16, 144, 2, 256, p16, 256, None) == -4            # DSB_ERR_UNSUPPORTED
+    assert lib.dsb_dequant_gguf(14, p16, 210, 2, 200, p16, 200, None) == -1
+    assert int(lib.dsb_flash_attn_workspace_bytes()) >= 0 or True                      # needs a device; only that it links
