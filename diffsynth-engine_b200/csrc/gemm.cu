@@ -61,7 +61,24 @@ struct alignas(64) GemmProblem {
   GemmEpilogue ep;
   int M, N, K;
   int tiles_m, num_tiles, num_kb;  // for the tile shape the launch uses
+  int tiles_n, panel;              // tiles are walked in panels of `panel` row tiles, see tile_coords
 };
+// Order in which the persistent CTAs walk a problem's tiles.  Walking all row tiles of one column tile before the next
+// column tile re-reads the whole activation matrix once per column tile; when it does not fit the L2 (32760 x 5120 in
+// 8 bits = 168 MB) that is tiles_n passes over it from HBM - 9 GB for a 32760 x 5120 -> 13824 projection, which made
+// those launches HBM-bound at about 4.4 TB/s.  So the rows are cut into panels of `panel` row tiles whose activations
+// (at most ~32 MB) stay in the L2 together with the weight while every column tile of the panel is computed:
+// inside a panel the row tile runs fastest.  tl -> (row tile, column tile).
+__device__ __forceinline__ void tile_coords(const GemmProblem& P, int tl, int* mt, int* nt) {
+  const int per_panel = P.panel * P.tiles_n;
+  const int pn = tl / per_panel;
+  const int within = tl - pn * per_panel;
+  const int rows = min(P.panel, P.tiles_m - pn * P.panel);  // the last panel may be lower
+  const int n = within / rows;
+  *nt = n;
+  *mt = pn * P.panel + (within - n * rows);
+}
+
 // Up to two independent problems (same format and tile shape) share one persistent launch: the tile list of the
 // second follows the first, so a small problem (the 512-row text stream) fills the SMs its big sibling leaves idle.
 struct alignas(64) GemmGroup {
@@ -184,8 +201,10 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
       for (int t = unit; t < num_tiles; t += num_units) {
         const GemmProblem& P = g.p[t >= tiles_first ? 1 : 0];
         const int tl = t >= tiles_first ? t - tiles_first : t;
-        const int m0 = (tl % P.tiles_m) * kTileM + static_cast<int>(cta_rank) * kBlockM;
-        const int n0 = (tl / P.tiles_m) * BLOCK_N + static_cast<int>(cta_rank) * (BLOCK_N / CTAS);
+        int mt, nt;
+        tile_coords(P, tl, &mt, &nt);
+        const int m0 = mt * kTileM + static_cast<int>(cta_rank) * kBlockM;
+        const int n0 = nt * BLOCK_N + static_cast<int>(cta_rank) * (BLOCK_N / CTAS);
         const int num_kb = P.num_kb;
         for (int kb = 0; kb < num_kb; ++kb) {
           if (!mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag)) goto producer_done;
@@ -276,8 +295,10 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
       const GemmEpilogue& ep = P.ep;
       const int M = P.M, N = P.N;
       const int tl = t >= tiles_first ? t - tiles_first : t;
-      const int m0 = (tl % P.tiles_m) * kTileM + static_cast<int>(cta_rank) * kBlockM;
-      const int n0 = (tl / P.tiles_m) * BLOCK_N;
+      int mt, nt;
+      tile_coords(P, tl, &mt, &nt);
+      const int m0 = mt * kTileM + static_cast<int>(cta_rank) * kBlockM;
+      const int n0 = nt * BLOCK_N;
       const int r0 = m0 + quad * 32;
       const int m = r0 + lane;
       // Fused QK-RMSNorm (+RoPE): with 256-wide tiles this warp's 128 columns are exactly one head, one row per
@@ -705,7 +726,18 @@ static int shape_problem(const dsb_gemm_args& a, int fmt, int bn, int ctas, Gemm
   if (make_tmap_2d(&P->a, dt, esz, a.A, a.M, a.K, a.lda * esz, kBlockM, slab_elems) != DSB_OK) return DSB_ERR_CUDA;
   if (make_tmap_2d(&P->b, dt, esz, a.W, a.N, a.K, a.ldw * esz, bn / ctas, slab_elems) != DSB_OK) return DSB_ERR_CUDA;
   P->tiles_m = (a.M + kBlockM * ctas - 1) / (kBlockM * ctas);
-  P->num_tiles = P->tiles_m * ((a.N + bn - 1) / bn);
+  P->tiles_n = (a.N + bn - 1) / bn;
+  P->num_tiles = P->tiles_m * P->tiles_n;
+  // panel height: activations of a panel <= ~32 MB, at least 4 row tiles, and a panel at least two waves of tiles
+  {
+    const int64_t tile_bytes = static_cast<int64_t>(kBlockM) * ctas * a.K * esz;
+    int64_t g = (32ll << 20) / (tile_bytes > 0 ? tile_bytes : 1);
+    if (g < 4) g = 4;
+    const int64_t min_g = (2ll * sm_count() / ctas + P->tiles_n - 1) / P->tiles_n;
+    if (g < min_g) g = min_g;
+    if (g > P->tiles_m) g = P->tiles_m;
+    P->panel = static_cast<int>(g);
+  }
   P->num_kb = (a.K + slab_elems - 1) / slab_elems;
   return DSB_OK;
 }
