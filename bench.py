@@ -775,6 +775,96 @@ def run_reference_gpu(ctx, args):
     return out
 
 
+def run_kernels(torch, pkg, dev):
+    """Per-kernel timings of the current build at the shapes of the two steps (CUDA events, each case 20-30
+    back-to-back launches after warm-up): the GEMM with each of its epilogues, the bandwidth-bound row kernels on
+    three rotating 335 MB inputs, attention at the sequence-parallel shards with and without the cut of the last wave.
+    The figures the notes under ``profiles/`` quote for "the current build" come from this workload."""
+    ops = pkg.ops
+
+    def timeit(fn, n=20, warm=3):
+        for _ in range(warm):
+            fn()
+        torch.cuda.synchronize()
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s.record()
+        for _ in range(n):
+            fn()
+        e.record()
+        torch.cuda.synchronize()
+        return s.elapsed_time(e) / n
+
+    def q8(M, K):
+        return torch.randn(M, K, device=dev).to(torch.float8_e4m3fn)
+
+    out = {"metric": "per-kernel timings", "unit": "us", "data": "synthetic", "gemm_fp8": [], "row_kernels": [],
+           "attention": []}
+    d = 3072
+    nq = torch.ones(128, device=dev)
+    for (M, K, N, kind) in [(4096, d, 3 * d, "plain"), (4096, d, 3 * d, "norm_rope"), (4608, d, 7 * d, "norm_rope_gelu8_split"),
+                            (4096, d, 4 * d, "gelu8"), (4096, 4 * d, d, "gate_resid"), (4096, d, d, "gate_resid"),
+                            (4608, 5 * d, d, "gate_resid"), (32760, 5120, 5120, "gate_resid"),
+                            (32760, 5120, 13824, "gelu8"), (32760, 13824, 5120, "gate_resid"), (8192, 8192, 8192, "plain")]:
+        a, w = q8(M, K), q8(N, K)
+        rs, cs, bias = torch.rand(M, device=dev) * 0.01, torch.rand(N, device=dev) * 0.01, torch.randn(N, device=dev)
+        base = dict(a=a, w=w, row_scale=rs, col_scale=cs, bias=bias)
+        if kind == "plain":
+            o = torch.empty(M, N, dtype=torch.bfloat16, device=dev)
+            fn = lambda: ops.gemm_group([dict(base, out=o)])
+        elif kind == "norm_rope":
+            o = torch.empty(M, N, dtype=torch.bfloat16, device=dev)
+            rope = torch.randn(M, 64, 2, device=dev).half()
+            fn = lambda: ops.gemm_group([dict(base, out=o, nq_w=nq, nk_w=nq, d_model=d, rope=rope)])
+        elif kind == "norm_rope_gelu8_split":
+            o = torch.empty(M, 3 * d, dtype=torch.bfloat16, device=dev)
+            o1 = torch.empty(M, N - 3 * d, dtype=torch.float8_e4m3fn, device=dev)
+            rope = torch.randn(M, 64, 2, device=dev).half()
+            fn = lambda: ops.gemm_group([dict(base, out=o, out1=o1, split_col=3 * d, act=ops.ACT_GELU_TANH,
+                                              act_col0=3 * d, nq_w=nq, nk_w=nq, d_model=d, rope=rope)])
+        elif kind == "gelu8":
+            o = torch.empty(M, N, dtype=torch.float8_e4m3fn, device=dev)
+            fn = lambda: ops.gemm_group([dict(base, out=o, act=ops.ACT_GELU_TANH)])
+        else:
+            o = torch.randn(M, N, device=dev).bfloat16()
+            gate = torch.randn(N, device=dev) * 0.01
+            fn = lambda: ops.gemm_group([dict(base, out=o, gate=gate, resid=o)])
+        t = timeit(fn, n=30 if M < 10000 else 10)
+        out["gemm_fp8"].append({"M": M, "K": K, "N": N, "epilogue": kind, "us": t * 1e3, "tflops": 2.0 * M * N * K / t / 1e9})
+        del a, w, o
+    for (M, D) in [(32760, 5120), (4096, 5120), (4608, 3072)]:
+        xs = [torch.randn(M, D, device=dev).bfloat16() for _ in range(3)]
+        shift, scale, wn = torch.randn(D, device=dev) * 0.1, torch.randn(D, device=dev) * 0.1, torch.ones(D, device=dev)
+        rope = torch.randn(M, 64, 2, device=dev)
+        oq, rs = torch.empty(M, D, dtype=torch.float8_e4m3fn, device=dev), torch.empty(M, device=dev)
+        i = [0]
+
+        def nxt():
+            i[0] = (i[0] + 1) % 3
+            return xs[i[0]]
+
+        for name, fn, nbytes in (
+                ("ln_modulate_e4m3", lambda: ops.ln_modulate(nxt(), shift, scale, 1e-6, ops.FMT_E4M3, out=oq, row_scale=rs), 3),
+                ("rmsnorm_full_rope", lambda: ops.rmsnorm_full(nxt(), wn, rope, 0, 1e-6), 4),
+                ("quant_rows_e4m3", lambda: ops.quant_rows(nxt(), ops.FMT_E4M3, out=oq, row_scale=rs), 3)):
+            t = timeit(fn)
+            out["row_kernels"].append({"kernel": name, "M": M, "D": D, "us": t * 1e3, "gbs": nbytes * M * D / t / 1e6})
+        del xs
+    ws = ops.flash_attn_workspace(dev)
+    for (H, Sq, Sk) in [(24, 4608, 4608), (40, 32760, 32760), (20, 32768, 32760), (10, 32768, 32760), (5, 32768, 32760)]:
+        q, k, v = (torch.randn(1, s_, H, 128, device=dev).bfloat16() for s_ in (Sq, Sk, Sk))
+        o = torch.empty_like(q)
+        n = 10 if H * Sq < 400000 else 4
+        t0 = timeit(lambda: ops.flash_attn(q, k, v, out=o), n=n)
+        t1 = timeit(lambda: ops.flash_attn_parts([q[0]], Sq, (H * 128, 128), k, v, [o[0]], Sq, (H * 128, 128), H, Sq,
+                                                 workspace=ws), n=n) if Sq % 128 == 0 else None
+        fl = 4.0 * Sq * Sk * H * 128
+        out["attention"].append({"H": H, "Sq": Sq, "Sk": Sk, "us": t0 * 1e3, "tflops": fl / t0 / 1e9,
+                                 "us_last_wave_cut": None if t1 is None else t1 * 1e3})
+        del q, k, v, o
+    ops.check_status(dev.index)
+    return out
+
+
 def run_sweeps(torch, pkg, dev):
     """Isolated kernel sweeps: FP8 e4m3 Linear (per-tensor and per-channel weight scale, bf16 out, fused
     bias + GELU-tanh) and joint attention (bf16, head_dim 128), N(0,1) values from a seed."""
@@ -835,7 +925,7 @@ def main():
     ap.add_argument("--no-parity", action="store_true", help="skip the correctness checks made before timing")
     ap.add_argument("--no-oracle-parity", action="store_true", help="skip only the CPU-oracle part of them")
     ap.add_argument("--blocks", default=None, help="n_double,n_single override (reduced-depth debugging; not a bench)")
-    ap.add_argument("--workload", default="both", choices=["flux", "wan", "both", "qwen", "sweeps", "reference-gpu"],
+    ap.add_argument("--workload", default="both", choices=["flux", "wan", "both", "qwen", "sweeps", "kernels", "reference-gpu"],
                     help="both (default): the Wan sequence-parallel step as the line's value, the Flux step attached "
                          "under 'flux' at one GPU; wan / flux / qwen: that workload alone as the line's value")
     ap.add_argument("--wan-fmt", default="fp8_channel")
@@ -904,6 +994,10 @@ def main():
     if args.workload == "sweeps":
         if rank == 0:
             emit(run_sweeps(torch, pkg, dev))
+        return
+    if args.workload == "kernels":
+        if rank == 0:
+            emit(run_kernels(torch, pkg, dev))
         return
     if args.workload == "reference-gpu":
         if rank == 0:
