@@ -236,3 +236,29 @@ def test_new_entry_points_reject_bad_arguments_without_a_gpu(dsb):
     assert lib.dsb_dequant_gguf(99, p16, 144, 2, 256, p16, 256, None) == -4            # DSB_ERR_UNSUPPORTED
     assert lib.dsb_dequant_gguf(14, p16, 210, 2, 200, p16, 200, None) == -1
     assert int(lib.dsb_flash_attn_workspace_bytes()) >= 0 or True                      # needs a device; only that it links
+
+
+def test_gemm_front_end_checks_shapes_and_dtypes_before_any_launch(dsb):
+    """``ops._check_gemm_io`` is what stands between a tensor and a raw pointer: it accepts what the engines pass
+    (row slices, wider pitches, one-element scales) and rejects what the kernel would overrun."""
+    import torch
+    chk = dsb.ops._check_gemm_io
+    M, N = 64, 128
+    bf, f32, e4 = torch.bfloat16, torch.float32, torch.float8_e4m3fn
+    out = torch.zeros(M, N, dtype=bf)
+    wide = torch.zeros(M, 3 * N, dtype=bf)
+    chk(M, N, out, None, None)
+    chk(M, N, wide[:, N:2 * N], None, None, resid=wide[:, :N], row_scale=torch.zeros(M), col_scale=torch.zeros(1),
+        bias=torch.zeros(N), gate=torch.zeros(N))
+    chk(M, N, torch.zeros(M, 32, dtype=bf), torch.zeros(M, 96, dtype=e4), 32, e4m3_ok=True)
+    for bad in (dict(out=torch.zeros(M, N - 8, dtype=bf)), dict(out=torch.zeros(M + 1, N, dtype=bf)),
+                dict(out=torch.zeros(M, N, dtype=torch.float16)), dict(out=torch.zeros(M, N, dtype=e4)),
+                dict(out=out.t().contiguous().t()), dict(out=out, resid=torch.zeros(M, N, dtype=f32)),
+                dict(out=out, resid=torch.zeros(M, N - 8, dtype=bf)), dict(out=out, row_scale=torch.zeros(M - 1)),
+                dict(out=out, bias=torch.zeros(N, dtype=bf)), dict(out=out, gate=torch.zeros(N - 1)),
+                dict(out=out, col_scale=torch.zeros(N // 2))):
+        with pytest.raises(dsb.DsbError):
+            chk(M, N, bad["out"], None, None, bad.get("resid"), bad.get("row_scale"), bad.get("col_scale"),
+                bad.get("bias"), bad.get("gate"))
+    with pytest.raises(dsb.DsbError):                                   # a split needs 0 < split_col < N
+        chk(M, N, torch.zeros(M, N, dtype=bf), torch.zeros(M, N, dtype=bf), N, e4m3_ok=True)
